@@ -1,0 +1,289 @@
+/*
+ * luaTL.so for B200 (sm_100a): C ABI of the lanternl language-model token loop.
+ *
+ * Two groups of entry points:
+ *
+ *  1. The reference's own FFI surface for this path, with identical names, argument
+ *     meaning, struct layouts, status codes and error-string behaviour, so that the
+ *     reference's LuaJIT bindings (ai/gpu/luaTL.lua:4-168, ai/gpu/luaTL_train.lua:8-90)
+ *     load this library unchanged.  Each declaration cites the reference definition it
+ *     replaces (file:line inside the reference project).
+ *
+ *  2. New entry points (luaTL_lm_*, luaTL_sgd, luaTL_comm_*): the fused, device-resident
+ *     model (training step, KV-cache prefill/decode, batched greedy generation, data-parallel
+ *     gradient all-reduce).  The reference builds the same computation from Lua as a list of
+ *     ops (ai/gpu/gpu_transformer.lua:309-517); these calls run it natively.
+ *
+ * Conventions (reference: cuda/luaTL_core.cu:108-156):
+ *   - int-returning functions return 0 on success or a negative status; the message is in
+ *     luaTL_get_last_error() until luaTL_clear_error().  Constructors return NULL on failure.
+ *   - luaTL_init returns the device COUNT (0 = failure).
+ *   - One-shot math entry points run on the library's stream and synchronise before they
+ *     return; Program / lm entry points synchronise at the end of run unless told otherwise.
+ *   - A GPU failure is always reported; nothing falls back to the CPU.
+ *   - Single host thread per process (unsynchronised globals), as in the reference.
+ */
+#ifndef LUATL_B200_H
+#define LUATL_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes: cuda/luaTL_core.cu:108-118 */
+#define LUATL_OK              0
+#define LUATL_ERR_NULL       -1
+#define LUATL_ERR_SHAPE      -2
+#define LUATL_ERR_DTYPE      -3
+#define LUATL_ERR_CUDA       -4
+#define LUATL_ERR_OOM        -5
+#define LUATL_ERR_ARG        -6
+#define LUATL_ERR_CAPACITY   -7
+#define LUATL_ERR_UNSUPPORT  -8
+
+/* dtype tags: ai/gpu/luaTL.lua:193 */
+#define LUATL_F32  0
+#define LUATL_F16  1
+#define LUATL_BF16 2
+
+/* cuda/luaTL_core.cu:163-196 */
+typedef struct {
+    int32_t  device, major, minor, mp_count, warp_size, max_threads_per_block,
+             max_threads_per_mp, max_blocks_per_mp, regs_per_block, regs_per_mp, clock_khz,
+             memory_clock_khz, memory_bus_width, l2_cache_size, concurrent_kernels,
+             async_engines, unified_addressing, cooperative_launch, has_tensor_cores, has_fp16,
+             has_bf16, ecc_enabled, integrated, cores_per_mp;
+    uint64_t shared_mem_per_block, shared_mem_per_mp, total_global_mem, free_global_mem;
+    double   peak_mem_bandwidth_gbs, peak_fp32_gflops, peak_fp16_gflops;
+    char     name[256];
+} luaTL_devinfo_t;
+
+/* cuda/luaTL_core.cu:214-227 */
+typedef struct {
+    uint64_t bytes_reserved, bytes_in_use, peak_in_use, block_count, free_block_count, n_alloc,
+             n_free, n_cuda_malloc, n_cuda_free, n_cache_hit, n_cache_miss, n_trim;
+} luaTL_pool_stats_t;
+
+typedef struct luaTL_pool_s luaTL_pool_t;
+
+/* cuda/luaTL_core.cu:238-249 (56 bytes; Lua reads and writes the fields directly) */
+typedef struct {
+    void*    data;
+    uint64_t nelem;
+    uint64_t nbytes;
+    int32_t  rows, cols, dtype, owns;
+    void*    pool;
+    int32_t  device, flags;
+} luaTL_tensor_t;
+
+/* cuda/luaTL_train.cu:94-101 (224 bytes; Lua fills every field, ai/gpu/luaTL_train.lua:344-363) */
+typedef struct {
+    int32_t  op, dtype, act, pre;
+    int32_t  i0, i1, i2, i3, i4, i5, i6, i7;
+    float    f0, f1, f2, f3, f4, f5, f6, f7;
+    int64_t  s0, s1, s2, s3, s4, s5, s6, s7, s8;
+    uint64_t n;
+    void    *p0, *p1, *p2, *p3, *p4, *p5, *p6, *p7;
+} luaTL_op_t;
+
+/* cuda/luaTL_train.cu:103-110 */
+typedef struct {
+    luaTL_op_t* ops;
+    int32_t     count, capacity, flags, status;
+    void       *stream, *ev_start, *ev_stop, *graph, *graph_exec;
+    double      last_ms;
+    uint64_t    total_runs, total_ops;
+    int32_t     owns_stream, timing, captured, capturing;
+} luaTL_prog_t;
+
+/* Program opcodes: cuda/luaTL_train.cu:57-86.  LUATL_P_SGD is new (the reference's GPU path
+ * has AdamW only; SGD follows ai/optim/optim2.lua:93-99). */
+enum {
+    LUATL_P_NOP = 0, LUATL_P_GEMM = 1, LUATL_P_EW = 2, LUATL_P_RMSNORM = 3, LUATL_P_RMSNORM_BWD = 4,
+    LUATL_P_SOFTMAX = 5, LUATL_P_SOFTMAX_BWD = 6, LUATL_P_SWIGLU = 7, LUATL_P_SWIGLU_BWD = 8,
+    LUATL_P_ROPE = 9, LUATL_P_EMBED = 10, LUATL_P_EMBED_BWD = 11, LUATL_P_CE = 12,
+    LUATL_P_REDUCE_COLS = 13, LUATL_P_L2 = 14, LUATL_P_CLIP = 15, LUATL_P_ADAMW = 16,
+    LUATL_P_ZERO = 17, LUATL_P_COPY = 18, LUATL_P_CAST = 19, LUATL_P_TRANSPOSE = 20,
+    LUATL_P_BCAST_ADD = 21, LUATL_P_SYNC = 22, LUATL_P_ARGMAX = 23, LUATL_P_SUM = 24,
+    LUATL_P_GATHER = 25, LUATL_P_ROWRMS = 26, LUATL_P_SGD = 27
+};
+
+/* ---------------- runtime (cuda/luaTL_core.cu:1674-1770, cuda/luaTL_train.cu:36-53,1305) --- */
+const char* luaTL_version(void);                         /* core.cu:1674 */
+const char* luaTL_train_version(void);                   /* train.cu:1073 */
+void        luaTL_set_verbose(int on);                   /* core.cu:1676 */
+int         luaTL_init(int device);                      /* core.cu:1678 */
+void        luaTL_shutdown(void);                        /* core.cu:1717 */
+void        luaTL_shutdown_safe(void);                   /* train.cu:39 */
+void        luaTL_finalize(void);                        /* train.cu:1305 */
+uint64_t    luaTL_epoch(void);                           /* train.cu:37 */
+const char* luaTL_device_name(void);                     /* core.cu:1738 */
+const char* luaTL_get_last_error(void);                  /* core.cu:1739 */
+int         luaTL_has_error(void);                       /* core.cu:1740 */
+void        luaTL_clear_error(void);                     /* core.cu:1742 */
+int         luaTL_sync(void);                            /* core.cu:1749 */
+int         luaTL_get_devinfo(int device, luaTL_devinfo_t* out);     /* core.cu:1755 */
+int         luaTL_mem_info(uint64_t* freeb, uint64_t* totalb);       /* core.cu:1765 */
+
+/* ---------------- pool and tensors (cuda/luaTL_core.cu:585-886,1839-2159) ---------------- */
+luaTL_pool_t* luaTL_default_pool(void);
+void*         luaTL_tensor_alloc(luaTL_pool_t* P, uint64_t bytes);
+void          luaTL_tensor_free(luaTL_pool_t* P, void* ptr);
+void          luaTL_pool_trim(luaTL_pool_t* P);
+int           luaTL_pool_get_stats(luaTL_pool_t* P, luaTL_pool_stats_t* out);
+int           luaTL_pool_owns(luaTL_pool_t* P, void* ptr);
+int  luaTL_tensor_init(luaTL_tensor_t* t, int rows, int cols, int dtype, luaTL_pool_t* P);
+int  luaTL_tensor_wrap(luaTL_tensor_t* t, void* data, int rows, int cols, int dtype);
+void luaTL_tensor_release(luaTL_tensor_t* t);
+void luaTL_tensor_release_safe(luaTL_tensor_t* t);       /* train.cu:47 */
+int  luaTL_tensor_view(luaTL_tensor_t* dst, const luaTL_tensor_t* src, int row_off, int rows, int cols);
+int  luaTL_tensor_zero(luaTL_tensor_t* t);
+int  luaTL_tensor_upload(luaTL_tensor_t* t, const float* host, uint64_t nelem);
+int  luaTL_tensor_download(const luaTL_tensor_t* t, float* host, uint64_t nelem);
+int  luaTL_tensor_copy(const luaTL_tensor_t* src, luaTL_tensor_t* dst);
+int  luaTL_tensor_cast(const luaTL_tensor_t* src, luaTL_tensor_t* dst);
+int  luaTL_gpu_copy(const float* src, float* dst, uint64_t nelem);
+int  luaTL_gpu_zero(float* p, uint64_t nelem);
+int  luaTL_upload_i32(void* dev, const int32_t* host, uint64_t n);       /* train.cu:1274 */
+int  luaTL_download_i32(const void* dev, int32_t* host, uint64_t n);     /* train.cu:1282 */
+int  luaTL_download_f32(const void* dev, float* host, uint64_t n);       /* train.cu:1290 */
+
+/* ---------------- one-shot math on the path (synchronous) ------------------------------- */
+/* cuda/luaTL_train.cu:1075: C = post(alpha * A B + bias) + beta * C with explicit strides.
+ * pre_op other than 0 is not supported here (LUATL_ERR_UNSUPPORT). */
+int luaTL_gemm_ex(const void* A, const void* B, void* C, const void* bias, const void* gamma,
+                  const float* rowscale, int M, int N, int K, int dtype,
+                  long long a_rs, long long a_cs, long long b_rs, long long b_cs,
+                  long long c_rs, long long c_cs, long long a_bs, long long b_bs, long long c_bs,
+                  int batch, float alpha, float beta, float eps, int pre_op, int post_op);
+/* cuda/luaTL_core.cu:2272 (contiguous row-major form of the above) */
+int luaTL_gemm(const void* A, const void* B, void* C, const void* bias, const void* gamma,
+               const float* rowscale, int M, int N, int K, int dtype, float alpha, float beta,
+               float eps, int pre_op, int post_op);
+int luaTL_rmsnorm(const void* x, const void* w, void* out, int rows, int cols, float eps, int dtype);     /* core.cu:2329 */
+int luaTL_rmsnorm_bwd(const void* x, const void* gamma, const void* dy, void* dx, float* dgamma,
+                      int rows, int cols, float eps, int dtype);                                          /* train.cu:1096 */
+int luaTL_softmax(const void* x, const void* bias, void* out, int rows, int cols, float scale,
+                  int causal, int mask_offset, int dtype);                                                /* core.cu:2351 */
+int luaTL_softmax_ex(const void* x, const void* bias, void* out, int rows, int cols, float scale,
+                     int causal, int group, int mask_offset, int dtype);                                  /* train.cu:1108 */
+int luaTL_softmax_bwd(const void* y, const void* dy, void* dx, int rows, int cols, float scale,
+                      int causal, int group, int mask_offset, int dtype);                                 /* train.cu:1120 */
+int luaTL_swiglu_fwd(const void* a, const void* b, void* out, int rows, int cols, int lda, int ldb,
+                     int ldo, int dtype);                                                                 /* train.cu:1131 */
+int luaTL_swiglu_bwd(const void* a, const void* b, const void* dout, void* da, void* db, int rows,
+                     int cols, int lda, int ldb, int ldo, int dtype);                                     /* train.cu:1142 */
+int luaTL_rope(void* x, const void* pos_ids, int rows, int heads, int head_dim, int row_stride,
+               int pos_offset, float theta, int interleaved, int inverse, int dtype);                     /* train.cu:1154 */
+int luaTL_embed_fwd(const void* ids, const void* table, void* out, int rows, int dim, int vocab, int dtype);   /* train.cu:1169 */
+int luaTL_embed_bwd(const void* ids, const void* dout, float* dtable, int rows, int dim, int vocab,
+                    float scale, int dtype);                                                              /* train.cu:1179 */
+int luaTL_cross_entropy(const void* logits, const void* targets, float* losses, void* dlogits,
+                        int rows, int vocab, int ignore_index, float grad_scale, int dtype);              /* train.cu:1189 */
+int luaTL_l2_accum(const void* x, uint64_t n, float* out, int dtype);                                     /* train.cu:1215 */
+int luaTL_clip_by_nsq(void* x, uint64_t n, const float* nsq, float max_norm, int dtype);                  /* train.cu:1223 */
+int luaTL_sum_f32(const float* x, uint64_t n, float* out, float scale);                                   /* train.cu:1233 */
+int luaTL_argmax_rows(const void* x, void* out_i32, int rows, int cols, int dtype);                       /* train.cu:1241 */
+int luaTL_elementwise(const void* A, const void* B, void* C, uint64_t n, int dtype, int op,
+                      float alpha, float beta);                                                           /* core.cu:2308 */
+int luaTL_adamw(float* w, const void* g, float* m, float* v, void* w_lp, uint64_t n, int grad_dtype,
+                float lr, float beta1, float beta2, float eps, float wd, int step, float clip);           /* core.cu:2412 */
+/* New: w -= lr * (f * g + wd * w) with f = min(1, max_norm / (sqrt(*nsq) + 1e-6)) when nsq != NULL
+ * and max_norm > 0 (rule: ai/optim/optim2.lua:93-99; clip factor: cuda/luaTL_train.cu:950-952). */
+int luaTL_sgd(float* w, const float* g, uint64_t n, float lr, float wd, const float* nsq, float max_norm);
+
+/* ---------------- Program: command buffer + CUDA graph (cuda/luaTL_train.cu:1506-1712) ---- */
+luaTL_prog_t* luaTL_prog_create(int capacity, int timing);
+void          luaTL_prog_destroy(luaTL_prog_t* P);
+void          luaTL_prog_reset(luaTL_prog_t* P);
+int           luaTL_prog_push(luaTL_prog_t* P, const luaTL_op_t* op);
+int           luaTL_prog_run(luaTL_prog_t* P);
+int           luaTL_prog_capture(luaTL_prog_t* P);
+int           luaTL_prog_replay(luaTL_prog_t* P);
+int           luaTL_prog_wait(luaTL_prog_t* P);
+void          luaTL_prog_graph_free(luaTL_prog_t* P);
+
+/* ---------------- fused device-resident model (new) ------------------------------------- */
+typedef struct {
+    int32_t vocab, dim, layers, heads, ffn;
+    int32_t max_seq;           /* T: training window and KV-cache length                      */
+    int32_t batch;             /* B: sequences per training / eval step                        */
+    int32_t decode_batch;      /* sequences held by the KV cache (0 = no cache)                */
+    int32_t tie;               /* 1: lm_head shares tok_emb                                    */
+    int32_t dtype;             /* LUATL_F32: fp32 weights and math; LUATL_BF16: bf16 weights   */
+                               /* and GEMM inputs, fp32 accumulation and residual stream       */
+    int32_t use_rope, rope_interleaved, causal;
+    int32_t kv_splits;         /* split-KV factor of decode attention, 0 = choose              */
+    float   eps, rope_base;
+} luaTL_lm_config_t;
+
+typedef struct {
+    float   loss;              /* mean CE over the valid targets of all ranks                  */
+    float   grad_norm;         /* global L2 norm of the gradient (0 if not computed)           */
+    int32_t correct, valid, finite;
+    float   step_ms;           /* device time of the step                                      */
+} luaTL_lm_result_t;
+
+typedef struct luaTL_lm_s luaTL_lm_t;
+
+luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg);
+void        luaTL_lm_destroy(luaTL_lm_t* m);
+/* Parameters live in one flat fp32 buffer in the reference's GPU order
+ * tok_emb, {ln1, wqkv, wo, ln2, w13, w2} x L, lnf [, head]  (ai/gpu/gpu_transformer.lua:224-239). */
+int64_t luaTL_lm_nparams(const luaTL_lm_t* m);
+int     luaTL_lm_ntensors(const luaTL_lm_t* m);
+int     luaTL_lm_tensor_info(const luaTL_lm_t* m, int i, char* name32, int32_t* rows, int32_t* cols,
+                             int64_t* offset, int32_t* decay);
+int luaTL_lm_write_params(luaTL_lm_t* m, int64_t offset, int64_t count, const float* host);
+int luaTL_lm_read_params(luaTL_lm_t* m, int64_t offset, int64_t count, float* host);
+int luaTL_lm_read_grads(luaTL_lm_t* m, int64_t offset, int64_t count, float* host);
+float* luaTL_lm_params_device(luaTL_lm_t* m);
+float* luaTL_lm_grads_device(luaTL_lm_t* m);
+
+/* One optimizer step on host id/target blocks [batch, max_seq] (pad: id 0, target -1).
+ * optimizer: 0 = SGD, 1 = AdamW.  valid_global <= 0: count the valid targets of this block. */
+typedef struct {
+    int32_t optimizer, step;
+    float   lr, weight_decay, clip_norm, beta1, beta2, adam_eps;
+    int32_t valid_global;      /* denominator of loss and gradient across all ranks            */
+    int32_t no_update;         /* 1: forward + backward only (gradients stay readable)         */
+} luaTL_lm_train_args_t;
+int luaTL_lm_train_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* targets,
+                        const luaTL_lm_train_args_t* a, luaTL_lm_result_t* out);
+/* Same with ids/targets already on the device. */
+int luaTL_lm_train_step_dev(luaTL_lm_t* m, const int32_t* d_ids, const int32_t* d_targets,
+                            const luaTL_lm_train_args_t* a, luaTL_lm_result_t* out);
+/* Forward only: loss / accuracy, optionally the logits [rows_out, vocab] to the host
+ * (last_only = 1: only row n_tokens - 1 of sequence 0, what generate reads). */
+int luaTL_lm_eval_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* targets, luaTL_lm_result_t* out);
+int luaTL_lm_forward(luaTL_lm_t* m, const int32_t* ids, int nseq, int ntok, float* logits_host, int last_only);
+
+/* KV-cache generation.  Sequences are independent; slot b uses cache slot b. */
+int luaTL_lm_state_reset(luaTL_lm_t* m);             /* every slot back to length 0 */
+int luaTL_lm_slot_reset(luaTL_lm_t* m, int slot);    /* one slot: what Transformer:new_state() gives */
+/* Mirrors Transformer:step (ai/nn/transformer.lua:297): feed one token to sequence slot
+ * `slot`, append its K/V, return the logits row [vocab] on the host. */
+int luaTL_lm_step(luaTL_lm_t* m, int slot, int32_t id, float* logits_host);
+int luaTL_lm_state_len(luaTL_lm_t* m, int slot);
+/* Batched greedy generation: prompts [nseq, n_prompt] on the host, out [nseq, n_new]. */
+int luaTL_lm_generate(luaTL_lm_t* m, const int32_t* prompts, int nseq, int n_prompt, int n_new,
+                      int32_t* out, luaTL_lm_result_t* timing);
+/* Same with prompts and out on the device (nothing crosses PCIe). */
+int luaTL_lm_generate_dev(luaTL_lm_t* m, const int32_t* d_prompts, int nseq, int n_prompt, int n_new,
+                          int32_t* d_out, luaTL_lm_result_t* timing);
+/* Device time (ms) and kernel launches of the last prefill and decode phases. */
+int luaTL_lm_last_timing(luaTL_lm_t* m, float* prefill_ms, float* decode_ms, int64_t* launches);
+
+/* ---------------- data-parallel gradient exchange (new; NCCL over NVLink) ---------------- */
+int luaTL_comm_unique_id(char* id128);                   /* rank 0 creates, caller broadcasts */
+int luaTL_comm_init(const char* id128, int world, int rank);
+int luaTL_comm_world(void);
+int luaTL_comm_allreduce_f32(float* dev, uint64_t n);
+void luaTL_comm_destroy(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

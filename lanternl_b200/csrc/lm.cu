@@ -1,0 +1,947 @@
+// The device-resident language model: flat parameter / gradient buffers, the training step
+// (forward, cross-entropy, backward, optimizer), the KV-cache prefill and the greedy decode
+// loop replayed as one CUDA graph per token.
+//
+// What it replaces: the op lists the reference's Lua host queues per step
+// (ai/gpu/gpu_transformer.lua:309-391 forward, :393-488 backward, :490-517 optimizer) and its
+// cache-less generate (ai/gpu/gpu_transformer.lua:677 re-runs a full [B, T] forward per
+// token).  Decode semantics follow the CPU model's step() (ai/nn/transformer.lua:297-434) and
+// the cache branch of generate (ai/optim/lmtrain.lua:1499-1519).
+//
+// Differences in structure (not in math): attention is one fused kernel per layer instead of
+// 2B batched GEMMs and a [B*H*T, T] softmax; residual adds ride in the GEMM epilogue instead
+// of a copy + beta = 1; all gradients live in one flat buffer (one memset, one all-reduce,
+// one optimizer launch).
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <map>
+#include <vector>
+
+#include "../../include/luatl_b200.h"
+#include "ops.h"
+
+int ltl_comm_world();
+int ltl_comm_allreduce(float* dev, uint64_t n, cudaStream_t s);
+
+namespace {
+
+struct TensorInfo { char name[32]; int rows, cols; int64_t off; int decay; int is_matrix; };
+struct LayerOff { int64_t ln1, wqkv, wo, ln2, w13, w2; };
+
+// Activation set.  layered = 1 keeps one copy per layer (needed by the backward).
+struct Act {
+    int rows_cap = 0, layered = 0;
+    float* res = nullptr;        // layered: [(L+1), rows, D]; else [rows, D]
+    float* mid = nullptr;        // layered only: [L, rows, D]
+    void *h1 = nullptr, *qkv = nullptr, *attn = nullptr, *h2 = nullptr, *h13 = nullptr, *hs = nullptr;
+    float* lse = nullptr;        // layered only: [L, B*H*T]
+    void* hf = nullptr;          // [rows, D]
+    float* logits = nullptr;     // [logit_rows, V]
+    int logit_rows = 0;
+    int32_t* posids = nullptr;   // [rows]
+    int posids_T = -1, posids_rows = -1;
+};
+
+struct GraphEntry { cudaGraph_t g = nullptr; cudaGraphExec_t ge = nullptr; int64_t launches = 0;
+                    const void* out = nullptr; int out_stride = 0; };
+
+}  // namespace
+
+struct luaTL_lm_s {
+    luaTL_lm_config_t c;
+    int D, H, hd, F, V, L, T, B, adt, splits;
+    float scale;
+    std::vector<TensorInfo> tens;
+    std::vector<LayerOff> lo;
+    int64_t np, off_emb, off_lnf, off_head;
+    float *W = nullptr, *G = nullptr, *M1 = nullptr, *M2 = nullptr;
+    bf16* Wb = nullptr;
+    int mirror_dirty = 1;
+    cudaStream_t s = nullptr;
+    float2* rope_tab = nullptr;
+    Act train, infer, dec;
+    // backward scratch
+    float *dres = nullptr, *dbr = nullptr, *dhf = nullptr, *dh1 = nullptr, *dqkv = nullptr,
+          *dattn = nullptr, *dh2 = nullptr, *dh13 = nullptr, *dhs = nullptr, *delta = nullptr;
+    float* losses = nullptr;
+    int32_t *d_ids = nullptr, *d_tgt = nullptr, *d_pred = nullptr;
+    float* ws = nullptr;         // rmsnorm_bwd partials, split-KV partials
+    size_t ws_floats = 0;
+    // decode state
+    int nseq_cap = 0;
+    void *kc = nullptr, *vc = nullptr;
+    int32_t *d_pos = nullptr, *d_count = nullptr, *d_next = nullptr, *d_hist = nullptr, *d_win = nullptr,
+            *d_prompt = nullptr, *d_out = nullptr;
+    int hist_cap = 0, prompt_cap = 0, out_cap = 0;
+    int* d_err = nullptr;
+    float* xlast = nullptr;
+    std::map<int, GraphEntry> graphs;
+    cudaEvent_t ev[4] = { nullptr, nullptr, nullptr, nullptr };
+    float prefill_ms = 0, decode_ms = 0;
+    int64_t launches = 0;
+    int adam_alloc = 0;
+};
+
+namespace {
+
+typedef luaTL_lm_s LM;
+
+int dalloc(void** p, size_t bytes, const char* what)
+{
+    if (bytes == 0) bytes = 16;
+    const cudaError_t e = cudaMalloc(p, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        *p = nullptr;
+        return ltl_fail(LTL_ERR_OOM, "lm: cudaMalloc of %zu bytes for %s failed: %s", bytes, what, cudaGetErrorString(e));
+    }
+    return LTL_OK;
+}
+#define DALLOC(ptr, bytes, what) LTL_TRY(dalloc((void**)&(ptr), (bytes), (what)))
+
+void add_tensor(LM* m, const char* name, int rows, int cols, int decay, int is_matrix)
+{
+    TensorInfo t;
+    memset(&t, 0, sizeof(t));
+    snprintf(t.name, sizeof(t.name), "%s", name);
+    t.rows = rows; t.cols = cols; t.off = m->np; t.decay = decay; t.is_matrix = is_matrix;
+    m->np += (int64_t)rows * cols;
+    m->tens.push_back(t);
+}
+
+void layout_params(LM* m)
+{
+    char nm[32];
+    m->np = 0;
+    m->off_emb = 0;
+    add_tensor(m, "tok_emb", m->V, m->D, 1, 0);
+    m->lo.resize(m->L);
+    for (int l = 0; l < m->L; ++l) {
+        LayerOff& o = m->lo[l];
+        snprintf(nm, sizeof(nm), "l%d.ln1", l + 1);  o.ln1 = m->np;  add_tensor(m, nm, 1, m->D, 0, 0);
+        snprintf(nm, sizeof(nm), "l%d.wqkv", l + 1); o.wqkv = m->np; add_tensor(m, nm, m->D, 3 * m->D, 1, 1);
+        snprintf(nm, sizeof(nm), "l%d.wo", l + 1);   o.wo = m->np;   add_tensor(m, nm, m->D, m->D, 1, 1);
+        snprintf(nm, sizeof(nm), "l%d.ln2", l + 1);  o.ln2 = m->np;  add_tensor(m, nm, 1, m->D, 0, 0);
+        snprintf(nm, sizeof(nm), "l%d.w13", l + 1);  o.w13 = m->np;  add_tensor(m, nm, m->D, 2 * m->F, 1, 1);
+        snprintf(nm, sizeof(nm), "l%d.w2", l + 1);   o.w2 = m->np;   add_tensor(m, nm, m->F, m->D, 1, 1);
+    }
+    m->off_lnf = m->np;
+    add_tensor(m, "lnf", 1, m->D, 0, 0);
+    m->off_head = -1;
+    if (!m->c.tie) { m->off_head = m->np; add_tensor(m, "head", m->D, m->V, 1, 1); }
+}
+
+size_t esz(int dt) { return ltl_dtype_size(dt); }
+
+int alloc_act(LM* m, Act& a, int rows, int layered, int logit_rows)
+{
+    if (a.rows_cap >= rows && a.layered == layered && a.logit_rows >= logit_rows) return LTL_OK;
+    if (a.rows_cap != 0) return ltl_fail(LTL_ERR_CAPACITY, "lm: activation set sized for %d rows, %d requested", a.rows_cap, rows);
+    const size_t D = m->D, F = m->F, V = m->V, L = m->L, R = rows, e = esz(m->adt), nl = layered ? L : 1;
+    DALLOC(a.res, (layered ? L + 1 : 1) * R * D * 4, "residual stream");
+    if (layered) DALLOC(a.mid, L * R * D * 4, "mid residual");
+    DALLOC(a.h1, nl * R * D * e, "h1");
+    DALLOC(a.qkv, nl * R * 3 * D * e, "qkv");
+    DALLOC(a.attn, nl * R * D * e, "attn");
+    DALLOC(a.h2, nl * R * D * e, "h2");
+    DALLOC(a.h13, nl * R * 2 * F * e, "h13");
+    DALLOC(a.hs, nl * R * F * e, "hs");
+    if (layered) DALLOC(a.lse, L * R * (size_t)m->H * 4, "lse");
+    DALLOC(a.hf, R * D * e, "hf");
+    DALLOC(a.logits, (size_t)logit_rows * V * 4, "logits");
+    DALLOC(a.posids, R * 4, "position ids");
+    a.rows_cap = rows; a.layered = layered; a.logit_rows = logit_rows;
+    return LTL_OK;
+}
+
+void free_act(Act& a)
+{
+    cudaFree(a.res); cudaFree(a.mid); cudaFree(a.h1); cudaFree(a.qkv); cudaFree(a.attn); cudaFree(a.h2);
+    cudaFree(a.h13); cudaFree(a.hs); cudaFree(a.lse); cudaFree(a.hf); cudaFree(a.logits); cudaFree(a.posids);
+    a = Act();
+}
+
+__global__ void posids_kernel(int32_t* p, int rows, int T) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < rows) p[i] = i % T;
+}
+
+int ensure_ws(LM* m, size_t floats)
+{
+    if (floats <= m->ws_floats) return LTL_OK;
+    LTL_CUDA("lm workspace sync", cudaStreamSynchronize(m->s));
+    cudaFree(m->ws); m->ws = nullptr; m->ws_floats = 0;
+    DALLOC(m->ws, floats * 4, "workspace");
+    m->ws_floats = floats;
+    return LTL_OK;
+}
+
+// bf16 mirror: matrices transposed to [out, in] (K contiguous, the layout the tensor-core
+// GEMM wants for its B operand), tok_emb and gains cast in place.
+int sync_mirror(LM* m)
+{
+    if (m->adt != LTL_BF16 || !m->mirror_dirty) return LTL_OK;
+    for (const TensorInfo& t : m->tens) {
+        if (t.is_matrix) LTL_TRY(ltl_transpose_to_bf16(m->W + t.off, m->Wb + t.off, t.rows, t.cols, m->s));
+        else LTL_TRY(ltl_cast(m->W + t.off, LTL_F32, m->Wb + t.off, LTL_BF16, (uint64_t)t.rows * t.cols, m->s));
+    }
+    m->mirror_dirty = 0;
+    return LTL_OK;
+}
+
+// C[M, Nout] = A[M, K] * Wt (+ R).  Weight `w_off` is [K, Nout] row-major in the fp32 master
+// and [Nout, K] in the bf16 mirror.  transposed_master = 1: the master itself is [Nout, K]
+// (tok_emb used as the tied head).
+int wgemm(LM* m, const void* A, int M, int K, int64_t w_off, int Nout, void* C, int c_dt, const void* R,
+          int transposed_master)
+{
+    GemmDesc g;
+    memset(&g, 0, sizeof(g));
+    g.A = A; g.C = C; g.R = R; g.M = M; g.N = Nout; g.K = K; g.batch = 1;
+    g.a_rs = K; g.a_cs = 1; g.c_rs = Nout; g.c_cs = 1;
+    g.alpha = 1.0f; g.beta = 0.0f; g.a_dtype = m->adt; g.b_dtype = m->adt; g.c_dtype = c_dt;
+    if (m->adt == LTL_F32) {
+        g.B = m->W + w_off;
+        if (transposed_master) { g.b_rs = 1; g.b_cs = K; } else { g.b_rs = Nout; g.b_cs = 1; }
+    } else {
+        g.B = m->Wb + w_off;
+        g.b_rs = 1; g.b_cs = K;
+    }
+    m->launches++;
+    return ltl_gemm_simt(g, m->s);
+}
+
+// Generic fp32 strided GEMM used by the backward.
+int sgemm(LM* m, const float* A, long long a_rs, long long a_cs, const float* B, long long b_rs, long long b_cs,
+          float* C, int M, int N, int K, float beta)
+{
+    GemmDesc g;
+    memset(&g, 0, sizeof(g));
+    g.A = A; g.B = B; g.C = C; g.M = M; g.N = N; g.K = K; g.batch = 1;
+    g.a_rs = a_rs; g.a_cs = a_cs; g.b_rs = b_rs; g.b_cs = b_cs; g.c_rs = N; g.c_cs = 1;
+    g.alpha = 1.0f; g.beta = beta;
+    m->launches++;
+    return ltl_gemm_simt(g, m->s);
+}
+
+inline char* layer_ptr(void* base, const Act& a, int l, size_t elems_per_layer, size_t e)
+{
+    return (char*)base + (a.layered ? (size_t)l * elems_per_layer * e : 0);
+}
+
+enum { MODE_TRAIN = 0, MODE_PREFILL = 1 };
+
+// Forward over nseq sequences of T tokens (ids on the device).  TRAIN: keep every layer's
+// activations and produce logits for all rows.  PREFILL: single activation set, K/V stored
+// in the cache, logits only for the last position of each sequence.
+int forward(LM* m, Act& a, const int32_t* d_ids, int nseq, int T, int mode)
+{
+    const int D = m->D, F = m->F, V = m->V, L = m->L, H = m->H, hd = m->hd, adt = m->adt;
+    const int rows = nseq * T;
+    const size_t e = esz(adt);
+    if (rows > a.rows_cap) return ltl_fail(LTL_ERR_CAPACITY, "lm forward: %d rows exceed the buffers (%d)", rows, a.rows_cap);
+    if (T > m->T) return ltl_fail(LTL_ERR_SHAPE, "lm forward: %d tokens exceed max_seq %d", T, m->T);
+    LTL_TRY(sync_mirror(m));
+    if (a.posids_T != T || a.posids_rows != rows) {
+        posids_kernel<<<(rows + 255) / 256, 256, 0, m->s>>>(a.posids, rows, T);
+        a.posids_T = T; a.posids_rows = rows;
+    }
+    const size_t RD = (size_t)a.rows_cap * D;
+    const void* table = adt == LTL_F32 ? (const void*)(m->W + m->off_emb) : (const void*)(m->Wb + m->off_emb);
+    LTL_TRY(ltl_lm_embed(d_ids, table, adt, a.res, rows, D, V, m->s));
+    m->launches++;
+    for (int l = 0; l < L; ++l) {
+        const LayerOff& o = m->lo[l];
+        float* xin = a.layered ? a.res + (size_t)l * RD : a.res;
+        float* mid = a.layered ? a.mid + (size_t)l * RD : a.res;
+        float* xout = a.layered ? a.res + (size_t)(l + 1) * RD : a.res;
+        void* h1 = layer_ptr(a.h1, a, l, RD, e);
+        void* qkv = layer_ptr(a.qkv, a, l, 3 * RD, e);
+        void* attn = layer_ptr(a.attn, a, l, RD, e);
+        void* h2 = layer_ptr(a.h2, a, l, RD, e);
+        void* h13 = layer_ptr(a.h13, a, l, (size_t)a.rows_cap * 2 * F, e);
+        void* hs = layer_ptr(a.hs, a, l, (size_t)a.rows_cap * F, e);
+        float* lse = a.layered ? a.lse + (size_t)l * a.rows_cap * H : nullptr;
+
+        LTL_TRY(ltl_lm_rmsnorm(xin, m->W + o.ln1, h1, adt, rows, D, m->c.eps, m->s));
+        LTL_TRY(wgemm(m, h1, rows, D, o.wqkv, 3 * D, qkv, adt, nullptr, 0));
+        if (m->c.use_rope)
+            LTL_TRY(ltl_rope(qkv, a.posids, rows, 2 * H, hd, 3 * D, 0, m->c.rope_base, m->c.rope_interleaved, 0,
+                             adt, m->rope_tab, m->T, m->s));
+        LTL_TRY(ltl_attn_fwd(qkv, attn, lse, nseq, T, H, hd, m->scale, m->c.causal, adt, m->s));
+        if (mode == MODE_PREFILL) {
+            const size_t cl = (size_t)m->nseq_cap * H * m->T * hd * e;
+            LTL_TRY(ltl_kv_store(qkv, (char*)m->kc + l * cl, (char*)m->vc + l * cl, nseq, T, H, hd, m->T, adt, m->s));
+            m->launches++;
+        }
+        LTL_TRY(wgemm(m, attn, rows, D, o.wo, D, mid, LTL_F32, xin, 0));
+        LTL_TRY(ltl_lm_rmsnorm(mid, m->W + o.ln2, h2, adt, rows, D, m->c.eps, m->s));
+        LTL_TRY(wgemm(m, h2, rows, D, o.w13, 2 * F, h13, adt, nullptr, 0));
+        LTL_TRY(ltl_swiglu_fwd(h13, (char*)h13 + (size_t)F * e, hs, rows, F, 2 * F, 2 * F, F, adt, m->s));
+        LTL_TRY(wgemm(m, hs, rows, F, o.w2, D, xout, LTL_F32, mid, 0));
+        m->launches += 5;
+    }
+    const float* xf = a.layered ? a.res + (size_t)L * RD : a.res;
+    int lrows = rows;
+    if (mode == MODE_PREFILL) {
+        LTL_TRY(ltl_gather_last_rows(xf, m->xlast, nseq, T, D, T - 1, m->s));
+        xf = m->xlast; lrows = nseq;
+        m->launches++;
+    }
+    if (lrows > a.logit_rows) return ltl_fail(LTL_ERR_CAPACITY, "lm forward: %d logit rows exceed the buffer (%d)", lrows, a.logit_rows);
+    LTL_TRY(ltl_lm_rmsnorm(xf, m->W + m->off_lnf, a.hf, adt, lrows, D, m->c.eps, m->s));
+    m->launches++;
+    if (m->c.tie) LTL_TRY(wgemm(m, a.hf, lrows, D, m->off_emb, V, a.logits, LTL_F32, nullptr, 1));
+    else LTL_TRY(wgemm(m, a.hf, lrows, D, m->off_head, V, a.logits, LTL_F32, nullptr, 0));
+    return LTL_OK;
+}
+
+int alloc_backward(LM* m)
+{
+    if (m->dres) return LTL_OK;
+    const size_t R = (size_t)m->B * m->T, D = m->D, F = m->F;
+    DALLOC(m->dres, R * D * 4, "dres"); DALLOC(m->dbr, R * D * 4, "dbr"); DALLOC(m->dhf, R * D * 4, "dhf");
+    DALLOC(m->dh1, R * D * 4, "dh1"); DALLOC(m->dqkv, R * 3 * D * 4, "dqkv"); DALLOC(m->dattn, R * D * 4, "dattn");
+    DALLOC(m->dh2, R * D * 4, "dh2"); DALLOC(m->dh13, R * 2 * F * 4, "dh13"); DALLOC(m->dhs, R * F * 4, "dhs");
+    DALLOC(m->delta, R * m->H * 4, "delta");
+    return LTL_OK;
+}
+
+// Backward of the fp32 model; dlogits already sits in a.logits.  Gradients accumulate into G.
+int backward(LM* m, Act& a, const int32_t* d_ids, int nseq, int T)
+{
+    const int D = m->D, F = m->F, V = m->V, L = m->L, H = m->H, hd = m->hd;
+    const int rows = nseq * T;
+    const size_t RD = (size_t)a.rows_cap * D;
+    float* W = m->W; float* G = m->G;
+    const float* dl = a.logits;
+    const float* hf = (const float*)a.hf;
+    LTL_TRY(ensure_ws(m, ltl_rmsnorm_bwd_scratch_floats(D)));
+    if (m->c.tie) {
+        LTL_TRY(sgemm(m, dl, 1, V, hf, D, 1, G + m->off_emb, V, D, rows, 1.0f));       // dEmb += dl^T hf
+        LTL_TRY(sgemm(m, dl, V, 1, W + m->off_emb, D, 1, m->dhf, rows, D, V, 0.0f));   // dhf = dl emb
+    } else {
+        LTL_TRY(sgemm(m, hf, 1, D, dl, V, 1, G + m->off_head, D, V, rows, 1.0f));      // dHead += hf^T dl
+        LTL_TRY(sgemm(m, dl, V, 1, W + m->off_head, 1, V, m->dhf, rows, D, V, 0.0f));  // dhf = dl head^T
+    }
+    LTL_TRY(ltl_rmsnorm_bwd(a.res + (size_t)L * RD, W + m->off_lnf, m->dhf, m->dres, G + m->off_lnf, rows, D,
+                            m->c.eps, LTL_F32, m->ws, m->s));
+    m->launches += 2;
+    for (int l = L - 1; l >= 0; --l) {
+        const LayerOff& o = m->lo[l];
+        const float* xin = a.res + (size_t)l * RD;
+        const float* mid = a.mid + (size_t)l * RD;
+        const float* h1 = (const float*)a.h1 + (size_t)l * RD;
+        const float* qkv = (const float*)a.qkv + (size_t)l * 3 * RD;
+        const float* attn = (const float*)a.attn + (size_t)l * RD;
+        const float* h2 = (const float*)a.h2 + (size_t)l * RD;
+        const float* h13 = (const float*)a.h13 + (size_t)l * a.rows_cap * 2 * F;
+        const float* hs = (const float*)a.hs + (size_t)l * a.rows_cap * F;
+        const float* lse = a.lse + (size_t)l * a.rows_cap * H;
+
+        // feed-forward
+        LTL_TRY(sgemm(m, m->dres, D, 1, W + o.w2, 1, D, m->dhs, rows, F, D, 0.0f));          // dhs = dres W2^T
+        LTL_TRY(sgemm(m, hs, 1, F, m->dres, D, 1, G + o.w2, F, D, rows, 1.0f));              // dW2 += hs^T dres
+        LTL_TRY(ltl_swiglu_bwd(h13, h13 + F, m->dhs, m->dh13, m->dh13 + F, rows, F, 2 * F, 2 * F, F, LTL_F32, m->s));
+        LTL_TRY(sgemm(m, h2, 1, D, m->dh13, 2 * F, 1, G + o.w13, D, 2 * F, rows, 1.0f));     // dW13 += h2^T dh13
+        LTL_TRY(sgemm(m, m->dh13, 2 * F, 1, W + o.w13, 1, 2 * F, m->dh2, rows, D, 2 * F, 0.0f));
+        LTL_TRY(ltl_rmsnorm_bwd(mid, W + o.ln2, m->dh2, m->dbr, G + o.ln2, rows, D, m->c.eps, LTL_F32, m->ws, m->s));
+        LTL_TRY(ltl_elementwise(m->dres, m->dbr, m->dres, (uint64_t)rows * D, LTL_F32, 6, 1.0f, 0.0f, m->s));
+        // attention
+        LTL_TRY(sgemm(m, m->dres, D, 1, W + o.wo, 1, D, m->dattn, rows, D, D, 0.0f));        // dattn = dres Wo^T
+        LTL_TRY(sgemm(m, attn, 1, D, m->dres, D, 1, G + o.wo, D, D, rows, 1.0f));            // dWo += attn^T dres
+        LTL_TRY(ltl_attn_bwd(qkv, attn, m->dattn, lse, m->delta, m->dqkv, nseq, T, H, hd, m->scale, m->c.causal,
+                             LTL_F32, m->s));
+        if (m->c.use_rope)
+            LTL_TRY(ltl_rope(m->dqkv, a.posids, rows, 2 * H, hd, 3 * D, 0, m->c.rope_base, m->c.rope_interleaved, 1,
+                             LTL_F32, m->rope_tab, m->T, m->s));
+        LTL_TRY(sgemm(m, h1, 1, D, m->dqkv, 3 * D, 1, G + o.wqkv, D, 3 * D, rows, 1.0f));    // dWqkv += h1^T dqkv
+        LTL_TRY(sgemm(m, m->dqkv, 3 * D, 1, W + o.wqkv, 1, 3 * D, m->dh1, rows, D, 3 * D, 0.0f));
+        LTL_TRY(ltl_rmsnorm_bwd(xin, W + o.ln1, m->dh1, m->dbr, G + o.ln1, rows, D, m->c.eps, LTL_F32, m->ws, m->s));
+        LTL_TRY(ltl_elementwise(m->dres, m->dbr, m->dres, (uint64_t)rows * D, LTL_F32, 6, 1.0f, 0.0f, m->s));
+        m->launches += 12;
+    }
+    LTL_TRY(ltl_embed_bwd(d_ids, m->dres, G + m->off_emb, rows, D, V, 1.0f, LTL_F32, m->s));
+    m->launches++;
+    return LTL_OK;
+}
+
+int count_valid(const int32_t* tgt, int n, int V)
+{
+    int v = 0;
+    for (int i = 0; i < n; ++i) if (tgt[i] >= 0 && tgt[i] < V) ++v;
+    return v;
+}
+
+int ensure_train(LM* m)
+{
+    const int rows = m->B * m->T;
+    LTL_TRY(alloc_act(m, m->train, rows, 1, rows));
+    if (!m->losses) {
+        DALLOC(m->losses, (size_t)rows * 4, "losses");
+        DALLOC(m->d_ids, (size_t)rows * 4, "ids");
+        DALLOC(m->d_tgt, (size_t)rows * 4, "targets");
+        DALLOC(m->d_pred, (size_t)rows * 4, "predictions");
+    }
+    return LTL_OK;
+}
+
+// tail of G: [np] loss accumulator, [np+1] correct count, [np+2] grad norm^2, [np+3] spare
+int loss_and_grad(LM* m, const int32_t* d_ids, const int32_t* d_tgt, int valid_global, int want_grad)
+{
+    const int rows = m->B * m->T;
+    Act& a = m->train;
+    const float gs = 1.0f / (float)(valid_global < 1 ? 1 : valid_global);
+    LTL_CUDA("zero gradients", cudaMemsetAsync(m->G, 0, (size_t)(m->np + 4) * 4, m->s));
+    LTL_TRY(forward(m, a, d_ids, m->B, m->T, MODE_TRAIN));
+    LTL_TRY(ltl_cross_entropy(a.logits, d_tgt, m->losses, want_grad ? a.logits : nullptr, m->d_pred, rows, m->V,
+                              -1, gs, LTL_F32, m->s));
+    LTL_TRY(ltl_sum_f32(m->losses, rows, m->G + m->np, gs, m->s));
+    LTL_TRY(ltl_count_correct(m->d_pred, d_tgt, rows, m->G + m->np + 1, m->s));
+    m->launches += 4;
+    if (want_grad) {
+        LTL_TRY(alloc_backward(m));
+        LTL_TRY(backward(m, a, d_ids, m->B, m->T));
+    }
+    return LTL_OK;
+}
+
+int train_step_dev(LM* m, const int32_t* d_ids, const int32_t* d_tgt, const luaTL_lm_train_args_t* a,
+                   luaTL_lm_result_t* out, int valid_local)
+{
+    if (m->adt != LTL_F32)
+        return ltl_fail(LTL_ERR_UNSUPPORTED, "lm train_step: the backward exists for dtype f32 only; "
+                        "create the model with dtype = LUATL_F32 to train");
+    LTL_TRY(ensure_train(m));
+    const int world = ltl_comm_world();
+    const int valid = a->valid_global > 0 ? a->valid_global : valid_local;
+    m->launches = 0;
+    LTL_CUDA("event", cudaEventRecord(m->ev[0], m->s));
+    LTL_TRY(loss_and_grad(m, d_ids, d_tgt, valid, 1));
+    if (world > 1) LTL_TRY(ltl_comm_allreduce(m->G, (uint64_t)m->np + 2, m->s));
+    float tail[4] = { 0, 0, 0, 0 };
+    LTL_CUDA("loss download", cudaMemcpyAsync(tail, m->G + m->np, 8, cudaMemcpyDeviceToHost, m->s));
+    LTL_CUDA("loss sync", cudaStreamSynchronize(m->s));
+    const int finite = isfinite(tail[0]) ? 1 : 0;
+    float gnorm = 0.0f;
+    if (finite && !a->no_update) {
+        const int need_norm = a->clip_norm > 0.0f;
+        if (need_norm) { LTL_TRY(ltl_l2_accum(m->G, (uint64_t)m->np, m->G + m->np + 2, LTL_F32, m->s)); m->launches++; }
+        if (a->optimizer == 0) {
+            if (a->weight_decay == 0.0f) {
+                LTL_TRY(ltl_sgd(m->W, m->G, nullptr, (uint64_t)m->np, a->lr, 0.0f, need_norm ? m->G + m->np + 2 : nullptr,
+                                a->clip_norm, m->s));
+                m->launches++;
+            } else {
+                for (const TensorInfo& t : m->tens) {
+                    LTL_TRY(ltl_sgd(m->W + t.off, m->G + t.off, nullptr, (uint64_t)t.rows * t.cols, a->lr,
+                                    t.decay ? a->weight_decay : 0.0f, need_norm ? m->G + m->np + 2 : nullptr,
+                                    a->clip_norm, m->s));
+                    m->launches++;
+                }
+            }
+        } else if (a->optimizer == 1) {
+            if (!m->adam_alloc) {
+                DALLOC(m->M1, (size_t)m->np * 4, "adam m"); DALLOC(m->M2, (size_t)m->np * 4, "adam v");
+                LTL_CUDA("adam zero", cudaMemsetAsync(m->M1, 0, (size_t)m->np * 4, m->s));
+                LTL_CUDA("adam zero", cudaMemsetAsync(m->M2, 0, (size_t)m->np * 4, m->s));
+                m->adam_alloc = 1;
+            }
+            if (need_norm) { LTL_TRY(ltl_clip_by_nsq(m->G, (uint64_t)m->np, m->G + m->np + 2, a->clip_norm, LTL_F32, m->s)); m->launches++; }
+            for (const TensorInfo& t : m->tens) {
+                LTL_TRY(ltl_adamw(m->W + t.off, m->G + t.off, m->M1 + t.off, m->M2 + t.off, nullptr,
+                                  (uint64_t)t.rows * t.cols, LTL_F32, a->lr, a->beta1, a->beta2, a->adam_eps,
+                                  t.decay ? a->weight_decay : 0.0f, a->step, 0.0f, m->s));
+                m->launches++;
+            }
+        } else return ltl_fail(LTL_ERR_ARG, "lm train_step: unknown optimizer %d", a->optimizer);
+        m->mirror_dirty = 1;
+        if (need_norm) {
+            LTL_CUDA("gnorm download", cudaMemcpyAsync(&tail[2], m->G + m->np + 2, 4, cudaMemcpyDeviceToHost, m->s));
+        }
+    }
+    LTL_CUDA("event", cudaEventRecord(m->ev[1], m->s));
+    LTL_CUDA("step sync", cudaStreamSynchronize(m->s));
+    if (tail[2] > 0.0f) gnorm = sqrtf(tail[2]);
+    if (out) {
+        out->loss = tail[0]; out->grad_norm = gnorm; out->correct = (int)(tail[1] + 0.5f);
+        out->valid = valid; out->finite = finite;
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, m->ev[0], m->ev[1]);
+        out->step_ms = ms;
+    }
+    return LTL_OK;
+}
+
+// ---------------- decode -----------------------------------------------------------------
+int ensure_decode(LM* m, int nseq, int n_prompt, int n_new)
+{
+    if (m->c.decode_batch <= 0) return ltl_fail(LTL_ERR_ARG, "lm: created with decode_batch = 0 (no KV cache)");
+    if (nseq > m->c.decode_batch) return ltl_fail(LTL_ERR_CAPACITY, "lm: %d sequences exceed decode_batch %d", nseq, m->c.decode_batch);
+    const size_t e = esz(m->adt);
+    if (!m->kc) {
+        m->nseq_cap = m->c.decode_batch;
+        const size_t cache = (size_t)m->L * m->nseq_cap * m->H * m->T * m->hd * e;
+        DALLOC(m->kc, cache, "K cache"); DALLOC(m->vc, cache, "V cache");
+        DALLOC(m->d_pos, (size_t)m->nseq_cap * 4, "positions"); DALLOC(m->d_count, (size_t)m->nseq_cap * 4, "counts");
+        DALLOC(m->d_next, (size_t)m->nseq_cap * 4, "next tokens"); DALLOC(m->d_err, 4, "error flag");
+        DALLOC(m->d_win, (size_t)m->nseq_cap * m->T * 4, "window ids");
+        DALLOC(m->xlast, (size_t)m->nseq_cap * m->D * 4, "last rows");
+        LTL_CUDA("memset", cudaMemsetAsync(m->d_pos, 0, (size_t)m->nseq_cap * 4, m->s));
+        LTL_CUDA("memset", cudaMemsetAsync(m->d_count, 0, (size_t)m->nseq_cap * 4, m->s));
+        LTL_CUDA("memset", cudaMemsetAsync(m->d_err, 0, 4, m->s));
+        LTL_TRY(alloc_act(m, m->dec, m->nseq_cap, 0, m->nseq_cap));
+        int sp = m->c.kv_splits;
+        if (sp <= 0) {
+            const int ctas = m->nseq_cap * m->H;
+            sp = (2 * ltl_sm_count() + ctas - 1) / ctas;
+            if (sp > 16) sp = 16;
+            if (sp < 1) sp = 1;
+        }
+        m->splits = sp;
+        LTL_TRY(ensure_ws(m, ltl_decode_attn_scratch_floats(m->nseq_cap, m->H, m->hd, sp) + 16));
+    }
+    if (n_prompt > 0) {
+        // Window of the prefill: the prompt, or the whole context once generation can fill it.
+        const int T = (n_prompt + n_new > m->T) ? m->T : n_prompt;
+        if (m->infer.rows_cap < nseq * T) {
+            if (m->infer.rows_cap) { LTL_CUDA("sync", cudaStreamSynchronize(m->s)); free_act(m->infer); }
+            LTL_TRY(alloc_act(m, m->infer, nseq * T, 0, m->nseq_cap));
+        }
+        const int hist = n_prompt + n_new;
+        if (m->hist_cap < m->nseq_cap * hist) {
+            LTL_CUDA("sync", cudaStreamSynchronize(m->s));
+            cudaFree(m->d_hist);
+            DALLOC(m->d_hist, (size_t)m->nseq_cap * hist * 4, "token history");
+            m->hist_cap = m->nseq_cap * hist;
+        }
+    }
+    return LTL_OK;
+}
+
+// One token for every sequence: consumes d_next / d_pos, appends K/V, picks the next token.
+// Everything it reads that changes between steps lives in device memory, so the launch
+// sequence can be captured once and replayed.
+int decode_step(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t* d_out, int out_stride, int pick)
+{
+    const int D = m->D, F = m->F, V = m->V, L = m->L, H = m->H, hd = m->hd, adt = m->adt;
+    const size_t e = esz(adt);
+    Act& a = m->dec;
+    float* x = a.res;
+    const void* table = adt == LTL_F32 ? (const void*)(m->W + m->off_emb) : (const void*)(m->Wb + m->off_emb);
+    const int32_t* pos = m->d_pos + slot0;
+    LTL_TRY(ltl_lm_embed(d_tok, table, adt, x, nseq, D, V, m->s));
+    m->launches++;
+    const size_t cl = (size_t)m->nseq_cap * H * m->T * hd * e;       // bytes per layer of cache
+    const size_t cslot = (size_t)slot0 * H * m->T * hd * e;
+    for (int l = 0; l < L; ++l) {
+        const LayerOff& o = m->lo[l];
+        void* kcl = (char*)m->kc + l * cl + cslot;
+        void* vcl = (char*)m->vc + l * cl + cslot;
+        LTL_TRY(ltl_lm_rmsnorm(x, m->W + o.ln1, a.h1, adt, nseq, D, m->c.eps, m->s));
+        LTL_TRY(wgemm(m, a.h1, nseq, D, o.wqkv, 3 * D, a.qkv, adt, nullptr, 0));
+        LTL_TRY(ltl_rope_append(a.qkv, kcl, vcl, pos, nseq, H, hd, m->T, m->rope_tab, m->c.rope_interleaved,
+                                m->c.use_rope, adt, m->d_err, m->s));
+        LTL_TRY(ltl_decode_attn(a.qkv, kcl, vcl, a.attn, pos, nseq, H, hd, m->T, m->scale, adt, m->splits, m->ws, m->s));
+        LTL_TRY(wgemm(m, a.attn, nseq, D, o.wo, D, x, LTL_F32, x, 0));
+        LTL_TRY(ltl_lm_rmsnorm(x, m->W + o.ln2, a.h2, adt, nseq, D, m->c.eps, m->s));
+        LTL_TRY(wgemm(m, a.h2, nseq, D, o.w13, 2 * F, a.h13, adt, nullptr, 0));
+        LTL_TRY(ltl_swiglu_fwd(a.h13, (char*)a.h13 + (size_t)F * e, a.hs, nseq, F, 2 * F, 2 * F, F, adt, m->s));
+        LTL_TRY(wgemm(m, a.hs, nseq, F, o.w2, D, x, LTL_F32, x, 0));
+        m->launches += 5 + (m->splits > 1 ? 1 : 0);
+    }
+    LTL_TRY(ltl_lm_rmsnorm(x, m->W + m->off_lnf, a.hf, adt, nseq, D, m->c.eps, m->s));
+    if (m->c.tie) LTL_TRY(wgemm(m, a.hf, nseq, D, m->off_emb, V, a.logits, LTL_F32, nullptr, 1));
+    else LTL_TRY(wgemm(m, a.hf, nseq, D, m->off_head, V, a.logits, LTL_F32, nullptr, 0));
+    m->launches++;
+    if (pick) {
+        LTL_TRY(ltl_pick_advance(a.logits, nseq, V, m->d_next + slot0, d_out, out_stride, m->d_count + slot0,
+                                 m->d_pos + slot0, m->s));
+        m->launches++;
+    }
+    return LTL_OK;
+}
+
+__global__ void window_kernel(const int32_t* __restrict__ hist, int hist_stride, int len, int32_t* __restrict__ win,
+                              int W, int nseq)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nseq * W) return;
+    const int b = i / W, t = i - b * W;
+    win[i] = hist[(size_t)b * hist_stride + (len - W) + t];
+}
+__global__ void append_hist_kernel(int32_t* __restrict__ hist, int hist_stride, int at, const int32_t* __restrict__ next, int nseq)
+{
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < nseq) hist[(size_t)b * hist_stride + at] = next[b];
+}
+__global__ void copy_prompt_kernel(const int32_t* __restrict__ prompts, int n_prompt, int32_t* __restrict__ hist,
+                                   int hist_stride, int nseq)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nseq * n_prompt) return;
+    const int b = i / n_prompt, t = i - b * n_prompt;
+    hist[(size_t)b * hist_stride + t] = prompts[i];
+}
+
+// Prefill the cache from the last min(len, max_seq) tokens of the history and pick a token.
+int prefill_and_pick(LM* m, int nseq, int len, int hist_stride, int32_t* d_out, int out_stride)
+{
+    const int Wn = len < m->T ? len : m->T;
+    window_kernel<<<(nseq * Wn + 255) / 256, 256, 0, m->s>>>(m->d_hist, hist_stride, len, m->d_win, Wn, nseq);
+    LTL_TRY(ltl_check_launch("window"));
+    LTL_TRY(forward(m, m->infer, m->d_win, nseq, Wn, MODE_PREFILL));
+    LTL_TRY(ltl_fill_i32(m->d_pos, nseq, Wn - 1, m->s));
+    LTL_TRY(ltl_pick_advance(m->infer.logits, nseq, m->V, m->d_next, d_out, out_stride, m->d_count, m->d_pos, m->s));
+    m->launches += 3;
+    return LTL_OK;
+}
+
+int generate_dev(LM* m, const int32_t* d_prompts, int nseq, int n_prompt, int n_new, int32_t* d_out,
+                 luaTL_lm_result_t* timing)
+{
+    if (nseq <= 0 || n_prompt <= 0 || n_new <= 0) return ltl_fail(LTL_ERR_SHAPE, "lm generate: nseq, n_prompt and n_new must be positive");
+    LTL_TRY(ensure_decode(m, nseq, n_prompt, n_new));
+    LTL_TRY(sync_mirror(m));
+    const int hs = n_prompt + n_new;
+    m->launches = 0;
+    LTL_CUDA("event", cudaEventRecord(m->ev[0], m->s));
+    LTL_CUDA("memset", cudaMemsetAsync(m->d_count, 0, (size_t)nseq * 4, m->s));
+    LTL_CUDA("memset", cudaMemsetAsync(m->d_err, 0, 4, m->s));
+    copy_prompt_kernel<<<(nseq * n_prompt + 255) / 256, 256, 0, m->s>>>(d_prompts, n_prompt, m->d_hist, hs, nseq);
+    LTL_TRY(ltl_check_launch("copy_prompt"));
+    LTL_TRY(prefill_and_pick(m, nseq, n_prompt, hs, d_out, n_new));
+    LTL_CUDA("event", cudaEventRecord(m->ev[1], m->s));
+    int len = n_prompt;                     // tokens in the history before the one just picked
+    int cached = n_prompt < m->T ? n_prompt : m->T;   // tokens in the cache
+    for (int step = 1; step < n_new; ++step) {
+        append_hist_kernel<<<(nseq + 255) / 256, 256, 0, m->s>>>(m->d_hist, hs, len, m->d_next, nseq);
+        ++len; m->launches++;
+        if (cached >= m->T) {
+            // cache full: rebuild it from the last max_seq tokens (ai/optim/lmtrain.lua:1511-1515)
+            LTL_TRY(prefill_and_pick(m, nseq, len, hs, d_out, n_new));
+            cached = m->T;
+            continue;
+        }
+        GraphEntry& ge = m->graphs[nseq];
+        if (ge.ge && (ge.out != d_out || ge.out_stride != n_new)) {   // captured for other buffers
+            cudaGraphExecDestroy(ge.ge); cudaGraphDestroy(ge.g);
+            ge = GraphEntry();
+        }
+        if (!ge.ge) {
+            // First use: run the step eagerly (it is a real step), then capture a copy for replay.
+            const int64_t before = m->launches;
+            LTL_TRY(decode_step(m, nseq, 0, m->d_next, d_out, n_new, 1));
+            const int64_t per_step = m->launches - before;
+            ++cached;
+            LTL_CUDA("pre-capture sync", cudaStreamSynchronize(m->s));
+            LTL_CUDA("begin capture", cudaStreamBeginCapture(m->s, cudaStreamCaptureModeThreadLocal));
+            const int rc = decode_step(m, nseq, 0, m->d_next, d_out, n_new, 1);
+            cudaGraph_t g = nullptr;
+            const cudaError_t ce = cudaStreamEndCapture(m->s, &g);
+            m->launches -= per_step;        // the captured copy did not execute
+            if (rc != LTL_OK) { if (g) cudaGraphDestroy(g); cudaGetLastError(); return rc; }
+            if (ce != cudaSuccess) return ltl_cuda_fail("end capture", ce);
+            cudaGraphExec_t gx = nullptr;
+            const cudaError_t ie = cudaGraphInstantiate(&gx, g, 0);
+            if (ie != cudaSuccess) { cudaGraphDestroy(g); return ltl_cuda_fail("graph instantiate", ie); }
+            ge.g = g; ge.ge = gx; ge.launches = per_step; ge.out = d_out; ge.out_stride = n_new;
+            continue;
+        }
+        LTL_CUDA("graph launch", cudaGraphLaunch(ge.ge, m->s));
+        m->launches += ge.launches;
+        ++cached;
+    }
+    LTL_CUDA("event", cudaEventRecord(m->ev[2], m->s));
+    int err = 0;
+    LTL_CUDA("error flag", cudaMemcpyAsync(&err, m->d_err, 4, cudaMemcpyDeviceToHost, m->s));
+    LTL_CUDA("generate sync", cudaStreamSynchronize(m->s));
+    if (err) return ltl_fail(LTL_ERR_CAPACITY, "lm generate: a position left the KV cache");
+    cudaEventElapsedTime(&m->prefill_ms, m->ev[0], m->ev[1]);
+    cudaEventElapsedTime(&m->decode_ms, m->ev[1], m->ev[2]);
+    if (timing) {
+        memset(timing, 0, sizeof(*timing));
+        timing->step_ms = m->prefill_ms + m->decode_ms;
+        timing->valid = nseq * n_new;
+        timing->finite = 1;
+    }
+    return LTL_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
+{
+    if (ltl_require_init("lm_create") != LTL_OK) return nullptr;
+    if (!cfg) { ltl_fail(LTL_ERR_NULL, "lm_create: null config"); return nullptr; }
+    const luaTL_lm_config_t& c = *cfg;
+    if (c.vocab < 1 || c.dim < 1 || c.layers < 1 || c.heads < 1 || c.ffn < 1 || c.max_seq < 1 || c.batch < 0) {
+        ltl_fail(LTL_ERR_ARG, "lm_create: vocab, dim, layers, heads, ffn and max_seq must be positive integers");
+        return nullptr;
+    }
+    if (c.dim % c.heads) { ltl_fail(LTL_ERR_ARG, "lm_create: dim (%d) must be divisible by heads (%d)", c.dim, c.heads); return nullptr; }
+    const int hd = c.dim / c.heads;
+    if (hd & 1) { ltl_fail(LTL_ERR_ARG, "lm_create: head_dim (dim/heads = %d) must be even for RoPE", hd); return nullptr; }
+    if (hd != 16 && hd != 32 && hd != 64 && hd != 128) {
+        ltl_fail(LTL_ERR_UNSUPPORTED, "lm_create: head_dim %d not in {16, 32, 64, 128}", hd); return nullptr;
+    }
+    if (c.dim % 8 || c.ffn % 8) { ltl_fail(LTL_ERR_UNSUPPORTED, "lm_create: dim and ffn must be multiples of 8"); return nullptr; }
+    if (c.dtype != LTL_F32 && c.dtype != LTL_BF16) { ltl_fail(LTL_ERR_DTYPE, "lm_create: dtype must be f32 or bf16"); return nullptr; }
+    LM* m = new LM();
+    m->c = c;
+    m->D = c.dim; m->H = c.heads; m->hd = hd; m->F = c.ffn; m->V = c.vocab; m->L = c.layers; m->T = c.max_seq;
+    m->B = c.batch; m->adt = c.dtype; m->splits = 1;
+    m->scale = 1.0f / sqrtf((float)hd);
+    m->s = ltl_default_stream();
+    layout_params(m);
+    int rc = LTL_OK;
+    auto A = [&](void** p, size_t bytes, const char* what) { if (rc == LTL_OK) rc = dalloc(p, bytes, what); };
+    A((void**)&m->W, (size_t)m->np * 4, "parameters");
+    A((void**)&m->G, (size_t)(m->np + 4) * 4, "gradients");
+    if (m->adt == LTL_BF16) A((void**)&m->Wb, (size_t)m->np * 2, "bf16 weights");
+    A((void**)&m->rope_tab, (size_t)m->T * (hd / 2) * sizeof(float2), "rope table");
+    for (int i = 0; i < 4 && rc == LTL_OK; ++i)
+        if (cudaEventCreate(&m->ev[i]) != cudaSuccess) rc = ltl_fail(LTL_ERR_CUDA, "lm_create: cudaEventCreate failed");
+    if (rc == LTL_OK) rc = ltl_rope_table(m->rope_tab, m->T, hd, c.rope_base, m->s);
+    if (rc == LTL_OK && cudaMemsetAsync(m->W, 0, (size_t)m->np * 4, m->s) != cudaSuccess) rc = ltl_fail(LTL_ERR_CUDA, "lm_create: memset failed");
+    if (rc == LTL_OK && cudaMemsetAsync(m->G, 0, (size_t)(m->np + 4) * 4, m->s) != cudaSuccess) rc = ltl_fail(LTL_ERR_CUDA, "lm_create: memset failed");
+    if (rc == LTL_OK && cudaStreamSynchronize(m->s) != cudaSuccess) rc = ltl_fail(LTL_ERR_CUDA, "lm_create: sync failed");
+    if (rc != LTL_OK) { luaTL_lm_destroy(m); return nullptr; }
+    return m;
+}
+
+void luaTL_lm_destroy(luaTL_lm_t* m)
+{
+    if (!m) return;
+    cudaDeviceSynchronize();
+    for (auto& kv : m->graphs) {
+        if (kv.second.ge) cudaGraphExecDestroy(kv.second.ge);
+        if (kv.second.g) cudaGraphDestroy(kv.second.g);
+    }
+    free_act(m->train); free_act(m->infer); free_act(m->dec);
+    void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
+                     m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
+                     m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast };
+    for (void* p : ptrs) if (p) cudaFree(p);
+    for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
+    cudaGetLastError();
+    delete m;
+}
+
+int64_t luaTL_lm_nparams(const luaTL_lm_t* m) { return m ? m->np : 0; }
+int luaTL_lm_ntensors(const luaTL_lm_t* m) { return m ? (int)m->tens.size() : 0; }
+int luaTL_lm_tensor_info(const luaTL_lm_t* m, int i, char* name32, int32_t* rows, int32_t* cols, int64_t* offset, int32_t* decay)
+{
+    if (!m) return ltl_fail(LTL_ERR_NULL, "lm_tensor_info: null model");
+    if (i < 0 || i >= (int)m->tens.size()) return ltl_fail(LTL_ERR_ARG, "lm_tensor_info: no parameter %d", i);
+    const TensorInfo& t = m->tens[i];
+    if (name32) memcpy(name32, t.name, 32);
+    if (rows) *rows = t.rows;
+    if (cols) *cols = t.cols;
+    if (offset) *offset = t.off;
+    if (decay) *decay = t.decay;
+    return LTL_OK;
+}
+
+static int check_range(const luaTL_lm_t* m, int64_t offset, int64_t count, const void* host, const char* ctx)
+{
+    if (!m || !host) return ltl_fail(LTL_ERR_NULL, "%s: null pointer", ctx);
+    if (offset < 0 || count < 0 || offset + count > m->np)
+        return ltl_fail(LTL_ERR_SHAPE, "%s: range %lld..%lld outside the %lld parameters", ctx, (long long)offset,
+                        (long long)(offset + count), (long long)m->np);
+    return LTL_OK;
+}
+int luaTL_lm_write_params(luaTL_lm_t* m, int64_t offset, int64_t count, const float* host)
+{
+    LTL_TRY(check_range(m, offset, count, host, "lm_write_params"));
+    LTL_CUDA("lm_write_params", cudaMemcpyAsync(m->W + offset, host, (size_t)count * 4, cudaMemcpyHostToDevice, m->s));
+    LTL_CUDA("lm_write_params", cudaStreamSynchronize(m->s));
+    m->mirror_dirty = 1;
+    return LTL_OK;
+}
+int luaTL_lm_read_params(luaTL_lm_t* m, int64_t offset, int64_t count, float* host)
+{
+    LTL_TRY(check_range(m, offset, count, host, "lm_read_params"));
+    LTL_CUDA("lm_read_params", cudaMemcpyAsync(host, m->W + offset, (size_t)count * 4, cudaMemcpyDeviceToHost, m->s));
+    LTL_CUDA("lm_read_params", cudaStreamSynchronize(m->s));
+    return LTL_OK;
+}
+int luaTL_lm_read_grads(luaTL_lm_t* m, int64_t offset, int64_t count, float* host)
+{
+    LTL_TRY(check_range(m, offset, count, host, "lm_read_grads"));
+    LTL_CUDA("lm_read_grads", cudaMemcpyAsync(host, m->G + offset, (size_t)count * 4, cudaMemcpyDeviceToHost, m->s));
+    LTL_CUDA("lm_read_grads", cudaStreamSynchronize(m->s));
+    return LTL_OK;
+}
+float* luaTL_lm_params_device(luaTL_lm_t* m) { if (m) m->mirror_dirty = 1; return m ? m->W : nullptr; }
+float* luaTL_lm_grads_device(luaTL_lm_t* m) { return m ? m->G : nullptr; }
+
+int luaTL_lm_train_step_dev(luaTL_lm_t* m, const int32_t* d_ids, const int32_t* d_targets,
+                            const luaTL_lm_train_args_t* a, luaTL_lm_result_t* out)
+{
+    if (!m || !d_ids || !d_targets || !a) return ltl_fail(LTL_ERR_NULL, "lm_train_step_dev: null pointer");
+    if (m->B < 1) return ltl_fail(LTL_ERR_ARG, "lm_train_step: model created with batch = 0");
+    if (a->valid_global <= 0) return ltl_fail(LTL_ERR_ARG, "lm_train_step_dev: valid_global must be given for device-resident targets");
+    return train_step_dev(m, d_ids, d_targets, a, out, a->valid_global);
+}
+
+int luaTL_lm_train_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* targets,
+                        const luaTL_lm_train_args_t* a, luaTL_lm_result_t* out)
+{
+    if (!m || !ids || !targets || !a) return ltl_fail(LTL_ERR_NULL, "lm_train_step: null pointer");
+    if (m->B < 1) return ltl_fail(LTL_ERR_ARG, "lm_train_step: model created with batch = 0");
+    LTL_TRY(ensure_train(m));
+    const int rows = m->B * m->T;
+    for (int i = 0; i < rows; ++i)
+        if (ids[i] < 0 || ids[i] >= m->V || targets[i] >= m->V)
+            return ltl_fail(LTL_ERR_ARG, "lm_train_step: token out of range at row %d (input %d, target %d, vocab %d)",
+                            i, ids[i], targets[i], m->V);
+    LTL_CUDA("ids upload", cudaMemcpyAsync(m->d_ids, ids, (size_t)rows * 4, cudaMemcpyHostToDevice, m->s));
+    LTL_CUDA("targets upload", cudaMemcpyAsync(m->d_tgt, targets, (size_t)rows * 4, cudaMemcpyHostToDevice, m->s));
+    return train_step_dev(m, m->d_ids, m->d_tgt, a, out, count_valid(targets, rows, m->V));
+}
+
+int luaTL_lm_eval_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* targets, luaTL_lm_result_t* out)
+{
+    if (!m || !ids || !targets) return ltl_fail(LTL_ERR_NULL, "lm_eval_step: null pointer");
+    if (m->B < 1) return ltl_fail(LTL_ERR_ARG, "lm_eval_step: model created with batch = 0");
+    LTL_TRY(ensure_train(m));
+    const int rows = m->B * m->T;
+    LTL_CUDA("ids upload", cudaMemcpyAsync(m->d_ids, ids, (size_t)rows * 4, cudaMemcpyHostToDevice, m->s));
+    LTL_CUDA("targets upload", cudaMemcpyAsync(m->d_tgt, targets, (size_t)rows * 4, cudaMemcpyHostToDevice, m->s));
+    const int valid = count_valid(targets, rows, m->V);
+    m->launches = 0;
+    LTL_CUDA("event", cudaEventRecord(m->ev[0], m->s));
+    LTL_TRY(loss_and_grad(m, m->d_ids, m->d_tgt, valid, 0));
+    LTL_CUDA("event", cudaEventRecord(m->ev[1], m->s));
+    float tail[2] = { 0, 0 };
+    LTL_CUDA("loss download", cudaMemcpyAsync(tail, m->G + m->np, 8, cudaMemcpyDeviceToHost, m->s));
+    LTL_CUDA("eval sync", cudaStreamSynchronize(m->s));
+    if (out) {
+        memset(out, 0, sizeof(*out));
+        out->loss = tail[0]; out->correct = (int)(tail[1] + 0.5f); out->valid = valid; out->finite = isfinite(tail[0]) ? 1 : 0;
+        cudaEventElapsedTime(&out->step_ms, m->ev[0], m->ev[1]);
+    }
+    return LTL_OK;
+}
+
+int luaTL_lm_forward(luaTL_lm_t* m, const int32_t* ids, int nseq, int ntok, float* logits_host, int last_only)
+{
+    if (!m || !ids || !logits_host) return ltl_fail(LTL_ERR_NULL, "lm_forward: null pointer");
+    if (m->B < 1) return ltl_fail(LTL_ERR_ARG, "lm_forward: model created with batch = 0");
+    if (nseq < 1 || nseq > m->B || ntok < 1 || ntok > m->T)
+        return ltl_fail(LTL_ERR_SHAPE, "lm_forward: %d sequences x %d tokens outside batch %d x max_seq %d", nseq, ntok, m->B, m->T);
+    LTL_TRY(ensure_train(m));
+    const int rows = nseq * ntok;
+    for (int i = 0; i < rows; ++i)
+        if (ids[i] < 0 || ids[i] >= m->V) return ltl_fail(LTL_ERR_ARG, "lm_forward: token %d out of range at row %d", ids[i], i);
+    LTL_CUDA("ids upload", cudaMemcpyAsync(m->d_ids, ids, (size_t)rows * 4, cudaMemcpyHostToDevice, m->s));
+    m->launches = 0;
+    LTL_TRY(forward(m, m->train, m->d_ids, nseq, ntok, MODE_TRAIN));
+    if (last_only)
+        LTL_CUDA("logits download", cudaMemcpyAsync(logits_host, m->train.logits + (size_t)(ntok - 1) * m->V, (size_t)m->V * 4,
+                                                    cudaMemcpyDeviceToHost, m->s));
+    else
+        LTL_CUDA("logits download", cudaMemcpyAsync(logits_host, m->train.logits, (size_t)rows * m->V * 4,
+                                                    cudaMemcpyDeviceToHost, m->s));
+    LTL_CUDA("forward sync", cudaStreamSynchronize(m->s));
+    return LTL_OK;
+}
+
+int luaTL_lm_state_reset(luaTL_lm_t* m)
+{
+    if (!m) return ltl_fail(LTL_ERR_NULL, "lm_state_reset: null model");
+    LTL_TRY(ensure_decode(m, 1, 0, 0));
+    LTL_CUDA("memset", cudaMemsetAsync(m->d_pos, 0, (size_t)m->nseq_cap * 4, m->s));
+    LTL_CUDA("memset", cudaMemsetAsync(m->d_count, 0, (size_t)m->nseq_cap * 4, m->s));
+    LTL_CUDA("memset", cudaMemsetAsync(m->d_err, 0, 4, m->s));
+    LTL_CUDA("state_reset sync", cudaStreamSynchronize(m->s));
+    return LTL_OK;
+}
+
+int luaTL_lm_slot_reset(luaTL_lm_t* m, int slot)
+{
+    if (!m) return ltl_fail(LTL_ERR_NULL, "lm_slot_reset: null model");
+    LTL_TRY(ensure_decode(m, 1, 0, 0));
+    if (slot < 0 || slot >= m->nseq_cap) return ltl_fail(LTL_ERR_ARG, "lm_slot_reset: slot %d outside 0..%d", slot, m->nseq_cap - 1);
+    LTL_CUDA("memset", cudaMemsetAsync(m->d_pos + slot, 0, 4, m->s));
+    LTL_CUDA("memset", cudaMemsetAsync(m->d_count + slot, 0, 4, m->s));
+    LTL_CUDA("slot_reset sync", cudaStreamSynchronize(m->s));
+    return LTL_OK;
+}
+
+int luaTL_lm_state_len(luaTL_lm_t* m, int slot)
+{
+    if (!m || !m->d_pos || slot < 0 || slot >= m->nseq_cap) return -1;
+    int v = -1;
+    if (cudaMemcpyAsync(&v, m->d_pos + slot, 4, cudaMemcpyDeviceToHost, m->s) != cudaSuccess) return -1;
+    if (cudaStreamSynchronize(m->s) != cudaSuccess) return -1;
+    return v;
+}
+
+int luaTL_lm_step(luaTL_lm_t* m, int slot, int32_t id, float* logits_host)
+{
+    if (!m || !logits_host) return ltl_fail(LTL_ERR_NULL, "lm_step: null pointer");
+    LTL_TRY(ensure_decode(m, 1, 0, 0));
+    if (slot < 0 || slot >= m->nseq_cap) return ltl_fail(LTL_ERR_ARG, "lm_step: slot %d outside 0..%d", slot, m->nseq_cap - 1);
+    if (id < 0 || id >= m->V) return ltl_fail(LTL_ERR_ARG, "lm_step: token id out of range: %d", id);
+    const int len = luaTL_lm_state_len(m, slot);
+    if (len < 0) return ltl_fail(LTL_ERR_CUDA, "lm_step: could not read the state length");
+    if (len >= m->T) return ltl_fail(LTL_ERR_CAPACITY, "lm_step: context is full (%d tokens)", m->T);
+    LTL_TRY(sync_mirror(m));
+    LTL_CUDA("token upload", cudaMemcpyAsync(m->d_next + slot, &id, 4, cudaMemcpyHostToDevice, m->s));
+    const int sp = m->splits;
+    LTL_TRY(decode_step(m, 1, slot, m->d_next + slot, nullptr, 0, 1));
+    m->splits = sp;
+    LTL_CUDA("logits download", cudaMemcpyAsync(logits_host, m->dec.logits, (size_t)m->V * 4, cudaMemcpyDeviceToHost, m->s));
+    LTL_CUDA("lm_step sync", cudaStreamSynchronize(m->s));
+    return LTL_OK;
+}
+
+int luaTL_lm_generate_dev(luaTL_lm_t* m, const int32_t* d_prompts, int nseq, int n_prompt, int n_new,
+                          int32_t* d_out, luaTL_lm_result_t* timing)
+{
+    if (!m || !d_prompts || !d_out) return ltl_fail(LTL_ERR_NULL, "lm_generate_dev: null pointer");
+    return generate_dev(m, d_prompts, nseq, n_prompt, n_new, d_out, timing);
+}
+
+int luaTL_lm_generate(luaTL_lm_t* m, const int32_t* prompts, int nseq, int n_prompt, int n_new,
+                      int32_t* out, luaTL_lm_result_t* timing)
+{
+    if (!m || !prompts || !out) return ltl_fail(LTL_ERR_NULL, "lm_generate: null pointer");
+    if (nseq <= 0 || n_prompt <= 0 || n_new <= 0) return ltl_fail(LTL_ERR_SHAPE, "lm_generate: nseq, n_prompt and n_new must be positive");
+    for (int i = 0; i < nseq * n_prompt; ++i)
+        if (prompts[i] < 0 || prompts[i] >= m->V) return ltl_fail(LTL_ERR_ARG, "lm_generate: token %d out of range at %d", prompts[i], i);
+    if (m->prompt_cap < nseq * n_prompt) {
+        cudaStreamSynchronize(m->s);
+        cudaFree(m->d_prompt);
+        DALLOC(m->d_prompt, (size_t)nseq * n_prompt * 4, "prompts");
+        m->prompt_cap = nseq * n_prompt;
+    }
+    if (m->out_cap < nseq * n_new) {
+        cudaStreamSynchronize(m->s);
+        cudaFree(m->d_out);
+        DALLOC(m->d_out, (size_t)nseq * n_new * 4, "generated ids");
+        m->out_cap = nseq * n_new;
+    }
+    LTL_CUDA("prompt upload", cudaMemcpyAsync(m->d_prompt, prompts, (size_t)nseq * n_prompt * 4, cudaMemcpyHostToDevice, m->s));
+    LTL_TRY(generate_dev(m, m->d_prompt, nseq, n_prompt, n_new, m->d_out, timing));
+    LTL_CUDA("ids download", cudaMemcpyAsync(out, m->d_out, (size_t)nseq * n_new * 4, cudaMemcpyDeviceToHost, m->s));
+    LTL_CUDA("generate sync", cudaStreamSynchronize(m->s));
+    return LTL_OK;
+}
+
+int luaTL_lm_last_timing(luaTL_lm_t* m, float* prefill_ms, float* decode_ms, int64_t* launches)
+{
+    if (!m) return ltl_fail(LTL_ERR_NULL, "lm_last_timing: null model");
+    if (prefill_ms) *prefill_ms = m->prefill_ms;
+    if (decode_ms) *decode_ms = m->decode_ms;
+    if (launches) *launches = m->launches;
+    return LTL_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,107 @@
+// Internal launchers shared by the C ABI, the Program interpreter and the LM runtime.
+// Every function enqueues on `s` and returns a status; none of them synchronises.
+#pragma once
+#include "common.cuh"
+
+// ---- bandwidth-bound row / element kernels (ops.cu) ----
+int ltl_rmsnorm(const void* x, const void* w, void* out, int rows, int cols, float eps,
+                int dtype, cudaStream_t s);
+// `scratch` holds rmsnorm_bwd_scratch_floats(cols) floats (per-CTA dgamma partials).
+size_t ltl_rmsnorm_bwd_scratch_floats(int cols);
+int ltl_rmsnorm_bwd(const void* x, const void* gamma, const void* dy, void* dx, float* dgamma,
+                    int rows, int cols, float eps, int dtype, float* scratch, cudaStream_t s);
+int ltl_softmax(const void* x, const void* bias, void* out, int rows, int cols, float scale,
+                int causal, int group, int mask_offset, int dtype, cudaStream_t s);
+int ltl_softmax_bwd(const void* y, const void* dy, void* dx, int rows, int cols, float scale,
+                    int causal, int group, int mask_offset, int dtype, cudaStream_t s);
+int ltl_swiglu_fwd(const void* a, const void* b, void* out, int rows, int cols, int lda, int ldb,
+                   int ldo, int dtype, cudaStream_t s);
+int ltl_swiglu_bwd(const void* a, const void* b, const void* dout, void* da, void* db, int rows,
+                   int cols, int lda, int ldb, int ldo, int dtype, cudaStream_t s);
+// cs_table: optional [npos, head_dim/2] float2 (cos, sin) table; NULL = compute angles inline.
+int ltl_rope(void* x, const int32_t* pos_ids, int rows, int heads, int head_dim, int row_stride,
+             int pos_offset, float theta, int interleaved, int inverse, int dtype,
+             const float2* cs_table, int table_rows, cudaStream_t s);
+int ltl_rope_table(float2* table, int npos, int head_dim, float theta, cudaStream_t s);
+int ltl_embed_fwd(const int32_t* ids, const void* table, void* out, int rows, int dim, int vocab,
+                  int dtype, cudaStream_t s);
+int ltl_embed_bwd(const int32_t* ids, const void* dout, float* dtable, int rows, int dim,
+                  int vocab, float scale, int dtype, cudaStream_t s);
+// pred (optional): row argmax of the logits (ties -> lowest index), written before dlogits.
+int ltl_cross_entropy(const void* logits, const int32_t* targets, float* losses, void* dlogits,
+                      int32_t* pred, int rows, int vocab, int ignore_index, float grad_scale,
+                      int dtype, cudaStream_t s);
+int ltl_argmax_rows(const void* x, int32_t* out, int rows, int cols, int dtype, cudaStream_t s);
+int ltl_l2_accum(const void* x, uint64_t n, float* out, int dtype, cudaStream_t s);
+int ltl_clip_by_nsq(void* x, uint64_t n, const float* nsq, float max_norm, int dtype,
+                    cudaStream_t s);
+int ltl_sum_f32(const float* x, uint64_t n, float* out, float scale, cudaStream_t s);
+int ltl_elementwise(const void* a, const void* b, void* c, uint64_t n, int dtype, int op,
+                    float alpha, float beta, cudaStream_t s);
+int ltl_cast(const void* src, int src_dtype, void* dst, int dst_dtype, uint64_t n, cudaStream_t s);
+int ltl_adamw(float* w, const void* g, float* m, float* v, void* w_lp, uint64_t n, int grad_dtype,
+              float lr, float beta1, float beta2, float eps, float wd, int step, float clip,
+              cudaStream_t s);
+// w -= lr * (f * g + wd * w), f = clip factor from *nsq (NULL or max_norm <= 0: f = 1).
+// w_lp (optional) receives the bf16 copy of the updated weights.
+int ltl_sgd(float* w, const float* g, bf16* w_lp, uint64_t n, float lr, float wd,
+            const float* nsq, float max_norm, cudaStream_t s);
+// out[c, r] = (bf16) in[r, c]
+int ltl_transpose_to_bf16(const float* in, bf16* out, int rows, int cols, cudaStream_t s);
+
+// ---- CUDA-core GEMM with explicit strides (gemm_simt.cu) ----
+struct GemmDesc {
+    const void* A; const void* B; void* C;
+    const void* bias;      // [N], optional
+    const void* R;         // residual with C's strides, optional: C = post(alpha*AB + bias) + beta*C + R
+    int M, N, K, batch;
+    long long a_rs, a_cs, b_rs, b_cs, c_rs, c_cs, a_bs, b_bs, c_bs;
+    float alpha, beta;
+    int post_op;           // 0 none, 1 relu, 2 gelu, 3 silu, 4 tanh, 5 sigmoid
+    int a_dtype, b_dtype, c_dtype;
+};
+int ltl_gemm_simt(const GemmDesc& g, cudaStream_t s);
+
+// ---- attention (attention.cu) ----
+// Causal self-attention over packed [rows, 3D] q|k|v (after RoPE), sequences of T rows.
+// out [rows, D]; lse [B*H*T] (log-sum-exp of the scaled scores, kept for the backward).
+int ltl_attn_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int hd, float scale,
+                 int causal, int dtype, cudaStream_t s);
+// dqkv [rows, 3D]; delta [B*H*T] scratch.
+int ltl_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse,
+                 float* delta, void* dqkv, int B, int T, int H, int hd, float scale, int causal,
+                 int dtype, cudaStream_t s);
+
+// ---- token-loop kernels (lm_kernels.cu) ----
+// res[r, :] = (float) table[ids[r], :]; table dtype f32 or bf16; ids outside [0, vocab) -> 0.
+int ltl_lm_embed(const int32_t* ids, const void* table, int table_dtype, float* res, int rows,
+                 int dim, int vocab, cudaStream_t s);
+// out[r, :] = rmsnorm(x[r, :]) * gain, x and gain fp32, out f32 or bf16.
+int ltl_lm_rmsnorm(const float* x, const float* gain, void* out, int out_dtype, int rows, int cols,
+                   float eps, cudaStream_t s);
+// One new token per sequence: rotate q in place inside qkv [B, 3D], write the rotated k and v
+// of every head at position pos[b] of the caches ([B, H, ctx, hd] each).  err (optional) is
+// set to 1 when a position is outside [0, ctx).
+int ltl_rope_append(void* qkv, void* kcache, void* vcache, const int32_t* pos, int B, int H, int hd,
+                    int ctx, const float2* cs_table, int interleaved, int use_rope, int dtype,
+                    int* err, cudaStream_t s);
+// Prefill: copy rotated k and v of rows [B, T] of qkv [B*T, 3D] into the caches at 0..T-1.
+int ltl_kv_store(const void* qkv, void* kcache, void* vcache, int B, int T, int H, int hd, int ctx,
+                 int dtype, cudaStream_t s);
+// Decode attention of one query per sequence over cache positions 0..pos[b].
+// splits > 1 spreads the keys of one (sequence, head) over several CTAs; scratch then holds
+// decode_attn_scratch_floats(B, H, hd, splits) floats.
+size_t ltl_decode_attn_scratch_floats(int B, int H, int hd, int splits);
+int ltl_decode_attn(const void* qkv, const void* kcache, const void* vcache, void* out,
+                    const int32_t* pos, int B, int H, int hd, int ctx, float scale, int dtype,
+                    int splits, float* scratch, cudaStream_t s);
+// Greedy pick and bookkeeping of one decode step, per sequence b:
+//   next[b] = argmax(logits[b, :]) (ties -> lowest index);
+//   out_ids[b * out_stride + count[b]] = next[b] when count[b] < out_stride; count[b] += 1; pos[b] += 1.
+int ltl_pick_advance(const float* logits, int B, int V, int32_t* next, int32_t* out_ids,
+                     int out_stride, int32_t* count, int32_t* pos, cudaStream_t s);
+int ltl_fill_i32(int32_t* p, int n, int32_t value, cudaStream_t s);
+// correct[0] += #{r : tgt[r] >= 0 and pred[r] == tgt[r]}  (as float)
+int ltl_count_correct(const int32_t* pred, const int32_t* tgt, int n, float* correct, cudaStream_t s);
+// Gather row (b * T + last) of x [B*T, cols] into out [B, cols].
+int ltl_gather_last_rows(const float* x, float* out, int B, int T, int cols, int last, cudaStream_t s);

@@ -1,0 +1,325 @@
+"""Whole-path parity of the device-resident model against the CPU oracle (float64
+restatement of the reference's CPU path) on the benchmark configurations: logits, loss,
+every gradient, the SGD update, KV-cache steps and greedy generations.
+
+Tolerances (north star): ids, argmax picks and gathers bit-exact; logits / losses / gradients
+within 1e-4 relative on the fp32 path, 2e-3 relative where bf16 inputs feed the GEMMs; greedy
+generations identical for the first 64 tokens."""
+import numpy as np
+import pytest
+
+from lanternl_b200 import gpu_transformer as GT, synth
+from lanternl_b200._lib import LuaTLError
+from oracle import cpu_ref
+from tests.util import CFG0, CFG1, CFG2, bf16_round, params_for, rel_err, shifted_targets, split_params
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-4
+TOL_BF16 = 2e-3
+
+
+def make(cfg, batch, w=None, decode_batch=1, **kw):
+    m = GT.new(dict(cfg, batch_size=batch, decode_batch=decode_batch, **kw))
+    if w is not None:
+        m.load_flat(w)
+    return m
+
+
+def oracle_for(cfg, **kw):
+    return cpu_ref.Oracle(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], cfg["max_seq"], **kw)
+
+
+# ---- configuration 0: tiny byte-level LM, the full workload ------------------------------------
+def test_config0_forward_sgd_step_and_greedy_generation():
+    cfg = CFG0
+    w = params_for(cfg, seed=0)
+    ids = synth.uniform_ids(1, 32, cfg["vocab"])                       # batch 1 of 32 ids, seed 1
+    T = cfg["max_seq"]
+    block = np.zeros((1, T), np.int32)
+    tgt = np.full((1, T), -1, np.int32)
+    block[0, :31], tgt[0, :31] = ids[:31], ids[1:32]
+    o = oracle_for(cfg)
+    m = make(cfg, 1, w, optimizer="sgd")
+
+    # forward
+    ref_logits = o.forward(w, ids[None, :])[0]
+    got_logits = m.logits_ids(ids[None, :])[0]
+    assert rel_err(got_logits, ref_logits) < TOL_F32
+    assert np.array_equal(got_logits.argmax(-1), ref_logits.argmax(-1))
+
+    # loss and every gradient (no update)
+    ref = o.loss_grad(w, block, tgt)
+    loss, correct, valid, _, finite = m.train_step_ids(block, tgt, lr=0.01, no_update=True)
+    assert finite and valid == 31 == ref["valid"]
+    assert abs(loss - ref["loss"]) < TOL_F32 * abs(ref["loss"])
+    assert correct == int((ref["pred"][tgt >= 0] == tgt[tgt >= 0]).sum())
+    got_g, ref_g = split_params(m.flat_grads(), cfg), split_params(ref["grads"], cfg)
+    for name in ref_g:
+        assert rel_err(got_g[name], ref_g[name]) < TOL_F32, name
+
+    # one SGD step, lr 0.01
+    m.train_step_ids(block, tgt, lr=0.01)
+    ref_w = o.sgd(w, ref["grads"], lr=0.01)
+    assert np.abs(m.flat_params() - ref_w).max() < 1e-7
+    assert m.steps == 1
+
+    # greedy generation of 64 tokens from the first 8 ids, KV cache on the device
+    m.load_flat(w)
+    ref_tokens = o.greedy(w, ids[None, :8], 64)[0]
+    got = m.generate_batch(ids[None, :8], 64, zero_indexed=True)[0]
+    assert np.array_equal(got, ref_tokens)
+
+
+def test_config0_kv_cache_step_matches_oracle_step_and_full_forward():
+    cfg = CFG0
+    w = params_for(cfg, seed=0)
+    ids = synth.uniform_ids(2, 20, cfg["vocab"])
+    o, m = oracle_for(cfg), make(cfg, 1, w)
+    ref = o.step_logits(w, ids)
+    st = m.new_state()
+    for i, t in enumerate(ids):
+        row = m.step(int(t) + 1, st)                                  # host API is 1-indexed
+        assert rel_err(row, ref[i]) < TOL_F32
+        assert int(np.argmax(row)) == int(np.argmax(ref[i]))
+    assert st.n == len(ids)
+    full = m.logits_ids(ids[None, :])[0]
+    assert rel_err(full, ref) < TOL_F32
+    # the duck-typed forward() of the reference: only the final row, 1-indexed proxy
+    out = m.forward([int(t) + 1 for t in ids])
+    assert out.data.rows == len(ids) and out.data.cols == cfg["vocab"]
+    base = (len(ids) - 1) * cfg["vocab"]
+    assert abs(out.data.data[base + 1] - full[-1, 0]) < 1e-6
+    with pytest.raises(IndexError):
+        out.data.data[1]
+    # a second state starts from an empty cache
+    st2 = m.new_state()
+    assert rel_err(m.step(int(ids[0]) + 1, st2), ref[0]) < TOL_F32
+
+
+def test_generation_refills_the_cache_when_the_context_is_full():
+    cfg = dict(CFG0, max_seq=16)
+    w = params_for(cfg, seed=3, std=0.1)
+    prompts = synth.uniform_ids(4, 2 * 5, cfg["vocab"]).reshape(2, 5)
+    o, m = oracle_for(cfg), make(cfg, 1, w, decode_batch=2)
+    n_new = 24                                                        # runs past max_seq
+    assert np.array_equal(m.generate_batch(prompts, n_new, zero_indexed=True), o.greedy(w, prompts, n_new))
+    st = m.new_state()
+    for t in range(16):
+        m.step(1, st)
+    with pytest.raises(RuntimeError, match="context is full"):
+        m.step(1, st)
+
+
+@pytest.mark.parametrize("tie", [True, False])
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_small_model_gradients_all_layouts(tie, interleaved):
+    """Untied head and the CPU model's interleaved RoPE pairing, padded batch, gain jitter."""
+    cfg = dict(vocab=97, dim=32, layers=2, heads=2, ffn=40, max_seq=24)
+    w = synth.init_params(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], tie=tie, seed=5,
+                          std=0.2, gain_jitter=0.1)
+    B, T = 3, cfg["max_seq"]
+    ids = synth.uniform_ids(6, B * T, cfg["vocab"]).reshape(B, T)
+    tgt = shifted_targets(ids)
+    tgt[1, 10:] = -1
+    ids[1, 10:] = 0
+    tgt[2, :] = -1                                                    # a fully padded window
+    o = oracle_for(cfg, tie=tie, rope_interleaved=interleaved)
+    m = make(cfg, B, w, tie=tie, rope_interleaved=interleaved, optimizer="sgd")
+    ref = o.loss_grad(w, ids, tgt, want_logits=True)
+    loss, correct, valid, _, _ = m.train_step_ids(ids, tgt, lr=0.0, no_update=True)
+    assert valid == ref["valid"] and abs(loss - ref["loss"]) < TOL_F32 * abs(ref["loss"])
+    assert rel_err(m.logits_ids(ids), ref["logits"]) < TOL_F32
+    got_g, ref_g = split_params(m.flat_grads(), cfg, tie), split_params(ref["grads"], cfg, tie)
+    for name in ref_g:
+        assert rel_err(got_g[name], ref_g[name]) < TOL_F32, name
+    assert correct == int((ref["pred"][tgt >= 0] == tgt[tgt >= 0]).sum())
+    ev = m.eval_step_ids(ids, tgt)
+    assert abs(ev[0] - ref["loss"]) < TOL_F32 * abs(ref["loss"]) and ev[2] == valid
+
+
+def test_sgd_weight_decay_clip_and_adamw_follow_the_oracle_rules():
+    cfg = dict(vocab=64, dim=32, layers=1, heads=2, ffn=48, max_seq=16)
+    w = params_for(cfg, seed=7, std=0.2)
+    B, T = 2, cfg["max_seq"]
+    ids = synth.uniform_ids(8, B * T, cfg["vocab"]).reshape(B, T)
+    tgt = shifted_targets(ids)
+    o = oracle_for(cfg)
+    ref = o.loss_grad(w, ids, tgt)
+    g = ref["grads"]
+    gn = cpu_ref.Oracle.grad_norm(g)
+    # weight decay on matrices only, gradient clipped to half its norm (GPU clip rule, c / (|g| + 1e-6))
+    m = make(cfg, B, w, optimizer="sgd", weight_decay=0.1, clip_norm=gn / 2)
+    _, _, _, gnorm, _ = m.train_step_ids(ids, tgt, lr=0.05)
+    assert abs(gnorm - gn) < 1e-4 * gn
+    f = (gn / 2) / (gn + 1e-6)
+    expect = w.astype(np.float64) - 0.05 * (f * g + 0.1 * o.decay_mask() * w.astype(np.float64))
+    assert np.abs(m.flat_params() - expect).max() < 2e-6
+    # AdamW, two steps (reference GPU optimizer: cuda/luaTL_core.cu:1348)
+    m2 = make(cfg, B, w, optimizer="adamw", weight_decay=0.0)
+    m2.train_step_ids(ids, tgt, lr=1e-2, step=1)
+    m_ = 0.1 * g
+    v_ = 0.05 * g * g
+    expect = w.astype(np.float64) - 1e-2 * (m_ / 0.1) / (np.sqrt(v_ / 0.05) + 1e-8)
+    assert np.abs(m2.flat_params() - expect).max() < 1e-5
+
+
+# ---- configuration 1: README GPU config, one training step -----------------------------------------
+def test_config1_training_step_all_gradients():
+    cfg = CFG1
+    B, T = 32, cfg["max_seq"]
+    w = params_for(cfg, seed=0)
+    ids = synth.zipf_ids(1, B * T, cfg["vocab"]).reshape(B, T)
+    tgt = shifted_targets(ids)
+    o, m = oracle_for(cfg), make(cfg, B, w, optimizer="sgd")
+    ref = o.loss_grad(w, ids, tgt)
+    loss, correct, valid, _, finite = m.train_step_ids(ids, tgt, lr=0.01, no_update=True)
+    assert finite and valid == B * (T - 1)
+    assert abs(loss - ref["loss"]) < TOL_F32 * abs(ref["loss"])
+    got_g, ref_g = split_params(m.flat_grads(), cfg), split_params(ref["grads"], cfg)
+    worst = max((rel_err(got_g[n], ref_g[n]), n) for n in ref_g)
+    assert worst[0] < TOL_F32, worst
+    assert correct == int((ref["pred"][tgt >= 0] == tgt[tgt >= 0]).sum())
+    m.train_step_ids(ids, tgt, lr=0.01)
+    assert np.abs(m.flat_params() - o.sgd(w, ref["grads"], lr=0.01)).max() < 1e-6
+    # ten more steps: the loss must fall, and a replay of the same step is bit-reproducible in loss
+    l0 = m.train_step_ids(ids, tgt, lr=0.1)[0]
+    for _ in range(10):
+        l1 = m.train_step_ids(ids, tgt, lr=0.1)[0]
+    assert l1 < l0
+
+
+# ---- bf16 weights, fp32 accumulation: the batched greedy decode ------------------------------------------
+def assert_tokens_consistent(o, w, prompts, got, tol):
+    """Teacher-forced check of a bf16 generation against the float64 oracle: every generated token
+    must be the oracle's greedy pick for the same history, except where the oracle's own margin
+    between that token and its maximum is below the bf16 tolerance (a tie at this precision).
+    Returns the number of such near-ties."""
+    near = 0
+    seqs = np.concatenate([prompts, got], axis=1)
+    logits = o.forward(w, seqs[:, :-1])
+    npr = prompts.shape[1]
+    for b in range(seqs.shape[0]):
+        for s in range(got.shape[1]):
+            row = logits[b, npr - 1 + s]
+            if int(np.argmax(row)) == got[b, s]:
+                continue
+            margin = (row.max() - row[got[b, s]]) / np.abs(row).max()
+            assert margin < tol, f"sequence {b}, token {s}: picked {got[b, s]}, oracle margin {margin:.2e}"
+            near += 1
+    return near
+
+
+def test_bf16_decode_small_model_logits_and_tokens():
+    cfg = dict(vocab=512, dim=128, layers=2, heads=2, ffn=192, max_seq=96)
+    w = bf16_round(params_for(cfg, seed=0, std=0.05))                 # the weights ARE bf16 values
+    nseq, npr, n_new = 6, 16, 64
+    prompts = synth.zipf_ids(1, nseq * npr, cfg["vocab"]).reshape(nseq, npr)
+    o = oracle_for(cfg)
+    m = make(cfg, 1, w, decode_batch=nseq, dtype="bf16")
+    ref_tokens, first_logits = o.greedy(w, prompts, n_new, want_first_logits=True)
+    got = m.generate_batch(prompts, n_new, zero_indexed=True)
+    # single steps give the logits of the prefill position
+    st = m.new_state(0)
+    row = None
+    for t in prompts[0]:
+        row = m.step(int(t) + 1, st)
+    assert rel_err(row, first_logits[0]) < TOL_BF16
+    near = assert_tokens_consistent(o, w, prompts, got, TOL_BF16)
+    same = (got == ref_tokens)
+    first_div = [int(np.argmin(r)) if not r.all() else n_new for r in same]
+    print(f"bf16 decode: first divergence from the float64 greedy run per sequence {first_div}, near-ties {near}")
+    assert near <= 2
+
+
+def test_config2_shapes_bf16_prefill_and_decode_agree_with_single_steps():
+    """Configuration 2 architecture (bf16, head_dim 64, ffn 1408), reduced batch: the batched
+    prefill + graph-replayed decode must produce the tokens the one-token-at-a-time path gives,
+    and its first logits must match the oracle within the bf16 tolerance."""
+    cfg = dict(CFG2, max_seq=160, layers=2)
+    w = bf16_round(params_for(cfg, seed=0))
+    nseq, npr, n_new = 4, 128, 24
+    prompts = synth.zipf_ids(1, nseq * npr, cfg["vocab"]).reshape(nseq, npr)
+    m = make(cfg, 1, w, decode_batch=nseq, dtype="bf16")
+    got = m.generate_batch(prompts, n_new, zero_indexed=True)
+    o = oracle_for(cfg)
+    ref_tokens, fl = o.greedy(w, prompts[:1], n_new, want_first_logits=True)
+    st = m.new_state(0)
+    row = None
+    for t in prompts[0]:
+        row = m.step(int(t) + 1, st)
+    assert rel_err(row, fl[0]) < TOL_BF16
+    toks = []
+    for _ in range(n_new):
+        nxt = int(np.argmax(row))
+        toks.append(nxt)
+        if len(toks) < n_new:
+            row = m.step(nxt + 1, st)
+    assert np.array_equal(got[0], np.asarray(toks))
+    assert_tokens_consistent(o, w, prompts[:2], got[:2], TOL_BF16)
+    t = m.last_timing()
+    assert t["launches"] > 0 and t["decode_ms"] > 0
+
+
+def test_split_kv_decode_matches_unsplit():
+    cfg = dict(vocab=300, dim=64, layers=2, heads=4, ffn=96, max_seq=200)
+    w = params_for(cfg, seed=9, std=0.1)
+    prompts = synth.uniform_ids(10, 3 * 150, cfg["vocab"]).reshape(3, 150)
+    a = make(cfg, 1, w, decode_batch=3, kv_splits=1).generate_batch(prompts, 40, zero_indexed=True)
+    b = make(cfg, 1, w, decode_batch=3, kv_splits=5).generate_batch(prompts, 40, zero_indexed=True)
+    assert np.array_equal(a, b)
+    assert np.array_equal(a, oracle_for(cfg).greedy(w, prompts, 40))
+
+
+# ---- interface behaviour -------------------------------------------------------------------------------------
+def test_model_duck_type_errors_and_checkpoint_streaming():
+    cfg = CFG0
+    with pytest.raises(ValueError, match="divisible by heads"):
+        GT.new(dict(cfg, heads=5, batch_size=1))
+    with pytest.raises(ValueError, match="not supported by the GPU backend"):
+        GT.new(dict(cfg, batch_size=1, pos="sinusoidal"))
+    with pytest.raises(ValueError, match="dropout"):
+        GT.new(dict(cfg, batch_size=1, dropout=0.1))
+    with pytest.raises(ValueError, match="positive integer"):
+        GT.new(dict(cfg, batch_size=0))
+    m = make(cfg, 2)
+    names = [p["name"] for p in m.parameters()]
+    assert names[:3] == ["tok_emb", "l1.ln1", "l1.wqkv"] and names[-1] == "lnf" and len(names) == 2 + 6 * cfg["layers"]
+    assert m.nparams() == 98624                                        # tied 256/64/2/4/128 model
+    w0 = m.flat_params()
+    assert abs(float(w0[:256 * 64].std()) - 0.02) < 2e-3              # N(0, 0.02) init
+    g = split_params(w0, cfg)
+    assert np.all(g["l1.ln1"] == 1.0) and abs(float(g["l1.wo"].std()) - 0.02 / 2) < 2e-3   # 1/sqrt(2L) = 1/2
+    # streaming read/write, 1-indexed ranges (what lmio uses)
+    chunk = m.read_param(3, 5, 7)
+    assert np.array_equal(chunk, g["l1.wqkv"].ravel()[4:11])
+    m.write_param(3, 5, 7, np.arange(7, dtype=np.float32))
+    assert np.array_equal(m.read_param(3, 5, 7), np.arange(7, dtype=np.float32))
+    with pytest.raises(IndexError):
+        m.read_param(3, 0, 1)
+    with pytest.raises(IndexError):
+        m.read_param(99, 1, 1)
+    # windows API (1-indexed ids) and validation of token range
+    win = [([1, 2, 3, 4], [2, 3, 4, 5], 4)]
+    loss, correct, valid, gnorm, finite = m.train_step(win, 1, 1e-3, 1)
+    assert valid == 4 and finite and abs(loss - np.log(256)) < 0.2
+    with pytest.raises(ValueError, match="token out of range"):
+        m.train_step([([0, 2], [2, 3], 2)], 1, 1e-3, 1)
+    # snapshot / restore are device-to-device
+    snap = m.snapshot()
+    before = m.flat_params()
+    m.train_step(win, 1, 1e-1, 2)
+    assert not np.array_equal(m.flat_params(), before)
+    assert m.restore(snap) and np.array_equal(m.flat_params(), before)
+    m.release_snapshot(snap)
+    f3, f1 = m.flops_per_step()
+    assert f3 == 3 * f1 and f1 > 0
+    m.free()
+    with pytest.raises(RuntimeError, match="freed model"):
+        m.read_param(1, 1, 1)
+
+
+def test_bf16_model_refuses_to_train():
+    m = make(dict(CFG0), 1, dtype="bf16")
+    with pytest.raises(LuaTLError, match="UNSUPPORTED"):
+        m.train_step_ids(np.zeros((1, 64), np.int32), np.zeros((1, 64), np.int32), lr=0.1)
