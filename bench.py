@@ -1,0 +1,371 @@
+#!/usr/bin/env python
+"""Benchmark of the lanternl token loop on B200.
+
+Default workload (BASELINE.json configs[2]): batched greedy decode - vocab 8000, dim 512,
+8 layers, 8 heads, ffn 1408, ctx 1024, bf16 weights, fp32 accumulation; 256 independent
+sequences with 128-token Zipf(1.1) prompts, prefill then 512 generated tokens each, the
+sequences sharded over the GPUs (256/N per GPU, no communication).  One step = one full pass
+(prefill + 511 decode steps) over this rank's sequences.  `--workload train` times the
+configs[1] training step (fp32, forward + CE + backward + SGD) instead.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|train]
+
+Prints ONE JSON line (rank 0).  `value` is timed with the inputs resident in HBM; `e2e` goes
+through the host-facing call with host buffers (H2D of the prompts / ids, D2H of the result).
+`--impl reference` times the CPU restatement of the reference's path (the reference's own CPU
+path is pure Lua and no Lua runtime exists on this image) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+DECODE = dict(vocab=8000, dim=512, layers=8, heads=8, ffn=1408, max_seq=1024)
+TRAIN = dict(vocab=2000, dim=128, layers=4, heads=8, ffn=256, max_seq=128)
+NSEQ_TOTAL, N_PROMPT, N_NEW = 256, 128, 512
+TRAIN_B = 32
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class Clocks:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], 0.0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx = max(mx, float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [x for x in sm if x > 0.5 * mx] or sm
+        return dict(sm_mhz=float(np.median(busy)) if busy else None, sm_max_mhz=mx or None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+# ---------------------------------------------------------------------------------------------
+class Dist:
+    """One process per GPU.  torch.distributed is plumbing only: barrier and max over ranks."""
+
+    def __init__(self, gpus):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        self.td = None
+        if self.world > 1:
+            import torch
+            import torch.distributed as td
+            torch.cuda.set_device(self.local)
+            td.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+            self.td, self.torch = td, torch
+        if gpus != self.world:
+            raise SystemExit(f"--gpus {gpus} but WORLD_SIZE is {self.world}: launch with torch.distributed.run")
+
+    def barrier(self):
+        if self.td:
+            self.td.barrier()
+            self.torch.cuda.synchronize()
+
+    def max(self, x):
+        if not self.td:
+            return x
+        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        self.td.all_reduce(t, op=self.td.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum(self, x):
+        if not self.td:
+            return x
+        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        self.td.all_reduce(t, op=self.td.ReduceOp.SUM)
+        return float(t.item())
+
+    def broadcast_bytes(self, b, n):
+        if not self.td:
+            return b
+        t = self.torch.zeros(n, dtype=self.torch.uint8, device="cuda")
+        if self.rank == 0:
+            t.copy_(self.torch.frombuffer(bytearray(b), dtype=self.torch.uint8))
+        self.td.broadcast(t, 0)
+        return bytes(t.cpu().numpy().tobytes())
+
+    def close(self):
+        if self.td:
+            self.td.destroy_process_group()
+
+
+def decode_bytes(cfg, nparams, nseq, n_prompt, n_new):
+    """Algorithmic HBM bytes of the decode phase on one GPU: per step the bf16 weights once, the
+    K/V of every cached position of every sequence once, and the appended K/V."""
+    L, D = cfg["layers"], cfg["dim"]
+    per_pos = nseq * L * 2 * D * 2
+    total = 0
+    for n in range(n_prompt + 1, n_prompt + n_new):          # cache length incl. the current token
+        total += 2 * nparams + per_pos * n + per_pos
+    return total
+
+
+def bf16_round(a):
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
+
+
+def run_decode(args, dist):
+    from lanternl_b200 import _lib, gpu_transformer as GT, luatl_adapter as ad, synth
+    cfg = DECODE
+    _lib.init(dist.local)
+    nseq = NSEQ_TOTAL // dist.world
+    m = GT.new(dict(cfg, batch_size=1, decode_batch=nseq, dtype="bf16"))
+    w = bf16_round(synth.init_params(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], seed=0))
+    m.load_flat(w)
+    allp = synth.zipf_ids(1, NSEQ_TOTAL * N_PROMPT, cfg["vocab"]).reshape(NSEQ_TOTAL, N_PROMPT)
+    prompts = np.ascontiguousarray(allp[dist.rank * nseq:(dist.rank + 1) * nseq])
+    d_prompts, d_out = ad.ids(nseq * N_PROMPT), ad.ids(nseq * N_NEW)
+    ad.upload_i32(d_prompts, prompts)
+    res = _lib.LmResult()
+
+    def step_dev():
+        _lib.call("luaTL_lm_generate_dev", m._h, d_prompts.t.data, nseq, N_PROMPT, N_NEW, d_out.t.data, C.byref(res))
+        return res.step_ms
+
+    for _ in range(args.warmup):
+        step_dev()
+    clocks = Clocks(dist.local)
+    clocks.start()
+    dist.barrier()
+    t0 = time.perf_counter()
+    dev_ms, pre_ms, dec_ms, launches = 0.0, 0.0, 0.0, 0
+    for _ in range(args.steps):
+        dev_ms += step_dev()
+        t = m.last_timing()
+        pre_ms += t["prefill_ms"]; dec_ms += t["decode_ms"]; launches += t["launches"]
+    ad.sync()
+    dist.barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    clk = clocks.stop()
+    ids_dev = ad.download_i32(d_out, nseq * N_NEW).reshape(nseq, N_NEW)
+
+    # end to end through the host-facing call: host prompts in, host ids out, every step
+    out_host = None
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        out_host = m.generate_batch(prompts, N_NEW, zero_indexed=True)
+    dist.barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    if not np.array_equal(out_host, ids_dev):
+        raise SystemExit("bench: host-path and device-path generations differ")
+
+    dev_ms, dec_ms, pre_ms, e2e_ms = dist.max(dev_ms), dist.max(dec_ms), dist.max(pre_ms), dist.max(e2e_ms)
+    tokens = NSEQ_TOTAL * N_NEW * args.steps
+    pk = peaks()
+    alg = decode_bytes(cfg, m.nparams(), nseq, N_PROMPT, N_NEW) * args.steps
+    achieved = alg / (dec_ms * 1e-3) / 1e9
+    line = dict(
+        metric="decode_tokens_per_s", value=tokens / (dev_ms * 1e-3), unit="tokens/s", n_gpus=dist.world,
+        steps=args.steps, warmup=args.warmup, ms_per_step=dev_ms / args.steps, higher_is_better=True,
+        scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
+        config=dict(workload="configs[2] batched greedy decode: V8000 D512 L8 H8 F1408 ctx1024, 256 seqs x "
+                             "(128 prompt + 512 generated), sequences sharded over GPUs",
+                    nseq_per_gpu=nseq, n_prompt=N_PROMPT, n_new=N_NEW, parallelism=f"dp{dist.world} (no collective)",
+                    l2="inputs larger than L2 (KV cache %.1f GB per GPU)" % (2 * cfg["layers"] * nseq * cfg["max_seq"] * cfg["dim"] * 2 / 1e9)),
+        e2e=dict(value=tokens / (e2e_ms * 1e-3), unit="tokens/s", h2d_bytes_per_step=int(prompts.nbytes) * dist.world,
+                 d2h_bytes_per_step=int(out_host.nbytes) * dist.world),
+        gpu_launches=int(launches),
+        roofline=dict(bound="hbm", achieved=achieved, peak=pk["hbm_gbs"], unit="GB/s", frac=achieved / pk["hbm_gbs"],
+                      traffic=None, kernel="decode phase (all kernels of the 511 decode steps)", peak_source=pk["source"],
+                      algorithmic_bytes_per_step=alg // args.steps),
+        phases=dict(prefill_ms=pre_ms / args.steps, decode_ms=dec_ms / args.steps,
+                    decode_only_tokens_per_s=NSEQ_TOTAL * (N_NEW - 1) * args.steps / (dec_ms * 1e-3)),
+        wall_ms_per_step=wall_ms / args.steps, clocks=clk)
+    m.free()
+    return line
+
+
+def run_train(args, dist):
+    """configs[1]: fp32 training step (forward, CE, backward, SGD lr 0.01), data parallel."""
+    from lanternl_b200 import _lib, gpu_transformer as GT, luatl_adapter as ad, synth
+    cfg = TRAIN
+    _lib.init(dist.local)
+    if dist.world > 1:
+        uid = C.create_string_buffer(128)
+        if dist.rank == 0:
+            _lib.call("luaTL_comm_unique_id", uid)
+        raw = dist.broadcast_bytes(uid.raw, 128)
+        _lib.call("luaTL_comm_init", raw, dist.world, dist.rank)
+    B, T = TRAIN_B, cfg["max_seq"]
+    m = GT.new(dict(cfg, batch_size=B, optimizer="sgd"))
+    m.load_flat(synth.init_params(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], seed=0))
+    ids = synth.zipf_ids(1 + dist.rank, B * T, cfg["vocab"]).reshape(B, T)
+    tgt = np.full_like(ids, -1)
+    tgt[:, :-1] = ids[:, 1:]
+    valid_global = int((tgt >= 0).sum()) * dist.world
+    d_ids, d_tgt = ad.ids(B * T), ad.ids(B * T)
+    ad.upload_i32(d_ids, ids)
+    ad.upload_i32(d_tgt, tgt)
+    res = _lib.LmResult()
+    a = m._args(0.01, 1, valid_global)
+
+    def step_dev():
+        _lib.call("luaTL_lm_train_step_dev", m._h, d_ids.t.data, d_tgt.t.data, C.byref(a), C.byref(res))
+        return res.step_ms
+
+    for _ in range(args.warmup):
+        step_dev()
+    clocks = Clocks(dist.local)
+    clocks.start()
+    dist.barrier()
+    dev_ms, launches = 0.0, 0
+    for _ in range(args.steps):
+        dev_ms += step_dev()
+        launches += m.last_timing()["launches"]
+    dist.barrier()
+    clk = clocks.stop()
+    loss = res.loss
+    dist.barrier()
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        m.train_step_ids(ids, tgt, 0.01, s + 1, valid_global=valid_global)
+    dist.barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    dev_ms, e2e_ms = dist.max(dev_ms), dist.max(e2e_ms)
+    tokens = B * T * dist.world * args.steps
+    pk = peaks()
+    flops3, _ = m.flops_per_step()
+    tf = flops3 * args.steps / (dev_ms * 1e-3) / 1e12
+    line = dict(
+        metric="train_tokens_per_s", value=tokens / (dev_ms * 1e-3), unit="tokens/s", n_gpus=dist.world,
+        steps=args.steps, warmup=args.warmup, ms_per_step=dev_ms / args.steps, higher_is_better=True, scaling="weak",
+        vs_baseline=None, dtype="f32", data="synthetic",
+        config=dict(workload="configs[1] training step: V2000 D128 L4 H8 F256 ctx128, batch 32x128 per GPU, fp32, "
+                             "forward + CE + backward + SGD", global_batch=B * dist.world, seq_len=T,
+                    parallelism=f"dp{dist.world}" + (" (NCCL all-reduce of the flat gradient)" if dist.world > 1 else ""),
+                    l2="working set fits in L2 (the configuration is 3.6 MB of weights); no flush"),
+        e2e=dict(value=tokens / (e2e_ms * 1e-3), unit="tokens/s", h2d_bytes_per_step=int(ids.nbytes + tgt.nbytes) * dist.world,
+                 d2h_bytes_per_step=8 * dist.world),
+        gpu_launches=int(launches),
+        roofline=dict(bound="tensor", achieved=tf, peak=pk["bf16_tflops"], unit="TFLOP/s", frac=tf / pk["bf16_tflops"],
+                      traffic=None, kernel="whole step by the reference's FLOP model (3 x forward GEMM FLOPs); "
+                      "fp32 CUDA-core GEMMs, so the tensor roof is context only", peak_source=pk["source"]),
+        final_loss=loss, clocks=clk)
+    m.free()
+    return line
+
+
+def cpu_sample(threads, n_new=24):
+    """The CPU restatement of the reference's path on a bounded sample of the decode workload:
+    `threads` sequences (one per host thread), 128-token prompt, n_new generated tokens each."""
+    from lanternl_b200 import synth
+    from oracle import cpu_ref
+    cfg = DECODE
+    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+    o = cpu_ref.Oracle(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], cfg["max_seq"])
+    w = bf16_round(synth.init_params(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], seed=0)).astype(np.float64)
+    prompts = synth.zipf_ids(1, NSEQ_TOTAL * N_PROMPT, cfg["vocab"]).reshape(NSEQ_TOTAL, N_PROMPT)[:threads]
+    t0 = time.perf_counter()
+    o.greedy(w, prompts, n_new)
+    dt = time.perf_counter() - t0
+    steps = threads * (N_PROMPT + n_new - 1)                  # one model step per prompt / generated token
+    rate = steps / dt
+    # the full workload costs (128 + 511) steps per sequence for 512 generated tokens
+    return rate * N_NEW / (N_PROMPT + N_NEW - 1), dt, f"{threads} sequences x ({N_PROMPT} prompt + {n_new} generated) " \
+        f"tokens through the KV-cache step, {dt:.1f} s; tokens/s scaled to the 128+512 workload by steps"
+
+
+def run_reference(args, dist):
+    if dist.rank != 0:
+        return None
+    threads = min(os.cpu_count() or 1, NSEQ_TOTAL)
+    vals = []
+    for _ in range(args.warmup):
+        cpu_sample(threads, n_new=2)
+    t0 = time.perf_counter()
+    sample = ""
+    for _ in range(args.steps):
+        v, _, sample = cpu_sample(threads, n_new=8)
+        vals.append(v)
+    wall = time.perf_counter() - t0
+    v = float(np.mean(vals))
+    return dict(impl="reference", metric="decode_tokens_per_s", value=v, unit="tokens/s", n_gpus=dist.world,
+                steps=args.steps, warmup=args.warmup, ms_per_step=wall * 1e3 / args.steps, higher_is_better=True,
+                scaling="strong", vs_baseline=None, dtype="f64", data="synthetic",
+                config=dict(workload="configs[2] batched greedy decode (bounded sample per step, see cpu_baseline.sample)"),
+                cpu_baseline=dict(value=v, unit="tokens/s", cores=threads, kind="port", sample=sample,
+                                  note="the reference's CPU path is pure Lua (no Lua runtime on this image); this is "
+                                       "its C restatement oracle/cpu_ref.c, one sequence per host thread"),
+                e2e=dict(value=v, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "train"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+        if rank == 0:
+            d = type("D", (), dict(world=world, rank=0, local=0))()
+            print(json.dumps(run_reference(args, d)), flush=True)
+        return
+    dist = Dist(args.gpus)
+    line = run_decode(args, dist) if args.workload == "decode" else run_train(args, dist)
+    if dist.rank == 0:
+        if dist.world == 1 and not args.no_cpu_baseline:
+            threads = min(os.cpu_count() or 1, NSEQ_TOTAL)
+            v, dt, sample = cpu_sample(threads)
+            line["cpu_baseline"] = dict(value=v, unit="tokens/s", cores=threads, kind="port", sample=sample)
+        print(json.dumps(line), flush=True)
+    dist.close()
+
+
+if __name__ == "__main__":
+    main()

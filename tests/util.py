@@ -41,3 +41,10 @@ def shifted_targets(ids):
     tgt = np.full_like(ids, -1)
     tgt[:, :-1] = ids[:, 1:]
     return tgt
+
+
+def l2_err(got, ref):
+    """||got - ref||_2 / ||ref||_2 over the whole tensor."""
+    got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
+    den = np.linalg.norm(ref)
+    return float(np.linalg.norm(got - ref) / (den if den > 0 else 1.0))
