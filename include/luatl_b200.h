@@ -194,6 +194,13 @@ int luaTL_adamw(float* w, const void* g, float* m, float* v, void* w_lp, uint64_
  * and max_norm > 0 (rule: ai/optim/optim2.lua:93-99; clip factor: cuda/luaTL_train.cu:950-952). */
 int luaTL_sgd(float* w, const float* g, uint64_t n, float lr, float wd, const float* nsq, float max_norm);
 
+/* New: tensor-core GEMM (tcgen05 + TMA).  C[M,N] = A[M,K] * B[N,K]^T + R with bf16 A and B (both
+ * K contiguous), fp32 accumulation, C and R of c_dtype (LUATL_F32 or LUATL_BF16), R optional.
+ * K must be a multiple of 8 and the operands 16-byte aligned.  tile_n: 0 = choose, else 32/64/128.
+ * The reference has no tensor-core path for bf16 (its only one is fp16 wmma, cuda/luaTL_core.cu:1296). */
+int luaTL_gemm_bf16_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                       int c_dtype, int tile_n);
+
 /* ---------------- Program: command buffer + CUDA graph (cuda/luaTL_train.cu:1506-1712) ---- */
 luaTL_prog_t* luaTL_prog_create(int capacity, int timing);
 void          luaTL_prog_destroy(luaTL_prog_t* P);

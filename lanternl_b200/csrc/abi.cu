@@ -584,6 +584,13 @@ int luaTL_adamw(float* w, const void* g, float* m, float* v, void* w_lp, uint64_
 {
     ONE_SHOT("adamw", ltl_adamw(w, g, m, v, w_lp, n, grad_dtype, lr, beta1, beta2, eps, wd, step, clip, g_stream));
 }
+int luaTL_gemm_bf16_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int c_dtype, int tile_n)
+{
+    LTL_TRY(ltl_require_init("gemm_bf16_tc"));
+    LTL_TRY(ltl_gemm_tc(A, B, C, R, M, N, K, c_dtype, tile_n, g_stream));
+    LTL_TRY(sync_stream("gemm_bf16_tc"));
+    return ltl_gemm_tc_check(g_stream);
+}
 int luaTL_sgd(float* w, const float* g, uint64_t n, float lr, float wd, const float* nsq, float max_norm)
 {
     ONE_SHOT("sgd", ltl_sgd(w, g, nullptr, n, lr, wd, nsq, max_norm, g_stream));

@@ -1,0 +1,325 @@
+// Tensor-core GEMM for sm_100a: C[M,N] = A[M,K] * B[N,K]^T (+ R), bf16 operands, fp32
+// accumulation in tensor memory.
+//
+//   - operands are staged by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill outside
+//     the matrix) into a 4-stage shared-memory ring guarded by full/empty mbarriers;
+//   - one elected thread issues tcgen05.mma (UMMA 128 x BN x 16, kind::f16, cta_group::1); the
+//     accumulator (128 lanes x BN fp32 columns) lives in TMEM allocated by the same warp;
+//   - four epilogue warps read their lane quadrant with tcgen05.ld, add the residual, convert
+//     and store rows of 32 consecutive columns.
+// Warp roles: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 = epilogue.
+// Every mbarrier wait is bounded; a wait that runs out raises a flag the host turns into an
+// error, and the kernel still releases its tensor memory and returns.
+//
+// Both operands are K-major: A is the activation matrix [M, K], B is a weight stored [N, K]
+// (the layout of the bf16 weight mirror, and of tok_emb when it is the tied lm_head).
+// No cluster launch and no TMA multicast: the kernel is the same on 1 and on N GPUs.
+#include <cuda.h>
+
+#include <map>
+#include <tuple>
+
+#include "ops.h"
+
+namespace {
+
+constexpr int BM = 128, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait on a phase parity.  Returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+{
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c_inner, int c_outer, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(c_inner), "r"(c_outer), "r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 128 bytes, groups
+// of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                            // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
+    d |= (uint64_t)1 << 46;                            // descriptor version
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D fp32, A and B bf16, both K-major, shape M x N.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N)
+{
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+
+template <int BN>
+struct Smem {
+    alignas(1024) uint8_t a[STAGES][BM * BK * 2];
+    alignas(1024) uint8_t b[STAGES][BN * BK * 2];
+    alignas(8) uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_ready;
+    uint32_t tmem_base;
+};
+
+template <int BN, typename TC>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               TC* __restrict__ C, const TC* R, int M, int N, int K, int* __restrict__ err)
+{
+    extern __shared__ uint8_t smem_raw[];
+    Smem<BN>& sm = *reinterpret_cast<Smem<BN>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int kblocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        mbar_init(&sm.acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;
+    bool ok = true;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer ----
+        for (int kb = 0; kb < kblocks && ok; ++kb) {
+            const int s = kb % STAGES;
+            if (kb >= STAGES) ok = mbar_wait(&sm.empty[s], ((kb / STAGES) - 1) & 1);
+            if (!ok) break;
+            mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+            tma_load_2d(sm.a[s], &map_a, kb * BK, m0, &sm.full[s]);
+            tma_load_2d(sm.b[s], &map_b, kb * BK, n0, &sm.full[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+        for (int kb = 0; kb < kblocks && ok; ++kb) {
+            const int s = kb % STAGES;
+            ok = mbar_wait(&sm.full[s], (kb / STAGES) & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t da = umma_desc_sw128(smem_u32(sm.a[s]));
+            const uint64_t db = umma_desc_sw128(smem_u32(sm.b[s]));
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)        // 32 bytes further along K per UMMA
+                umma_bf16(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+            umma_commit(&sm.empty[s]);                    // frees the stage when these MMAs retire
+        }
+        umma_commit(&sm.acc_ready);
+    } else if (warp >= 2) {
+        // ---- epilogue: TMEM -> registers -> global ----
+        ok = mbar_wait(&sm.acc_ready, 0);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int quad = warp & 3;                        // TMEM lane quadrant this warp may read
+        const int row = m0 + quad * 32 + lane;
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < M) {
+                    const size_t base = (size_t)row * N + n0 + c0;
+                    const int ncols = min(32, N - (n0 + c0));
+                    if (ncols == 32 && (N % Vec16<TC>::N) == 0) {
+                        constexpr int NV = Vec16<TC>::N;
+#pragma unroll
+                        for (int j = 0; j < 32; j += NV) {
+                            float o[NV];
+#pragma unroll
+                            for (int i = 0; i < NV; ++i) o[i] = __uint_as_float(v[j + i]);
+                            if (R) {
+                                float rr[NV];
+                                ld16<TC>(R + base + j, rr);
+#pragma unroll
+                                for (int i = 0; i < NV; ++i) o[i] += rr[i];
+                            }
+                            st16<TC>(C + base + j, o);
+                        }
+                    } else {
+                        for (int j = 0; j < ncols; ++j) {
+                            float o = __uint_as_float(v[j]);
+                            if (R) o += Cvt<TC>::ld(R, base + j);
+                            Cvt<TC>::st(C, base + j, o);
+                        }
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    if (!ok && err) atomicExch(err, 1);
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+encode_fn g_encode = nullptr;
+
+int get_encode()
+{
+    if (g_encode) return LTL_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || !fn || q != cudaDriverEntryPointSuccess) {
+        cudaGetLastError();
+        return ltl_fail(LTL_ERR_UNSUPPORTED, "gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
+    }
+    g_encode = (encode_fn)fn;
+    return LTL_OK;
+}
+
+// 2-D bf16 row-major [rows, cols] with a box of box_rows x 64 columns, 128-byte swizzle.
+std::map<std::tuple<const void*, int, int, int>, CUtensorMap> g_maps;
+
+int tensor_map(const void* base, int rows, int cols, int box_rows, CUtensorMap* out)
+{
+    const auto key = std::make_tuple(base, rows, cols, box_rows);
+    const auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *out = it->second; return LTL_OK; }
+    LTL_TRY(get_encode());
+    const cuuint64_t dims[2] = { (cuuint64_t)cols, (cuuint64_t)rows };
+    const cuuint64_t strides[1] = { (cuuint64_t)cols * 2 };
+    const cuuint32_t box[2] = { (cuuint32_t)BK, (cuuint32_t)box_rows };
+    const cuuint32_t estr[2] = { 1, 1 };
+    const CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ltl_fail(LTL_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled failed (%d) for %dx%d", (int)r, rows, cols);
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps[key] = *out;
+    return LTL_OK;
+}
+
+int* g_err_flag = nullptr;
+
+template <int BN, typename TC>
+int launch(const void* A, const void* B, void* C, const void* R, int M, int N, int K, cudaStream_t s)
+{
+    CUtensorMap ma, mb;
+    LTL_TRY(tensor_map(A, M, K, BM, &ma));
+    LTL_TRY(tensor_map(B, N, K, BN, &mb));
+    const size_t smem = sizeof(Smem<BN>) + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        LTL_CUDA("gemm_tc attr", cudaFuncSetAttribute(gemm_tc_kernel<BN, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    gemm_tc_kernel<BN, TC><<<grid, 192, smem, s>>>(ma, mb, (TC*)C, (const TC*)R, M, N, K, g_err_flag);
+    return ltl_check_launch("gemm_tc");
+}
+
+}  // namespace
+
+bool ltl_gemm_tc_supported(const void* A, const void* B, int M, int N, int K)
+{
+    return M > 0 && N > 0 && K > 0 && K % 8 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
+           (reinterpret_cast<uintptr_t>(B) & 15) == 0;
+}
+
+// C[M,N] (c_dtype f32 or bf16, row-major) = A[M,K] B[N,K]^T + R.  bn = 0 picks the tile width.
+int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int c_dtype, int bn,
+                cudaStream_t s)
+{
+    if (!A || !B || !C) return ltl_fail(LTL_ERR_NULL, "gemm_tc: null operand");
+    if (!ltl_gemm_tc_supported(A, B, M, N, K))
+        return ltl_fail(LTL_ERR_UNSUPPORTED, "gemm_tc: needs K %% 8 == 0 and 16-byte aligned operands (M=%d N=%d K=%d)", M, N, K);
+    if (!g_err_flag) {
+        LTL_CUDA("gemm_tc flag", cudaMalloc(&g_err_flag, sizeof(int)));
+        LTL_CUDA("gemm_tc flag", cudaMemset(g_err_flag, 0, sizeof(int)));
+    }
+    if (bn == 0) {
+        // enough CTAs to occupy the SMs: narrower tiles for small N
+        const int mt = (M + BM - 1) / BM;
+        bn = 128;
+        if (mt * ((N + 127) / 128) < ltl_sm_count()) bn = 64;
+        if (mt * ((N + 63) / 64) < ltl_sm_count() / 2) bn = 32;
+    }
+#define TC_CASE(BNV)                                                                         \
+    if (bn == BNV) {                                                                         \
+        if (c_dtype == LTL_F32) return launch<BNV, float>(A, B, C, R, M, N, K, s);           \
+        if (c_dtype == LTL_BF16) return launch<BNV, bf16>(A, B, C, R, M, N, K, s);           \
+        return ltl_fail(LTL_ERR_DTYPE, "gemm_tc: output dtype %d", c_dtype);                 \
+    }
+    TC_CASE(32) TC_CASE(64) TC_CASE(128)
+#undef TC_CASE
+    return ltl_fail(LTL_ERR_ARG, "gemm_tc: tile width %d not in {32, 64, 128}", bn);
+}
+
+// 1 when a bounded wait inside the kernel ran out since the last call (and clears the flag).
+int ltl_gemm_tc_check(cudaStream_t s)
+{
+    if (!g_err_flag) return LTL_OK;
+    int v = 0;
+    LTL_CUDA("gemm_tc flag read", cudaMemcpyAsync(&v, g_err_flag, sizeof(int), cudaMemcpyDeviceToHost, s));
+    LTL_CUDA("gemm_tc flag sync", cudaStreamSynchronize(s));
+    if (v) {
+        cudaMemsetAsync(g_err_flag, 0, sizeof(int), s);
+        return ltl_fail(LTL_ERR_CUDA, "gemm_tc: a pipeline wait ran out inside the kernel (TMA or MMA never arrived)");
+    }
+    return LTL_OK;
+}

@@ -14,6 +14,7 @@
 // one optimizer launch).
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <map>
@@ -82,6 +83,7 @@ struct luaTL_lm_s {
     float prefill_ms = 0, decode_ms = 0;
     int64_t launches = 0;
     int adam_alloc = 0;
+    int use_tc = 1;
 };
 
 namespace {
@@ -202,14 +204,17 @@ int wgemm(LM* m, const void* A, int M, int K, int64_t w_off, int Nout, void* C, 
     g.A = A; g.C = C; g.R = R; g.M = M; g.N = Nout; g.K = K; g.batch = 1;
     g.a_rs = K; g.a_cs = 1; g.c_rs = Nout; g.c_cs = 1;
     g.alpha = 1.0f; g.beta = 0.0f; g.a_dtype = m->adt; g.b_dtype = m->adt; g.c_dtype = c_dt;
+    m->launches++;
     if (m->adt == LTL_F32) {
         g.B = m->W + w_off;
         if (transposed_master) { g.b_rs = 1; g.b_cs = K; } else { g.b_rs = Nout; g.b_cs = 1; }
     } else {
         g.B = m->Wb + w_off;
         g.b_rs = 1; g.b_cs = K;
+        // bf16: activations [M, K] and the mirrored weight [Nout, K] are both K-major -> tensor cores
+        if (m->use_tc && ltl_gemm_tc_supported(A, g.B, M, Nout, K))
+            return ltl_gemm_tc(A, g.B, C, R, M, Nout, K, c_dt, 0, m->s);
     }
-    m->launches++;
     return ltl_gemm_simt(g, m->s);
 }
 
@@ -659,6 +664,7 @@ int generate_dev(LM* m, const int32_t* d_prompts, int nseq, int n_prompt, int n_
     LTL_CUDA("error flag", cudaMemcpyAsync(&err, m->d_err, 4, cudaMemcpyDeviceToHost, m->s));
     LTL_CUDA("generate sync", cudaStreamSynchronize(m->s));
     if (err) return ltl_fail(LTL_ERR_CAPACITY, "lm generate: a position left the KV cache");
+    if (m->adt == LTL_BF16 && m->use_tc) LTL_TRY(ltl_gemm_tc_check(m->s));
     cudaEventElapsedTime(&m->prefill_ms, m->ev[0], m->ev[1]);
     cudaEventElapsedTime(&m->decode_ms, m->ev[1], m->ev[2]);
     if (timing) {
@@ -697,6 +703,10 @@ luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
     m->B = c.batch; m->adt = c.dtype; m->splits = 1;
     m->scale = 1.0f / sqrtf((float)hd);
     m->s = ltl_default_stream();
+    {   // LUATL_DISABLE_TC=1 routes the bf16 GEMMs through the CUDA-core kernel (A/B comparison)
+        const char* e = getenv("LUATL_DISABLE_TC");
+        m->use_tc = !(e && e[0] == '1');
+    }
     layout_params(m);
     int rc = LTL_OK;
     auto A = [&](void** p, size_t bytes, const char* what) { if (rc == LTL_OK) rc = dalloc(p, bytes, what); };

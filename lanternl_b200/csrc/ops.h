@@ -105,3 +105,9 @@ int ltl_fill_i32(int32_t* p, int n, int32_t value, cudaStream_t s);
 int ltl_count_correct(const int32_t* pred, const int32_t* tgt, int n, float* correct, cudaStream_t s);
 // Gather row (b * T + last) of x [B*T, cols] into out [B, cols].
 int ltl_gather_last_rows(const float* x, float* out, int B, int T, int cols, int last, cudaStream_t s);
+
+// ---- tcgen05 / TMA GEMM (gemm_tc.cu): C[M,N] = A[M,K] B[N,K]^T + R, bf16 in, fp32 accumulate ----
+bool ltl_gemm_tc_supported(const void* A, const void* B, int M, int N, int K);
+int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int c_dtype,
+                int bn, cudaStream_t s);
+int ltl_gemm_tc_check(cudaStream_t s);

@@ -1,0 +1,60 @@
+"""The tcgen05 / TMA GEMM through the C ABI against float64 on the same bf16-rounded inputs:
+every tile width, tails in M, N and K, residual epilogue, fp32 and bf16 outputs, and the
+shapes of the batched-decode configuration."""
+import numpy as np
+import pytest
+
+from lanternl_b200 import _lib, luatl_adapter as ad, synth
+from tests.util import bf16_round, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def bf16_dev(a):
+    t = ad.TensorView(a.shape[0], a.shape[1], _lib.BF16)
+    t.upload(a.ravel())
+    return t
+
+
+def run(M, N, K, tile, c_dtype=_lib.F32, residual=False, seed=0):
+    a = bf16_round((synth.normal(seed, 0, M * K)).reshape(M, K).astype(np.float32))
+    b = bf16_round((synth.normal(seed + 1, 0, N * K) * 0.1).reshape(N, K).astype(np.float32))
+    r = synth.normal(seed + 2, 0, M * N).reshape(M, N).astype(np.float32) if residual else None
+    if r is not None and c_dtype == _lib.BF16:
+        r = bf16_round(r)
+    A, B = bf16_dev(a), bf16_dev(b)
+    Cc = ad.TensorView(M, N, c_dtype)
+    if r is not None:
+        Cc.upload(r.ravel())                              # in-place residual: R == C
+    _lib.call("luaTL_gemm_bf16_tc", A.data, B.data, Cc.data, Cc.data if residual else None, M, N, K, c_dtype, tile)
+    got = Cc.download().reshape(M, N)
+    ref = a.astype(np.float64) @ b.astype(np.float64).T + (r.astype(np.float64) if r is not None else 0.0)
+    return got, ref
+
+
+@pytest.mark.parametrize("tile", [32, 64, 128])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 512), (128, 64, 1408)])
+def test_exact_tiles(M, N, K, tile):
+    got, ref = run(M, N, K, tile)
+    assert rel_err(got, ref) < 1e-5
+
+
+@pytest.mark.parametrize("M,N,K,tile", [(300, 200, 72, 32), (7, 8000, 512, 128), (129, 33, 8, 64), (256, 1536, 512, 0),
+                                       (256, 2816, 512, 0), (256, 512, 1408, 0), (32, 8000, 512, 0), (1, 48, 264, 64)])
+def test_tails_and_decode_shapes(M, N, K, tile):
+    got, ref = run(M, N, K, tile, seed=3)
+    assert rel_err(got, ref) < 1e-5
+
+
+@pytest.mark.parametrize("c_dtype,tol", [(_lib.F32, 1e-5), (_lib.BF16, 8e-3)])
+def test_residual_epilogue_and_output_types(c_dtype, tol):
+    got, ref = run(256, 512, 512, 0, c_dtype=c_dtype, residual=True, seed=5)
+    assert rel_err(got, ref) < tol
+    got, ref = run(70, 100, 136, 64, c_dtype=c_dtype, residual=True, seed=6)
+    assert rel_err(got, ref) < tol
+
+
+def test_rejects_unaligned_k():
+    A, B, Cc = bf16_dev(np.zeros((4, 12), np.float32)), bf16_dev(np.zeros((4, 12), np.float32)), ad.TensorView(4, 4)
+    with pytest.raises(_lib.LuaTLError, match="UNSUPPORTED"):
+        _lib.call("luaTL_gemm_bf16_tc", A.data, B.data, Cc.data, None, 4, 4, 12, _lib.F32, 0)
