@@ -52,7 +52,29 @@
 typedef struct {
     int32_t vocab, dim, layers, heads, ffn, max_seq, tie, rope_interleaved;
     double  eps, rope_base;
+    int32_t act_bf16, pad_;
 } ora_cfg;
+
+/* act_bf16 = 1 models the bf16 configuration: every activation that the reference's kernels
+ * would STORE in a bf16 tensor (its TAcc<bf16> store, cuda/luaTL_core.cu bf16 traits) is rounded
+ * to bfloat16 (nearest even) where it is stored - the normed GEMM inputs, q|k|v before and after
+ * RoPE (the K/V cache holds these), the attention output, the gate|up projection and the SwiGLU
+ * output.  The residual stream, the accumulations and the logits stay in full precision. */
+static double rbf(double x)
+{
+    float f = (float)x;
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7F800000u) == 0x7F800000u) return x;
+    u = (u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u;
+    memcpy(&f, &u, 4);
+    return (double)f;
+}
+static void round_bf16(const ora_cfg *c, double *x, int64_t n)
+{
+    if (!c->act_bf16) return;
+    for (int64_t i = 0; i < n; ++i) x[i] = rbf(x[i]);
+}
 
 typedef struct {
     const double *emb, *lnf, *head;
@@ -277,11 +299,14 @@ static void forward_seq(const ora_cfg *c, const double *P, const int32_t *ids, i
         double *hs = a->hs + (int64_t)l * T * F;
 
         rmsnorm_rows(xin, w.ln1, h1, a->inv1 + (int64_t)l * T, T, D, c->eps);
+        round_bf16(c, h1, (int64_t)T * D);
         mm(h1, w.wqkv, qkv, T, D, 3 * D, 0);
+        round_bf16(c, qkv, (int64_t)T * 3 * D);
         for (int h = 0; h < H; ++h) {
             rope_head(qkv + h * hd, T, hd, 3 * D, 0, c->rope_base, c->rope_interleaved, 0);
             rope_head(qkv + D + h * hd, T, hd, 3 * D, 0, c->rope_base, c->rope_interleaved, 0);
         }
+        round_bf16(c, qkv, (int64_t)T * 3 * D);
         for (int h = 0; h < H; ++h) {
             for (int t = 0; t < T; ++t)
                 for (int j = 0; j < hd; ++j) {
@@ -311,20 +336,25 @@ static void forward_seq(const ora_cfg *c, const double *P, const int32_t *ids, i
             for (int t = 0; t < T; ++t)
                 for (int j = 0; j < hd; ++j) ctx[(int64_t)t * D + h * hd + j] = oh[t * hd + j];
         }
+        round_bf16(c, ctx, (int64_t)T * D);
         mm(ctx, w.wo, tmp, T, D, D, 0);
         for (int64_t i = 0; i < (int64_t)T * D; ++i) mid[i] = xin[i] + tmp[i];
 
         rmsnorm_rows(mid, w.ln2, h2, a->inv2 + (int64_t)l * T, T, D, c->eps);
+        round_bf16(c, h2, (int64_t)T * D);
         mm(h2, w.w13, h13, T, D, 2 * F, 0);
+        round_bf16(c, h13, (int64_t)T * 2 * F);
         for (int t = 0; t < T; ++t)
             for (int j = 0; j < F; ++j) {
                 const double g = h13[(int64_t)t * 2 * F + j], u = h13[(int64_t)t * 2 * F + F + j];
                 hs[(int64_t)t * F + j] = g * sigmoid_stable(g) * u;
             }
+        round_bf16(c, hs, (int64_t)T * F);
         mm(hs, w.w2, tmp, T, F, D, 0);
         for (int64_t i = 0; i < (int64_t)T * D; ++i) xout[i] = mid[i] + tmp[i];
     }
     rmsnorm_rows(a->res + (int64_t)L * T * D, P + lnf_off(c), a->hf, a->invf, T, D, c->eps);
+    round_bf16(c, a->hf, (int64_t)T * D);
     if (c->tie) mm_nt(a->hf, P, logits, T, D, V, 0);
     else        mm(a->hf, P + lnf_off(c) + D, logits, T, D, V, 0);
 
@@ -579,11 +609,14 @@ int ora_step(const ora_cfg *c, const double *P, ora_state *st, int id, double *l
     for (int l = 0; l < c->layers; ++l) {
         ora_w w; set_layer(c, P, l, &w);
         rmsnorm_rows(x, w.ln1, h, NULL, 1, D, c->eps);
+        round_bf16(c, h, D);
         vecmat(h, w.wqkv, D, 3 * D, 3 * D, qkv);
+        round_bf16(c, qkv, 3 * D);
         for (int hh = 0; hh < H; ++hh) {
             rope_head(qkv + hh * hd, 1, hd, 3 * D, pos, c->rope_base, c->rope_interleaved, 0);
             rope_head(qkv + D + hh * hd, 1, hd, 3 * D, pos, c->rope_base, c->rope_interleaved, 0);
         }
+        round_bf16(c, qkv, 3 * D);
         double *kc = st->k + (int64_t)l * st->cap * D, *vc = st->v + (int64_t)l * st->cap * D;
         for (int j = 0; j < D; ++j) {
             kc[(int64_t)pos * D + j] = qkv[D + j];
@@ -609,15 +642,20 @@ int ora_step(const ora_cfg *c, const double *P, ora_state *st, int id, double *l
                 for (int j = 0; j < hd; ++j) ctx[off + j] += wt * vc[(int64_t)t * D + off + j];
             }
         }
+        round_bf16(c, ctx, D);
         vecmat(ctx, w.wo, D, D, D, o);
         for (int j = 0; j < D; ++j) x[j] += o[j];
         rmsnorm_rows(x, w.ln2, h, NULL, 1, D, c->eps);
+        round_bf16(c, h, D);
         vecmat(h, w.w13, D, 2 * F, 2 * F, gu);
+        round_bf16(c, gu, 2 * F);
         for (int j = 0; j < F; ++j) hsv[j] = gu[j] * sigmoid_stable(gu[j]) * gu[F + j];
+        round_bf16(c, hsv, F);
         vecmat(hsv, w.w2, F, D, D, o);
         for (int j = 0; j < D; ++j) x[j] += o[j];
     }
     rmsnorm_rows(x, P + lnf_off(c), h, NULL, 1, D, c->eps);
+    round_bf16(c, h, D);
     if (c->tie) {
         for (int r = 0; r < V; ++r) {
             double s = 0.0;

@@ -19,7 +19,7 @@ class Cfg(C.Structure):
     _fields_ = [("vocab", C.c_int32), ("dim", C.c_int32), ("layers", C.c_int32),
                 ("heads", C.c_int32), ("ffn", C.c_int32), ("max_seq", C.c_int32),
                 ("tie", C.c_int32), ("rope_interleaved", C.c_int32),
-                ("eps", C.c_double), ("rope_base", C.c_double)]
+                ("eps", C.c_double), ("rope_base", C.c_double), ("act_bf16", C.c_int32), ("pad_", C.c_int32)]
 
 
 def build(force: bool = False) -> str:
@@ -83,9 +83,9 @@ class Oracle:
     """The reference CPU model with GPU-layout weights (see cpu_ref.c for citations)."""
 
     def __init__(self, vocab, dim, layers, heads, ffn, max_seq, tie=True, eps=1e-5,
-                 rope_base=10000.0, rope_interleaved=False):
+                 rope_base=10000.0, rope_interleaved=False, act_bf16=False):
         self.cfg = Cfg(vocab, dim, layers, heads, ffn, max_seq, int(tie), int(rope_interleaved),
-                       eps, rope_base)
+                       eps, rope_base, int(act_bf16), 0)
         self.vocab, self.dim, self.max_seq = vocab, dim, max_seq
         self.nparams = lib().ora_nparams(C.byref(self.cfg))
 
