@@ -196,7 +196,9 @@ int luaTL_sgd(float* w, const float* g, uint64_t n, float lr, float wd, const fl
 
 /* New: tensor-core GEMM (tcgen05 + TMA).  C[M,N] = A[M,K] * B[N,K]^T + R with bf16 A and B (both
  * K contiguous), fp32 accumulation, C and R of c_dtype (LUATL_F32 or LUATL_BF16), R optional.
- * K must be a multiple of 8 and the operands 16-byte aligned.  tile_n: 0 = choose, else 32/64/128.
+ * K must be a multiple of 8 and the operands 16-byte aligned.  tile_n bits 0-15: tile width, 0 = choose,
+ * else 32/64/128.  tile_n bit 16: SwiGLU epilogue - the rows of B alternate gate_j / up_j, both are rounded to
+ * bf16 and C [M, N/2] (bf16) = silu(gate) * up.
  * The reference has no tensor-core path for bf16 (its only one is fp16 wmma, cuda/luaTL_core.cu:1296). */
 int luaTL_gemm_bf16_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
                        int c_dtype, int tile_n);

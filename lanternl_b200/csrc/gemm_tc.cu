@@ -2,7 +2,7 @@
 // accumulation in tensor memory.
 //
 //   - operands are staged by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill outside
-//     the matrix) into a 4-stage shared-memory ring guarded by full/empty mbarriers;
+//     the matrix) into a shared-memory ring (6 to 10 stages) guarded by full/empty mbarriers;
 //   - one elected thread issues tcgen05.mma (UMMA 128 x BN x 16, kind::f16, cta_group::1); the
 //     accumulator (128 lanes x BN fp32 columns) lives in TMEM allocated by the same warp;
 //   - four epilogue warps read their lane quadrant with tcgen05.ld, add the residual, convert
@@ -23,7 +23,13 @@
 
 namespace {
 
-constexpr int BM = 128, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
+// Ring depth per tile width: about 190 KB of operands in flight per CTA.  The GEMMs of a decode
+// step are short (K = 512 ... 1408, 8 ... 22 k-blocks); with a deep ring most of a CTA's operand
+// bytes are requested at once and the kernel is bound by one memory round trip, not by one per
+// four k-blocks.
+template <int BN> struct Ring { static constexpr int STAGES = BN == 32 ? 10 : (BN == 64 ? 8 : 6); };
+enum { EPI_NONE = 0, EPI_SWIGLU = 1 };
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -101,6 +107,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
 
 template <int BN>
 struct Smem {
+    static constexpr int STAGES = Ring<BN>::STAGES;
     alignas(1024) uint8_t a[STAGES][BM * BK * 2];
     alignas(1024) uint8_t b[STAGES][BN * BK * 2];
     alignas(8) uint64_t full[STAGES];
@@ -109,13 +116,17 @@ struct Smem {
     uint32_t tmem_base;
 };
 
-template <int BN, typename TC>
+// EPI_SWIGLU: the B rows are interleaved (gate_j, up_j, gate_j+1, ...); the epilogue rounds both to
+// the output type (what a stored gate|up tensor would hold), applies silu(gate) * up and writes
+// N / 2 columns.  R is ignored.
+template <int BN, typename TC, int EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                TC* __restrict__ C, const TC* R, int M, int N, int K, int* __restrict__ err)
 {
     extern __shared__ uint8_t smem_raw[];
     Smem<BN>& sm = *reinterpret_cast<Smem<BN>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int STAGES = Ring<BN>::STAGES;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     constexpr uint32_t STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -175,7 +186,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t v[32];
                 tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < M) {
+                if (EPI == EPI_SWIGLU) {
+                    if (row < M) {
+                        const int No = N >> 1;
+                        const int ncols = min(32, N - (n0 + c0)) >> 1;
+                        const size_t base = (size_t)row * No + ((n0 + c0) >> 1);
+                        float o[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            float g = __uint_as_float(v[2 * j]), u = __uint_as_float(v[2 * j + 1]);
+                            if (sizeof(TC) == 2) { g = __bfloat162float(__float2bfloat16_rn(g)); u = __bfloat162float(__float2bfloat16_rn(u)); }
+                            o[j] = silu_f(g) * u;
+                        }
+                        if (ncols == 16 && (No % 8) == 0 && sizeof(TC) == 2) {
+                            float lo[8], hi[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) { lo[j] = o[j]; hi[j] = o[8 + j]; }
+                            st16<bf16>(reinterpret_cast<bf16*>(C) + base, lo);
+                            st16<bf16>(reinterpret_cast<bf16*>(C) + base + 8, hi);
+                        } else {
+                            for (int j = 0; j < ncols; ++j) Cvt<TC>::st(C, base + j, o[j]);
+                        }
+                    }
+                } else if (row < M) {
                     const size_t base = (size_t)row * N + n0 + c0;
                     const int ncols = min(32, N - (n0 + c0));
                     if (ncols == 32 && (N % Vec16<TC>::N) == 0) {
@@ -256,7 +289,7 @@ int tensor_map(const void* base, int rows, int cols, int box_rows, CUtensorMap* 
 
 int* g_err_flag = nullptr;
 
-template <int BN, typename TC>
+template <int BN, typename TC, int EPI>
 int launch(const void* A, const void* B, void* C, const void* R, int M, int N, int K, cudaStream_t s)
 {
     CUtensorMap ma, mb;
@@ -265,11 +298,11 @@ int launch(const void* A, const void* B, void* C, const void* R, int M, int N, i
     const size_t smem = sizeof(Smem<BN>) + 1024;
     static bool attr_set = false;
     if (!attr_set) {
-        LTL_CUDA("gemm_tc attr", cudaFuncSetAttribute(gemm_tc_kernel<BN, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LTL_CUDA("gemm_tc attr", cudaFuncSetAttribute(gemm_tc_kernel<BN, TC, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_tc_kernel<BN, TC><<<grid, 192, smem, s>>>(ma, mb, (TC*)C, (const TC*)R, M, N, K, g_err_flag);
+    gemm_tc_kernel<BN, TC, EPI><<<grid, 192, smem, s>>>(ma, mb, (TC*)C, (const TC*)R, M, N, K, g_err_flag);
     return ltl_check_launch("gemm_tc");
 }
 
@@ -281,29 +314,40 @@ bool ltl_gemm_tc_supported(const void* A, const void* B, int M, int N, int K)
            (reinterpret_cast<uintptr_t>(B) & 15) == 0;
 }
 
+static int pick_bn(int M, int N)
+{
+    // Widest single wave: the tile width with the most CTAs that still fit the SMs at one CTA each.
+    const int mt = (M + BM - 1) / BM, sms = ltl_sm_count();
+    int best = 128, best_ctas = -1;
+    const int cand[3] = { 128, 64, 32 };
+    for (int c : cand) {
+        const int ctas = mt * ((N + c - 1) / c);
+        if (ctas <= sms && ctas > best_ctas) { best = c; best_ctas = ctas; }
+    }
+    return best;
+}
+
 // C[M,N] (c_dtype f32 or bf16, row-major) = A[M,K] B[N,K]^T + R.  bn = 0 picks the tile width.
+// epi = 1: SwiGLU epilogue (see the kernel), C is [M, N/2] bf16.
 int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int c_dtype, int bn,
-                cudaStream_t s)
+                int epi, cudaStream_t s)
 {
     if (!A || !B || !C) return ltl_fail(LTL_ERR_NULL, "gemm_tc: null operand");
     if (!ltl_gemm_tc_supported(A, B, M, N, K))
         return ltl_fail(LTL_ERR_UNSUPPORTED, "gemm_tc: needs K %% 8 == 0 and 16-byte aligned operands (M=%d N=%d K=%d)", M, N, K);
+    if (epi == EPI_SWIGLU && (c_dtype != LTL_BF16 || (N & 1)))
+        return ltl_fail(LTL_ERR_ARG, "gemm_tc: the SwiGLU epilogue writes bf16 and needs an even N");
     if (!g_err_flag) {
         LTL_CUDA("gemm_tc flag", cudaMalloc(&g_err_flag, sizeof(int)));
         LTL_CUDA("gemm_tc flag", cudaMemset(g_err_flag, 0, sizeof(int)));
     }
-    if (bn == 0) {
-        // enough CTAs to occupy the SMs: narrower tiles for small N
-        const int mt = (M + BM - 1) / BM;
-        bn = 128;
-        if (mt * ((N + 127) / 128) < ltl_sm_count()) bn = 64;
-        if (mt * ((N + 63) / 64) < ltl_sm_count() / 2) bn = 32;
-    }
-#define TC_CASE(BNV)                                                                         \
-    if (bn == BNV) {                                                                         \
-        if (c_dtype == LTL_F32) return launch<BNV, float>(A, B, C, R, M, N, K, s);           \
-        if (c_dtype == LTL_BF16) return launch<BNV, bf16>(A, B, C, R, M, N, K, s);           \
-        return ltl_fail(LTL_ERR_DTYPE, "gemm_tc: output dtype %d", c_dtype);                 \
+    if (bn == 0) bn = pick_bn(M, N);
+#define TC_CASE(BNV)                                                                                     \
+    if (bn == BNV) {                                                                                     \
+        if (epi == EPI_SWIGLU) return launch<BNV, bf16, EPI_SWIGLU>(A, B, C, nullptr, M, N, K, s);       \
+        if (c_dtype == LTL_F32) return launch<BNV, float, EPI_NONE>(A, B, C, R, M, N, K, s);             \
+        if (c_dtype == LTL_BF16) return launch<BNV, bf16, EPI_NONE>(A, B, C, R, M, N, K, s);             \
+        return ltl_fail(LTL_ERR_DTYPE, "gemm_tc: output dtype %d", c_dtype);                             \
     }
     TC_CASE(32) TC_CASE(64) TC_CASE(128)
 #undef TC_CASE

@@ -46,7 +46,8 @@ struct Act {
 };
 
 struct GraphEntry { cudaGraph_t g = nullptr; cudaGraphExec_t ge = nullptr; int64_t launches = 0;
-                    const void* out = nullptr; int out_stride = 0; };
+                    const void* out = nullptr; int out_stride = 0;
+                    const void* hist = nullptr; int hist_stride = 0, hist_base = 0; };
 
 }  // namespace
 
@@ -83,7 +84,7 @@ struct luaTL_lm_s {
     float prefill_ms = 0, decode_ms = 0;
     int64_t launches = 0;
     int adam_alloc = 0;
-    int use_tc = 1;
+    int use_tc = 1, fuse_swiglu = 0;
 };
 
 namespace {
@@ -186,7 +187,11 @@ int sync_mirror(LM* m)
 {
     if (m->adt != LTL_BF16 || !m->mirror_dirty) return LTL_OK;
     for (const TensorInfo& t : m->tens) {
-        if (t.is_matrix) LTL_TRY(ltl_transpose_to_bf16(m->W + t.off, m->Wb + t.off, t.rows, t.cols, m->s));
+        if (t.is_matrix) {
+            // w13 [D, 2F]: with the fused SwiGLU epilogue its mirror rows alternate gate_j / up_j
+            const int half = (m->fuse_swiglu && t.cols == 2 * m->F && t.rows == m->D && strstr(t.name, "w13")) ? m->F : 0;
+            LTL_TRY(ltl_transpose_to_bf16(m->W + t.off, m->Wb + t.off, t.rows, t.cols, half, m->s));
+        }
         else LTL_TRY(ltl_cast(m->W + t.off, LTL_F32, m->Wb + t.off, LTL_BF16, (uint64_t)t.rows * t.cols, m->s));
     }
     m->mirror_dirty = 0;
@@ -197,7 +202,7 @@ int sync_mirror(LM* m)
 // and [Nout, K] in the bf16 mirror.  transposed_master = 1: the master itself is [Nout, K]
 // (tok_emb used as the tied head).
 int wgemm(LM* m, const void* A, int M, int K, int64_t w_off, int Nout, void* C, int c_dt, const void* R,
-          int transposed_master)
+          int transposed_master, int epi = 0)
 {
     GemmDesc g;
     memset(&g, 0, sizeof(g));
@@ -213,7 +218,8 @@ int wgemm(LM* m, const void* A, int M, int K, int64_t w_off, int Nout, void* C, 
         g.b_rs = 1; g.b_cs = K;
         // bf16: activations [M, K] and the mirrored weight [Nout, K] are both K-major -> tensor cores
         if (m->use_tc && ltl_gemm_tc_supported(A, g.B, M, Nout, K))
-            return ltl_gemm_tc(A, g.B, C, R, M, Nout, K, c_dt, 0, m->s);
+            return ltl_gemm_tc(A, g.B, C, R, M, Nout, K, c_dt, 0, epi, m->s);
+        if (epi) return ltl_fail(LTL_ERR_UNSUPPORTED, "lm: fused SwiGLU needs the tensor-core GEMM");
     }
     return ltl_gemm_simt(g, m->s);
 }
@@ -283,10 +289,15 @@ int forward(LM* m, Act& a, const int32_t* d_ids, int nseq, int T, int mode)
         }
         LTL_TRY(wgemm(m, attn, rows, D, o.wo, D, mid, LTL_F32, xin, 0));
         LTL_TRY(ltl_lm_rmsnorm(mid, m->W + o.ln2, h2, adt, rows, D, m->c.eps, m->s));
-        LTL_TRY(wgemm(m, h2, rows, D, o.w13, 2 * F, h13, adt, nullptr, 0));
-        LTL_TRY(ltl_swiglu_fwd(h13, (char*)h13 + (size_t)F * e, hs, rows, F, 2 * F, 2 * F, F, adt, m->s));
+        if (m->fuse_swiglu) {
+            LTL_TRY(wgemm(m, h2, rows, D, o.w13, 2 * F, hs, adt, nullptr, 0, 1));
+            m->launches += 4;
+        } else {
+            LTL_TRY(wgemm(m, h2, rows, D, o.w13, 2 * F, h13, adt, nullptr, 0));
+            LTL_TRY(ltl_swiglu_fwd(h13, (char*)h13 + (size_t)F * e, hs, rows, F, 2 * F, 2 * F, F, adt, m->s));
+            m->launches += 5;
+        }
         LTL_TRY(wgemm(m, hs, rows, F, o.w2, D, xout, LTL_F32, mid, 0));
-        m->launches += 5;
     }
     const float* xf = a.layered ? a.res + (size_t)L * RD : a.res;
     int lrows = rows;
@@ -529,7 +540,8 @@ int ensure_decode(LM* m, int nseq, int n_prompt, int n_new)
 // One token for every sequence: consumes d_next / d_pos, appends K/V, picks the next token.
 // Everything it reads that changes between steps lives in device memory, so the launch
 // sequence can be captured once and replayed.
-int decode_step(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t* d_out, int out_stride, int pick)
+int decode_step(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t* d_out, int out_stride, int pick,
+                int32_t* hist = nullptr, int hist_stride = 0, int hist_base = 0)
 {
     const int D = m->D, F = m->F, V = m->V, L = m->L, H = m->H, hd = m->hd, adt = m->adt;
     const size_t e = esz(adt);
@@ -547,15 +559,19 @@ int decode_step(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t* d_out
         void* vcl = (char*)m->vc + l * cl + cslot;
         LTL_TRY(ltl_lm_rmsnorm(x, m->W + o.ln1, a.h1, adt, nseq, D, m->c.eps, m->s));
         LTL_TRY(wgemm(m, a.h1, nseq, D, o.wqkv, 3 * D, a.qkv, adt, nullptr, 0));
-        LTL_TRY(ltl_rope_append(a.qkv, kcl, vcl, pos, nseq, H, hd, m->T, m->rope_tab, m->c.rope_interleaved,
-                                m->c.use_rope, adt, m->d_err, m->s));
-        LTL_TRY(ltl_decode_attn(a.qkv, kcl, vcl, a.attn, pos, nseq, H, hd, m->T, m->scale, adt, m->splits, m->ws, m->s));
+        LTL_TRY(ltl_decode_attn(a.qkv, kcl, vcl, a.attn, pos, nseq, H, hd, m->T, m->scale, adt, m->splits, m->ws,
+                                m->rope_tab, m->c.rope_interleaved, m->c.use_rope, m->d_err, m->s));
         LTL_TRY(wgemm(m, a.attn, nseq, D, o.wo, D, x, LTL_F32, x, 0));
         LTL_TRY(ltl_lm_rmsnorm(x, m->W + o.ln2, a.h2, adt, nseq, D, m->c.eps, m->s));
-        LTL_TRY(wgemm(m, a.h2, nseq, D, o.w13, 2 * F, a.h13, adt, nullptr, 0));
-        LTL_TRY(ltl_swiglu_fwd(a.h13, (char*)a.h13 + (size_t)F * e, a.hs, nseq, F, 2 * F, 2 * F, F, adt, m->s));
+        if (m->fuse_swiglu) {
+            LTL_TRY(wgemm(m, a.h2, nseq, D, o.w13, 2 * F, a.hs, adt, nullptr, 0, 1));
+        } else {
+            LTL_TRY(wgemm(m, a.h2, nseq, D, o.w13, 2 * F, a.h13, adt, nullptr, 0));
+            LTL_TRY(ltl_swiglu_fwd(a.h13, (char*)a.h13 + (size_t)F * e, a.hs, nseq, F, 2 * F, 2 * F, F, adt, m->s));
+            m->launches++;
+        }
         LTL_TRY(wgemm(m, a.hs, nseq, F, o.w2, D, x, LTL_F32, x, 0));
-        m->launches += 5 + (m->splits > 1 ? 1 : 0);
+        m->launches += 3 + (m->splits > 1 ? 1 : 0);
     }
     LTL_TRY(ltl_lm_rmsnorm(x, m->W + m->off_lnf, a.hf, adt, nseq, D, m->c.eps, m->s));
     if (m->c.tie) LTL_TRY(wgemm(m, a.hf, nseq, D, m->off_emb, V, a.logits, LTL_F32, nullptr, 1));
@@ -563,7 +579,7 @@ int decode_step(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t* d_out
     m->launches++;
     if (pick) {
         LTL_TRY(ltl_pick_advance(a.logits, nseq, V, m->d_next + slot0, d_out, out_stride, m->d_count + slot0,
-                                 m->d_pos + slot0, m->s));
+                                 m->d_pos + slot0, hist, hist_stride, hist_base, m->s));
         m->launches++;
     }
     return LTL_OK;
@@ -577,11 +593,6 @@ __global__ void window_kernel(const int32_t* __restrict__ hist, int hist_stride,
     const int b = i / W, t = i - b * W;
     win[i] = hist[(size_t)b * hist_stride + (len - W) + t];
 }
-__global__ void append_hist_kernel(int32_t* __restrict__ hist, int hist_stride, int at, const int32_t* __restrict__ next, int nseq)
-{
-    const int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b < nseq) hist[(size_t)b * hist_stride + at] = next[b];
-}
 __global__ void copy_prompt_kernel(const int32_t* __restrict__ prompts, int n_prompt, int32_t* __restrict__ hist,
                                    int hist_stride, int nseq)
 {
@@ -592,14 +603,15 @@ __global__ void copy_prompt_kernel(const int32_t* __restrict__ prompts, int n_pr
 }
 
 // Prefill the cache from the last min(len, max_seq) tokens of the history and pick a token.
-int prefill_and_pick(LM* m, int nseq, int len, int hist_stride, int32_t* d_out, int out_stride)
+int prefill_and_pick(LM* m, int nseq, int len, int hist_stride, int hist_base, int32_t* d_out, int out_stride)
 {
     const int Wn = len < m->T ? len : m->T;
     window_kernel<<<(nseq * Wn + 255) / 256, 256, 0, m->s>>>(m->d_hist, hist_stride, len, m->d_win, Wn, nseq);
     LTL_TRY(ltl_check_launch("window"));
     LTL_TRY(forward(m, m->infer, m->d_win, nseq, Wn, MODE_PREFILL));
     LTL_TRY(ltl_fill_i32(m->d_pos, nseq, Wn - 1, m->s));
-    LTL_TRY(ltl_pick_advance(m->infer.logits, nseq, m->V, m->d_next, d_out, out_stride, m->d_count, m->d_pos, m->s));
+    LTL_TRY(ltl_pick_advance(m->infer.logits, nseq, m->V, m->d_next, d_out, out_stride, m->d_count, m->d_pos,
+                             m->d_hist, hist_stride, hist_base, m->s));
     m->launches += 3;
     return LTL_OK;
 }
@@ -617,33 +629,33 @@ int generate_dev(LM* m, const int32_t* d_prompts, int nseq, int n_prompt, int n_
     LTL_CUDA("memset", cudaMemsetAsync(m->d_err, 0, 4, m->s));
     copy_prompt_kernel<<<(nseq * n_prompt + 255) / 256, 256, 0, m->s>>>(d_prompts, n_prompt, m->d_hist, hs, nseq);
     LTL_TRY(ltl_check_launch("copy_prompt"));
-    LTL_TRY(prefill_and_pick(m, nseq, n_prompt, hs, d_out, n_new));
+    LTL_TRY(prefill_and_pick(m, nseq, n_prompt, hs, n_prompt, d_out, n_new));
     LTL_CUDA("event", cudaEventRecord(m->ev[1], m->s));
     int len = n_prompt;                     // tokens in the history before the one just picked
     int cached = n_prompt < m->T ? n_prompt : m->T;   // tokens in the cache
     for (int step = 1; step < n_new; ++step) {
-        append_hist_kernel<<<(nseq + 255) / 256, 256, 0, m->s>>>(m->d_hist, hs, len, m->d_next, nseq);
-        ++len; m->launches++;
+        ++len;                                // the pick that produced d_next also appended it to the history
         if (cached >= m->T) {
             // cache full: rebuild it from the last max_seq tokens (ai/optim/lmtrain.lua:1511-1515)
-            LTL_TRY(prefill_and_pick(m, nseq, len, hs, d_out, n_new));
+            LTL_TRY(prefill_and_pick(m, nseq, len, hs, n_prompt, d_out, n_new));
             cached = m->T;
             continue;
         }
         GraphEntry& ge = m->graphs[nseq];
-        if (ge.ge && (ge.out != d_out || ge.out_stride != n_new)) {   // captured for other buffers
+        if (ge.ge && (ge.out != d_out || ge.out_stride != n_new || ge.hist != m->d_hist || ge.hist_stride != hs ||
+                      ge.hist_base != n_prompt)) {   // captured for other buffers
             cudaGraphExecDestroy(ge.ge); cudaGraphDestroy(ge.g);
             ge = GraphEntry();
         }
         if (!ge.ge) {
             // First use: run the step eagerly (it is a real step), then capture a copy for replay.
             const int64_t before = m->launches;
-            LTL_TRY(decode_step(m, nseq, 0, m->d_next, d_out, n_new, 1));
+            LTL_TRY(decode_step(m, nseq, 0, m->d_next, d_out, n_new, 1, m->d_hist, hs, n_prompt));
             const int64_t per_step = m->launches - before;
             ++cached;
             LTL_CUDA("pre-capture sync", cudaStreamSynchronize(m->s));
             LTL_CUDA("begin capture", cudaStreamBeginCapture(m->s, cudaStreamCaptureModeThreadLocal));
-            const int rc = decode_step(m, nseq, 0, m->d_next, d_out, n_new, 1);
+            const int rc = decode_step(m, nseq, 0, m->d_next, d_out, n_new, 1, m->d_hist, hs, n_prompt);
             cudaGraph_t g = nullptr;
             const cudaError_t ce = cudaStreamEndCapture(m->s, &g);
             m->launches -= per_step;        // the captured copy did not execute
@@ -653,6 +665,7 @@ int generate_dev(LM* m, const int32_t* d_prompts, int nseq, int n_prompt, int n_
             const cudaError_t ie = cudaGraphInstantiate(&gx, g, 0);
             if (ie != cudaSuccess) { cudaGraphDestroy(g); return ltl_cuda_fail("graph instantiate", ie); }
             ge.g = g; ge.ge = gx; ge.launches = per_step; ge.out = d_out; ge.out_stride = n_new;
+            ge.hist = m->d_hist; ge.hist_stride = hs; ge.hist_base = n_prompt;
             continue;
         }
         LTL_CUDA("graph launch", cudaGraphLaunch(ge.ge, m->s));
@@ -706,6 +719,7 @@ luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
     {   // LUATL_DISABLE_TC=1 routes the bf16 GEMMs through the CUDA-core kernel (A/B comparison)
         const char* e = getenv("LUATL_DISABLE_TC");
         m->use_tc = !(e && e[0] == '1');
+        m->fuse_swiglu = m->use_tc && m->adt == LTL_BF16;
     }
     layout_params(m);
     int rc = LTL_OK;

@@ -1,12 +1,14 @@
 // Kernels that exist only inside the token loop: embedding gather into the fp32 residual
-// stream, RMSNorm from the fp32 stream into the GEMM input type, RoPE + KV-cache append,
-// decode attention over the device-resident KV cache, greedy pick + position advance.
+// stream, RMSNorm from the fp32 stream into the GEMM input type, decode attention over the
+// device-resident KV cache (fused with RoPE and the cache append), greedy pick + position advance.
 //
 // KV cache layout: K and V are separate arrays [B, H, ctx, hd]; all positions of one
 // (sequence, head) are contiguous, so decode attention streams each head's keys and values
 // front to back with 16-byte loads.  The reference has no device KV cache (its GPU model
 // re-runs a full forward per token, ai/gpu/gpu_transformer.lua:677); the semantics follow the
 // CPU model's step() (ai/nn/transformer.lua:297-434).
+#include <stdlib.h>
+
 #include "ops.h"
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -84,50 +86,6 @@ int ltl_lm_rmsnorm(const float* x, const float* gain, void* out, int out_dtype, 
 }
 
 // ------------------------------------------------------------------------------------------
-// RoPE of the new token's q and k, and append of k, v to the cache at pos[b].
-template <typename T>
-__global__ void rope_append_kernel(T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
-                                   const int32_t* __restrict__ pos, int B, int H, int hd, int ctx,
-                                   const float2* __restrict__ cs, int interleaved, int use_rope,
-                                   int* __restrict__ err)
-{
-    const int pairs = hd >> 1;
-    const int n = B * H * pairs;
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= n) return;
-    const int p = idx % pairs, h = (idx / pairs) % H, b = idx / (pairs * H);
-    const int D = H * hd;
-    const int ps = pos[b];
-    if (ps < 0 || ps >= ctx) { if (err) *err = 1; return; }
-    float c = 1.0f, sn = 0.0f;
-    if (use_rope) { const float2 t = cs[(size_t)ps * pairs + p]; c = t.x; sn = t.y; }
-    const int i0 = interleaved ? 2 * p : p, i1 = interleaved ? 2 * p + 1 : p + pairs;
-    T* row = qkv + (size_t)b * 3 * D + (size_t)h * hd;
-    const float q0 = Cvt<T>::ld(row, i0), q1 = Cvt<T>::ld(row, i1);
-    Cvt<T>::st(row, i0, q0 * c - q1 * sn);
-    Cvt<T>::st(row, i1, q1 * c + q0 * sn);
-    const float k0 = Cvt<T>::ld(row + D, i0), k1 = Cvt<T>::ld(row + D, i1);
-    const size_t co = (((size_t)b * H + h) * ctx + ps) * hd;
-    Cvt<T>::st(kc, co + i0, k0 * c - k1 * sn);
-    Cvt<T>::st(kc, co + i1, k1 * c + k0 * sn);
-    vc[co + i0] = row[2 * D + i0];
-    vc[co + i1] = row[2 * D + i1];
-}
-
-int ltl_rope_append(void* qkv, void* kcache, void* vcache, const int32_t* pos, int B, int H, int hd,
-                    int ctx, const float2* cs_table, int interleaved, int use_rope, int dtype,
-                    int* err, cudaStream_t s)
-{
-    if (!qkv || !kcache || !vcache || !pos) return ltl_fail(LTL_ERR_NULL, "rope_append: null pointer");
-    if (use_rope && !cs_table) return ltl_fail(LTL_ERR_NULL, "rope_append: missing angle table");
-    const int n = B * H * (hd / 2);
-    if (n <= 0) return LTL_OK;
-    if (dtype == LTL_F32) rope_append_kernel<float><<<(n + 255) / 256, 256, 0, s>>>((float*)qkv, (float*)kcache, (float*)vcache, pos, B, H, hd, ctx, cs_table, interleaved, use_rope, err);
-    else if (dtype == LTL_BF16) rope_append_kernel<bf16><<<(n + 255) / 256, 256, 0, s>>>((bf16*)qkv, (bf16*)kcache, (bf16*)vcache, pos, B, H, hd, ctx, cs_table, interleaved, use_rope, err);
-    else return ltl_fail(LTL_ERR_DTYPE, "rope_append: dtype %d", dtype);
-    return ltl_check_launch("rope_append");
-}
-
 template <typename T>
 __global__ void kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
                                 int B, int T_, int H, int hd, int ctx)
@@ -164,40 +122,84 @@ int ltl_kv_store(const void* qkv, void* kcache, void* vcache, int B, int T, int 
 }
 
 // ------------------------------------------------------------------------------------------
-// Decode attention.  One CTA (128 threads) per (head, sequence, split).  A key of hd elements
-// is covered by GL = hd * sizeof(T) / 16 lanes, each holding one 16-byte packet; the 128 / GL
-// lane groups of the CTA walk the keys round-robin, four keys in flight per group, each group
-// keeping its own online-softmax state; the groups are merged through shared memory.
-// Bytes per (sequence, head): 2 * n * hd * sizeof(T) read once - HBM-bound.
+// Decode attention, fused with RoPE of the new token and the KV-cache append.
+// One CTA (128 threads) per (head, sequence, split).  A key of hd elements is covered by
+// GL = hd * sizeof(T) / 16 lanes, each holding one 16-byte packet; the 128 / GL lane groups of
+// the CTA walk the cached keys 0 .. pos-1 round-robin, four keys in flight per group, each group
+// keeping its own online-softmax state; the groups are merged through shared memory.  The new
+// token's q and k are rotated in registers (rounded to the storage type, as a stored tensor would
+// be), its k and v are written to position pos of the cache by one group and enter the softmax
+// from registers.  Bytes per (sequence, head): 2 * pos * hd * sizeof(T) read once - HBM-bound.
 // ------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float round_to(float x);
+template <> __device__ __forceinline__ float round_to<float>(float x) { return x; }
+template <> __device__ __forceinline__ float round_to<bf16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
 template <typename T, int HD>
 __global__ void __launch_bounds__(128)
-decode_attn_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, const T* __restrict__ vc,
+decode_attn_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
                    T* __restrict__ out, const int32_t* __restrict__ pos, int H, int ctx, float scale,
-                   int splits, float* __restrict__ scratch)
+                   int splits, float* __restrict__ scratch, const float2* __restrict__ cs,
+                   int interleaved, int use_rope, int* __restrict__ err)
 {
     constexpr int N = Vec16<T>::N;
     constexpr int GL = HD / N;           // lanes per key
     constexpr int NG = 128 / GL;         // key groups per CTA
     constexpr int U = 4;                 // keys in flight per group
-    static_assert(GL >= 1 && GL <= 32 && (GL & (GL - 1)) == 0, "head_dim / packet must be a power of two <= 32");
+    static_assert(GL >= 2 && GL <= 32 && (GL & (GL - 1)) == 0, "head_dim / packet must be a power of two in 2..32");
     __shared__ float sm_m[NG], sm_l[NG];
     __shared__ float sm_acc[NG][HD + 1];
     const int h = blockIdx.x, b = blockIdx.y, z = blockIdx.z;
     const int D = H * HD;
     const int g = threadIdx.x / GL, r = threadIdx.x % GL;
-    int n = pos[b] + 1;
-    if (n > ctx) n = ctx;
-    if (n < 0) n = 0;
-    const int chunk = (n + splits - 1) / splits;
-    const int kbeg = z * chunk, kend = min(n, kbeg + chunk);
+    int ps = pos[b];
+    const bool in_range = ps >= 0 && ps < ctx;
+    if (!in_range) { if (err && threadIdx.x == 0) *err = 1; ps = ps < 0 ? 0 : ctx; }
 
-    float q[N];
-    ld16<T>(qkv + (size_t)b * 3 * D + (size_t)h * HD + r * N, q);
+    // the new token: q, k, v of this head from the projection row
+    const T* row = qkv + (size_t)b * 3 * D + (size_t)h * HD + r * N;
+    float q[N], kn[N], vn[N];
+    ld16<T>(row, q);
+    ld16<T>(row + D, kn);
+    ld16<T>(row + 2 * D, vn);
+    if (use_rope) {
+        const float2* tab = cs + (size_t)(in_range ? ps : 0) * (HD / 2);
+        if (interleaved) {
+#pragma unroll
+            for (int i = 0; i < N; i += 2) {
+                const float2 t = tab[(r * N + i) >> 1];
+                const float q0 = q[i], q1 = q[i + 1], k0 = kn[i], k1 = kn[i + 1];
+                q[i] = q0 * t.x - q1 * t.y; q[i + 1] = q1 * t.x + q0 * t.y;
+                kn[i] = k0 * t.x - k1 * t.y; kn[i + 1] = k1 * t.x + k0 * t.y;
+            }
+        } else {
+            // pairs (p, p + hd/2): the partner element lives GL/2 lanes away
+            const bool low = r < GL / 2;
+            const int pbase = (r % (GL / 2)) * N;
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                const float qo = __shfl_xor_sync(0xFFFFFFFFu, q[i], GL / 2);
+                const float ko = __shfl_xor_sync(0xFFFFFFFFu, kn[i], GL / 2);
+                const float2 t = tab[pbase + i];
+                q[i] = low ? q[i] * t.x - qo * t.y : q[i] * t.x + qo * t.y;
+                kn[i] = low ? kn[i] * t.x - ko * t.y : kn[i] * t.x + ko * t.y;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < N; ++i) { q[i] = round_to<T>(q[i]); kn[i] = round_to<T>(kn[i]); }
+    }
+    const size_t cbase = ((size_t)b * H + h) * ctx * HD + r * N;
+    if (z == 0 && g == 0 && in_range) {
+        st16<T>(kc + cbase + (size_t)ps * HD, kn);
+        st16<T>(vc + cbase + (size_t)ps * HD, vn);
+    }
 #pragma unroll
     for (int i = 0; i < N; ++i) q[i] *= scale;
-    const T* kb = kc + ((size_t)b * H + h) * ctx * HD + r * N;
-    const T* vb = vc + ((size_t)b * H + h) * ctx * HD + r * N;
+
+    const int chunk = (ps + splits - 1) / splits;            // cached keys 0 .. ps-1 over the splits
+    const int kbeg = z * chunk, kend = min(ps, kbeg + chunk);
+    const T* kb = kc + cbase;
+    const T* vb = vc + cbase;
 
     float m = -INFINITY, l = 0.0f, acc[N];
 #pragma unroll
@@ -238,6 +240,22 @@ decode_attn_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, const T*
             }
         }
     }
+    {   // the new token itself, from registers (every group computes the dot, one group uses it)
+        float sdot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < N; ++i) sdot = fmaf(q[i], kn[i], sdot);
+#pragma unroll
+        for (int o = GL / 2; o > 0; o >>= 1) sdot += __shfl_xor_sync(0xFFFFFFFFu, sdot, o);
+        if (z == 0 && g == 0) {
+            const float mn = fmaxf(m, sdot);
+            const float corr = expf(m - mn);
+            const float p = expf(sdot - mn);
+            l = l * corr + p;
+#pragma unroll
+            for (int i = 0; i < N; ++i) acc[i] = fmaf(p, vn[i], acc[i] * corr);
+            m = mn;
+        }
+    }
     if (r == 0) { sm_m[g] = m; sm_l[g] = l; }
 #pragma unroll
     for (int i = 0; i < N; ++i) sm_acc[g][r * N + i] = acc[i];
@@ -253,6 +271,218 @@ decode_attn_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, const T*
                 const float w = expf(sm_m[i] - M);       // empty group: exp(-inf) = 0
                 L = fmaf(sm_l[i], w, L);
                 o = fmaf(sm_acc[i][d], w, o);
+            }
+        }
+        if (splits == 1) {
+            Cvt<T>::st(out, (size_t)b * D + (size_t)h * HD + d, L > 0.0f ? o / L : 0.0f);
+        } else {
+            float* sp = scratch + (((size_t)b * H + h) * splits + z) * (HD + 2);
+            sp[2 + d] = o;
+            if (d == 0) { sp[0] = M; sp[1] = L; }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Decode attention, bulk-copy staged (rows of 128 bytes: bf16 head_dim 64, fp32 head_dim 32).
+// The K and V rows of one (sequence, head) are contiguous in the cache, so one thread streams
+// them into a 4-stage shared-memory ring with cp.async.bulk (64 keys = 8 KB of K and 8 KB of V
+// per stage, completion on an mbarrier) while the four warps consume: two threads per key form
+// the score from 16-byte chunks read in a rotated order (bank-conflict free), each warp keeps an
+// online-softmax state for its 16 keys of the tile and accumulates P V with one 4-byte word of
+// every V row per lane.  192 KB of loads can be in flight per SM without holding registers.
+// The new token (RoPE, cache append, its own score) is handled as in the register kernel.
+// ------------------------------------------------------------------------------------------
+namespace bulk {
+constexpr int KT = 64, STG = 4, ROWB = 128;
+constexpr uint32_t SPIN = 1u << 22;
+__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity)
+{
+    const uint32_t a = s32(bar);
+    for (uint32_t i = 0; i < SPIN; ++i) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(a), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
+}
+struct Smem {
+    alignas(128) uint8_t k[STG][KT * ROWB];
+    alignas(128) uint8_t v[STG][KT * ROWB];
+    alignas(16) float q[64], kn[64], vn[64];
+    float wm[4], wl[4], wacc[4][64];
+    alignas(8) uint64_t full[STG];
+};
+}  // namespace bulk
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(128)
+decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
+                        T* __restrict__ out, const int32_t* __restrict__ pos, int H, int ctx, float scale,
+                        int splits, float* __restrict__ scratch, const float2* __restrict__ cs,
+                        int interleaved, int use_rope, int* __restrict__ err)
+{
+    using namespace bulk;
+    static_assert(HD * sizeof(T) == ROWB && HD <= 64, "rows of 128 bytes");
+    constexpr int N = Vec16<T>::N;           // elements per 16-byte chunk
+    constexpr int GL = HD / N;               // 8 chunks per row
+    constexpr int EPW = 4 / sizeof(T);       // elements per 4-byte word (dims per lane in P V)
+    extern __shared__ uint8_t smem_raw[];
+    Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    const int h = blockIdx.x, b = blockIdx.y, z = blockIdx.z;
+    const int D = H * HD, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int ps = pos[b];
+    const bool in_range = ps >= 0 && ps < ctx;
+    if (!in_range) { if (err && tid == 0) *err = 1; ps = ps < 0 ? 0 : ctx; }
+    const int chunk = (ps + splits - 1) / splits;
+    const int kbeg = z * chunk, kend = min(ps, kbeg + chunk);
+    const int ntiles = kend > kbeg ? (kend - kbeg + KT - 1) / KT : 0;
+    const size_t cbase = ((size_t)b * H + h) * ctx * HD;
+    const uint8_t* kg = reinterpret_cast<const uint8_t*>(kc + cbase);
+    const uint8_t* vg = reinterpret_cast<const uint8_t*>(vc + cbase);
+
+    if (tid == 0) {
+        for (int s = 0; s < STG; ++s)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&sm.full[s])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int t = 0; t < ntiles && t < STG; ++t) {
+            const int k0 = kbeg + t * KT;
+            const uint32_t bytes = (uint32_t)min(KT, kend - k0) * ROWB;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(&sm.full[t])), "r"(2 * bytes) : "memory");
+            copy(sm.k[t], kg + (size_t)k0 * ROWB, bytes, &sm.full[t]);
+            copy(sm.v[t], vg + (size_t)k0 * ROWB, bytes, &sm.full[t]);
+        }
+    }
+    // new token: the first GL lanes of warp 1 rotate q and k, append k / v, publish q, k, v as fp32
+    if (warp == 1 && lane < GL) {
+        const int r = lane;
+        const T* row = qkv + (size_t)b * 3 * D + (size_t)h * HD + r * N;
+        float q[N], kn[N], vn[N];
+        ld16<T>(row, q); ld16<T>(row + D, kn); ld16<T>(row + 2 * D, vn);
+        if (use_rope) {
+            const float2* tab = cs + (size_t)(in_range ? ps : 0) * (HD / 2);
+            constexpr unsigned GM = (1u << GL) - 1u;
+            if (interleaved) {
+#pragma unroll
+                for (int i = 0; i < N; i += 2) {
+                    const float2 t = tab[(r * N + i) >> 1];
+                    const float q0 = q[i], q1 = q[i + 1], k0 = kn[i], k1 = kn[i + 1];
+                    q[i] = q0 * t.x - q1 * t.y; q[i + 1] = q1 * t.x + q0 * t.y;
+                    kn[i] = k0 * t.x - k1 * t.y; kn[i + 1] = k1 * t.x + k0 * t.y;
+                }
+            } else {
+                const bool low = r < GL / 2;
+                const int pbase = (r % (GL / 2)) * N;
+#pragma unroll
+                for (int i = 0; i < N; ++i) {
+                    const float qo = __shfl_xor_sync(GM, q[i], GL / 2);
+                    const float ko = __shfl_xor_sync(GM, kn[i], GL / 2);
+                    const float2 t = tab[pbase + i];
+                    q[i] = low ? q[i] * t.x - qo * t.y : q[i] * t.x + qo * t.y;
+                    kn[i] = low ? kn[i] * t.x - ko * t.y : kn[i] * t.x + ko * t.y;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < N; ++i) { q[i] = round_to<T>(q[i]); kn[i] = round_to<T>(kn[i]); }
+        }
+        if (z == 0 && in_range) {
+            st16<T>(kc + cbase + (size_t)ps * HD + r * N, kn);
+            st16<T>(vc + cbase + (size_t)ps * HD + r * N, vn);
+        }
+#pragma unroll
+        for (int i = 0; i < N; ++i) { sm.q[r * N + i] = q[i] * scale; sm.kn[r * N + i] = kn[i]; sm.vn[r * N + i] = vn[i]; }
+    }
+    __syncthreads();
+
+    const int j = tid >> 1, half = tid & 1;          // two threads per key of the tile
+    float m = -INFINITY, l = 0.0f, acc[EPW];
+#pragma unroll
+    for (int i = 0; i < EPW; ++i) acc[i] = 0.0f;
+    bool ok = true;
+    for (int t = 0; t < ntiles; ++t) {
+        const int s = t % STG;
+        ok = wait(&sm.full[s], (t / STG) & 1) && ok;
+        const int nk = min(KT, kend - (kbeg + t * KT));
+        const T* krow = reinterpret_cast<const T*>(sm.k[s] + j * ROWB);
+        float sdot = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int cc = (2 * c + half + 2 * j) & 7;      // rotated chunk order: conflict-free 16-byte reads
+            float kv[N];
+            ld16<T>(krow + cc * N, kv);
+            const float* qq = sm.q + cc * N;
+#pragma unroll
+            for (int i = 0; i < N; ++i) sdot = fmaf(qq[i], kv[i], sdot);
+        }
+        sdot += __shfl_xor_sync(0xFFFFFFFFu, sdot, 1);
+        const bool valid = j < nk;
+        const float sv = valid ? sdot : -INFINITY;
+        const float mn = fmaxf(m, warp_max(sv));
+        const float corr = (mn == -INFINITY) ? 1.0f : expf(m - mn);
+        const float p = valid ? expf(sv - mn) : 0.0f;
+        l = l * corr + 0.5f * warp_sum(p);                   // every key sits in two lanes
+        m = mn;
+#pragma unroll
+        for (int i = 0; i < EPW; ++i) acc[i] *= corr;
+        const uint32_t* vrows = reinterpret_cast<const uint32_t*>(sm.v[s]) + (size_t)(warp * 16) * (ROWB / 4) + lane;
+        const int nmine = min(16, nk - warp * 16);          // rows past the tile's end hold stale bytes
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+            if (jj >= nmine) break;                              // warp-uniform
+            const float pj = __shfl_sync(0xFFFFFFFFu, p, 2 * jj);
+            const uint32_t w = vrows[jj * (ROWB / 4)];
+            if (sizeof(T) == 2) {
+                acc[0] = fmaf(pj, __uint_as_float(w << 16), acc[0]);
+                acc[EPW - 1] = fmaf(pj, __uint_as_float(w & 0xFFFF0000u), acc[EPW - 1]);
+            } else {
+                acc[0] = fmaf(pj, __uint_as_float(w), acc[0]);
+            }
+        }
+        __syncthreads();                                      // everyone is done with stage s
+        if (tid == 0 && t + STG < ntiles) {
+            const int k0 = kbeg + (t + STG) * KT;
+            const uint32_t bytes = (uint32_t)min(KT, kend - k0) * ROWB;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(&sm.full[s])), "r"(2 * bytes) : "memory");
+            copy(sm.k[s], kg + (size_t)k0 * ROWB, bytes, &sm.full[s]);
+            copy(sm.v[s], vg + (size_t)k0 * ROWB, bytes, &sm.full[s]);
+        }
+    }
+    if (!ok && err && tid == 0) *err = 2;
+    if (warp == 0 && z == 0) {     // the new token's own score, from the fp32 copies
+        float sdot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < EPW; ++i) sdot = fmaf(sm.q[lane * EPW + i], sm.kn[lane * EPW + i], sdot);
+        sdot = warp_sum(sdot);
+        const float mn = fmaxf(m, sdot);
+        const float corr = (m == -INFINITY) ? 0.0f : expf(m - mn);
+        const float p = expf(sdot - mn);
+        l = l * corr + p;
+#pragma unroll
+        for (int i = 0; i < EPW; ++i) acc[i] = fmaf(p, sm.vn[lane * EPW + i], acc[i] * corr);
+        m = mn;
+    }
+    if (lane == 0) { sm.wm[warp] = m; sm.wl[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < EPW; ++i) sm.wacc[warp][lane * EPW + i] = acc[i];
+    __syncthreads();
+    if (tid < HD) {
+        const int d = tid;
+        float M = fmaxf(fmaxf(sm.wm[0], sm.wm[1]), fmaxf(sm.wm[2], sm.wm[3]));
+        float L = 0.0f, o = 0.0f;
+        if (M > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float e = expf(sm.wm[w] - M);
+                L = fmaf(sm.wl[w], e, L);
+                o = fmaf(sm.wacc[w][d], e, o);
             }
         }
         if (splits == 1) {
@@ -291,13 +521,34 @@ size_t ltl_decode_attn_scratch_floats(int B, int H, int hd, int splits)
 }
 
 template <typename T, int HD>
-static int launch_decode_attn(const void* qkv, const void* kc, const void* vc, void* out,
+static int launch_decode_attn(const void* qkv, void* kc, void* vc, void* out,
                               const int32_t* pos, int B, int H, int ctx, float scale, int splits,
-                              float* scratch, cudaStream_t s)
+                              float* scratch, const float2* cs, int interleaved, int use_rope, int* err,
+                              cudaStream_t s)
 {
     dim3 grid(H, B, splits);
-    decode_attn_kernel<T, HD><<<grid, 128, 0, s>>>((const T*)qkv, (const T*)kc, (const T*)vc, (T*)out,
-                                                   pos, H, ctx, scale, splits, scratch);
+    if constexpr (HD * sizeof(T) == 128 && HD <= 64) {
+        // 128-byte rows: the bulk-copy staged kernel (LUATL_ATTN_REGS=1 selects the register kernel)
+        static const bool use_regs = [] { const char* e = getenv("LUATL_ATTN_REGS"); return e && e[0] == '1'; }();
+        if (!use_regs) {
+            const size_t smem = sizeof(bulk::Smem) + 128;
+            static bool attr = false;
+            if (!attr) {
+                LTL_CUDA("decode_attn attr", cudaFuncSetAttribute(decode_attn_bulk_kernel<T, HD>,
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                attr = true;
+            }
+            decode_attn_bulk_kernel<T, HD><<<grid, 128, smem, s>>>((const T*)qkv, (T*)kc, (T*)vc, (T*)out, pos, H, ctx,
+                                                                   scale, splits, scratch, cs, interleaved, use_rope, err);
+            if (splits > 1) {
+                dim3 g2(H, B);
+                decode_attn_combine_kernel<T, HD><<<g2, HD < 32 ? 32 : HD, 0, s>>>(scratch, (T*)out, H, splits);
+            }
+            return ltl_check_launch("decode_attn");
+        }
+    }
+    decode_attn_kernel<T, HD><<<grid, 128, 0, s>>>((const T*)qkv, (T*)kc, (T*)vc, (T*)out, pos, H, ctx, scale,
+                                                   splits, scratch, cs, interleaved, use_rope, err);
     if (splits > 1) {
         dim3 g2(H, B);
         decode_attn_combine_kernel<T, HD><<<g2, HD < 32 ? 32 : HD, 0, s>>>(scratch, (T*)out, H, splits);
@@ -305,10 +556,12 @@ static int launch_decode_attn(const void* qkv, const void* kc, const void* vc, v
     return ltl_check_launch("decode_attn");
 }
 
-int ltl_decode_attn(const void* qkv, const void* kcache, const void* vcache, void* out,
+int ltl_decode_attn(const void* qkv, void* kcache, void* vcache, void* out,
                     const int32_t* pos, int B, int H, int hd, int ctx, float scale, int dtype,
-                    int splits, float* scratch, cudaStream_t s)
+                    int splits, float* scratch, const float2* cs_table, int interleaved, int use_rope,
+                    int* err, cudaStream_t s)
 {
+    if (use_rope && !cs_table) return ltl_fail(LTL_ERR_NULL, "decode_attn: missing angle table");
     if (!qkv || !kcache || !vcache || !out || !pos) return ltl_fail(LTL_ERR_NULL, "decode_attn: null pointer");
     if (B <= 0 || H <= 0) return ltl_fail(LTL_ERR_SHAPE, "decode_attn: bad shape");
     if (B > 65535 || splits > 65535) return ltl_fail(LTL_ERR_SHAPE, "decode_attn: grid too large");
@@ -316,7 +569,7 @@ int ltl_decode_attn(const void* qkv, const void* kcache, const void* vcache, voi
     if (splits > 1 && !scratch) return ltl_fail(LTL_ERR_NULL, "decode_attn: split-KV needs scratch");
     if (!aligned16(qkv) || !aligned16(kcache) || !aligned16(vcache))
         return ltl_fail(LTL_ERR_ARG, "decode_attn: operands must be 16-byte aligned");
-#define DA(TT, HH) return launch_decode_attn<TT, HH>(qkv, kcache, vcache, out, pos, B, H, ctx, scale, splits, scratch, s)
+#define DA(TT, HH) return launch_decode_attn<TT, HH>(qkv, kcache, vcache, out, pos, B, H, ctx, scale, splits, scratch, cs_table, interleaved, use_rope, err, s)
     if (dtype == LTL_F32) {
         if (hd == 16) DA(float, 16);
         if (hd == 32) DA(float, 32);
@@ -335,7 +588,8 @@ int ltl_decode_attn(const void* qkv, const void* kcache, const void* vcache, voi
 // ------------------------------------------------------------------------------------------
 __global__ void pick_advance_kernel(const float* __restrict__ logits, int V, int32_t* __restrict__ next,
                                     int32_t* __restrict__ out_ids, int out_stride,
-                                    int32_t* __restrict__ count, int32_t* __restrict__ pos)
+                                    int32_t* __restrict__ count, int32_t* __restrict__ pos,
+                                    int32_t* __restrict__ hist, int hist_stride, int hist_base)
 {
     __shared__ float red_v[32];
     __shared__ int red_i[32];
@@ -370,6 +624,7 @@ __global__ void pick_advance_kernel(const float* __restrict__ logits, int V, int
             next[b] = bi;
             const int c = count[b];
             if (out_ids && c < out_stride) out_ids[(size_t)b * out_stride + c] = bi;
+            if (hist && hist_base + c < hist_stride) hist[(size_t)b * hist_stride + hist_base + c] = bi;
             count[b] = c + 1;
             pos[b] += 1;
         }
@@ -377,11 +632,12 @@ __global__ void pick_advance_kernel(const float* __restrict__ logits, int V, int
 }
 
 int ltl_pick_advance(const float* logits, int B, int V, int32_t* next, int32_t* out_ids,
-                     int out_stride, int32_t* count, int32_t* pos, cudaStream_t s)
+                     int out_stride, int32_t* count, int32_t* pos, int32_t* hist, int hist_stride,
+                     int hist_base, cudaStream_t s)
 {
     if (!logits || !next || !count || !pos) return ltl_fail(LTL_ERR_NULL, "pick_advance: null pointer");
     if (B <= 0) return LTL_OK;
-    pick_advance_kernel<<<B, 256, 0, s>>>(logits, V, next, out_ids, out_stride, count, pos);
+    pick_advance_kernel<<<B, 256, 0, s>>>(logits, V, next, out_ids, out_stride, count, pos, hist, hist_stride, hist_base);
     return ltl_check_launch("pick_advance");
 }
 

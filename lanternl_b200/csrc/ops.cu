@@ -1090,7 +1090,7 @@ int ltl_cast(const void* src, int sd, void* dst, int dd, uint64_t n, cudaStream_
 }
 
 __global__ void transpose_to_bf16_kernel(const float* __restrict__ in, bf16* __restrict__ out,
-                                         int rows, int cols)
+                                         int rows, int cols, int half)
 {
     __shared__ float tile[32][33];
     const int x = blockIdx.x * 32 + threadIdx.x, y0 = blockIdx.y * 32;
@@ -1100,16 +1100,19 @@ __global__ void transpose_to_bf16_kernel(const float* __restrict__ in, bf16* __r
     const int ox = y0 + threadIdx.x;               // column in out = row in in
     for (int j = threadIdx.y; j < 32; j += 8) {
         const int oy = blockIdx.x * 32 + j;        // row in out = column in in
-        if (oy < cols && ox < rows) out[(size_t)oy * rows + ox] = __float2bfloat16_rn(tile[threadIdx.x][j]);
+        if (oy < cols && ox < rows) {
+            const int orow = half > 0 ? (oy < half ? 2 * oy : 2 * (oy - half) + 1) : oy;
+            out[(size_t)orow * rows + ox] = __float2bfloat16_rn(tile[threadIdx.x][j]);
+        }
     }
 }
 
-int ltl_transpose_to_bf16(const float* in, bf16* out, int rows, int cols, cudaStream_t s)
+int ltl_transpose_to_bf16(const float* in, bf16* out, int rows, int cols, int interleave_half, cudaStream_t s)
 {
     if (!in || !out) return ltl_fail(LTL_ERR_NULL, "transpose_to_bf16: null pointer");
     if (rows <= 0 || cols <= 0) return LTL_OK;
     dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
-    transpose_to_bf16_kernel<<<grid, block, 0, s>>>(in, out, rows, cols);
+    transpose_to_bf16_kernel<<<grid, block, 0, s>>>(in, out, rows, cols, interleave_half);
     return ltl_check_launch("transpose_to_bf16");
 }
 

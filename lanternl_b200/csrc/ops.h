@@ -47,7 +47,8 @@ int ltl_adamw(float* w, const void* g, float* m, float* v, void* w_lp, uint64_t 
 int ltl_sgd(float* w, const float* g, bf16* w_lp, uint64_t n, float lr, float wd,
             const float* nsq, float max_norm, cudaStream_t s);
 // out[c, r] = (bf16) in[r, c]
-int ltl_transpose_to_bf16(const float* in, bf16* out, int rows, int cols, cudaStream_t s);
+// interleave_half = F > 0: output row j < F goes to row 2j, row F + j to row 2j + 1 (gate/up pairs).
+int ltl_transpose_to_bf16(const float* in, bf16* out, int rows, int cols, int interleave_half, cudaStream_t s);
 
 // ---- CUDA-core GEMM with explicit strides (gemm_simt.cu) ----
 struct GemmDesc {
@@ -79,27 +80,27 @@ int ltl_lm_embed(const int32_t* ids, const void* table, int table_dtype, float* 
 // out[r, :] = rmsnorm(x[r, :]) * gain, x and gain fp32, out f32 or bf16.
 int ltl_lm_rmsnorm(const float* x, const float* gain, void* out, int out_dtype, int rows, int cols,
                    float eps, cudaStream_t s);
-// One new token per sequence: rotate q in place inside qkv [B, 3D], write the rotated k and v
-// of every head at position pos[b] of the caches ([B, H, ctx, hd] each).  err (optional) is
-// set to 1 when a position is outside [0, ctx).
-int ltl_rope_append(void* qkv, void* kcache, void* vcache, const int32_t* pos, int B, int H, int hd,
-                    int ctx, const float2* cs_table, int interleaved, int use_rope, int dtype,
-                    int* err, cudaStream_t s);
 // Prefill: copy rotated k and v of rows [B, T] of qkv [B*T, 3D] into the caches at 0..T-1.
 int ltl_kv_store(const void* qkv, void* kcache, void* vcache, int B, int T, int H, int hd, int ctx,
                  int dtype, cudaStream_t s);
-// Decode attention of one query per sequence over cache positions 0..pos[b].
+// Decode attention of one new token per sequence, fused with its RoPE and KV-cache append:
+// q and k of row b of qkv [B, 3D] are rotated for position pos[b], k and v are written to that
+// position of the caches, and the query attends cache positions 0..pos[b].
 // splits > 1 spreads the keys of one (sequence, head) over several CTAs; scratch then holds
-// decode_attn_scratch_floats(B, H, hd, splits) floats.
+// decode_attn_scratch_floats(B, H, hd, splits) floats.  err is set to 1 if a position is outside
+// [0, ctx).
 size_t ltl_decode_attn_scratch_floats(int B, int H, int hd, int splits);
-int ltl_decode_attn(const void* qkv, const void* kcache, const void* vcache, void* out,
+int ltl_decode_attn(const void* qkv, void* kcache, void* vcache, void* out,
                     const int32_t* pos, int B, int H, int hd, int ctx, float scale, int dtype,
-                    int splits, float* scratch, cudaStream_t s);
+                    int splits, float* scratch, const float2* cs_table, int interleaved, int use_rope,
+                    int* err, cudaStream_t s);
 // Greedy pick and bookkeeping of one decode step, per sequence b:
 //   next[b] = argmax(logits[b, :]) (ties -> lowest index);
 //   out_ids[b * out_stride + count[b]] = next[b] when count[b] < out_stride; count[b] += 1; pos[b] += 1.
+//   hist (optional): hist[b * hist_stride + hist_base + count[b]] = next[b] as well.
 int ltl_pick_advance(const float* logits, int B, int V, int32_t* next, int32_t* out_ids,
-                     int out_stride, int32_t* count, int32_t* pos, cudaStream_t s);
+                     int out_stride, int32_t* count, int32_t* pos, int32_t* hist, int hist_stride,
+                     int hist_base, cudaStream_t s);
 int ltl_fill_i32(int32_t* p, int n, int32_t value, cudaStream_t s);
 // correct[0] += #{r : tgt[r] >= 0 and pred[r] == tgt[r]}  (as float)
 int ltl_count_correct(const int32_t* pred, const int32_t* tgt, int n, float* correct, cudaStream_t s);
@@ -108,6 +109,7 @@ int ltl_gather_last_rows(const float* x, float* out, int B, int T, int cols, int
 
 // ---- tcgen05 / TMA GEMM (gemm_tc.cu): C[M,N] = A[M,K] B[N,K]^T + R, bf16 in, fp32 accumulate ----
 bool ltl_gemm_tc_supported(const void* A, const void* B, int M, int N, int K);
+// epi = 1: B rows interleave gate/up, C [M, N/2] bf16 = silu(gate) * up (R ignored).
 int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int c_dtype,
-                int bn, cudaStream_t s);
+                int bn, int epi, cudaStream_t s);
 int ltl_gemm_tc_check(cudaStream_t s);

@@ -58,3 +58,22 @@ def test_rejects_unaligned_k():
     A, B, Cc = bf16_dev(np.zeros((4, 12), np.float32)), bf16_dev(np.zeros((4, 12), np.float32)), ad.TensorView(4, 4)
     with pytest.raises(_lib.LuaTLError, match="UNSUPPORTED"):
         _lib.call("luaTL_gemm_bf16_tc", A.data, B.data, Cc.data, None, 4, 4, 12, _lib.F32, 0)
+
+
+@pytest.mark.parametrize("M,F,K,tile", [(256, 1408, 512, 0), (70, 40, 72, 32), (128, 64, 64, 64), (5, 192, 128, 128)])
+def test_swiglu_epilogue(M, F, K, tile):
+    """B rows alternate gate_j / up_j; C [M, F] = silu(bf16(gate)) * bf16(up), stored as bf16."""
+    a = bf16_round(synth.normal(11, 0, M * K).reshape(M, K).astype(np.float32))
+    wg = bf16_round((synth.normal(12, 0, F * K) * 0.1).reshape(F, K).astype(np.float32))
+    wu = bf16_round((synth.normal(13, 0, F * K) * 0.1).reshape(F, K).astype(np.float32))
+    b = np.empty((2 * F, K), np.float32)
+    b[0::2], b[1::2] = wg, wu
+    A, B, Cc = bf16_dev(a), bf16_dev(b), ad.TensorView(M, F, _lib.BF16)
+    _lib.call("luaTL_gemm_bf16_tc", A.data, B.data, Cc.data, None, M, 2 * F, K, _lib.BF16, tile | (1 << 16))
+    got = Cc.download().reshape(M, F)
+    g = bf16_round((a.astype(np.float64) @ wg.astype(np.float64).T).astype(np.float32)).astype(np.float64)
+    u = bf16_round((a.astype(np.float64) @ wu.astype(np.float64).T).astype(np.float32)).astype(np.float64)
+    ref = g / (1 + np.exp(-g)) * u
+    # one bf16 ulp of the output, plus rare flips of the rounded gate / up
+    assert np.abs(got - ref).max() <= 2 ** -7 * np.abs(ref).max()
+    assert np.median(np.abs(got - ref)) <= 2 ** -9 * np.abs(ref).max()
