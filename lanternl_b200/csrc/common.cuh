@@ -19,6 +19,8 @@ int  ltl_cuda_fail(const char* ctx, cudaError_t e);
 int  ltl_check_launch(const char* ctx);            // cudaGetLastError -> status
 int  ltl_require_init(const char* ctx);            // LTL_ERR_CUDA unless luaTL_init succeeded
 cudaStream_t ltl_default_stream();
+bool ltl_pdl_enabled();               // programmatic dependent launch for the decode-step kernels
+void ltl_pdl_set(bool on);
 int  ltl_sm_count();
 
 #define LTL_CUDA(ctx, call)                                               \
@@ -34,6 +36,26 @@ static inline size_t ltl_dtype_size(int dt) { return dt == LTL_F32 ? 4 : 2; }
 #ifdef __CUDACC__
 
 typedef __nv_bfloat16 bf16;
+
+// Programmatic dependent launch.  A kernel launched with the attribute may start while its
+// predecessor in the stream is still running: it must call pdl_wait() before it reads anything the
+// predecessor wrote or writes anything the predecessor reads.  pdl_trigger() lets the successor
+// start its own prologue early.  Both are no-ops for a plain launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ltl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                     bool pdl, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 template <typename T> struct Cvt;
 template <> struct Cvt<float> {

@@ -124,6 +124,8 @@ __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                TC* __restrict__ C, const TC* R, int M, int N, int K, int* __restrict__ err)
 {
+    // gridDim.z > 1: split-K.  Slice z covers a contiguous range of k-blocks and writes its partial
+    // sums to C + z * M * N (the consumer adds the slices in a fixed order).
     extern __shared__ uint8_t smem_raw[];
     Smem<BN>& sm = *reinterpret_cast<Smem<BN>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int STAGES = Ring<BN>::STAGES;
@@ -131,7 +133,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr uint32_t STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    const int kblocks = (K + BK - 1) / BK;
+    const int kb_all = (K + BK - 1) / BK;
+    const int kb_per = (kb_all + gridDim.z - 1) / gridDim.z;
+    const int kb0 = blockIdx.z * kb_per;
+    const int kblocks = max(0, min(kb_all, kb0 + kb_per) - kb0);
+    C += (size_t)blockIdx.z * M * N;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
@@ -147,6 +153,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = sm.tmem_base;
     bool ok = true;
+    pdl_trigger();          // the next kernel may set itself up
+    pdl_wait();             // barriers and TMEM are ready; now the predecessor's output may be read
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer ----
@@ -155,8 +163,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (kb >= STAGES) ok = mbar_wait(&sm.empty[s], ((kb / STAGES) - 1) & 1);
             if (!ok) break;
             mbar_expect_tx(&sm.full[s], STAGE_BYTES);
-            tma_load_2d(sm.a[s], &map_a, kb * BK, m0, &sm.full[s]);
-            tma_load_2d(sm.b[s], &map_b, kb * BK, n0, &sm.full[s]);
+            tma_load_2d(sm.a[s], &map_a, (kb0 + kb) * BK, m0, &sm.full[s]);
+            tma_load_2d(sm.b[s], &map_b, (kb0 + kb) * BK, n0, &sm.full[s]);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
@@ -186,6 +194,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t v[32];
                 tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (kblocks == 0) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0u;
+                }
                 if (EPI == EPI_SWIGLU) {
                     if (row < M) {
                         const int No = N >> 1;
@@ -290,7 +302,7 @@ int tensor_map(const void* base, int rows, int cols, int box_rows, CUtensorMap* 
 int* g_err_flag = nullptr;
 
 template <int BN, typename TC, int EPI>
-int launch(const void* A, const void* B, void* C, const void* R, int M, int N, int K, cudaStream_t s)
+int launch(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int ksplit, cudaStream_t s)
 {
     CUtensorMap ma, mb;
     LTL_TRY(tensor_map(A, M, K, BM, &ma));
@@ -301,8 +313,9 @@ int launch(const void* A, const void* B, void* C, const void* R, int M, int N, i
         LTL_CUDA("gemm_tc attr", cudaFuncSetAttribute(gemm_tc_kernel<BN, TC, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_tc_kernel<BN, TC, EPI><<<grid, 192, smem, s>>>(ma, mb, (TC*)C, (const TC*)R, M, N, K, g_err_flag);
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, ksplit < 1 ? 1 : ksplit);
+    LTL_CUDA("gemm_tc launch", ltl_launch(gemm_tc_kernel<BN, TC, EPI>, grid, dim3(192), smem, s, ltl_pdl_enabled(),
+                                          ma, mb, (TC*)C, (const TC*)R, M, N, K, g_err_flag));
     return ltl_check_launch("gemm_tc");
 }
 
@@ -327,11 +340,28 @@ static int pick_bn(int M, int N)
     return best;
 }
 
+// Split-K plan for a skinny GEMM: tile width and slice count that fill the SMs in one wave.
+void ltl_gemm_tc_plan_split(int M, int N, int K, int* bn, int* ksplit)
+{
+    const int mt = (M + BM - 1) / BM, sms = ltl_sm_count(), kb = (K + BK - 1) / BK;
+    *bn = 32;
+    const int tiles = mt * ((N + 31) / 32);
+    int s = tiles > 0 ? sms / tiles : 1;
+    if (s > 8) s = 8;
+    if (s > kb) s = kb;
+    if (s < 1) s = 1;
+    *ksplit = s;
+}
+
 // C[M,N] (c_dtype f32 or bf16, row-major) = A[M,K] B[N,K]^T + R.  bn = 0 picks the tile width.
 // epi = 1: SwiGLU epilogue (see the kernel), C is [M, N/2] bf16.
+// ksplit > 1: split-K, C receives ksplit fp32 partial matrices [ksplit][M][N] (bn should then be the
+// width the caller sized the grid for; see ltl_gemm_tc_plan_split).
 int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int c_dtype, int bn,
-                int epi, cudaStream_t s)
+                int epi, int ksplit, cudaStream_t s)
 {
+    if (ksplit > 1 && (c_dtype != LTL_F32 || R || epi))
+        return ltl_fail(LTL_ERR_ARG, "gemm_tc: split-K writes fp32 partial sums and takes no residual or epilogue");
     if (!A || !B || !C) return ltl_fail(LTL_ERR_NULL, "gemm_tc: null operand");
     if (!ltl_gemm_tc_supported(A, B, M, N, K))
         return ltl_fail(LTL_ERR_UNSUPPORTED, "gemm_tc: needs K %% 8 == 0 and 16-byte aligned operands (M=%d N=%d K=%d)", M, N, K);
@@ -344,9 +374,9 @@ int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int
     if (bn == 0) bn = pick_bn(M, N);
 #define TC_CASE(BNV)                                                                                     \
     if (bn == BNV) {                                                                                     \
-        if (epi == EPI_SWIGLU) return launch<BNV, bf16, EPI_SWIGLU>(A, B, C, nullptr, M, N, K, s);       \
-        if (c_dtype == LTL_F32) return launch<BNV, float, EPI_NONE>(A, B, C, R, M, N, K, s);             \
-        if (c_dtype == LTL_BF16) return launch<BNV, bf16, EPI_NONE>(A, B, C, R, M, N, K, s);             \
+        if (epi == EPI_SWIGLU) return launch<BNV, bf16, EPI_SWIGLU>(A, B, C, nullptr, M, N, K, 1, s);       \
+        if (c_dtype == LTL_F32) return launch<BNV, float, EPI_NONE>(A, B, C, R, M, N, K, ksplit, s);             \
+        if (c_dtype == LTL_BF16) return launch<BNV, bf16, EPI_NONE>(A, B, C, R, M, N, K, 1, s);             \
         return ltl_fail(LTL_ERR_DTYPE, "gemm_tc: output dtype %d", c_dtype);                             \
     }
     TC_CASE(32) TC_CASE(64) TC_CASE(128)

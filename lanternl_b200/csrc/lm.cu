@@ -79,12 +79,13 @@ struct luaTL_lm_s {
     int hist_cap = 0, prompt_cap = 0, out_cap = 0;
     int* d_err = nullptr;
     float* xlast = nullptr;
+    float* part = nullptr;       // split-K partial sums of the decode GEMMs [8][nseq_cap][D]
     std::map<int, GraphEntry> graphs;
     cudaEvent_t ev[4] = { nullptr, nullptr, nullptr, nullptr };
     float prefill_ms = 0, decode_ms = 0;
     int64_t launches = 0;
     int adam_alloc = 0;
-    int use_tc = 1, fuse_swiglu = 0;
+    int use_tc = 1, fuse_swiglu = 0, use_pdl = 1;
 };
 
 namespace {
@@ -218,7 +219,7 @@ int wgemm(LM* m, const void* A, int M, int K, int64_t w_off, int Nout, void* C, 
         g.b_rs = 1; g.b_cs = K;
         // bf16: activations [M, K] and the mirrored weight [Nout, K] are both K-major -> tensor cores
         if (m->use_tc && ltl_gemm_tc_supported(A, g.B, M, Nout, K))
-            return ltl_gemm_tc(A, g.B, C, R, M, Nout, K, c_dt, 0, epi, m->s);
+            return ltl_gemm_tc(A, g.B, C, R, M, Nout, K, c_dt, 0, epi, 1, m->s);
         if (epi) return ltl_fail(LTL_ERR_UNSUPPORTED, "lm: fused SwiGLU needs the tensor-core GEMM");
     }
     return ltl_gemm_simt(g, m->s);
@@ -505,6 +506,7 @@ int ensure_decode(LM* m, int nseq, int n_prompt, int n_new)
         DALLOC(m->d_next, (size_t)m->nseq_cap * 4, "next tokens"); DALLOC(m->d_err, 4, "error flag");
         DALLOC(m->d_win, (size_t)m->nseq_cap * m->T * 4, "window ids");
         DALLOC(m->xlast, (size_t)m->nseq_cap * m->D * 4, "last rows");
+        DALLOC(m->part, (size_t)8 * m->nseq_cap * m->D * 4, "split-K partial sums");
         LTL_CUDA("memset", cudaMemsetAsync(m->d_pos, 0, (size_t)m->nseq_cap * 4, m->s));
         LTL_CUDA("memset", cudaMemsetAsync(m->d_count, 0, (size_t)m->nseq_cap * 4, m->s));
         LTL_CUDA("memset", cudaMemsetAsync(m->d_err, 0, 4, m->s));
@@ -537,6 +539,55 @@ int ensure_decode(LM* m, int nseq, int n_prompt, int n_new)
     return LTL_OK;
 }
 
+// Decode step of the bf16 tensor-core path.  The two residual GEMMs of a layer (attention output
+// and FFN down projection: N = D, few tiles) run split-K so that every SM pulls weights; their
+// fp32 partial sums are added to the residual stream, in a fixed order, by the RMSNorm kernel that
+// follows anyway.  Launches per step: 2 + 6 L.
+int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t* d_out, int out_stride, int pick,
+                      int32_t* hist, int hist_stride, int hist_base)
+{
+    const int D = m->D, F = m->F, V = m->V, L = m->L, H = m->H, hd = m->hd;
+    const size_t e = 2;
+    Act& a = m->dec;
+    float* x = a.res;
+    const int32_t* pos = m->d_pos + slot0;
+    const size_t cl = (size_t)m->nseq_cap * H * m->T * hd * e;
+    const size_t cslot = (size_t)slot0 * H * m->T * hd * e;
+    // Every kernel of the step is launched with programmatic stream serialization: each calls
+    // griddepcontrol.wait before touching its inputs, so only launch latency and prologues overlap.
+    struct PdlScope { bool prev; PdlScope(bool on) : prev(ltl_pdl_enabled()) { ltl_pdl_set(on); } ~PdlScope() { ltl_pdl_set(prev); } } pdl(m->use_pdl);
+    int bn_o, s_o, bn_d, s_d;
+    ltl_gemm_tc_plan_split(nseq, D, D, &bn_o, &s_o);
+    ltl_gemm_tc_plan_split(nseq, D, F, &bn_d, &s_d);
+    LTL_TRY(ltl_lm_embed_rmsnorm(d_tok, m->Wb + m->off_emb, LTL_BF16, x, m->W + m->lo[0].ln1, a.h1, LTL_BF16, nseq, D, V,
+                                 m->c.eps, m->s));
+    m->launches++;
+    for (int l = 0; l < L; ++l) {
+        const LayerOff& o = m->lo[l];
+        void* kcl = (char*)m->kc + l * cl + cslot;
+        void* vcl = (char*)m->vc + l * cl + cslot;
+        LTL_TRY(ltl_gemm_tc(a.h1, m->Wb + o.wqkv, a.qkv, nullptr, nseq, 3 * D, D, LTL_BF16, 0, 0, 1, m->s));
+        LTL_TRY(ltl_decode_attn(a.qkv, kcl, vcl, a.attn, pos, nseq, H, hd, m->T, m->scale, LTL_BF16, m->splits, m->ws,
+                                m->rope_tab, m->c.rope_interleaved, m->c.use_rope, m->d_err, m->s));
+        LTL_TRY(ltl_gemm_tc(a.attn, m->Wb + o.wo, m->part, nullptr, nseq, D, D, LTL_F32, bn_o, 0, s_o, m->s));
+        LTL_TRY(ltl_lm_residual_rmsnorm(x, m->part, s_o, m->W + o.ln2, a.h2, LTL_BF16, nseq, D, m->c.eps, m->s));
+        LTL_TRY(ltl_gemm_tc(a.h2, m->Wb + o.w13, a.hs, nullptr, nseq, 2 * F, D, LTL_BF16, 0, 1, 1, m->s));
+        LTL_TRY(ltl_gemm_tc(a.hs, m->Wb + o.w2, m->part, nullptr, nseq, D, F, LTL_F32, bn_d, 0, s_d, m->s));
+        const bool last = l + 1 == L;
+        LTL_TRY(ltl_lm_residual_rmsnorm(x, m->part, s_d, m->W + (last ? m->off_lnf : m->lo[l + 1].ln1),
+                                        last ? a.hf : a.h1, LTL_BF16, nseq, D, m->c.eps, m->s));
+        m->launches += 7 + (m->splits > 1 ? 1 : 0);
+    }
+    LTL_TRY(ltl_gemm_tc(a.hf, m->Wb + (m->c.tie ? m->off_emb : m->off_head), a.logits, nullptr, nseq, V, D, LTL_F32, 0, 0, 1, m->s));
+    m->launches++;
+    if (pick) {
+        LTL_TRY(ltl_pick_advance(a.logits, nseq, V, m->d_next + slot0, d_out, out_stride, m->d_count + slot0,
+                                 m->d_pos + slot0, hist, hist_stride, hist_base, m->s));
+        m->launches++;
+    }
+    return LTL_OK;
+}
+
 // One token for every sequence: consumes d_next / d_pos, appends K/V, picks the next token.
 // Everything it reads that changes between steps lives in device memory, so the launch
 // sequence can be captured once and replayed.
@@ -544,6 +595,8 @@ int decode_step(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t* d_out
                 int32_t* hist = nullptr, int hist_stride = 0, int hist_base = 0)
 {
     const int D = m->D, F = m->F, V = m->V, L = m->L, H = m->H, hd = m->hd, adt = m->adt;
+    if (m->fuse_swiglu && ltl_gemm_tc_supported(m->dec.h1, m->Wb, nseq, D, D) && F % 8 == 0 && D % 8 == 0)
+        return decode_step_split(m, nseq, slot0, d_tok, d_out, out_stride, pick, hist, hist_stride, hist_base);
     const size_t e = esz(adt);
     Act& a = m->dec;
     float* x = a.res;
@@ -720,6 +773,8 @@ luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
         const char* e = getenv("LUATL_DISABLE_TC");
         m->use_tc = !(e && e[0] == '1');
         m->fuse_swiglu = m->use_tc && m->adt == LTL_BF16;
+        const char* p = getenv("LUATL_PDL");
+        m->use_pdl = !(p && p[0] == '0');
     }
     layout_params(m);
     int rc = LTL_OK;
@@ -749,7 +804,7 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
     free_act(m->train); free_act(m->infer); free_act(m->dec);
     void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
                      m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
-                     m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast };
+                     m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part };
     for (void* p : ptrs) if (p) cudaFree(p);
     for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
     cudaGetLastError();

@@ -85,6 +85,113 @@ int ltl_lm_rmsnorm(const float* x, const float* gain, void* out, int out_dtype, 
     return ltl_check_launch("lm_rmsnorm");
 }
 
+
+// Consumer of the split-K GEMMs: x += partial[0] + partial[1] + ... (fixed order, so the result
+// does not depend on scheduling), then RMSNorm of the updated row.  One warp per row.
+template <typename TO>
+__global__ void __launch_bounds__(128)
+lm_residual_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ partial, int nparts,
+                           const float* __restrict__ gain, TO* __restrict__ out, int rows, int cols, float eps)
+{
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    float* xr = x + (size_t)row * cols;
+    const size_t slice = (size_t)rows * cols;
+    float ss = 0.0f;
+    for (int c = lane * 4; c < cols; c += 128) {
+        float4 v = *reinterpret_cast<const float4*>(xr + c);
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int p = 0; p < nparts; ++p) {
+            const float4 q = *reinterpret_cast<const float4*>(partial + p * slice + (size_t)row * cols + c);
+            acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+        }
+        v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;
+        *reinterpret_cast<float4*>(xr + c) = v;
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+    ss = warp_sum(ss);
+    const float sc = 1.0f / sqrtf(ss / (float)cols + eps);
+    TO* orow = out + (size_t)row * cols;
+    for (int c = lane * 4; c < cols; c += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + c);   // written by this lane above
+        const float4 g = *reinterpret_cast<const float4*>(gain + c);
+        Cvt<TO>::st(orow, c, v.x * sc * g.x);
+        Cvt<TO>::st(orow, c + 1, v.y * sc * g.y);
+        Cvt<TO>::st(orow, c + 2, v.z * sc * g.z);
+        Cvt<TO>::st(orow, c + 3, v.w * sc * g.w);
+    }
+}
+
+int ltl_lm_residual_rmsnorm(float* x, const float* partial, int nparts, const float* gain, void* out,
+                            int out_dtype, int rows, int cols, float eps, cudaStream_t s)
+{
+    if (!x || !partial || !gain || !out) return ltl_fail(LTL_ERR_NULL, "lm_residual_rmsnorm: null pointer");
+    if (cols % 4 || !aligned16(x) || !aligned16(gain) || !aligned16(partial))
+        return ltl_fail(LTL_ERR_SHAPE, "lm_residual_rmsnorm: width %d must be a multiple of 4 and 16-byte aligned", cols);
+    if (rows <= 0) return LTL_OK;
+    const int grid = (rows + 3) / 4;
+    if (out_dtype == LTL_F32) lm_residual_rmsnorm_kernel<float><<<grid, 128, 0, s>>>(x, partial, nparts, gain, (float*)out, rows, cols, eps);
+    else if (out_dtype == LTL_BF16) LTL_CUDA("lm_residual_rmsnorm launch", ltl_launch(lm_residual_rmsnorm_kernel<bf16>, dim3(grid), dim3(128), 0, s, ltl_pdl_enabled(), x, partial, nparts, gain, (bf16*)out, rows, cols, eps));
+    else return ltl_fail(LTL_ERR_DTYPE, "lm_residual_rmsnorm: out dtype %d", out_dtype);
+    return ltl_check_launch("lm_residual_rmsnorm");
+}
+
+// Embedding gather into the residual stream fused with the first RMSNorm (one warp per row).
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(128)
+lm_embed_rmsnorm_kernel(const int32_t* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ x,
+                        const float* __restrict__ gain, TO* __restrict__ out, int rows, int cols, int vocab, float eps)
+{
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int t = ids[row];
+    const bool okid = t >= 0 && t < vocab;
+    float* xr = x + (size_t)row * cols;
+    float ss = 0.0f;
+    for (int c = lane * 4; c < cols; c += 128) {
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (okid) {
+            const TW* src = table + (size_t)t * cols + c;
+            v = make_float4(Cvt<TW>::ld(src, 0), Cvt<TW>::ld(src, 1), Cvt<TW>::ld(src, 2), Cvt<TW>::ld(src, 3));
+        }
+        *reinterpret_cast<float4*>(xr + c) = v;
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+    ss = warp_sum(ss);
+    const float sc = 1.0f / sqrtf(ss / (float)cols + eps);
+    TO* orow = out + (size_t)row * cols;
+    for (int c = lane * 4; c < cols; c += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + c);
+        const float4 g = *reinterpret_cast<const float4*>(gain + c);
+        Cvt<TO>::st(orow, c, v.x * sc * g.x);
+        Cvt<TO>::st(orow, c + 1, v.y * sc * g.y);
+        Cvt<TO>::st(orow, c + 2, v.z * sc * g.z);
+        Cvt<TO>::st(orow, c + 3, v.w * sc * g.w);
+    }
+}
+
+int ltl_lm_embed_rmsnorm(const int32_t* ids, const void* table, int table_dtype, float* x, const float* gain,
+                         void* out, int out_dtype, int rows, int cols, int vocab, float eps, cudaStream_t s)
+{
+    if (!ids || !table || !x || !gain || !out) return ltl_fail(LTL_ERR_NULL, "lm_embed_rmsnorm: null pointer");
+    if (cols % 4 || !aligned16(x) || !aligned16(gain))
+        return ltl_fail(LTL_ERR_SHAPE, "lm_embed_rmsnorm: width %d must be a multiple of 4 and 16-byte aligned", cols);
+    if (rows <= 0) return LTL_OK;
+    const int grid = (rows + 3) / 4;
+    if (table_dtype == LTL_F32 && out_dtype == LTL_F32)
+        lm_embed_rmsnorm_kernel<float, float><<<grid, 128, 0, s>>>(ids, (const float*)table, x, gain, (float*)out, rows, cols, vocab, eps);
+    else if (table_dtype == LTL_BF16 && out_dtype == LTL_BF16)
+        LTL_CUDA("lm_embed_rmsnorm launch", ltl_launch(lm_embed_rmsnorm_kernel<bf16, bf16>, dim3(grid), dim3(128), 0, s, ltl_pdl_enabled(), ids, (const bf16*)table, x, gain, (bf16*)out, rows, cols, vocab, eps));
+    else return ltl_fail(LTL_ERR_DTYPE, "lm_embed_rmsnorm: table dtype %d / out dtype %d", table_dtype, out_dtype);
+    return ltl_check_launch("lm_embed_rmsnorm");
+}
+
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
@@ -294,7 +401,7 @@ decode_attn_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict_
 // The new token (RoPE, cache append, its own score) is handled as in the register kernel.
 // ------------------------------------------------------------------------------------------
 namespace bulk {
-constexpr int KT = 64, STG = 4, ROWB = 128;
+constexpr int KT = 64, ROWB = 128;
 constexpr uint32_t SPIN = 1u << 22;
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity)
@@ -313,6 +420,7 @@ __device__ __forceinline__ void copy(void* dst, const void* src, uint32_t bytes,
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
 }
+template <int STG>
 struct Smem {
     alignas(128) uint8_t k[STG][KT * ROWB];
     alignas(128) uint8_t v[STG][KT * ROWB];
@@ -322,7 +430,7 @@ struct Smem {
 };
 }  // namespace bulk
 
-template <typename T, int HD>
+template <typename T, int HD, int STG>
 __global__ void __launch_bounds__(128)
 decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
                         T* __restrict__ out, const int32_t* __restrict__ pos, int H, int ctx, float scale,
@@ -335,9 +443,11 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     constexpr int GL = HD / N;               // 8 chunks per row
     constexpr int EPW = 4 / sizeof(T);       // elements per 4-byte word (dims per lane in P V)
     extern __shared__ uint8_t smem_raw[];
-    Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    Smem<STG>& sm = *reinterpret_cast<Smem<STG>*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     const int h = blockIdx.x, b = blockIdx.y, z = blockIdx.z;
     const int D = H * HD, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_trigger();
+    pdl_wait();
     int ps = pos[b];
     const bool in_range = ps >= 0 && ps < ctx;
     if (!in_range) { if (err && tid == 0) *err = 1; ps = ps < 0 ? 0 : ctx; }
@@ -530,16 +640,23 @@ static int launch_decode_attn(const void* qkv, void* kc, void* vc, void* out,
     if constexpr (HD * sizeof(T) == 128 && HD <= 64) {
         // 128-byte rows: the bulk-copy staged kernel (LUATL_ATTN_REGS=1 selects the register kernel)
         static const bool use_regs = [] { const char* e = getenv("LUATL_ATTN_REGS"); return e && e[0] == '1'; }();
+        static const int stages = [] { const char* e = getenv("LUATL_ATTN_STAGES"); return e ? atoi(e) : 2; }();
         if (!use_regs) {
-            const size_t smem = sizeof(bulk::Smem) + 128;
-            static bool attr = false;
-            if (!attr) {
-                LTL_CUDA("decode_attn attr", cudaFuncSetAttribute(decode_attn_bulk_kernel<T, HD>,
-                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                attr = true;
+#define BULK_LAUNCH(STG)                                                                                           \
+            {                                                                                                      \
+                const size_t smem = sizeof(bulk::Smem<STG>) + 128;                                                 \
+                static bool attr = false;                                                                          \
+                if (!attr) {                                                                                       \
+                    LTL_CUDA("decode_attn attr", cudaFuncSetAttribute(decode_attn_bulk_kernel<T, HD, STG>,         \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                             \
+                    attr = true;                                                                                   \
+                }                                                                                                  \
+                LTL_CUDA("decode_attn launch", ltl_launch(decode_attn_bulk_kernel<T, HD, STG>, grid, dim3(128), smem, s,     \
+                    ltl_pdl_enabled() && splits == 1, (const T*)qkv, (T*)kc, (T*)vc, (T*)out, pos, H, ctx, scale,   \
+                    splits, scratch, cs, interleaved, use_rope, err));                                             \
             }
-            decode_attn_bulk_kernel<T, HD><<<grid, 128, smem, s>>>((const T*)qkv, (T*)kc, (T*)vc, (T*)out, pos, H, ctx,
-                                                                   scale, splits, scratch, cs, interleaved, use_rope, err);
+            if (stages <= 1) BULK_LAUNCH(1) else if (stages == 2) BULK_LAUNCH(2) else BULK_LAUNCH(4)
+#undef BULK_LAUNCH
             if (splits > 1) {
                 dim3 g2(H, B);
                 decode_attn_combine_kernel<T, HD><<<g2, HD < 32 ? 32 : HD, 0, s>>>(scratch, (T*)out, H, splits);
@@ -593,13 +710,25 @@ __global__ void pick_advance_kernel(const float* __restrict__ logits, int V, int
 {
     __shared__ float red_v[32];
     __shared__ int red_i[32];
+    pdl_trigger();
+    pdl_wait();
     const int b = blockIdx.x;
     const float* row = logits + (size_t)b * V;
     float best = -INFINITY;
     int bi = 0x7FFFFFFF;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best) { best = v; bi = i; }
+    if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) {      // ascending per thread: first maximum wins
+            const float4 q = *reinterpret_cast<const float4*>(row + i);
+            if (q.x > best) { best = q.x; bi = i; }
+            if (q.y > best) { best = q.y; bi = i + 1; }
+            if (q.z > best) { best = q.z; bi = i + 2; }
+            if (q.w > best) { best = q.w; bi = i + 3; }
+        }
+    } else {
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float v = row[i];
+            if (v > best) { best = v; bi = i; }
+        }
     }
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
 #pragma unroll
@@ -637,7 +766,7 @@ int ltl_pick_advance(const float* logits, int B, int V, int32_t* next, int32_t* 
 {
     if (!logits || !next || !count || !pos) return ltl_fail(LTL_ERR_NULL, "pick_advance: null pointer");
     if (B <= 0) return LTL_OK;
-    pick_advance_kernel<<<B, 256, 0, s>>>(logits, V, next, out_ids, out_stride, count, pos, hist, hist_stride, hist_base);
+    LTL_CUDA("pick_advance launch", ltl_launch(pick_advance_kernel, dim3(B), dim3(V >= 4096 ? 1024 : 256), 0, s, ltl_pdl_enabled(), logits, V, next, out_ids, out_stride, count, pos, hist, hist_stride, hist_base));
     return ltl_check_launch("pick_advance");
 }
 

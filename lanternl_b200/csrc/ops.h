@@ -80,6 +80,13 @@ int ltl_lm_embed(const int32_t* ids, const void* table, int table_dtype, float* 
 // out[r, :] = rmsnorm(x[r, :]) * gain, x and gain fp32, out f32 or bf16.
 int ltl_lm_rmsnorm(const float* x, const float* gain, void* out, int out_dtype, int rows, int cols,
                    float eps, cudaStream_t s);
+// x[r, :] += sum_s partial[s][r, :] (s = 0 .. nparts-1 in order; slices rows*cols apart), then
+// out[r, :] = rmsnorm(x[r, :]) * gain.  The consumer side of the split-K GEMMs.
+int ltl_lm_residual_rmsnorm(float* x, const float* partial, int nparts, const float* gain, void* out,
+                            int out_dtype, int rows, int cols, float eps, cudaStream_t s);
+// x[r, :] = table[ids[r], :] and out[r, :] = rmsnorm(x[r, :]) * gain in one launch.
+int ltl_lm_embed_rmsnorm(const int32_t* ids, const void* table, int table_dtype, float* x, const float* gain,
+                         void* out, int out_dtype, int rows, int cols, int vocab, float eps, cudaStream_t s);
 // Prefill: copy rotated k and v of rows [B, T] of qkv [B*T, 3D] into the caches at 0..T-1.
 int ltl_kv_store(const void* qkv, void* kcache, void* vcache, int B, int T, int H, int hd, int ctx,
                  int dtype, cudaStream_t s);
@@ -110,6 +117,8 @@ int ltl_gather_last_rows(const float* x, float* out, int B, int T, int cols, int
 // ---- tcgen05 / TMA GEMM (gemm_tc.cu): C[M,N] = A[M,K] B[N,K]^T + R, bf16 in, fp32 accumulate ----
 bool ltl_gemm_tc_supported(const void* A, const void* B, int M, int N, int K);
 // epi = 1: B rows interleave gate/up, C [M, N/2] bf16 = silu(gate) * up (R ignored).
+// ksplit > 1: C receives ksplit fp32 partial matrices [ksplit][M][N] (no residual, no epilogue).
 int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int c_dtype,
-                int bn, int epi, cudaStream_t s);
+                int bn, int epi, int ksplit, cudaStream_t s);
+void ltl_gemm_tc_plan_split(int M, int N, int K, int* bn, int* ksplit);
 int ltl_gemm_tc_check(cudaStream_t s);

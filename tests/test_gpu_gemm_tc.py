@@ -77,3 +77,22 @@ def test_swiglu_epilogue(M, F, K, tile):
     # one bf16 ulp of the output, plus rare flips of the rounded gate / up
     assert np.abs(got - ref).max() <= 2 ** -7 * np.abs(ref).max()
     assert np.median(np.abs(got - ref)) <= 2 ** -9 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("M,N,K,ks", [(256, 512, 512, 4), (256, 512, 1408, 4), (1, 512, 1408, 8), (130, 96, 200, 8), (64, 64, 64, 3)])
+def test_split_k_partials_sum_to_the_product(M, N, K, ks):
+    """Split-K: slice z writes its partial sums to C + z*M*N; slices past the last k-block are zero."""
+    a = bf16_round(synth.normal(21, 0, M * K).reshape(M, K).astype(np.float32))
+    b = bf16_round((synth.normal(22, 0, N * K) * 0.1).reshape(N, K).astype(np.float32))
+    A, B, Cc = bf16_dev(a), bf16_dev(b), ad.TensorView(ks * M, N, _lib.F32)
+    Cc.upload(np.full(ks * M * N, 7.0, np.float32))          # must be overwritten, not accumulated
+    _lib.call("luaTL_gemm_bf16_tc", A.data, B.data, Cc.data, None, M, N, K, _lib.F32, 32 | (ks << 20))
+    parts = Cc.download().reshape(ks, M, N).astype(np.float64)
+    ref = a.astype(np.float64) @ b.astype(np.float64).T
+    assert rel_err(parts.sum(0), ref) < 1e-5
+    kb = (K + 63) // 64
+    per = (kb + ks - 1) // ks
+    for z in range(ks):
+        lo, hi = z * per * 64, min(K, (z + 1) * per * 64)
+        want = a[:, lo:hi].astype(np.float64) @ b[:, lo:hi].astype(np.float64).T if lo < K else np.zeros((M, N))
+        assert rel_err(parts[z], want) < 1e-5 or np.abs(parts[z] - want).max() < 1e-6
