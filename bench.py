@@ -201,11 +201,20 @@ def run_decode(args, dist):
     if not np.array_equal(out_host, ids_dev):
         raise SystemExit("bench: host-path and device-path generations differ")
 
+    # the dominant kernel alone: decode attention at the mean cache length of the run (and at the last)
+    attn = {}
+    ms = C.c_float()
+    for n in ((N_PROMPT + 1 + N_PROMPT + N_NEW - 1) // 2, N_PROMPT + N_NEW - 1):
+        _lib.call("luaTL_lm_time_decode_attn", m._h, nseq, n, 20, C.byref(ms))
+        nbytes = nseq * cfg["heads"] * (cfg["dim"] // cfg["heads"]) * 2 * 2 * (n + 1)      # K and V rows, bf16
+        attn[n] = dict(us=ms.value * 1e3, bytes=nbytes, gbs=nbytes / (ms.value * 1e-3) / 1e9)
     dev_ms, dec_ms, pre_ms, e2e_ms = dist.max(dev_ms), dist.max(dec_ms), dist.max(pre_ms), dist.max(e2e_ms)
     tokens = NSEQ_TOTAL * N_NEW * args.steps
     pk = peaks()
     alg = decode_bytes(cfg, m.nparams(), nseq, N_PROMPT, N_NEW) * args.steps
-    achieved = alg / (dec_ms * 1e-3) / 1e9
+    phase_gbs = alg / (dec_ms * 1e-3) / 1e9
+    n_mid = sorted(attn)[0]
+    achieved = attn[n_mid]["gbs"]
     line = dict(
         metric="decode_tokens_per_s", value=tokens / (dev_ms * 1e-3), unit="tokens/s", n_gpus=dist.world,
         steps=args.steps, warmup=args.warmup, ms_per_step=dev_ms / args.steps, higher_is_better=True,
@@ -218,8 +227,15 @@ def run_decode(args, dist):
                  d2h_bytes_per_step=int(out_host.nbytes) * dist.world),
         gpu_launches=int(launches),
         roofline=dict(bound="hbm", achieved=achieved, peak=pk["hbm_gbs"], unit="GB/s", frac=achieved / pk["hbm_gbs"],
-                      traffic=None, kernel="decode phase (all kernels of the 511 decode steps)", peak_source=pk["source"],
-                      algorithmic_bytes_per_step=alg // args.steps),
+                      traffic=None, peak_source=pk["source"],
+                      kernel=f"decode_attn_bulk_kernel<bf16,64>, {nseq} sequences at cache length {n_mid} (mean of the run), "
+                             "one launch per layer, CUDA events on the launching stream",
+                      algorithmic_bytes_per_launch=attn[n_mid]["bytes"], us_per_launch=attn[n_mid]["us"],
+                      at_last_step={k: attn[sorted(attn)[1]][k] for k in ("us", "bytes", "gbs")},
+                      decode_phase=dict(note="all kernels of the 511 decode steps against the bytes a step must move "
+                                             "(bf16 weights once + K/V of every cached position)",
+                                        algorithmic_bytes_per_step=alg // args.steps, achieved=phase_gbs,
+                                        frac=phase_gbs / pk["hbm_gbs"])),
         phases=dict(prefill_ms=pre_ms / args.steps, decode_ms=dec_ms / args.steps,
                     decode_only_tokens_per_s=NSEQ_TOTAL * (N_NEW - 1) * args.steps / (dec_ms * 1e-3)),
         wall_ms_per_step=wall_ms / args.steps, clocks=clk)
@@ -317,9 +333,44 @@ def cpu_sample(threads, n_new=24):
         f"tokens through the KV-cache step, {dt:.1f} s; tokens/s scaled to the 128+512 workload by steps"
 
 
+def run_reference_train(args, dist):
+    """The reference's own fp32 CUDA path (its unmodified kernels in oracle/_ref, driven op for op as its
+    Lua model queues them) on configs[1]: zero grads, forward + backward, clip + AdamW - its only GPU
+    optimizer.  Timed with the reference's own CUDA events around each Program."""
+    from lanternl_b200 import synth
+    from oracle import ref_driver
+    cfg = TRAIN
+    if not ref_driver.available():
+        return dict(impl="reference", unavailable="oracle/_ref/luaTL_ref.so was not built (reference tree absent at build time)")
+    B, T = TRAIN_B, cfg["max_seq"]
+    r = ref_driver.RefModel(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], T, B)
+    r.load_flat(synth.init_params(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], seed=0))
+    ids = synth.zipf_ids(1, B * T, cfg["vocab"]).reshape(B, T)
+    tgt = np.full_like(ids, -1)
+    tgt[:, :-1] = ids[:, 1:]
+    for s in range(args.warmup):
+        r.loss_grad(ids, tgt)
+        r.adamw_step(1e-3, s + 1)
+    ms, t0 = 0.0, time.perf_counter()
+    for s in range(args.steps):
+        ms += r.loss_grad(ids, tgt)["ms"]
+        ms += r.adamw_step(1e-3, args.warmup + s + 1)
+    wall = (time.perf_counter() - t0) * 1e3
+    v = B * T * args.steps / (wall * 1e-3)
+    return dict(impl="reference", metric="train_tokens_per_s", value=v, unit="tokens/s", n_gpus=1, steps=args.steps,
+                warmup=args.warmup, ms_per_step=wall / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None,
+                dtype="f32", data="synthetic",
+                config=dict(workload="configs[1] training step on the reference's own CUDA kernels (sm_100 build), "
+                                     "op list of ai/gpu/gpu_transformer.lua, AdamW", ops_per_step=r.p_step.size() + r.p_opt.size()),
+                device_ms_per_step=ms / args.steps, gpu_launches=0,
+                e2e=dict(value=v, unit="tokens/s", h2d_bytes_per_step=int(ids.nbytes + tgt.nbytes), d2h_bytes_per_step=4 + B * T * 4))
+
+
 def run_reference(args, dist):
     if dist.rank != 0:
         return None
+    if args.workload == "train":
+        return run_reference_train(args, dist)
     threads = min(os.cpu_count() or 1, NSEQ_TOTAL)
     vals = []
     for _ in range(args.warmup):

@@ -282,6 +282,11 @@ int luaTL_lm_generate(luaTL_lm_t* m, const int32_t* prompts, int nseq, int n_pro
 /* Same with prompts and out on the device (nothing crosses PCIe). */
 int luaTL_lm_generate_dev(luaTL_lm_t* m, const int32_t* d_prompts, int nseq, int n_prompt, int n_new,
                           int32_t* d_out, luaTL_lm_result_t* timing);
+/* Measurement aid: average device time (CUDA events on the library stream, 3 warm-up rounds) of one
+ * decode-attention launch with every sequence at `cache_len` cached positions; one round = one
+ * launch per layer, each over its own layer of the cache (inputs larger than L2).  Leaves the
+ * generation state reset. */
+int luaTL_lm_time_decode_attn(luaTL_lm_t* m, int nseq, int cache_len, int iters, float* ms_per_launch);
 /* Device time (ms) and kernel launches of the last prefill and decode phases. */
 int luaTL_lm_last_timing(luaTL_lm_t* m, float* prefill_ms, float* decode_ms, int64_t* launches);
 

@@ -34,16 +34,25 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
                  const TI* __restrict__ bias, const TC* R, int M, int N, int K,
                  long long a_rs, long long a_cs, long long b_rs, long long b_cs,
                  long long c_rs, long long c_cs, long long a_bs, long long b_bs, long long c_bs,
-                 float alpha, float beta, int post_op)
+                 float alpha, float beta, int post_op, int ksplit)
 {
     __shared__ __align__(16) float As[BK][BM + PAD];
     __shared__ __align__(16) float Bs[BK][BN + PAD];
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    A += (long long)blockIdx.z * a_bs;
-    B += (long long)blockIdx.z * b_bs;
-    C += (long long)blockIdx.z * c_bs;
-    if (R) R += (long long)blockIdx.z * c_bs;
+    // ksplit > 1 (batch == 1 only): blockIdx.z selects a slice of K and the partial product is
+    // added to C with atomics (the caller guarantees beta == 1, fp32 C, no bias / activation / R).
+    int k_begin = 0, k_end = K;
+    if (ksplit > 1) {
+        const int per = ((K + ksplit - 1) / ksplit + BK - 1) / BK * BK;
+        k_begin = blockIdx.z * per;
+        k_end = min(K, k_begin + per);
+    } else {
+        A += (long long)blockIdx.z * a_bs;
+        B += (long long)blockIdx.z * b_bs;
+        C += (long long)blockIdx.z * c_bs;
+        if (R) R += (long long)blockIdx.z * c_bs;
+    }
     const int tx = tid & 15, ty = tid >> 4;
     const bool a_kfast = (a_cs == 1);      // k contiguous in memory
     const bool b_nfast = (b_cs == 1);      // n contiguous in memory
@@ -54,19 +63,19 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
 
-    for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int k0 = k_begin; k0 < k_end; k0 += BK) {
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
             int mm, kk;
             if (a_kfast) { kk = tid & 15; mm = (tid >> 4) + 16 * p; }
             else         { mm = tid & 63; kk = (tid >> 6) + 4 * p; }
             const int gm = m0 + mm, gk = k0 + kk;
-            As[kk][mm] = (gm < M && gk < K) ? Cvt<TI>::ld(A, (size_t)(gm * a_rs + gk * a_cs)) : 0.0f;
+            As[kk][mm] = (gm < M && gk < k_end) ? Cvt<TI>::ld(A, (size_t)(gm * a_rs + gk * a_cs)) : 0.0f;
             int nn, kb;
             if (b_nfast) { nn = tid & 63; kb = (tid >> 6) + 4 * p; }
             else         { kb = tid & 15; nn = (tid >> 4) + 16 * p; }
             const int gn = n0 + nn, gkb = k0 + kb;
-            Bs[kb][nn] = (gn < N && gkb < K) ? Cvt<TI>::ld(B, (size_t)(gkb * b_rs + gn * b_cs)) : 0.0f;
+            Bs[kb][nn] = (gn < N && gkb < k_end) ? Cvt<TI>::ld(B, (size_t)(gkb * b_rs + gn * b_cs)) : 0.0f;
         }
         __syncthreads();
 #pragma unroll
@@ -90,6 +99,10 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
             const int gn = n0 + tx * 4 + j;
             if (gn >= N) continue;
             const size_t ci = (size_t)(gm * c_rs + gn * c_cs);
+            if (ksplit > 1) {
+                if (sizeof(TC) == 4) atomicAdd(reinterpret_cast<float*>(C) + ci, alpha * acc[i][j]);
+                continue;
+            }
             float v = alpha * acc[i][j];
             if (bias) v += Cvt<TI>::ld(bias, gn);
             v = act_apply(post_op, v);
@@ -103,11 +116,22 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
 template <typename TI, typename TC>
 int launch(const GemmDesc& g, cudaStream_t s)
 {
-    dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM, g.batch);
+    // Weight-gradient shape (dW += X^T dY): a small output with a very long reduction would run on a
+    // handful of CTAs; spread K over the SMs and accumulate with fp32 atomics instead.
+    int ksplit = 1;
+    const int tiles = ((g.N + BN - 1) / BN) * ((g.M + BM - 1) / BM);
+    if (g.batch == 1 && g.beta == 1.0f && !g.bias && !g.R && g.post_op == 0 && sizeof(TC) == 4 &&
+        tiles * 2 <= ltl_sm_count() && g.K >= 8 * BK) {
+        ksplit = (2 * ltl_sm_count() + tiles - 1) / tiles;
+        if (ksplit > g.K / (2 * BK)) ksplit = g.K / (2 * BK);
+        if (ksplit > 64) ksplit = 64;
+        if (ksplit < 1) ksplit = 1;
+    }
+    dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM, ksplit > 1 ? ksplit : g.batch);
     gemm_simt_kernel<TI, TC><<<grid, 256, 0, s>>>(
         (const TI*)g.A, (const TI*)g.B, (TC*)g.C, (const TI*)g.bias, (const TC*)g.R, g.M, g.N, g.K,
         g.a_rs, g.a_cs, g.b_rs, g.b_cs, g.c_rs, g.c_cs, g.a_bs, g.b_bs, g.c_bs, g.alpha, g.beta,
-        g.post_op);
+        g.post_op, ksplit);
     return ltl_check_launch("gemm");
 }
 

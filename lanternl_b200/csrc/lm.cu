@@ -1014,6 +1014,36 @@ int luaTL_lm_generate(luaTL_lm_t* m, const int32_t* prompts, int nseq, int n_pro
     return LTL_OK;
 }
 
+int luaTL_lm_time_decode_attn(luaTL_lm_t* m, int nseq, int cache_len, int iters, float* ms_per_launch)
+{
+    if (!m || !ms_per_launch) return ltl_fail(LTL_ERR_NULL, "lm_time_decode_attn: null pointer");
+    if (nseq < 1 || iters < 1 || cache_len < 0 || cache_len >= m->T)
+        return ltl_fail(LTL_ERR_ARG, "lm_time_decode_attn: need 0 <= cache_len < max_seq, nseq >= 1, iters >= 1");
+    LTL_TRY(ensure_decode(m, nseq, 0, 0));
+    const size_t e = esz(m->adt);
+    const size_t cl = (size_t)m->nseq_cap * m->H * m->T * m->hd * e;
+    LTL_TRY(ltl_fill_i32(m->d_pos, nseq, cache_len, m->s));
+    auto round = [&]() -> int {
+        for (int l = 0; l < m->L; ++l)
+            LTL_TRY(ltl_decode_attn(m->dec.qkv, (char*)m->kc + l * cl, (char*)m->vc + l * cl, m->dec.attn, m->d_pos, nseq,
+                                    m->H, m->hd, m->T, m->scale, m->adt, m->splits, m->ws, m->rope_tab,
+                                    m->c.rope_interleaved, m->c.use_rope, m->d_err, m->s));
+        return LTL_OK;
+    };
+    for (int w = 0; w < 3; ++w) LTL_TRY(round());
+    LTL_CUDA("event", cudaEventRecord(m->ev[0], m->s));
+    for (int i = 0; i < iters; ++i) LTL_TRY(round());
+    LTL_CUDA("event", cudaEventRecord(m->ev[1], m->s));
+    LTL_CUDA("sync", cudaStreamSynchronize(m->s));
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, m->ev[0], m->ev[1]);
+    *ms_per_launch = ms / (float)(iters * m->L);
+    LTL_CUDA("memset", cudaMemsetAsync(m->d_pos, 0, (size_t)m->nseq_cap * 4, m->s));
+    LTL_CUDA("memset", cudaMemsetAsync(m->d_err, 0, 4, m->s));
+    LTL_CUDA("sync", cudaStreamSynchronize(m->s));
+    return LTL_OK;
+}
+
 int luaTL_lm_last_timing(luaTL_lm_t* m, float* prefill_ms, float* decode_ms, int64_t* launches)
 {
     if (!m) return ltl_fail(LTL_ERR_NULL, "lm_last_timing: null model");
