@@ -165,6 +165,16 @@ int luaTL_gemm(const void* A, const void* B, void* C, const void* bias, const vo
 int luaTL_rmsnorm(const void* x, const void* w, void* out, int rows, int cols, float eps, int dtype);     /* core.cu:2329 */
 int luaTL_rmsnorm_bwd(const void* x, const void* gamma, const void* dy, void* dx, float* dgamma,
                       int rows, int cols, float eps, int dtype);                                          /* train.cu:1096 */
+/* No counterpart in the reference.  Same result as luaTL_rmsnorm_bwd, but allocates nothing: the
+ * per-warp dgamma partials go to a fixed 4.6 MB array inside the library's device image instead of
+ * a cudaMalloc'ed workspace.  For callers that cannot allocate when they need a gradient (all device
+ * memory already handed to their own arena, loops that cannot take cudaMalloc's device
+ * synchronisation).  Limits: with dgamma, rows of at most 1024 columns on a
+ * 148-SM GPU (LUATL_ERR_CAPACITY beyond); every call shares the array, so calls that overlap on the
+ * GPU race; the first call on a device looks the array's address up and should come before any
+ * stream capture. */
+int luaTL_rmsnorm_bwd_noalloc(const void* x, const void* gamma, const void* dy, void* dx, float* dgamma,
+                              int rows, int cols, float eps, int dtype);
 int luaTL_softmax(const void* x, const void* bias, void* out, int rows, int cols, float scale,
                   int causal, int mask_offset, int dtype);                                                /* core.cu:2351 */
 int luaTL_softmax_ex(const void* x, const void* bias, void* out, int rows, int cols, float scale,

@@ -114,6 +114,7 @@ SIGNATURES = {
     "luaTL_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _f, _i, _i]),
     "luaTL_rmsnorm": (_i, [_vp, _vp, _vp, _i, _i, _f, _i]),
     "luaTL_rmsnorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i]),
+    "luaTL_rmsnorm_bwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i]),
     "luaTL_softmax": (_i, [_vp, _vp, _vp, _i, _i, _f, _i, _i, _i]),
     "luaTL_softmax_ex": (_i, [_vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i]),
     "luaTL_softmax_bwd": (_i, [_vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i]),

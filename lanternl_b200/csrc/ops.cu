@@ -1200,3 +1200,49 @@ int ltl_sgd(float* w, const float* g, bf16* w_lp, uint64_t n, float lr, float wd
     sgd_kernel<<<grid1d((n + 3) / 4, 256), 256, 0, s>>>(w, g, w_lp, n, lr, wd, nsq, max_norm, vec);
     return ltl_check_launch("sgd");
 }
+
+// ------------------------------------------------------------------------------------------
+// RMSNorm backward without any allocation.
+//
+// Who needs it: code that may not call cudaMalloc when it wants a gradient - a host that has
+// handed all device memory to its own arena and forbids further driver allocations, or a
+// latency-critical loop that cannot afford the implicit device synchronisation of
+// cudaMalloc / cudaFree.  luaTL_rmsnorm_bwd takes its dgamma scratch (one partial row per warp)
+// from a workspace the library grows with cudaMalloc on demand; this entry point uses a fixed
+// array in the library's own device image instead.
+//
+// The array costs RMSNORM_BWD_STATIC_FLOATS * 4 bytes (4.6 MB) on every GPU that loads the
+// library, from load until exit.  The kernel overwrites every partial row it later sums, so
+// nothing in the array has to be cleared between calls; but all calls share it, so two calls
+// that overlap on the GPU (different streams, or another host thread) race on it.
+// ------------------------------------------------------------------------------------------
+constexpr size_t RMSNORM_BWD_STATIC_FLOATS = (size_t)1184 * 1024;   // 148 SMs * 2 CTAs * 4 warps rows of <= 1024 columns
+static __device__ __align__(256) float g_rmsnorm_bwd_static[RMSNORM_BWD_STATIC_FLOATS];
+
+extern "C" int luaTL_rmsnorm_bwd_noalloc(const void* x, const void* gamma, const void* dy, void* dx, float* dgamma,
+                                         int rows, int cols, float eps, int dtype)
+{
+    LTL_TRY(ltl_require_init("rmsnorm_bwd_noalloc"));
+    // In host code the array's name is only a handle: the device address has to be asked for, once
+    // per device, with that device current.  The first call on a device does it (so make that first
+    // call outside of any stream capture).
+    static float* dev_ptr[64] = { nullptr };
+    int dev = -1;
+    LTL_CUDA("cudaGetDevice", cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return ltl_fail(LTL_ERR_ARG, "rmsnorm_bwd_noalloc: device ordinal %d not supported", dev);
+    if (!dev_ptr[dev]) {
+        float* p = nullptr;
+        LTL_CUDA("cudaGetSymbolAddress(rmsnorm_bwd scratch)", cudaGetSymbolAddress((void**)&p, g_rmsnorm_bwd_static));
+        if (!p) return ltl_fail(LTL_ERR_CUDA, "rmsnorm_bwd_noalloc: the static scratch has no device address");
+        dev_ptr[dev] = p;
+    }
+    if (dgamma && cols > 0 && ltl_rmsnorm_bwd_scratch_floats(cols) > RMSNORM_BWD_STATIC_FLOATS)
+        return ltl_fail(LTL_ERR_CAPACITY, "rmsnorm_bwd_noalloc: %d columns need %zu scratch floats, the static scratch holds %zu "
+                        "(at most %zu columns on this GPU); use luaTL_rmsnorm_bwd for wider rows", cols,
+                        ltl_rmsnorm_bwd_scratch_floats(cols), RMSNORM_BWD_STATIC_FLOATS,
+                        RMSNORM_BWD_STATIC_FLOATS / ((size_t)ltl_sm_count() * 2 * ROW_WARPS));
+    cudaStream_t s = ltl_default_stream();
+    LTL_TRY(ltl_rmsnorm_bwd(x, gamma, dy, dx, dgamma, rows, cols, eps, dtype, dev_ptr[dev], s));
+    LTL_CUDA("rmsnorm_bwd_noalloc", cudaStreamSynchronize(s));
+    return LTL_OK;
+}
