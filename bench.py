@@ -219,8 +219,8 @@ def run_decode(args, dist):
         metric="decode_tokens_per_s", value=tokens / (dev_ms * 1e-3), unit="tokens/s", n_gpus=dist.world,
         steps=args.steps, warmup=args.warmup, ms_per_step=dev_ms / args.steps, higher_is_better=True,
         scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
-        config=dict(workload="configs[2] batched greedy decode: V8000 D512 L8 H8 F1408 ctx1024, 256 seqs x "
-                             "(128 prompt + 512 generated), sequences sharded over GPUs",
+        config=dict(workload=f"configs[2] batched greedy decode: V8000 D512 L8 H8 F1408 ctx1024, {NSEQ_TOTAL} seqs x "
+                             f"({N_PROMPT} prompt + {N_NEW} generated), sequences sharded over GPUs",
                     nseq_per_gpu=nseq, n_prompt=N_PROMPT, n_new=N_NEW, parallelism=f"dp{dist.world} (no collective)",
                     l2="inputs larger than L2 (KV cache %.1f GB per GPU)" % (2 * cfg["layers"] * nseq * cfg["max_seq"] * cfg["dim"] * 2 / 1e9)),
         e2e=dict(value=tokens / (e2e_ms * 1e-3), unit="tokens/s", h2d_bytes_per_step=int(prompts.nbytes) * dist.world,
@@ -393,6 +393,7 @@ def run_reference(args, dist):
 
 
 def main():
+    global NSEQ_TOTAL, N_PROMPT, N_NEW
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -400,7 +401,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "train"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--nseq", type=int, default=NSEQ_TOTAL, help="sequences over all GPUs (profiling aid; the metric uses 256)")
+    ap.add_argument("--n-prompt", type=int, default=N_PROMPT, help="prompt length (profiling aid; the metric uses 128)")
+    ap.add_argument("--n-new", type=int, default=N_NEW, help="generated tokens per sequence (profiling aid; the metric uses 512)")
     args = ap.parse_args()
+    NSEQ_TOTAL, N_PROMPT, N_NEW = args.nseq, args.n_prompt, args.n_new
     if args.impl == "reference":
         world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
         if rank == 0:
