@@ -92,16 +92,20 @@ class Clocks:
 class Dist:
     """One process per GPU.  torch.distributed is plumbing only: barrier and max over ranks."""
 
-    def __init__(self, gpus):
+    def __init__(self, gpus, backend="nccl"):
         self.world = int(os.environ.get("WORLD_SIZE", "1"))
         self.rank = int(os.environ.get("RANK", "0"))
         self.local = int(os.environ.get("LOCAL_RANK", "0"))
         self.td = None
+        self.dev = "cuda" if backend == "nccl" else "cpu"      # "gloo": the CPU tests of this plumbing
         if self.world > 1:
             import torch
             import torch.distributed as td
-            torch.cuda.set_device(self.local)
-            td.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+            if backend == "nccl":
+                torch.cuda.set_device(self.local)
+                td.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+            else:
+                td.init_process_group(backend)
             self.td, self.torch = td, torch
         if gpus != self.world:
             raise SystemExit(f"--gpus {gpus} but WORLD_SIZE is {self.world}: launch with torch.distributed.run")
@@ -109,26 +113,27 @@ class Dist:
     def barrier(self):
         if self.td:
             self.td.barrier()
-            self.torch.cuda.synchronize()
+            if self.dev == "cuda":
+                self.torch.cuda.synchronize()
 
     def max(self, x):
         if not self.td:
             return x
-        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        t = self.torch.tensor([x], dtype=self.torch.float64, device=self.dev)
         self.td.all_reduce(t, op=self.td.ReduceOp.MAX)
         return float(t.item())
 
     def sum(self, x):
         if not self.td:
             return x
-        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        t = self.torch.tensor([x], dtype=self.torch.float64, device=self.dev)
         self.td.all_reduce(t, op=self.td.ReduceOp.SUM)
         return float(t.item())
 
     def broadcast_bytes(self, b, n):
         if not self.td:
             return b
-        t = self.torch.zeros(n, dtype=self.torch.uint8, device="cuda")
+        t = self.torch.zeros(n, dtype=self.torch.uint8, device=self.dev)
         if self.rank == 0:
             t.copy_(self.torch.frombuffer(bytearray(b), dtype=self.torch.uint8))
         self.td.broadcast(t, 0)
@@ -137,6 +142,15 @@ class Dist:
     def close(self):
         if self.td:
             self.td.destroy_process_group()
+
+
+def shard_rows(rows, world, rank):
+    """This rank's contiguous block of the job's sequences (world must divide the row count: every rank then
+    runs the same number of decode steps on the same shapes, which the max-over-ranks timing assumes)."""
+    if len(rows) % world:
+        raise SystemExit(f"{len(rows)} sequences do not split over {world} ranks")
+    n = len(rows) // world
+    return np.ascontiguousarray(rows[rank * n:(rank + 1) * n])
 
 
 def decode_bytes(cfg, nparams, nseq, n_prompt, n_new):
@@ -164,7 +178,7 @@ def run_decode(args, dist):
     w = bf16_round(synth.init_params(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], seed=0))
     m.load_flat(w)
     allp = synth.zipf_ids(1, NSEQ_TOTAL * N_PROMPT, cfg["vocab"]).reshape(NSEQ_TOTAL, N_PROMPT)
-    prompts = np.ascontiguousarray(allp[dist.rank * nseq:(dist.rank + 1) * nseq])
+    prompts = shard_rows(allp, dist.world, dist.rank)
     d_prompts, d_out = ad.ids(nseq * N_PROMPT), ad.ids(nseq * N_NEW)
     ad.upload_i32(d_prompts, prompts)
     res = _lib.LmResult()
@@ -313,13 +327,22 @@ def run_train(args, dist):
     return line
 
 
+def host_threads():
+    """Host threads this process may use (cgroup / affinity aware), at most 32 and at most one per sequence."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(1, min(n, 32, NSEQ_TOTAL))
+
+
 def cpu_sample(threads, n_new=24):
     """The CPU restatement of the reference's path on a bounded sample of the decode workload:
     `threads` sequences (one per host thread), 128-token prompt, n_new generated tokens each."""
     from lanternl_b200 import synth
     from oracle import cpu_ref
     cfg = DECODE
-    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+    os.environ["OMP_NUM_THREADS"] = str(threads)      # torchrun presets it to 1; the oracle library reads it at load
     o = cpu_ref.Oracle(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], cfg["max_seq"])
     w = bf16_round(synth.init_params(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], seed=0)).astype(np.float64)
     prompts = synth.zipf_ids(1, NSEQ_TOTAL * N_PROMPT, cfg["vocab"]).reshape(NSEQ_TOTAL, N_PROMPT)[:threads]
@@ -371,7 +394,7 @@ def run_reference(args, dist):
         return None
     if args.workload == "train":
         return run_reference_train(args, dist)
-    threads = min(os.cpu_count() or 1, NSEQ_TOTAL)
+    threads = host_threads()
     vals = []
     for _ in range(args.warmup):
         cpu_sample(threads, n_new=2)
@@ -416,7 +439,7 @@ def main():
     line = run_decode(args, dist) if args.workload == "decode" else run_train(args, dist)
     if dist.rank == 0:
         if dist.world == 1 and not args.no_cpu_baseline:
-            threads = min(os.cpu_count() or 1, NSEQ_TOTAL)
+            threads = host_threads()
             v, dt, sample = cpu_sample(threads)
             line["cpu_baseline"] = dict(value=v, unit="tokens/s", cores=threads, kind="port", sample=sample)
         print(json.dumps(line), flush=True)
