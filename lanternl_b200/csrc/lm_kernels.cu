@@ -420,6 +420,87 @@ __device__ __forceinline__ void copy(void* dst, const void* src, uint32_t bytes,
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
 }
+// Maximum over the warp with one redux instruction: floats are mapped to integers of the same order.
+__device__ __forceinline__ float warp_max_redux(float x)
+{
+    int i = __float_as_int(x);
+    i = i >= 0 ? i : i ^ 0x7FFFFFFF;
+    i = __reduce_max_sync(0xFFFFFFFFu, i);
+    return __int_as_float(i >= 0 ? i : i ^ 0x7FFFFFFF);
+}
+// The four 16-byte chunks of q a thread multiplies with (key j, half): the chunks of its half of the
+// row, in the rotated order that keeps the 16-byte reads of the K rows free of bank conflicts.
+template <int N>
+__device__ __forceinline__ void load_q_chunks(const float* qs, int j, int half, float (&qr)[4][N])
+{
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int cc = (2 * c + half + 2 * j) & 7;
+#pragma unroll
+        for (int e = 0; e < N; e += 4) {
+            const float4 t = *reinterpret_cast<const float4*>(qs + cc * N + e);
+            qr[c][e] = t.x; qr[c][e + 1] = t.y; qr[c][e + 2] = t.z; qr[c][e + 3] = t.w;
+        }
+    }
+}
+// One 64-key tile for one warp: scores of the warp's 16 keys (two threads per key), online-softmax
+// update of the warp's running maximum m, the thread's share of the denominator (lsum: summed over
+// the warp at the end of the item; every key is counted by two threads) and P V with one 4-byte word
+// of every V row per lane.
+template <typename T, int N, int EPW>
+__device__ __forceinline__ void consume_tile(const uint8_t* ks, const uint8_t* vs, int nk, const float (&qr)[4][N],
+                                             int j, int half, int warp, int lane, float& m, float& lsum, float (&acc)[EPW])
+{
+    const T* krow = reinterpret_cast<const T*>(ks + j * ROWB);
+    float part[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int cc = (2 * c + half + 2 * j) & 7;
+        float kv[N];
+        ld16<T>(krow + cc * N, kv);
+        part[c] = 0.0f;
+#pragma unroll
+        for (int e = 0; e < N; ++e) part[c] = fmaf(qr[c][e], kv[e], part[c]);
+    }
+    float sdot = (part[0] + part[1]) + (part[2] + part[3]);
+    sdot += __shfl_xor_sync(0xFFFFFFFFu, sdot, 1);
+    const bool valid = j < nk;
+    const float sv = valid ? sdot : -INFINITY;
+    const float mn = fmaxf(m, warp_max_redux(sv));
+    const float corr = (mn == -INFINITY) ? 1.0f : __expf(m - mn);
+    const float pr = valid ? __expf(sv - mn) : 0.0f;
+    lsum = fmaf(lsum, corr, pr);
+    m = mn;
+#pragma unroll
+    for (int e = 0; e < EPW; ++e) acc[e] *= corr;
+    const uint32_t* vrows = reinterpret_cast<const uint32_t*>(vs) + (size_t)(warp * 16) * (ROWB / 4) + lane;
+    const int nmine = nk - warp * 16;                    // rows past the tile's end hold stale bytes: read as zero
+    // All 16 row words and probabilities are fetched before the multiply-adds (no early exit in the
+    // loop), so the shared-memory and shuffle latencies overlap; two partial sums halve the add chain.
+    uint32_t w[16];
+    float pj[16];
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) w[jj] = jj < nmine ? vrows[jj * (ROWB / 4)] : 0u;
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) pj[jj] = __shfl_sync(0xFFFFFFFFu, pr, 2 * jj);
+    float odd[EPW];
+#pragma unroll
+    for (int e = 0; e < EPW; ++e) odd[e] = 0.0f;
+#pragma unroll
+    for (int jj = 0; jj < 16; jj += 2) {
+        if (sizeof(T) == 2) {
+            acc[0] = fmaf(pj[jj], __uint_as_float(w[jj] << 16), acc[0]);
+            acc[EPW - 1] = fmaf(pj[jj], __uint_as_float(w[jj] & 0xFFFF0000u), acc[EPW - 1]);
+            odd[0] = fmaf(pj[jj + 1], __uint_as_float(w[jj + 1] << 16), odd[0]);
+            odd[EPW - 1] = fmaf(pj[jj + 1], __uint_as_float(w[jj + 1] & 0xFFFF0000u), odd[EPW - 1]);
+        } else {
+            acc[0] = fmaf(pj[jj], __uint_as_float(w[jj]), acc[0]);
+            odd[0] = fmaf(pj[jj + 1], __uint_as_float(w[jj + 1]), odd[0]);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < EPW; ++e) acc[e] += odd[e];
+}
 template <int STG>
 struct Smem {
     alignas(128) uint8_t k[STG][KT * ROWB];
@@ -513,49 +594,17 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     __syncthreads();
 
     const int j = tid >> 1, half = tid & 1;          // two threads per key of the tile
-    float m = -INFINITY, l = 0.0f, acc[EPW];
+    float m = -INFINITY, lsum = 0.0f, acc[EPW];
 #pragma unroll
     for (int i = 0; i < EPW; ++i) acc[i] = 0.0f;
+    float qr[4][N];
+    load_q_chunks<N>(sm.q, j, half, qr);
     bool ok = true;
     for (int t = 0; t < ntiles; ++t) {
         const int s = t % STG;
         ok = wait(&sm.full[s], (t / STG) & 1) && ok;
         const int nk = min(KT, kend - (kbeg + t * KT));
-        const T* krow = reinterpret_cast<const T*>(sm.k[s] + j * ROWB);
-        float sdot = 0.0f;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int cc = (2 * c + half + 2 * j) & 7;      // rotated chunk order: conflict-free 16-byte reads
-            float kv[N];
-            ld16<T>(krow + cc * N, kv);
-            const float* qq = sm.q + cc * N;
-#pragma unroll
-            for (int i = 0; i < N; ++i) sdot = fmaf(qq[i], kv[i], sdot);
-        }
-        sdot += __shfl_xor_sync(0xFFFFFFFFu, sdot, 1);
-        const bool valid = j < nk;
-        const float sv = valid ? sdot : -INFINITY;
-        const float mn = fmaxf(m, warp_max(sv));
-        const float corr = (mn == -INFINITY) ? 1.0f : expf(m - mn);
-        const float p = valid ? expf(sv - mn) : 0.0f;
-        l = l * corr + 0.5f * warp_sum(p);                   // every key sits in two lanes
-        m = mn;
-#pragma unroll
-        for (int i = 0; i < EPW; ++i) acc[i] *= corr;
-        const uint32_t* vrows = reinterpret_cast<const uint32_t*>(sm.v[s]) + (size_t)(warp * 16) * (ROWB / 4) + lane;
-        const int nmine = min(16, nk - warp * 16);          // rows past the tile's end hold stale bytes
-#pragma unroll
-        for (int jj = 0; jj < 16; ++jj) {
-            if (jj >= nmine) break;                              // warp-uniform
-            const float pj = __shfl_sync(0xFFFFFFFFu, p, 2 * jj);
-            const uint32_t w = vrows[jj * (ROWB / 4)];
-            if (sizeof(T) == 2) {
-                acc[0] = fmaf(pj, __uint_as_float(w << 16), acc[0]);
-                acc[EPW - 1] = fmaf(pj, __uint_as_float(w & 0xFFFF0000u), acc[EPW - 1]);
-            } else {
-                acc[0] = fmaf(pj, __uint_as_float(w), acc[0]);
-            }
-        }
+        consume_tile<T, N, EPW>(sm.k[s], sm.v[s], nk, qr, j, half, warp, lane, m, lsum, acc);
         __syncthreads();                                      // everyone is done with stage s
         if (tid == 0 && t + STG < ntiles) {
             const int k0 = kbeg + (t + STG) * KT;
@@ -566,6 +615,7 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
         }
     }
     if (!ok && err && tid == 0) *err = 2;
+    float l = 0.5f * warp_sum(lsum);                             // every key sits in two lanes
     if (warp == 0 && z == 0) {     // the new token's own score, from the fp32 copies
         float sdot = 0.0f;
 #pragma unroll
