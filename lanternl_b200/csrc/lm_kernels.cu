@@ -86,6 +86,12 @@ int ltl_lm_rmsnorm(const float* x, const float* gain, void* out, int out_dtype, 
 }
 
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&t);
+}
+
 // Consumer of the split-K GEMMs: x += partial[0] + partial[1] + ... (fixed order, so the result
 // does not depend on scheduling), then RMSNorm of the updated row.  One warp per row.
 template <typename TO>
@@ -125,6 +131,52 @@ lm_residual_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ part
     }
 }
 
+// The same with one CTA per row and one 16-byte chunk per thread (rows of up to 4096 columns): every load
+// of a thread is independent and issued at once, the updated row stays in registers, and the sum of
+// squares crosses the warps through shared memory.  Same summation order per element as above.
+template <typename TO>
+__global__ void __launch_bounds__(1024)
+lm_residual_rmsnorm_row_kernel(float* __restrict__ x, const float* __restrict__ partial, int nparts,
+                               const float* __restrict__ gain, TO* __restrict__ out, int rows, int cols, float eps)
+{
+    __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x, c = threadIdx.x * 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    const bool live = c < cols;
+    const size_t slice = (size_t)rows * cols, off = (size_t)row * cols + c;
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f), g = v, acc = v;
+    if (live) {
+        v = *reinterpret_cast<const float4*>(x + off);
+        g = *reinterpret_cast<const float4*>(gain + c);
+#pragma unroll 4
+        for (int p = 0; p < nparts; ++p) {
+            const float4 q = *reinterpret_cast<const float4*>(partial + p * slice + off);
+            acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+        }
+        v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;
+        *reinterpret_cast<float4*>(x + off) = v;
+    }
+    float ss = warp_sum(fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w))));
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    ss = 0.0f;
+    for (int w = 0; w < nwarps; ++w) ss += red[w];             // same order in every thread
+    const float sc = 1.0f / sqrtf(ss / (float)cols + eps);
+    if (live) {
+        const float o[4] = { v.x * sc * g.x, v.y * sc * g.y, v.z * sc * g.z, v.w * sc * g.w };
+        if (sizeof(TO) == 2) {
+            uint2 pk;
+            pk.x = pack_bf16x2(o[0], o[1]);
+            pk.y = pack_bf16x2(o[2], o[3]);
+            *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + off) = pk;
+        } else {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + off) = make_float4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 int ltl_lm_residual_rmsnorm(float* x, const float* partial, int nparts, const float* gain, void* out,
                             int out_dtype, int rows, int cols, float eps, cudaStream_t s)
 {
@@ -132,6 +184,12 @@ int ltl_lm_residual_rmsnorm(float* x, const float* partial, int nparts, const fl
     if (cols % 4 || !aligned16(x) || !aligned16(gain) || !aligned16(partial))
         return ltl_fail(LTL_ERR_SHAPE, "lm_residual_rmsnorm: width %d must be a multiple of 4 and 16-byte aligned", cols);
     if (rows <= 0) return LTL_OK;
+    if (cols <= 4096 && out_dtype == LTL_BF16 && aligned16(out) && cols % 8 == 0) {
+        const int threads = ((cols / 4) + 31) / 32 * 32;
+        LTL_CUDA("lm_residual_rmsnorm launch", ltl_launch(lm_residual_rmsnorm_row_kernel<bf16>, dim3(rows), dim3(threads), 0, s,
+                                                          ltl_pdl_enabled(), x, partial, nparts, gain, (bf16*)out, rows, cols, eps));
+        return ltl_check_launch("lm_residual_rmsnorm");
+    }
     const int grid = (rows + 3) / 4;
     if (out_dtype == LTL_F32) lm_residual_rmsnorm_kernel<float><<<grid, 128, 0, s>>>(x, partial, nparts, gain, (float*)out, rows, cols, eps);
     else if (out_dtype == LTL_BF16) LTL_CUDA("lm_residual_rmsnorm launch", ltl_launch(lm_residual_rmsnorm_kernel<bf16>, dim3(grid), dim3(128), 0, s, ltl_pdl_enabled(), x, partial, nparts, gain, (bf16*)out, rows, cols, eps));
@@ -415,10 +473,18 @@ __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity)
     }
     return false;
 }
-__device__ __forceinline__ void copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
+// The cache is read once per step and is far larger than L2: its lines are marked evict-first so that
+// they do not push the weights and activations (re-read every step) out of L2.
+__device__ __forceinline__ uint64_t evict_first_policy()
 {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)), "l"(policy) : "memory");
 }
 // Maximum over the warp with one redux instruction: floats are mapped to integers of the same order.
 __device__ __forceinline__ float warp_max_redux(float x)
@@ -539,6 +605,7 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     const uint8_t* kg = reinterpret_cast<const uint8_t*>(kc + cbase);
     const uint8_t* vg = reinterpret_cast<const uint8_t*>(vc + cbase);
 
+    const uint64_t pol = evict_first_policy();
     if (tid == 0) {
         for (int s = 0; s < STG; ++s)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&sm.full[s])));
@@ -548,8 +615,8 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
             const int k0 = kbeg + t * KT;
             const uint32_t bytes = (uint32_t)min(KT, kend - k0) * ROWB;
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(&sm.full[t])), "r"(2 * bytes) : "memory");
-            copy(sm.k[t], kg + (size_t)k0 * ROWB, bytes, &sm.full[t]);
-            copy(sm.v[t], vg + (size_t)k0 * ROWB, bytes, &sm.full[t]);
+            copy(sm.k[t], kg + (size_t)k0 * ROWB, bytes, &sm.full[t], pol);
+            copy(sm.v[t], vg + (size_t)k0 * ROWB, bytes, &sm.full[t], pol);
         }
     }
     // new token: the first GL lanes of warp 1 rotate q and k, append k / v, publish q, k, v as fp32
@@ -610,8 +677,8 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
             const int k0 = kbeg + (t + STG) * KT;
             const uint32_t bytes = (uint32_t)min(KT, kend - k0) * ROWB;
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(&sm.full[s])), "r"(2 * bytes) : "memory");
-            copy(sm.k[s], kg + (size_t)k0 * ROWB, bytes, &sm.full[s]);
-            copy(sm.v[s], vg + (size_t)k0 * ROWB, bytes, &sm.full[s]);
+            copy(sm.k[s], kg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
+            copy(sm.v[s], vg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
         }
     }
     if (!ok && err && tid == 0) *err = 2;
