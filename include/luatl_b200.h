@@ -208,7 +208,9 @@ int luaTL_sgd(float* w, const float* g, uint64_t n, float lr, float wd, const fl
  * K contiguous), fp32 accumulation, C and R of c_dtype (LUATL_F32 or LUATL_BF16), R optional.
  * K must be a multiple of 8 and the operands 16-byte aligned.  tile_n bits 0-15: tile width, 0 = choose,
  * else 32/64/128.  tile_n bit 16: SwiGLU epilogue - the rows of B alternate gate_j / up_j, both are rounded to
- * bf16 and C [M, N/2] (bf16) = silu(gate) * up.
+ * bf16 and C [M, N/2] (bf16) = silu(gate) * up.  tile_n bit 17: accumulating epilogue - C (fp32) += A B^T with
+ * atomic adds (R must be NULL).  tile_n bits 20-27: split-K slice count (0/1 = none); without bit 17 C then
+ * receives the slices' partial products [slices][M][N].
  * The reference has no tensor-core path for bf16 (its only one is fp16 wmma, cuda/luaTL_core.cu:1296). */
 int luaTL_gemm_bf16_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
                        int c_dtype, int tile_n);
@@ -262,12 +264,19 @@ float* luaTL_lm_params_device(luaTL_lm_t* m);
 float* luaTL_lm_grads_device(luaTL_lm_t* m);
 
 /* One optimizer step on host id/target blocks [batch, max_seq] (pad: id 0, target -1).
- * optimizer: 0 = SGD, 1 = AdamW.  valid_global <= 0: count the valid targets of this block. */
+ * optimizer: 0 = SGD, 1 = AdamW.  valid_global <= 0: count the valid targets of this block.
+ * dtype f32: exact fp32 arithmetic (CUDA-core GEMMs).  dtype bf16: mixed precision - fp32 master
+ * weights, gradients and residual stream, bf16 activations, every contraction on the tensor cores with
+ * fp32 accumulation; needs batch x max_seq, dim, ffn and vocab to be multiples of 8.  The first training
+ * call of a bf16 model switches it to the training weight layout (captured decode graphs are dropped). */
 typedef struct {
     int32_t optimizer, step;
     float   lr, weight_decay, clip_norm, beta1, beta2, adam_eps;
     int32_t valid_global;      /* denominator of loss and gradient across all ranks            */
     int32_t no_update;         /* 1: forward + backward only (gradients stay readable)         */
+    int32_t accumulate;        /* 1: add to the gradients and loss already in the buffer (micro-batches of one
+                                *    optimizer step: first call 0, later calls 1, no_update = 1 on all but the last) */
+    int32_t skip_allreduce;    /* 1: leave the gradients rank-local (set on all but the last micro-batch)  */
 } luaTL_lm_train_args_t;
 int luaTL_lm_train_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* targets,
                         const luaTL_lm_train_args_t* a, luaTL_lm_result_t* out);

@@ -80,7 +80,8 @@ class LmResult(C.Structure):
 class LmTrainArgs(C.Structure):
     _fields_ = [("optimizer", C.c_int32), ("step", C.c_int32), ("lr", C.c_float), ("weight_decay", C.c_float),
                 ("clip_norm", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("adam_eps", C.c_float),
-                ("valid_global", C.c_int32), ("no_update", C.c_int32)]
+                ("valid_global", C.c_int32), ("no_update", C.c_int32), ("accumulate", C.c_int32),
+                ("skip_allreduce", C.c_int32)]
 
 
 _vp, _i, _f, _u64, _i64, _ll = C.c_void_p, C.c_int, C.c_float, C.c_uint64, C.c_int64, C.c_longlong

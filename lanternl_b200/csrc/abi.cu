@@ -590,7 +590,7 @@ int luaTL_adamw(float* w, const void* g, float* m, float* v, void* w_lp, uint64_
 int luaTL_gemm_bf16_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int c_dtype, int tile_n)
 {
     LTL_TRY(ltl_require_init("gemm_bf16_tc"));
-    LTL_TRY(ltl_gemm_tc(A, B, C, R, M, N, K, c_dtype, tile_n & 0xFFFF, (tile_n >> 16) & 1, (tile_n >> 20) & 0xF, g_stream));
+    LTL_TRY(ltl_gemm_tc(A, B, C, R, M, N, K, c_dtype, tile_n & 0xFFFF, (tile_n >> 16) & 3, (tile_n >> 20) & 0xFF, g_stream));
     LTL_TRY(sync_stream("gemm_bf16_tc"));
     return ltl_gemm_tc_check(g_stream);
 }

@@ -29,7 +29,7 @@ constexpr int BM = 128, BK = 64, UMMA_K = 16;
 // bytes are requested at once and the kernel is bound by one memory round trip, not by one per
 // four k-blocks.
 template <int BN> struct Ring { static constexpr int STAGES = BN == 32 ? 10 : (BN == 64 ? 8 : 6); };
-enum { EPI_NONE = 0, EPI_SWIGLU = 1 };
+enum { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ATOMIC = 2 };
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -105,30 +105,39 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
         : "r"(taddr));
 }
 
-template <int BN>
-struct Smem {
-    static constexpr int STAGES = Ring<BN>::STAGES;
-    alignas(1024) uint8_t a[STAGES][BM * BK * 2];
-    alignas(1024) uint8_t b[STAGES][BN * BK * 2];
-    alignas(8) uint64_t full[STAGES];
-    uint64_t empty[STAGES];
+// Shared memory of one CTA, carved from the dynamic allocation (1024-byte aligned for the 128-byte
+// swizzle): `stages` A tiles, `stages` B tiles, then the barriers.  The ring depth is a launch
+// parameter: a grid of a few latency-bound CTAs (a decode step) takes the deep ring and an SM each;
+// a grid of many tiles (prefill, training) takes a ring shallow enough for two CTAs per SM, so that
+// one CTA's epilogue overlaps the other's loads and MMAs.
+constexpr int MAX_STAGES = 10;
+struct Bars {
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
     uint64_t acc_ready;
     uint32_t tmem_base;
 };
+template <int BN> constexpr size_t stage_bytes() { return (size_t)(BM + BN) * BK * 2; }
+template <int BN> size_t smem_bytes(int stages) { return stages * stage_bytes<BN>() + sizeof(Bars) + 1024; }
 
 // EPI_SWIGLU: the B rows are interleaved (gate_j, up_j, gate_j+1, ...); the epilogue rounds both to
 // the output type (what a stored gate|up tensor would hold), applies silu(gate) * up and writes
 // N / 2 columns.  R is ignored.
+// EPI_ATOMIC: C (fp32) += the product, with red.global.add; every split-K slice adds into the same C.
+// This is the weight-gradient form (dW += X^T dY with a long reduction over the tokens).
 template <int BN, typename TC, int EPI>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               TC* __restrict__ C, const TC* R, int M, int N, int K, int* __restrict__ err)
+               TC* C, const TC* R, int M, int N, int K, int STAGES, int* __restrict__ err)
 {
     // gridDim.z > 1: split-K.  Slice z covers a contiguous range of k-blocks and writes its partial
     // sums to C + z * M * N (the consumer adds the slices in a fixed order).
     extern __shared__ uint8_t smem_raw[];
-    Smem<BN>& sm = *reinterpret_cast<Smem<BN>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr int STAGES = Ring<BN>::STAGES;
+    uint8_t* const tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* const tiles_b = tiles + (size_t)STAGES * (BM * BK * 2);
+    Bars& sm = *reinterpret_cast<Bars*>(tiles_b + (size_t)STAGES * (BN * BK * 2));
+    auto a_tile = [&](int st) { return tiles + (size_t)st * (BM * BK * 2); };
+    auto b_tile = [&](int st) { return tiles_b + (size_t)st * (BN * BK * 2); };
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     constexpr uint32_t STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -137,7 +146,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int kb_per = (kb_all + gridDim.z - 1) / gridDim.z;
     const int kb0 = blockIdx.z * kb_per;
     const int kblocks = max(0, min(kb_all, kb0 + kb_per) - kb0);
-    C += (size_t)blockIdx.z * M * N;
+    if (EPI != EPI_ATOMIC) C += (size_t)blockIdx.z * M * N;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
@@ -158,24 +167,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer ----
-        for (int kb = 0; kb < kblocks && ok; ++kb) {
-            const int s = kb % STAGES;
-            if (kb >= STAGES) ok = mbar_wait(&sm.empty[s], ((kb / STAGES) - 1) & 1);
+        int s = 0;
+        uint32_t round = 0;                               // kb / STAGES, kept without a division
+        for (int kb = 0; kb < kblocks && ok; ++kb, ++s) {
+            if (s == STAGES) { s = 0; ++round; }
+            if (round > 0) ok = mbar_wait(&sm.empty[s], (round - 1) & 1);
             if (!ok) break;
             mbar_expect_tx(&sm.full[s], STAGE_BYTES);
-            tma_load_2d(sm.a[s], &map_a, (kb0 + kb) * BK, m0, &sm.full[s]);
-            tma_load_2d(sm.b[s], &map_b, (kb0 + kb) * BK, n0, &sm.full[s]);
+            tma_load_2d(a_tile(s), &map_a, (kb0 + kb) * BK, m0, &sm.full[s]);
+            tma_load_2d(b_tile(s), &map_b, (kb0 + kb) * BK, n0, &sm.full[s]);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
         constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
-        for (int kb = 0; kb < kblocks && ok; ++kb) {
-            const int s = kb % STAGES;
-            ok = mbar_wait(&sm.full[s], (kb / STAGES) & 1);
+        int s = 0;
+        uint32_t round = 0;
+        for (int kb = 0; kb < kblocks && ok; ++kb, ++s) {
+            if (s == STAGES) { s = 0; ++round; }
+            ok = mbar_wait(&sm.full[s], round & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t da = umma_desc_sw128(smem_u32(sm.a[s]));
-            const uint64_t db = umma_desc_sw128(smem_u32(sm.b[s]));
+            const uint64_t da = umma_desc_sw128(smem_u32(a_tile(s)));
+            const uint64_t db = umma_desc_sw128(smem_u32(b_tile(s)));
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k)        // 32 bytes further along K per UMMA
                 umma_bf16(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
@@ -218,6 +231,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             st16<bf16>(reinterpret_cast<bf16*>(C) + base + 8, hi);
                         } else {
                             for (int j = 0; j < ncols; ++j) Cvt<TC>::st(C, base + j, o[j]);
+                        }
+                    }
+                } else if (EPI == EPI_ATOMIC) {
+                    if (row < M && kblocks > 0) {
+                        float* dst = reinterpret_cast<float*>(C) + (size_t)row * N + n0 + c0;
+                        const int ncols = min(32, N - (n0 + c0));
+                        if (ncols == 32 && (N & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j),
+                                             "f"(__uint_as_float(v[j])), "f"(__uint_as_float(v[j + 1])),
+                                             "f"(__uint_as_float(v[j + 2])), "f"(__uint_as_float(v[j + 3])) : "memory");
+                        } else {
+                            for (int j = 0; j < ncols; ++j) atomicAdd(dst + j, __uint_as_float(v[j]));
                         }
                     }
                 } else if (row < M) {
@@ -307,15 +334,25 @@ int launch(const void* A, const void* B, void* C, const void* R, int M, int N, i
     CUtensorMap ma, mb;
     LTL_TRY(tensor_map(A, M, K, BM, &ma));
     LTL_TRY(tensor_map(B, N, K, BN, &mb));
-    const size_t smem = sizeof(Smem<BN>) + 1024;
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, ksplit < 1 ? 1 : ksplit);
+    const int kb_all = (K + BK - 1) / BK;
+    const int kb_per = (kb_all + (int)grid.z - 1) / (int)grid.z;
+    int stages = Ring<BN>::STAGES;
+    // Many tiles per SM: two CTAs per SM (about 100 KB of ring each).  Otherwise the allocation stays that of
+    // the full ring whatever the depth used, which keeps one CTA per SM (each then has an SM's load path alone).
+    const bool many = (long long)grid.x * grid.y * grid.z >= 2LL * ltl_sm_count();
+    if (many) stages = BN == 128 ? 3 : (BN == 64 ? 4 : 5);
+    if (stages > kb_per) stages = kb_per;
+    if (stages < 1) stages = 1;
+    const size_t smem = smem_bytes<BN>(many ? stages : Ring<BN>::STAGES);
     static bool attr_set = false;
     if (!attr_set) {
-        LTL_CUDA("gemm_tc attr", cudaFuncSetAttribute(gemm_tc_kernel<BN, TC, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LTL_CUDA("gemm_tc attr", cudaFuncSetAttribute(gemm_tc_kernel<BN, TC, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      (int)smem_bytes<BN>(Ring<BN>::STAGES)));
         attr_set = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, ksplit < 1 ? 1 : ksplit);
     LTL_CUDA("gemm_tc launch", ltl_launch(gemm_tc_kernel<BN, TC, EPI>, grid, dim3(192), smem, s, ltl_pdl_enabled(),
-                                          ma, mb, (TC*)C, (const TC*)R, M, N, K, g_err_flag));
+                                          ma, mb, (TC*)C, (const TC*)R, M, N, K, stages, g_err_flag));
     return ltl_check_launch("gemm_tc");
 }
 
@@ -353,14 +390,28 @@ void ltl_gemm_tc_plan_split(int M, int N, int K, int* bn, int* ksplit)
     *ksplit = s;
 }
 
+// Slice count for an accumulating GEMM (epi = 2) with tiles of width bn: enough slices of at least 4
+// k-blocks to give every SM about two CTAs.
+int ltl_gemm_tc_plan_accum(int M, int N, int K, int bn)
+{
+    const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn), kb = (K + BK - 1) / BK;
+    int s = (2 * ltl_sm_count() + tiles - 1) / tiles;
+    if (s > kb / 4) s = kb / 4;
+    if (s > 64) s = 64;
+    return s < 1 ? 1 : s;
+}
+
 // C[M,N] (c_dtype f32 or bf16, row-major) = A[M,K] B[N,K]^T + R.  bn = 0 picks the tile width.
+// epi = 2: C (fp32) += A B^T through atomic adds, over ksplit slices of K.
 // epi = 1: SwiGLU epilogue (see the kernel), C is [M, N/2] bf16.
 // ksplit > 1: split-K, C receives ksplit fp32 partial matrices [ksplit][M][N] (bn should then be the
 // width the caller sized the grid for; see ltl_gemm_tc_plan_split).
 int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int c_dtype, int bn,
                 int epi, int ksplit, cudaStream_t s)
 {
-    if (ksplit > 1 && (c_dtype != LTL_F32 || R || epi))
+    if (epi == EPI_ATOMIC && (c_dtype != LTL_F32 || R))
+        return ltl_fail(LTL_ERR_ARG, "gemm_tc: the accumulating epilogue adds into an fp32 C and takes no residual");
+    if (epi != EPI_ATOMIC && ksplit > 1 && (c_dtype != LTL_F32 || R || epi))
         return ltl_fail(LTL_ERR_ARG, "gemm_tc: split-K writes fp32 partial sums and takes no residual or epilogue");
     if (!A || !B || !C) return ltl_fail(LTL_ERR_NULL, "gemm_tc: null operand");
     if (!ltl_gemm_tc_supported(A, B, M, N, K))
@@ -375,6 +426,7 @@ int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int
 #define TC_CASE(BNV)                                                                                     \
     if (bn == BNV) {                                                                                     \
         if (epi == EPI_SWIGLU) return launch<BNV, bf16, EPI_SWIGLU>(A, B, C, nullptr, M, N, K, 1, s);       \
+        if (epi == EPI_ATOMIC) return launch<BNV, float, EPI_ATOMIC>(A, B, C, nullptr, M, N, K, ksplit, s);    \
         if (c_dtype == LTL_F32) return launch<BNV, float, EPI_NONE>(A, B, C, R, M, N, K, ksplit, s);             \
         if (c_dtype == LTL_BF16) return launch<BNV, bf16, EPI_NONE>(A, B, C, R, M, N, K, 1, s);             \
         return ltl_fail(LTL_ERR_DTYPE, "gemm_tc: output dtype %d", c_dtype);                             \

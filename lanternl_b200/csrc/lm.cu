@@ -17,6 +17,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <map>
 #include <vector>
 
@@ -59,8 +60,13 @@ struct luaTL_lm_s {
     std::vector<LayerOff> lo;
     int64_t np, off_emb, off_lnf, off_head;
     float *W = nullptr, *G = nullptr, *M1 = nullptr, *M2 = nullptr;
-    bf16* Wb = nullptr;
+    bf16* Wb = nullptr;          // bf16 mirror, matrices transposed to [out, in]
+    bf16* Wm = nullptr;          // second bf16 mirror for the backward: the other orientation of every matrix
     int mirror_dirty = 1;
+    int train_tc = 0;            // bf16 model that has been asked to train: mixed-precision step
+    // mixed-precision backward scratch (bf16): activation gradients and token-major transposes
+    bf16 *b_dres = nullptr, *b_dhs = nullptr, *b_dh13 = nullptr, *b_dattn = nullptr, *b_dqkv = nullptr, *b_dl = nullptr,
+         *tX = nullptr, *tG = nullptr;
     cudaStream_t s = nullptr;
     float2* rope_tab = nullptr;
     Act train, infer, dec;
@@ -192,8 +198,13 @@ int sync_mirror(LM* m)
             // w13 [D, 2F]: with the fused SwiGLU epilogue its mirror rows alternate gate_j / up_j
             const int half = (m->fuse_swiglu && t.cols == 2 * m->F && t.rows == m->D && strstr(t.name, "w13")) ? m->F : 0;
             LTL_TRY(ltl_transpose_to_bf16(m->W + t.off, m->Wb + t.off, t.rows, t.cols, half, m->s));
+            if (m->Wm) LTL_TRY(ltl_cast(m->W + t.off, LTL_F32, m->Wm + t.off, LTL_BF16, (uint64_t)t.rows * t.cols, m->s));
+        } else {
+            LTL_TRY(ltl_cast(m->W + t.off, LTL_F32, m->Wb + t.off, LTL_BF16, (uint64_t)t.rows * t.cols, m->s));
+            // tok_emb [V, D] is read as [out = V, in = D] by the tied head: its other orientation is the transpose
+            if (m->Wm && t.off == m->off_emb && t.rows == m->V)
+                LTL_TRY(ltl_transpose_any_to_bf16(m->W + t.off, LTL_F32, m->Wm + t.off, t.rows, t.cols, m->s));
         }
-        else LTL_TRY(ltl_cast(m->W + t.off, LTL_F32, m->Wb + t.off, LTL_BF16, (uint64_t)t.rows * t.cols, m->s));
     }
     m->mirror_dirty = 0;
     return LTL_OK;
@@ -385,6 +396,106 @@ int backward(LM* m, Act& a, const int32_t* d_ids, int nseq, int T)
     return LTL_OK;
 }
 
+// ---------------- mixed-precision backward (bf16 model) ----------------------------------------
+// The saved activations are bf16, the residual stream and its gradient fp32, the weight gradients fp32.
+// Every contraction runs on the tensor-core GEMM, which takes both operands with the contraction
+// dimension contiguous:
+//   dX[R, in]  = dY[R, out] . W[in, out]^T     B = the second weight mirror (Wm, master orientation)
+//   dW[in, out] += X^T[in, R] . dY^T[out, R]^T  both operands transposed to token-major copies (tX, tG),
+//                                               accumulated into G by the split-K atomic epilogue.
+int alloc_backward_tc(LM* m)
+{
+    if (m->b_dres) return LTL_OK;
+    const size_t R = (size_t)m->B * m->T, D = m->D, F = m->F, V = m->V;
+    if (!m->dres) {
+        DALLOC(m->dres, R * D * 4, "dres"); DALLOC(m->dbr, R * D * 4, "dbr"); DALLOC(m->dhf, R * D * 4, "dhf");
+        DALLOC(m->dh1, R * D * 4, "dh1"); DALLOC(m->dh2, R * D * 4, "dh2"); DALLOC(m->delta, R * m->H * 4, "delta");
+    }
+    DALLOC(m->b_dres, R * D * 2, "dres bf16"); DALLOC(m->b_dhs, R * F * 2, "dhs bf16");
+    DALLOC(m->b_dh13, R * 2 * F * 2, "dh13 bf16"); DALLOC(m->b_dattn, R * D * 2, "dattn bf16");
+    DALLOC(m->b_dqkv, R * 3 * D * 2, "dqkv bf16"); DALLOC(m->b_dl, R * V * 2, "dlogits bf16");
+    const size_t wx = std::max(std::max(F, D), V), wg = std::max(std::max(2 * F, 3 * D), D);
+    DALLOC(m->tX, R * wx * 2, "token-major activations"); DALLOC(m->tG, R * wg * 2, "token-major gradients");
+    return LTL_OK;
+}
+
+// dW[wr, wc] += X^T . dY with X [R, wr] and dY [R, wc] given in the dtypes named.
+int dw_gemm(LM* m, const void* X, int x_dt, int wr, const void* dY, int dy_dt, int wc, float* dW, int R)
+{
+    LTL_TRY(ltl_transpose_any_to_bf16(X, x_dt, m->tX, R, wr, m->s));
+    LTL_TRY(ltl_transpose_any_to_bf16(dY, dy_dt, m->tG, R, wc, m->s));
+    const int bn = 128;
+    LTL_TRY(ltl_gemm_tc(m->tX, m->tG, dW, nullptr, wr, wc, R, LTL_F32, bn, 2, ltl_gemm_tc_plan_accum(wr, wc, R, bn), m->s));
+    m->launches += 3;
+    return LTL_OK;
+}
+// dX[R, n_in] = dY[R, n_out] . Wt^T with Wt = the mirror that holds the weight as [n_in, n_out].
+int dx_gemm(LM* m, const bf16* dY, int n_out, const bf16* Wt, int n_in, void* dX, int dx_dt, int R)
+{
+    m->launches++;
+    return ltl_gemm_tc(dY, Wt, dX, nullptr, R, n_in, n_out, dx_dt, 0, 0, 1, m->s);
+}
+
+int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T)
+{
+    const int D = m->D, F = m->F, V = m->V, L = m->L, H = m->H, hd = m->hd;
+    const int rows = nseq * T;
+    const size_t RD = (size_t)a.rows_cap * D;
+    float* W = m->W; float* G = m->G;
+    LTL_TRY(ensure_ws(m, ltl_rmsnorm_bwd_scratch_floats(D)));
+    // head: dlogits (fp32, in a.logits) -> bf16
+    LTL_TRY(ltl_cast(a.logits, LTL_F32, m->b_dl, LTL_BF16, (uint64_t)rows * V, m->s));
+    if (m->c.tie) {
+        LTL_TRY(dw_gemm(m, m->b_dl, LTL_BF16, V, a.hf, LTL_BF16, D, G + m->off_emb, rows));         // dEmb += dl^T hf
+        LTL_TRY(dx_gemm(m, m->b_dl, V, m->Wm + m->off_emb, D, m->dhf, LTL_F32, rows));              // dhf = dl emb
+    } else {
+        LTL_TRY(dw_gemm(m, a.hf, LTL_BF16, D, m->b_dl, LTL_BF16, V, G + m->off_head, rows));        // dHead += hf^T dl
+        LTL_TRY(dx_gemm(m, m->b_dl, V, m->Wm + m->off_head, D, m->dhf, LTL_F32, rows));             // dhf = dl head^T
+    }
+    LTL_TRY(ltl_rmsnorm_bwd(a.res + (size_t)L * RD, W + m->off_lnf, m->dhf, m->dres, G + m->off_lnf, rows, D,
+                            m->c.eps, LTL_F32, m->ws, m->s));
+    m->launches += 2;
+    for (int l = L - 1; l >= 0; --l) {
+        const LayerOff& o = m->lo[l];
+        const float* xin = a.res + (size_t)l * RD;
+        const float* mid = a.mid + (size_t)l * RD;
+        const bf16* h1 = (const bf16*)a.h1 + (size_t)l * RD;
+        const bf16* qkv = (const bf16*)a.qkv + (size_t)l * 3 * RD;
+        const bf16* attn = (const bf16*)a.attn + (size_t)l * RD;
+        const bf16* h2 = (const bf16*)a.h2 + (size_t)l * RD;
+        const bf16* h13 = (const bf16*)a.h13 + (size_t)l * a.rows_cap * 2 * F;
+        const bf16* hs = (const bf16*)a.hs + (size_t)l * a.rows_cap * F;
+        const float* lse = a.lse + (size_t)l * a.rows_cap * H;
+
+        // feed-forward
+        LTL_TRY(ltl_cast(m->dres, LTL_F32, m->b_dres, LTL_BF16, (uint64_t)rows * D, m->s));
+        LTL_TRY(dx_gemm(m, m->b_dres, D, m->Wm + o.w2, F, m->b_dhs, LTL_BF16, rows));               // dhs = dres W2^T
+        LTL_TRY(dw_gemm(m, hs, LTL_BF16, F, m->b_dres, LTL_BF16, D, G + o.w2, rows));               // dW2 += hs^T dres
+        LTL_TRY(ltl_swiglu_bwd(h13, h13 + F, m->b_dhs, m->b_dh13, m->b_dh13 + F, rows, F, 2 * F, 2 * F, F, LTL_BF16, m->s));
+        LTL_TRY(dw_gemm(m, h2, LTL_BF16, D, m->b_dh13, LTL_BF16, 2 * F, G + o.w13, rows));          // dW13 += h2^T dh13
+        LTL_TRY(dx_gemm(m, m->b_dh13, 2 * F, m->Wm + o.w13, D, m->dh2, LTL_F32, rows));             // dh2 = dh13 W13^T
+        LTL_TRY(ltl_rmsnorm_bwd(mid, W + o.ln2, m->dh2, m->dbr, G + o.ln2, rows, D, m->c.eps, LTL_F32, m->ws, m->s));
+        LTL_TRY(ltl_elementwise(m->dres, m->dbr, m->dres, (uint64_t)rows * D, LTL_F32, 6, 1.0f, 0.0f, m->s));
+        // attention
+        LTL_TRY(ltl_cast(m->dres, LTL_F32, m->b_dres, LTL_BF16, (uint64_t)rows * D, m->s));
+        LTL_TRY(dx_gemm(m, m->b_dres, D, m->Wm + o.wo, D, m->b_dattn, LTL_BF16, rows));             // dattn = dres Wo^T
+        LTL_TRY(dw_gemm(m, attn, LTL_BF16, D, m->b_dres, LTL_BF16, D, G + o.wo, rows));             // dWo += attn^T dres
+        LTL_TRY(ltl_attn_bwd(qkv, attn, m->b_dattn, lse, m->delta, m->b_dqkv, nseq, T, H, hd, m->scale, m->c.causal,
+                             LTL_BF16, m->s));
+        if (m->c.use_rope)
+            LTL_TRY(ltl_rope(m->b_dqkv, a.posids, rows, 2 * H, hd, 3 * D, 0, m->c.rope_base, m->c.rope_interleaved, 1,
+                             LTL_BF16, m->rope_tab, m->T, m->s));
+        LTL_TRY(dw_gemm(m, h1, LTL_BF16, D, m->b_dqkv, LTL_BF16, 3 * D, G + o.wqkv, rows));         // dWqkv += h1^T dqkv
+        LTL_TRY(dx_gemm(m, m->b_dqkv, 3 * D, m->Wm + o.wqkv, D, m->dh1, LTL_F32, rows));            // dh1 = dqkv Wqkv^T
+        LTL_TRY(ltl_rmsnorm_bwd(xin, W + o.ln1, m->dh1, m->dbr, G + o.ln1, rows, D, m->c.eps, LTL_F32, m->ws, m->s));
+        LTL_TRY(ltl_elementwise(m->dres, m->dbr, m->dres, (uint64_t)rows * D, LTL_F32, 6, 1.0f, 0.0f, m->s));
+        m->launches += 10;
+    }
+    LTL_TRY(ltl_embed_bwd(d_ids, m->dres, G + m->off_emb, rows, D, V, 1.0f, LTL_F32, m->s));
+    m->launches++;
+    return LTL_OK;
+}
+
 int count_valid(const int32_t* tgt, int n, int V)
 {
     int v = 0;
@@ -406,38 +517,66 @@ int ensure_train(LM* m)
 }
 
 // tail of G: [np] loss accumulator, [np+1] correct count, [np+2] grad norm^2, [np+3] spare
-int loss_and_grad(LM* m, const int32_t* d_ids, const int32_t* d_tgt, int valid_global, int want_grad)
+int loss_and_grad(LM* m, const int32_t* d_ids, const int32_t* d_tgt, int valid_global, int want_grad, int accumulate = 0)
 {
     const int rows = m->B * m->T;
     Act& a = m->train;
     const float gs = 1.0f / (float)(valid_global < 1 ? 1 : valid_global);
-    LTL_CUDA("zero gradients", cudaMemsetAsync(m->G, 0, (size_t)(m->np + 4) * 4, m->s));
+    if (!accumulate) LTL_CUDA("zero gradients", cudaMemsetAsync(m->G, 0, (size_t)(m->np + 4) * 4, m->s));
     LTL_TRY(forward(m, a, d_ids, m->B, m->T, MODE_TRAIN));
     LTL_TRY(ltl_cross_entropy(a.logits, d_tgt, m->losses, want_grad ? a.logits : nullptr, m->d_pred, rows, m->V,
                               -1, gs, LTL_F32, m->s));
     LTL_TRY(ltl_sum_f32(m->losses, rows, m->G + m->np, gs, m->s));
     LTL_TRY(ltl_count_correct(m->d_pred, d_tgt, rows, m->G + m->np + 1, m->s));
     m->launches += 4;
-    if (want_grad) {
+    if (want_grad && m->adt == LTL_BF16) {
+        LTL_TRY(alloc_backward_tc(m));
+        LTL_TRY(backward_tc(m, a, d_ids, m->B, m->T));
+    } else if (want_grad) {
         LTL_TRY(alloc_backward(m));
         LTL_TRY(backward(m, a, d_ids, m->B, m->T));
     }
     return LTL_OK;
 }
 
+void drop_graphs(LM* m)
+{
+    for (auto& kv : m->graphs) {
+        if (kv.second.ge) cudaGraphExecDestroy(kv.second.ge);
+        if (kv.second.g) cudaGraphDestroy(kv.second.g);
+    }
+    m->graphs.clear();
+}
+
+// A bf16 model asked to train: from now on the feed-forward keeps gate|up (the backward needs them), so the
+// fused SwiGLU epilogue and its interleaved weight mirror are dropped, and the second mirror is kept.
+int enter_train_tc(LM* m)
+{
+    if (m->train_tc) return LTL_OK;
+    if (!m->use_tc) return ltl_fail(LTL_ERR_UNSUPPORTED, "lm train_step: the bf16 training step needs the tensor-core GEMM");
+    if ((m->B * m->T) % 8 || m->D % 8 || m->F % 8 || m->V % 8)
+        return ltl_fail(LTL_ERR_SHAPE, "lm train_step: the bf16 training step needs batch x max_seq, dim, ffn and vocab to be "
+                        "multiples of 8 (got %d x %d, %d, %d, %d)", m->B, m->T, m->D, m->F, m->V);
+    LTL_CUDA("sync", cudaStreamSynchronize(m->s));
+    drop_graphs(m);
+    DALLOC(m->Wm, (size_t)m->np * 2, "second bf16 weight mirror");
+    m->fuse_swiglu = 0;
+    m->mirror_dirty = 1;
+    m->train_tc = 1;
+    return LTL_OK;
+}
+
 int train_step_dev(LM* m, const int32_t* d_ids, const int32_t* d_tgt, const luaTL_lm_train_args_t* a,
                    luaTL_lm_result_t* out, int valid_local)
 {
-    if (m->adt != LTL_F32)
-        return ltl_fail(LTL_ERR_UNSUPPORTED, "lm train_step: the backward exists for dtype f32 only; "
-                        "create the model with dtype = LUATL_F32 to train");
+    if (m->adt == LTL_BF16) LTL_TRY(enter_train_tc(m));
     LTL_TRY(ensure_train(m));
     const int world = ltl_comm_world();
     const int valid = a->valid_global > 0 ? a->valid_global : valid_local;
     m->launches = 0;
     LTL_CUDA("event", cudaEventRecord(m->ev[0], m->s));
-    LTL_TRY(loss_and_grad(m, d_ids, d_tgt, valid, 1));
-    if (world > 1) LTL_TRY(ltl_comm_allreduce(m->G, (uint64_t)m->np + 2, m->s));
+    LTL_TRY(loss_and_grad(m, d_ids, d_tgt, valid, 1, a->accumulate));
+    if (world > 1 && !a->skip_allreduce) LTL_TRY(ltl_comm_allreduce(m->G, (uint64_t)m->np + 2, m->s));
     float tail[4] = { 0, 0, 0, 0 };
     LTL_CUDA("loss download", cudaMemcpyAsync(tail, m->G + m->np, 8, cudaMemcpyDeviceToHost, m->s));
     LTL_CUDA("loss sync", cudaStreamSynchronize(m->s));
@@ -797,14 +936,12 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
 {
     if (!m) return;
     cudaDeviceSynchronize();
-    for (auto& kv : m->graphs) {
-        if (kv.second.ge) cudaGraphExecDestroy(kv.second.ge);
-        if (kv.second.g) cudaGraphDestroy(kv.second.g);
-    }
+    drop_graphs(m);
     free_act(m->train); free_act(m->infer); free_act(m->dec);
     void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
                      m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
-                     m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part };
+                     m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part,
+                     m->Wm, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl, m->tX, m->tG };
     for (void* p : ptrs) if (p) cudaFree(p);
     for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
     cudaGetLastError();

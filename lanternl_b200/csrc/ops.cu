@@ -1116,6 +1116,56 @@ int ltl_transpose_to_bf16(const float* in, bf16* out, int rows, int cols, int in
     return ltl_check_launch("transpose_to_bf16");
 }
 
+// out[C, R] (bf16) = in[R, C]^T for an fp32 or bf16 input: 64 x 64 tiles through shared memory, two
+// elements per thread on both sides, so that reads and writes are 128-byte segments per warp.  The
+// backward's weight-gradient GEMMs take both operands with the token dimension contiguous.
+template <typename TI>
+__global__ void __launch_bounds__(256)
+transpose_any_to_bf16_kernel(const TI* __restrict__ in, bf16* __restrict__ out, int rows, int cols)
+{
+    __shared__ float tile[64][65];
+    const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;          // 32 x 8
+    for (int j = ty; j < 64; j += 8) {
+        const int r = r0 + j, c = c0 + 2 * tx;
+        float a = 0.0f, b = 0.0f;
+        if (r < rows) {
+            if (c + 1 < cols && (cols & 1) == 0) {
+                if (sizeof(TI) == 4) { const float2 v = *reinterpret_cast<const float2*>(in + (size_t)r * cols + c); a = v.x; b = v.y; }
+                else { const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(in + (size_t)r * cols + c); a = __low2float(v); b = __high2float(v); }
+            } else {
+                if (c < cols) a = Cvt<TI>::ld(in, (size_t)r * cols + c);
+                if (c + 1 < cols) b = Cvt<TI>::ld(in, (size_t)r * cols + c + 1);
+            }
+        }
+        tile[j][2 * tx] = a; tile[j][2 * tx + 1] = b;
+    }
+    __syncthreads();
+    for (int j = ty; j < 64; j += 8) {
+        const int oc = c0 + j, orr = r0 + 2 * tx;                   // out row = input column
+        if (oc >= cols) continue;
+        const float a = tile[2 * tx][j], b = tile[2 * tx + 1][j];
+        if (orr + 1 < rows && (rows & 1) == 0) {
+            *reinterpret_cast<__nv_bfloat162*>(out + (size_t)oc * rows + orr) = __floats2bfloat162_rn(a, b);
+        } else {
+            if (orr < rows) out[(size_t)oc * rows + orr] = __float2bfloat16_rn(a);
+            if (orr + 1 < rows) out[(size_t)oc * rows + orr + 1] = __float2bfloat16_rn(b);
+        }
+    }
+}
+
+int ltl_transpose_any_to_bf16(const void* in, int in_dtype, bf16* out, int rows, int cols, cudaStream_t s)
+{
+    if (!in || !out) return ltl_fail(LTL_ERR_NULL, "transpose: null pointer");
+    if (rows <= 0 || cols <= 0) return LTL_OK;
+    dim3 grid((cols + 63) / 64, (rows + 63) / 64);
+    if (grid.y > 65535) return ltl_fail(LTL_ERR_SHAPE, "transpose: %d rows exceed the grid", rows);
+    if (in_dtype == LTL_F32) transpose_any_to_bf16_kernel<float><<<grid, 256, 0, s>>>((const float*)in, out, rows, cols);
+    else if (in_dtype == LTL_BF16) transpose_any_to_bf16_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)in, out, rows, cols);
+    else return ltl_fail(LTL_ERR_DTYPE, "transpose: input dtype %d", in_dtype);
+    return ltl_check_launch("transpose");
+}
+
 // ------------------------------------------------------------------------------------------
 // Optimisers.  AdamW as the reference's GPU path (cuda/luaTL_core.cu:1348; bias correction
 // cuda/luaTL_train.cu:1428-1431); SGD as the reference's CPU path

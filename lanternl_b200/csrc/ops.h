@@ -48,6 +48,7 @@ int ltl_sgd(float* w, const float* g, bf16* w_lp, uint64_t n, float lr, float wd
             const float* nsq, float max_norm, cudaStream_t s);
 // out[c, r] = (bf16) in[r, c]
 // interleave_half = F > 0: output row j < F goes to row 2j, row F + j to row 2j + 1 (gate/up pairs).
+int ltl_transpose_any_to_bf16(const void* in, int in_dtype, bf16* out, int rows, int cols, cudaStream_t s);
 int ltl_transpose_to_bf16(const float* in, bf16* out, int rows, int cols, int interleave_half, cudaStream_t s);
 
 // ---- CUDA-core GEMM with explicit strides (gemm_simt.cu) ----
@@ -122,3 +123,4 @@ int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int
                 int bn, int epi, int ksplit, cudaStream_t s);
 void ltl_gemm_tc_plan_split(int M, int N, int K, int* bn, int* ksplit);
 int ltl_gemm_tc_check(cudaStream_t s);
+int ltl_gemm_tc_plan_accum(int M, int N, int K, int bn);

@@ -199,21 +199,24 @@ class Model:
             valid += n
         return ids, tgt, valid
 
-    def _args(self, lr, step, valid_global=0, no_update=False):
+    def _args(self, lr, step, valid_global=0, no_update=False, accumulate=False, skip_allreduce=False):
         return _lib.LmTrainArgs(0 if self.optimizer == "sgd" else 1, int(step), lr, self.weight_decay,
                                 self.clip_norm, self.beta1, self.beta2, self.adam_eps, int(valid_global),
-                                int(no_update))
+                                int(no_update), int(accumulate), int(skip_allreduce))
 
     # ---- public API ----
-    def train_step_ids(self, ids, tgt, lr, step=1, valid_global=0, no_update=False):
-        """0-indexed [B, T] int32 blocks (pad: id 0, target -1)."""
+    def train_step_ids(self, ids, tgt, lr, step=1, valid_global=0, no_update=False, accumulate=False,
+                       skip_allreduce=False):
+        """0-indexed [B, T] int32 blocks (pad: id 0, target -1).  accumulate / no_update / skip_allreduce split one
+        optimizer step into micro-batches: first block accumulate=False, the others True; no_update (and
+        skip_allreduce) True on all but the last; valid_global = valid targets of the whole step."""
         self._alive("train_step")
         ids = np.ascontiguousarray(ids, dtype=np.int32)
         tgt = np.ascontiguousarray(tgt, dtype=np.int32)
         if ids.shape != (self.B, self.T) or tgt.shape != (self.B, self.T):
             raise ValueError(f"gpu_transformer: expected [{self.B}, {self.T}] id and target blocks")
         res = _lib.LmResult()
-        a = self._args(lr, step, valid_global, no_update)
+        a = self._args(lr, step, valid_global, no_update, accumulate, skip_allreduce)
         _lib.call("luaTL_lm_train_step", self._h, ids.ctypes.data_as(C.c_void_p), tgt.ctypes.data_as(C.c_void_p),
                   C.byref(a), C.byref(res))
         self._last_ms = res.step_ms

@@ -96,3 +96,29 @@ def test_split_k_partials_sum_to_the_product(M, N, K, ks):
         lo, hi = z * per * 64, min(K, (z + 1) * per * 64)
         want = a[:, lo:hi].astype(np.float64) @ b[:, lo:hi].astype(np.float64).T if lo < K else np.zeros((M, N))
         assert rel_err(parts[z], want) < 1e-5 or np.abs(parts[z] - want).max() < 1e-6
+
+
+@pytest.mark.parametrize("M,N,K,tile,ks", [(128, 384, 4096, 128, 16), (200, 136, 1000, 64, 3), (2048, 2048, 2048, 128, 1),
+                                          (64, 8, 264, 32, 5)])
+def test_accumulating_epilogue_adds_into_c(M, N, K, tile, ks):
+    """Weight-gradient form: C += A B^T over split-K slices with atomic adds; two calls add twice.  The big case has
+    enough tiles for the two-CTAs-per-SM ring."""
+    a = bf16_round(synth.normal(21, 0, M * K).reshape(M, K).astype(np.float32))
+    b = bf16_round((synth.normal(22, 0, N * K) * 0.1).reshape(N, K).astype(np.float32))
+    c0 = synth.normal(23, 0, M * N).reshape(M, N).astype(np.float32)
+    A, B = bf16_dev(a), bf16_dev(b)
+    Cc = ad.TensorView(M, N, _lib.F32)
+    Cc.upload(c0.ravel())
+    flags = tile | (1 << 17) | (ks << 20)
+    for _ in range(2):
+        _lib.call("luaTL_gemm_bf16_tc", A.data, B.data, Cc.data, None, M, N, K, _lib.F32, flags)
+    ref = c0.astype(np.float64) + 2.0 * (a.astype(np.float64) @ b.astype(np.float64).T)
+    assert rel_err(Cc.download().reshape(M, N), ref) < 1e-5
+
+
+def test_many_tile_grid_uses_the_shallow_ring():
+    """4096 x 2816 x 512 (704 tiles): the two-CTAs-per-SM launch configuration of prefill and training."""
+    got, ref = run(4096, 2816, 512, 128, seed=9)
+    assert rel_err(got, ref) < 1e-5
+    got, ref = run(4096, 1536, 520, 64, c_dtype=_lib.BF16, seed=10)
+    assert rel_err(got, ref) < 8e-3

@@ -338,9 +338,9 @@ def test_model_duck_type_errors_and_checkpoint_streaming():
         m.read_param(1, 1, 1)
 
 
-def test_bf16_model_refuses_to_train():
-    m = make(dict(CFG0), 1, dtype="bf16")
-    with pytest.raises(LuaTLError, match="UNSUPPORTED"):
+def test_bf16_training_needs_multiples_of_8():
+    m = make(dict(CFG0, vocab=300), 1, dtype="bf16")
+    with pytest.raises(LuaTLError, match="SHAPE"):
         m.train_step_ids(np.zeros((1, 64), np.int32), np.zeros((1, 64), np.int32), lr=0.1)
 
 
@@ -362,3 +362,58 @@ def test_bulk_staged_decode_attention_long_context(dtype, heads):
         else:
             assert_tokens_consistent(o, w, prompts, got, 5e-3)
         m.free()
+
+
+# Mixed-precision training step (bf16 model): fp32 master weights and gradients, bf16 activations, every
+# contraction on the tensor cores.  Bounds, against the oracle run with the same bf16 stores in its forward:
+# loss 2e-3 relative; each gradient tensor 3e-2 relative in L2 (the backward rounds activation gradients and
+# both GEMM operands to bf16, 2^-9 per element, which the oracle's backward does not).
+MIXED_LOSS_TOL, MIXED_GRAD_TOL = 2e-3, 3e-2
+
+
+@pytest.mark.parametrize("cfg,B", [(CFG0, 2), (CFG1, 32)])
+def test_mixed_precision_training_step_loss_and_gradients(cfg, B):
+    T = cfg["max_seq"]
+    w = bf16_round(params_for(cfg, seed=0, gain_jitter=0.1))
+    ids = synth.zipf_ids(3, B * T, cfg["vocab"]).reshape(B, T)
+    tgt = shifted_targets(ids)
+    tgt[B - 1, T // 2:] = -1
+    o = oracle_for(cfg, act_bf16=True)
+    ref = o.loss_grad(w, ids, tgt)
+    m = make(cfg, B, w, dtype="bf16", optimizer="sgd")
+    loss, correct, valid, _, finite = m.train_step_ids(ids, tgt, lr=0.0, no_update=True)
+    assert finite and valid == ref["valid"]
+    assert abs(loss - ref["loss"]) < MIXED_LOSS_TOL * abs(ref["loss"])
+    got, want = split_params(m.flat_grads(), cfg), split_params(ref["grads"], cfg)
+    worst = max((l2_err(got[n], want[n]), n) for n in want)
+    assert worst[0] < MIXED_GRAD_TOL, worst
+    # the update acts on the fp32 master weights
+    lr = 0.05
+    m.train_step_ids(ids, tgt, lr=lr)
+    g = m.flat_grads()
+    assert np.allclose(m.flat_params(), w - lr * g, rtol=0, atol=1e-7)
+    m.free()
+
+
+def test_mixed_precision_micro_batches_accumulate_into_one_step():
+    cfg, T = CFG0, CFG0["max_seq"]
+    w = bf16_round(params_for(cfg, seed=4))
+    ids = synth.uniform_ids(5, 4 * T, cfg["vocab"]).reshape(4, T)
+    tgt = shifted_targets(ids)
+    tgt[3, 10:] = -1
+    valid = int((tgt >= 0).sum())
+    full = make(cfg, 4, w, dtype="bf16", optimizer="sgd")
+    loss_full, *_ = full.train_step_ids(ids, tgt, lr=0.0, no_update=True)
+    g_full = full.flat_grads()
+    full.free()
+    m = make(cfg, 2, w, dtype="bf16", optimizer="sgd", decode_batch=1)
+    m.train_step_ids(ids[:2], tgt[:2], lr=0.0, valid_global=valid, no_update=True, skip_allreduce=True)
+    loss, *_ = m.train_step_ids(ids[2:], tgt[2:], lr=0.1, valid_global=valid, accumulate=True)
+    assert abs(loss - loss_full) < 1e-4 * abs(loss_full)
+    g = m.flat_grads()
+    assert l2_err(g, g_full) < 2e-3               # same arithmetic, other split of the token sum
+    assert np.allclose(m.flat_params(), w - 0.1 * g, rtol=0, atol=1e-7)
+    # generation after training: the decode path runs on the re-laid-out weights
+    got = m.generate_batch(ids[:1, :8], 6, zero_indexed=True)
+    assert got.shape == (1, 6) and (got >= 0).all() and (got < cfg["vocab"]).all()
+    m.free()
