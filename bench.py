@@ -35,6 +35,8 @@ DECODE = dict(vocab=8000, dim=512, layers=8, heads=8, ffn=1408, max_seq=1024)
 TRAIN = dict(vocab=2000, dim=128, layers=4, heads=8, ffn=256, max_seq=128)
 NSEQ_TOTAL, N_PROMPT, N_NEW = 256, 128, 512
 TRAIN_B = 32
+TRAIN4 = dict(vocab=32000, dim=2048, layers=16, heads=16, ffn=5632, max_seq=2048)
+TRAIN4_GLOBAL_BATCH = 64
 
 
 def peaks():
@@ -327,6 +329,138 @@ def run_train(args, dist):
     return line
 
 
+def fill_params_tiled(m, seed=0, std=0.02, block=1 << 24):
+    """N(0, std) weights for a model too large to draw element by element on the host in reasonable time: one block
+    of 16 M seeded normal values is written over the flat parameter buffer again and again (every matrix still
+    holds N(0, std) values; the matrices are not independent of each other, which throughput does not see),
+    then the gains are set to 1."""
+    from lanternl_b200 import _lib, synth
+    blk = (synth.normal(seed, 0, block) * std).astype(np.float32)
+    n = m.nparams()
+    for off in range(0, n, block):
+        cnt = min(block, n - off)
+        _lib.call("luaTL_lm_write_params", m._h, off, cnt, blk.ctypes.data_as(C.c_void_p))
+    for t in m.params:
+        if t["rows"] == 1:
+            ones = np.ones(t["nelem"], np.float32)
+            _lib.call("luaTL_lm_write_params", m._h, t["offset"], t["nelem"], ones.ctypes.data_as(C.c_void_p))
+
+
+def run_train4(args, dist):
+    """configs[4]: data-parallel mixed-precision training (bf16 tensor-core GEMMs, fp32 master weights, SGD).  The
+    global batch of 64 sequences x 2048 tokens is split over the ranks; each rank walks its share in micro-batches
+    that accumulate into the flat gradient, then one NCCL all-reduce and the SGD kernel."""
+    from lanternl_b200 import _lib, gpu_transformer as GT, luatl_adapter as ad, synth
+    cfg = dict(TRAIN4)
+    if args.layers:
+        cfg["layers"] = args.layers
+    _lib.init(dist.local)
+    if dist.world > 1:
+        uid = C.create_string_buffer(128)
+        if dist.rank == 0:
+            _lib.call("luaTL_comm_unique_id", uid)
+        raw = dist.broadcast_bytes(uid.raw, 128)
+        _lib.call("luaTL_comm_init", raw, dist.world, dist.rank)
+    T = cfg["max_seq"]
+    gb = args.global_batch
+    if gb % dist.world:
+        raise SystemExit(f"global batch {gb} does not split over {dist.world} ranks")
+    per_rank = gb // dist.world
+    mb = min(args.micro_batch, per_rank)
+    if per_rank % mb:
+        raise SystemExit(f"{per_rank} sequences per rank do not split into micro-batches of {mb}")
+    n_micro = per_rank // mb
+    m = GT.new(dict(cfg, batch_size=mb, decode_batch=0, dtype="bf16", optimizer="sgd", init=False))
+    fill_params_tiled(m)
+    ids = synth.zipf_ids(1 + dist.rank, per_rank * T, cfg["vocab"]).reshape(n_micro, mb, T)
+    tgt = np.full_like(ids, -1)
+    tgt[:, :, :-1] = ids[:, :, 1:]
+    valid_global = int((tgt >= 0).sum()) * dist.world
+    d_ids = [ad.ids(mb * T) for _ in range(n_micro)]
+    d_tgt = [ad.ids(mb * T) for _ in range(n_micro)]
+    for i in range(n_micro):
+        ad.upload_i32(d_ids[i], ids[i])
+        ad.upload_i32(d_tgt[i], tgt[i])
+    res = _lib.LmResult()
+
+    def micro_args(i, step):
+        last = i == n_micro - 1
+        return m._args(0.01, step, valid_global, no_update=not last, accumulate=i > 0, skip_allreduce=not last)
+
+    def step_dev(step):
+        ms, launches = 0.0, 0
+        for i in range(n_micro):
+            a = micro_args(i, step)
+            _lib.call("luaTL_lm_train_step_dev", m._h, d_ids[i].t.data, d_tgt[i].t.data, C.byref(a), C.byref(res))
+            ms += res.step_ms
+            launches += m.last_timing()["launches"]
+        return ms, launches
+
+    for w in range(args.warmup):
+        step_dev(w + 1)
+    clocks = Clocks(dist.local)
+    clocks.start()
+    dist.barrier()
+    dev_ms, launches = 0.0, 0
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        ms, ln = step_dev(s + 1)
+        dev_ms += ms
+        launches += ln
+    dist.barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    clk = clocks.stop()
+    loss = res.loss
+    # end to end: ids and targets come from host memory every micro-batch, the loss goes back
+    dist.barrier()
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        for i in range(n_micro):
+            last = i == n_micro - 1
+            m.train_step_ids(ids[i], tgt[i], 0.01, s + 1, valid_global=valid_global, no_update=not last,
+                             accumulate=i > 0, skip_allreduce=not last)
+    dist.barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    dev_ms, e2e_ms, wall_ms = dist.max(dev_ms), dist.max(e2e_ms), dist.max(wall_ms)
+    tokens = gb * T * args.steps
+    pk = peaks()
+    # dominant GEMM alone: the feed-forward up projection of one micro-batch, [mb*T, D] x [D, 2F]
+    R, D, F2 = mb * T, cfg["dim"], 2 * cfg["ffn"]
+    A, B, Cc = ad.TensorView(R, D, _lib.BF16), ad.TensorView(F2, D, _lib.BF16), ad.TensorView(R, F2, _lib.BF16)
+    gms = C.c_float()
+    _lib.call("luaTL_gemm_bf16_tc_time", A.data, B.data, Cc.data, R, F2, D, _lib.BF16, 0, 10, C.byref(gms))
+    gemm_tf = 2.0 * R * F2 * D / (gms.value * 1e-3) / 1e12
+    # model FLOPs of the step: 6 x parameters in matrices x tokens (+ attention)
+    L, H, hd, V = cfg["layers"], cfg["heads"], cfg["dim"] // cfg["heads"], cfg["vocab"]
+    mat = L * (4 * D * D + 3 * D * cfg["ffn"]) + V * D
+    gemm_flops = 6.0 * mat * gb * T
+    attn_flops = 3.0 * L * gb * H * 2 * T * T * hd          # causal halves the 4 T^2 hd of QK^T + PV; x3 for fwd + bwd
+    step_tf = (gemm_flops + attn_flops) * args.steps / (dev_ms * 1e-3) / 1e12 / dist.world
+    line = dict(
+        metric="train_tokens_per_s", value=tokens / (dev_ms * 1e-3), unit="tokens/s", n_gpus=dist.world,
+        steps=args.steps, warmup=args.warmup, ms_per_step=dev_ms / args.steps, higher_is_better=True, scaling="strong",
+        vs_baseline=None, dtype="bf16", data="synthetic",
+        config=dict(workload=f"configs[4] data-parallel training: V32000 D2048 L{L} H16 F5632 ctx2048, global batch {gb} x 2048 "
+                             "(Zipf 1.1), bf16 tensor-core GEMMs with fp32 master weights, gradients and residual stream, SGD",
+                    global_batch=gb, seq_len=T, micro_batch=mb, micro_batches_per_rank=n_micro,
+                    parallelism=f"dp{dist.world}" + (" (NCCL all-reduce of the flat gradient)" if dist.world > 1 else ""),
+                    l2="working set far larger than L2 (11 GB of weights and gradients, > 10 GB of activations)",
+                    weights="N(0, 0.02): one seeded block of 16 M values tiled over the parameter buffer, gains 1"),
+        e2e=dict(value=tokens / (e2e_ms * 1e-3), unit="tokens/s", h2d_bytes_per_step=int(ids.nbytes + tgt.nbytes) * dist.world,
+                 d2h_bytes_per_step=8 * n_micro * dist.world),
+        gpu_launches=int(launches),
+        roofline=dict(bound="tensor", achieved=gemm_tf, peak=pk["bf16_tflops"], unit="TFLOP/s", frac=gemm_tf / pk["bf16_tflops"],
+                      traffic=None, peak_source=pk["source"],
+                      kernel=f"gemm_tc_kernel<128,bf16>: feed-forward up projection of one micro-batch, {R} x {F2} x {D}, "
+                             "10 launches back to back, CUDA events on the launching stream",
+                      flops_per_launch=2.0 * R * F2 * D, us_per_launch=gms.value * 1e3,
+                      whole_step=dict(note="model FLOPs (6 x matrix parameters x tokens + causal attention) over the step time, per GPU",
+                                      achieved=step_tf, frac=step_tf / pk["bf16_tflops"])),
+        final_loss=loss, wall_ms_per_step=wall_ms / args.steps, clocks=clk)
+    m.free()
+    return line
+
+
 def host_threads():
     """Host threads this process may use (cgroup / affinity aware), at most 32 and at most one per sequence."""
     try:
@@ -422,7 +556,10 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "train"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "train", "train4"])
+    ap.add_argument("--micro-batch", type=int, default=8, help="train4: sequences per micro-batch")
+    ap.add_argument("--global-batch", type=int, default=TRAIN4_GLOBAL_BATCH, help="train4: sequences per optimizer step over all GPUs")
+    ap.add_argument("--layers", type=int, default=0, help="train4: layer count override (profiling aid; the metric uses 16)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--nseq", type=int, default=NSEQ_TOTAL, help="sequences over all GPUs (profiling aid; the metric uses 256)")
     ap.add_argument("--n-prompt", type=int, default=N_PROMPT, help="prompt length (profiling aid; the metric uses 128)")
@@ -436,7 +573,7 @@ def main():
             print(json.dumps(run_reference(args, d)), flush=True)
         return
     dist = Dist(args.gpus)
-    line = run_decode(args, dist) if args.workload == "decode" else run_train(args, dist)
+    line = {"decode": run_decode, "train": run_train, "train4": run_train4}[args.workload](args, dist)
     if dist.rank == 0:
         if dist.world == 1 and not args.no_cpu_baseline:
             threads = host_threads()

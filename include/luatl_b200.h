@@ -214,6 +214,17 @@ int luaTL_sgd(float* w, const float* g, uint64_t n, float lr, float wd, const fl
  * The reference has no tensor-core path for bf16 (its only one is fp16 wmma, cuda/luaTL_core.cu:1296). */
 int luaTL_gemm_bf16_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
                        int c_dtype, int tile_n);
+/* New: fused causal attention over a packed qkv [B*T, 3*H*head_dim] (q | k | v in every row): out [B*T, H*head_dim],
+ * lse [B*H*T] (natural log of the softmax denominator, may be NULL).  The reference composes attention from
+ * batched score GEMMs, a [B*H*T, T] softmax and a second GEMM (ai/gpu/gpu_transformer.lua:333-352); it has no fused
+ * counterpart.  impl: 0 = choose, 1 = CUDA-core kernel (f32 / bf16, head_dim 16..128), 2 = tcgen05 kernel (bf16,
+ * head_dim 64 or 128, T a multiple of 8). */
+int luaTL_attention_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int hd, float scale, int causal,
+                        int dtype, int impl);
+/* New: the same GEMM launched `iters` times back to back on the library stream and timed with CUDA events
+ * (ms per launch), for roofline measurements without host gaps.  No residual operand. */
+int luaTL_gemm_bf16_tc_time(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int tile_n,
+                            int iters, float* ms_per_launch);
 
 /* ---------------- Program: command buffer + CUDA graph (cuda/luaTL_train.cu:1506-1712) ---- */
 luaTL_prog_t* luaTL_prog_create(int capacity, int timing);

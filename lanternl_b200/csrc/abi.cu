@@ -594,6 +594,49 @@ int luaTL_gemm_bf16_tc(const void* A, const void* B, void* C, const void* R, int
     LTL_TRY(sync_stream("gemm_bf16_tc"));
     return ltl_gemm_tc_check(g_stream);
 }
+int luaTL_gemm_bf16_tc_time(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int tile_n,
+                            int iters, float* ms_per_launch)
+{
+    LTL_TRY(ltl_require_init("gemm_bf16_tc_time"));
+    if (!ms_per_launch || iters < 1) return ltl_fail(LTL_ERR_ARG, "gemm_bf16_tc_time: iters >= 1 and a result pointer are needed");
+    cudaEvent_t e0, e1;
+    LTL_CUDA("event", cudaEventCreate(&e0));
+    LTL_CUDA("event", cudaEventCreate(&e1));
+    int rc = LTL_OK;
+    for (int i = 0; i < 2 && rc == LTL_OK; ++i)          // warm-up (tensor maps, attributes)
+        rc = ltl_gemm_tc(A, B, C, nullptr, M, N, K, c_dtype, tile_n & 0xFFFF, (tile_n >> 16) & 3, (tile_n >> 20) & 0xFF, g_stream);
+    cudaEventRecord(e0, g_stream);
+    for (int i = 0; i < iters && rc == LTL_OK; ++i)
+        rc = ltl_gemm_tc(A, B, C, nullptr, M, N, K, c_dtype, tile_n & 0xFFFF, (tile_n >> 16) & 3, (tile_n >> 20) & 0xFF, g_stream);
+    cudaEventRecord(e1, g_stream);
+    const cudaError_t se = cudaStreamSynchronize(g_stream);
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    if (rc != LTL_OK) return rc;
+    if (se != cudaSuccess) return ltl_cuda_fail("gemm_bf16_tc_time", se);
+    *ms_per_launch = ms / (float)iters;
+    return ltl_gemm_tc_check(g_stream);
+}
+// Fused causal attention over a packed qkv [B*T, 3*H*hd] (q | k | v per row).  impl: 0 = choose, 1 = CUDA cores,
+// 2 = tensor cores (bf16, head_dim 64 / 128, T a multiple of 8).
+int luaTL_attention_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int hd, float scale, int causal,
+                        int dtype, int impl)
+{
+    LTL_TRY(ltl_require_init("attention_fwd"));
+    const bool tc_ok = ltl_attn_tc_supported(T, H, hd, dtype);
+    if (impl == 2 && !tc_ok) return ltl_fail(LTL_ERR_UNSUPPORTED, "attention_fwd: the tensor-core kernel needs bf16, head_dim 64 or 128 and T %% 8 == 0");
+    if (impl == 2 || (impl == 0 && tc_ok)) {
+        void* vt = nullptr;
+        LTL_CUDA("attention_fwd scratch", cudaMalloc(&vt, (size_t)B * T * H * hd * 2));
+        int rc = ltl_attn_fwd_tc(qkv, vt, out, lse, B, T, H, hd, scale, causal, g_stream);
+        if (rc == LTL_OK) rc = sync_stream("attention_fwd");
+        cudaFree(vt);
+        LTL_TRY(rc);
+        return ltl_gemm_tc_check(g_stream);
+    }
+    ONE_SHOT("attention_fwd", ltl_attn_fwd(qkv, out, lse, B, T, H, hd, scale, causal, dtype, g_stream));
+}
 int luaTL_sgd(float* w, const float* g, uint64_t n, float lr, float wd, const float* nsq, float max_norm)
 {
     ONE_SHOT("sgd", ltl_sgd(w, g, nullptr, n, lr, wd, nsq, max_norm, g_stream));

@@ -20,6 +20,7 @@
 #include <tuple>
 
 #include "ops.h"
+#include "tc_common.cuh"
 
 namespace {
 
@@ -30,80 +31,7 @@ constexpr int BM = 128, BK = 64, UMMA_K = 16;
 // four k-blocks.
 template <int BN> struct Ring { static constexpr int STAGES = BN == 32 ? 10 : (BN == 64 ? 8 : 6); };
 enum { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ATOMIC = 2 };
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait on a phase parity.  Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
-{
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c_inner, int c_outer, uint64_t* bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(c_inner), "r"(c_outer), "r"(smem_u32(bar)) : "memory");
-}
-
-// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 128 bytes, groups
-// of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);          // start address
-    d |= (uint64_t)1 << 16;                            // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
-    d |= (uint64_t)1 << 46;                            // descriptor version
-    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor: D fp32, A and B bf16, both K-major, shape M x N.
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N)
-{
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
+using namespace tc;
 
 // Shared memory of one CTA, carved from the dynamic allocation (1024-byte aligned for the 128-byte
 // swizzle): `stages` A tiles, `stages` B tiles, then the barriers.  The ring depth is a launch
@@ -304,17 +232,18 @@ int get_encode()
     return LTL_OK;
 }
 
-// 2-D bf16 row-major [rows, cols] with a box of box_rows x 64 columns, 128-byte swizzle.
-std::map<std::tuple<const void*, int, int, int>, CUtensorMap> g_maps;
+// 2-D bf16 matrix [rows, cols] whose rows are `pitch` elements apart, with a box of box_rows x 64 columns,
+// 128-byte swizzle, zero fill outside.
+std::map<std::tuple<const void*, int, int, long long, int>, CUtensorMap> g_maps;
 
-int tensor_map(const void* base, int rows, int cols, int box_rows, CUtensorMap* out)
+int tensor_map(const void* base, int rows, int cols, long long pitch, int box_rows, CUtensorMap* out)
 {
-    const auto key = std::make_tuple(base, rows, cols, box_rows);
+    const auto key = std::make_tuple(base, rows, cols, pitch, box_rows);
     const auto it = g_maps.find(key);
     if (it != g_maps.end()) { *out = it->second; return LTL_OK; }
     LTL_TRY(get_encode());
     const cuuint64_t dims[2] = { (cuuint64_t)cols, (cuuint64_t)rows };
-    const cuuint64_t strides[1] = { (cuuint64_t)cols * 2 };
+    const cuuint64_t strides[1] = { (cuuint64_t)pitch * 2 };
     const cuuint32_t box[2] = { (cuuint32_t)BK, (cuuint32_t)box_rows };
     const cuuint32_t estr[2] = { 1, 1 };
     const CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
@@ -332,8 +261,8 @@ template <int BN, typename TC, int EPI>
 int launch(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int ksplit, cudaStream_t s)
 {
     CUtensorMap ma, mb;
-    LTL_TRY(tensor_map(A, M, K, BM, &ma));
-    LTL_TRY(tensor_map(B, N, K, BN, &mb));
+    LTL_TRY(tensor_map(A, M, K, K, BM, &ma));
+    LTL_TRY(tensor_map(B, N, K, K, BN, &mb));
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, ksplit < 1 ? 1 : ksplit);
     const int kb_all = (K + BK - 1) / BK;
     const int kb_per = (kb_all + (int)grid.z - 1) / (int)grid.z;
@@ -357,6 +286,21 @@ int launch(const void* A, const void* B, void* C, const void* R, int M, int N, i
 }
 
 }  // namespace
+
+int ltl_tensor_map_bf16(const void* base, int rows, int cols, long long pitch, int box_rows, void* out_map)
+{
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch * 2) % 16)
+        return ltl_fail(LTL_ERR_ARG, "tensor map: base and row pitch must be 16-byte aligned");
+    return tensor_map(base, rows, cols, pitch, box_rows, reinterpret_cast<CUtensorMap*>(out_map));
+}
+int* ltl_tc_err_flag()
+{
+    if (!g_err_flag) {
+        if (cudaMalloc(&g_err_flag, sizeof(int)) != cudaSuccess) { g_err_flag = nullptr; return nullptr; }
+        cudaMemset(g_err_flag, 0, sizeof(int));
+    }
+    return g_err_flag;
+}
 
 bool ltl_gemm_tc_supported(const void* A, const void* B, int M, int N, int K)
 {

@@ -124,3 +124,11 @@ int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int
 void ltl_gemm_tc_plan_split(int M, int N, int K, int* bn, int* ksplit);
 int ltl_gemm_tc_check(cudaStream_t s);
 int ltl_gemm_tc_plan_accum(int M, int N, int K, int bn);
+// CUtensorMap (128 bytes, written to out_map) of a bf16 matrix [rows, cols] with rows `pitch` elements apart:
+// boxes of box_rows x 64 columns, 128-byte swizzle.  Cached per (base, shape).
+int ltl_tensor_map_bf16(const void* base, int rows, int cols, long long pitch, int box_rows, void* out_map);
+// Tensor-core flash attention (attention_tc.cu): bf16, head_dim 64 / 128, T a multiple of 8.
+bool ltl_attn_tc_supported(int T, int H, int hd, int dtype);
+int ltl_attn_fwd_tc(const void* qkv, void* vt_scratch, void* out, float* lse, int B, int T, int H, int hd, float scale,
+                    int causal, cudaStream_t s);
+int* ltl_tc_err_flag();        // device flag raised by a bounded wait that ran out (read by ltl_gemm_tc_check)

@@ -114,7 +114,8 @@ class Model:
             _lib.call("luaTL_lm_tensor_info", self._h, i, name, C.byref(r), C.byref(cc), C.byref(off), C.byref(dec))
             self.params.append(dict(name=name.value.decode(), rows=r.value, cols=cc.value, nelem=r.value * cc.value,
                                     offset=off.value, decay=bool(dec.value)))
-        self._init_weights(cfg.get("seed"))
+        if cfg.get("init", True):           # init = False: weights stay zero until load_flat / write_param
+            self._init_weights(cfg.get("seed"))
         self._slots_used = 0
 
     # ---- parameters ----
