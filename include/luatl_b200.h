@@ -221,6 +221,10 @@ int luaTL_gemm_bf16_tc(const void* A, const void* B, void* C, const void* R, int
  * head_dim 64 or 128, T a multiple of 8). */
 int luaTL_attention_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, int hd, float scale, int causal,
                         int dtype, int impl);
+/* New: backward of luaTL_attention_fwd.  dqkv [B*T, 3*H*head_dim] (dq | dk | dv per row, before the inverse RoPE)
+ * from out and dout [B*T, H*head_dim] and the lse the forward wrote.  Same impl values. */
+int luaTL_attention_bwd(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv, int B, int T,
+                        int H, int hd, float scale, int causal, int dtype, int impl);
 /* New: the same GEMM launched `iters` times back to back on the library stream and timed with CUDA events
  * (ms per launch), for roofline measurements without host gaps.  No residual operand. */
 int luaTL_gemm_bf16_tc_time(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int tile_n,

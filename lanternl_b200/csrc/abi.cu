@@ -637,6 +637,27 @@ int luaTL_attention_fwd(const void* qkv, void* out, float* lse, int B, int T, in
     }
     ONE_SHOT("attention_fwd", ltl_attn_fwd(qkv, out, lse, B, T, H, hd, scale, causal, dtype, g_stream));
 }
+// Backward of luaTL_attention_fwd: dqkv [B*T, 3*H*hd] from out, dout [B*T, H*hd] and lse [B*H*T].
+int luaTL_attention_bwd(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv, int B, int T,
+                        int H, int hd, float scale, int causal, int dtype, int impl)
+{
+    LTL_TRY(ltl_require_init("attention_bwd"));
+    const bool tc_ok = ltl_attn_tc_supported(T, H, hd, dtype);
+    if (impl == 2 && !tc_ok) return ltl_fail(LTL_ERR_UNSUPPORTED, "attention_bwd: the tensor-core kernels need bf16, head_dim 64 or 128 and T %% 8 == 0");
+    const bool tc = impl == 2 || (impl == 0 && tc_ok);
+    const size_t hm = (size_t)B * T * H * hd;
+    float* delta = nullptr;
+    void* scratch = nullptr;
+    LTL_CUDA("attention_bwd scratch", cudaMalloc(&delta, (size_t)B * H * T * 4));
+    if (tc && cudaMalloc(&scratch, 3 * hm * 2) != cudaSuccess) { cudaFree(delta); cudaGetLastError(); return ltl_fail(LTL_ERR_OOM, "attention_bwd: scratch"); }
+    int rc = tc ? ltl_attn_bwd_tc(qkv, out, dout, lse, delta, scratch, dqkv, B, T, H, hd, scale, causal, g_stream)
+                : ltl_attn_bwd(qkv, out, dout, lse, delta, dqkv, B, T, H, hd, scale, causal, dtype, g_stream);
+    if (rc == LTL_OK) rc = sync_stream("attention_bwd");
+    cudaFree(delta);
+    if (scratch) cudaFree(scratch);
+    LTL_TRY(rc);
+    return tc ? ltl_gemm_tc_check(g_stream) : LTL_OK;
+}
 int luaTL_sgd(float* w, const float* g, uint64_t n, float lr, float wd, const float* nsq, float max_norm)
 {
     ONE_SHOT("sgd", ltl_sgd(w, g, nullptr, n, lr, wd, nsq, max_norm, g_stream));

@@ -382,6 +382,16 @@ int ltl_attn_fwd(const void* qkv, void* out, float* lse, int B, int T, int H, in
     ATTN_DISPATCH(launch_fwd, qkv, out, lse, B, T, H, scale, causal, s);
 }
 
+// delta[b, h, t] = sum_d dO[t, d] O[t, d], the row term of the softmax backward.
+int ltl_attn_delta(const void* out, const void* dout, float* delta, int B, int T, int H, int hd, int dtype, cudaStream_t s)
+{
+    const int nw = B * T * H;
+    if (dtype == LTL_F32) attn_delta_kernel<float><<<(nw * 32 + 255) / 256, 256, 0, s>>>((const float*)out, (const float*)dout, delta, B, T, H, hd);
+    else if (dtype == LTL_BF16) attn_delta_kernel<bf16><<<(nw * 32 + 255) / 256, 256, 0, s>>>((const bf16*)out, (const bf16*)dout, delta, B, T, H, hd);
+    else return ltl_fail(LTL_ERR_DTYPE, "attn_delta: dtype %d", dtype);
+    return ltl_check_launch("attn_delta");
+}
+
 int ltl_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
                  void* dqkv, int B, int T, int H, int hd, float scale, int causal, int dtype,
                  cudaStream_t s)

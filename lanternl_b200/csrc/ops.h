@@ -131,4 +131,7 @@ int ltl_tensor_map_bf16(const void* base, int rows, int cols, long long pitch, i
 bool ltl_attn_tc_supported(int T, int H, int hd, int dtype);
 int ltl_attn_fwd_tc(const void* qkv, void* vt_scratch, void* out, float* lse, int B, int T, int H, int hd, float scale,
                     int causal, cudaStream_t s);
+int ltl_attn_bwd_tc(const void* qkv, const void* out, const void* dout, const float* lse, float* delta, void* scratch,
+                    void* dqkv, int B, int T, int H, int hd, float scale, int causal, cudaStream_t s);
+int ltl_attn_delta(const void* out, const void* dout, float* delta, int B, int T, int H, int hd, int dtype, cudaStream_t s);
 int* ltl_tc_err_flag();        // device flag raised by a bounded wait that ran out (read by ltl_gemm_tc_check)

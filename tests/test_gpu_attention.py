@@ -63,3 +63,49 @@ def test_tensor_core_attention_rejects_unsupported_shapes():
     o = ad.TensorView(100, 32, _lib.BF16)
     with pytest.raises(_lib.LuaTLError, match="UNSUPPORT"):
         _lib.call("luaTL_attention_fwd", x.data, o.data, None, 1, 100, 1, 32, 0.1, 1, _lib.BF16, 2)
+
+
+def reference_bwd(qkv, dout, B, T, H, hd, scale):
+    D = H * hd
+    x = qkv.astype(np.float64).reshape(B, T, 3, H, hd)
+    q, k, v = x[:, :, 0], x[:, :, 1], x[:, :, 2]
+    do = dout.astype(np.float64).reshape(B, T, H, hd)
+    s = np.einsum("bthd,bshd->bhts", q, k) * scale
+    s = np.where(np.tril(np.ones((T, T), bool))[None, None], s, -np.inf)
+    p = np.exp(s - s.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    dv = np.einsum("bhts,bthd->bshd", p, do)
+    dp = np.einsum("bthd,bshd->bhts", do, v)
+    ds = p * (dp - (dp * p).sum(-1, keepdims=True)) * scale
+    dq = np.einsum("bhts,bshd->bthd", ds, k)
+    dk = np.einsum("bhts,bthd->bshd", ds, q)
+    return np.stack([dq, dk, dv], axis=2).reshape(B * T, 3 * D)
+
+
+def run_bwd(B, T, H, hd, impl, seed):
+    D = H * hd
+    qkv = bf16_round(synth.normal(seed, 0, B * T * 3 * D).reshape(B * T, 3 * D).astype(np.float32))
+    dout = bf16_round(synth.normal(seed + 1, 0, B * T * D).reshape(B * T, D).astype(np.float32))
+    scale = 1.0 / np.sqrt(hd)
+    x, o = ad.TensorView(B * T, 3 * D, _lib.BF16), ad.TensorView(B * T, D, _lib.BF16)
+    g, dx = ad.TensorView(B * T, D, _lib.BF16), ad.TensorView(B * T, 3 * D, _lib.BF16)
+    lse = ad.TensorView(B * H, T, _lib.F32)
+    x.upload(qkv.ravel())
+    g.upload(dout.ravel())
+    _lib.call("luaTL_attention_fwd", x.data, o.data, lse.data, B, T, H, hd, scale, 1, _lib.BF16, impl)
+    _lib.call("luaTL_attention_bwd", x.data, o.data, g.data, lse.data, dx.data, B, T, H, hd, scale, 1, _lib.BF16, impl)
+    return dx.download().reshape(B * T, 3 * D), reference_bwd(qkv, dout, B, T, H, hd, scale)
+
+
+# dq, dk, dv are bf16 outputs of bf16 tensor-core products (P, dS and the operands rounded to bf16)
+TOL_GRAD = 1.5e-2
+
+
+@pytest.mark.parametrize("impl", [1, 2])
+@pytest.mark.parametrize("B,T,H,hd", [(2, 128, 2, 64), (1, 256, 2, 128), (2, 200, 1, 64), (1, 520, 2, 128), (2, 64, 2, 64)])
+def test_attention_backward_matches_float64(B, T, H, hd, impl):
+    got, ref = run_bwd(B, T, H, hd, impl, seed=7 * T + hd)
+    D = H * hd
+    for name, sl in (("dq", slice(0, D)), ("dk", slice(D, 2 * D)), ("dv", slice(2 * D, 3 * D))):
+        e = rel_err(got[:, sl], ref[:, sl])
+        assert e < TOL_GRAD, (name, e)
