@@ -64,6 +64,9 @@ struct luaTL_lm_s {
     bf16* Wm = nullptr;          // second bf16 mirror for the backward: the other orientation of every matrix
     int mirror_dirty = 1;
     int train_tc = 0;            // bf16 model that has been asked to train: mixed-precision step
+    int attn_tc = 1;             // tensor-core attention where the shape allows (LUATL_ATTN_TC=0 turns it off)
+    bf16* att_scratch = nullptr; // head-major copies for the tensor-core attention (V; Q, K, dO in the backward)
+    size_t att_scratch_elems = 0;
     // mixed-precision backward scratch (bf16): activation gradients and token-major transposes
     bf16 *b_dres = nullptr, *b_dhs = nullptr, *b_dh13 = nullptr, *b_dattn = nullptr, *b_dqkv = nullptr, *b_dl = nullptr,
          *tX = nullptr, *tG = nullptr;
@@ -188,6 +191,19 @@ int ensure_ws(LM* m, size_t floats)
     return LTL_OK;
 }
 
+int ensure_att_scratch(LM* m, size_t elems)
+{
+    if (m->att_scratch_elems >= elems) return LTL_OK;
+    if (m->att_scratch) { LTL_CUDA("sync", cudaStreamSynchronize(m->s)); cudaFree(m->att_scratch); m->att_scratch = nullptr; }
+    DALLOC(m->att_scratch, elems * 2, "attention scratch");
+    m->att_scratch_elems = elems;
+    return LTL_OK;
+}
+bool use_attn_tc(const LM* m, int T)
+{
+    return m->attn_tc && m->use_tc && m->adt == LTL_BF16 && m->c.causal && ltl_attn_tc_supported(T, m->H, m->hd, LTL_BF16);
+}
+
 // bf16 mirror: matrices transposed to [out, in] (K contiguous, the layout the tensor-core
 // GEMM wants for its B operand), tok_emb and gains cast in place.
 int sync_mirror(LM* m)
@@ -293,7 +309,13 @@ int forward(LM* m, Act& a, const int32_t* d_ids, int nseq, int T, int mode)
         if (m->c.use_rope)
             LTL_TRY(ltl_rope(qkv, a.posids, rows, 2 * H, hd, 3 * D, 0, m->c.rope_base, m->c.rope_interleaved, 0,
                              adt, m->rope_tab, m->T, m->s));
-        LTL_TRY(ltl_attn_fwd(qkv, attn, lse, nseq, T, H, hd, m->scale, m->c.causal, adt, m->s));
+        if (use_attn_tc(m, T)) {
+            LTL_TRY(ensure_att_scratch(m, (size_t)rows * D));
+            LTL_TRY(ltl_attn_fwd_tc(qkv, m->att_scratch, attn, lse, nseq, T, H, hd, m->scale, 1, m->s));
+            m->launches++;
+        } else {
+            LTL_TRY(ltl_attn_fwd(qkv, attn, lse, nseq, T, H, hd, m->scale, m->c.causal, adt, m->s));
+        }
         if (mode == MODE_PREFILL) {
             const size_t cl = (size_t)m->nseq_cap * H * m->T * hd * e;
             LTL_TRY(ltl_kv_store(qkv, (char*)m->kc + l * cl, (char*)m->vc + l * cl, nseq, T, H, hd, m->T, adt, m->s));
@@ -480,8 +502,14 @@ int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T)
         LTL_TRY(ltl_cast(m->dres, LTL_F32, m->b_dres, LTL_BF16, (uint64_t)rows * D, m->s));
         LTL_TRY(dx_gemm(m, m->b_dres, D, m->Wm + o.wo, D, m->b_dattn, LTL_BF16, rows));             // dattn = dres Wo^T
         LTL_TRY(dw_gemm(m, attn, LTL_BF16, D, m->b_dres, LTL_BF16, D, G + o.wo, rows));             // dWo += attn^T dres
-        LTL_TRY(ltl_attn_bwd(qkv, attn, m->b_dattn, lse, m->delta, m->b_dqkv, nseq, T, H, hd, m->scale, m->c.causal,
-                             LTL_BF16, m->s));
+        if (use_attn_tc(m, T)) {
+            LTL_TRY(ensure_att_scratch(m, (size_t)3 * rows * D));
+            LTL_TRY(ltl_attn_bwd_tc(qkv, attn, m->b_dattn, lse, m->delta, m->att_scratch, m->b_dqkv, nseq, T, H, hd, m->scale, 1, m->s));
+            m->launches += 3;
+        } else {
+            LTL_TRY(ltl_attn_bwd(qkv, attn, m->b_dattn, lse, m->delta, m->b_dqkv, nseq, T, H, hd, m->scale, m->c.causal,
+                                 LTL_BF16, m->s));
+        }
         if (m->c.use_rope)
             LTL_TRY(ltl_rope(m->b_dqkv, a.posids, rows, 2 * H, hd, 3 * D, 0, m->c.rope_base, m->c.rope_interleaved, 1,
                              LTL_BF16, m->rope_tab, m->T, m->s));
@@ -914,6 +942,8 @@ luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
         m->fuse_swiglu = m->use_tc && m->adt == LTL_BF16;
         const char* p = getenv("LUATL_PDL");
         m->use_pdl = !(p && p[0] == '0');
+        const char* at = getenv("LUATL_ATTN_TC");
+        m->attn_tc = !(at && at[0] == '0');
     }
     layout_params(m);
     int rc = LTL_OK;
@@ -941,7 +971,7 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
     void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
                      m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
                      m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part,
-                     m->Wm, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl, m->tX, m->tG };
+                     m->Wm, m->att_scratch, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl, m->tX, m->tG };
     for (void* p : ptrs) if (p) cudaFree(p);
     for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
     cudaGetLastError();
