@@ -225,6 +225,10 @@ int luaTL_attention_fwd(const void* qkv, void* out, float* lse, int B, int T, in
  * from out and dout [B*T, H*head_dim] and the lse the forward wrote.  Same impl values. */
 int luaTL_attention_bwd(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv, int B, int T,
                         int H, int hd, float scale, int causal, int dtype, int impl);
+/* New: C[M,N] (fp32) += X^T Y with X [K, M] and Y [K, N] bf16 row-major: the weight-gradient product of two
+ * token-major matrices (both tensor-core operands MN-major, nothing is transposed in memory).  M, N multiples
+ * of 8.  ksplit: slices of K added with atomics (0/1 = one). */
+int luaTL_gemm_bf16_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K, int ksplit);
 /* New: the same GEMM launched `iters` times back to back on the library stream and timed with CUDA events
  * (ms per launch), for roofline measurements without host gaps.  No residual operand. */
 int luaTL_gemm_bf16_tc_time(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int tile_n,
@@ -282,7 +286,7 @@ float* luaTL_lm_grads_device(luaTL_lm_t* m);
  * optimizer: 0 = SGD, 1 = AdamW.  valid_global <= 0: count the valid targets of this block.
  * dtype f32: exact fp32 arithmetic (CUDA-core GEMMs).  dtype bf16: mixed precision - fp32 master
  * weights, gradients and residual stream, bf16 activations, every contraction on the tensor cores with
- * fp32 accumulation; needs batch x max_seq, dim, ffn and vocab to be multiples of 8.  The first training
+ * fp32 accumulation; needs dim, ffn and vocab to be multiples of 8.  The first training
  * call of a bf16 model switches it to the training weight layout (captured decode graphs are dropped). */
 typedef struct {
     int32_t optimizer, step;

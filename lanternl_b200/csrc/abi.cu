@@ -594,6 +594,13 @@ int luaTL_gemm_bf16_tc(const void* A, const void* B, void* C, const void* R, int
     LTL_TRY(sync_stream("gemm_bf16_tc"));
     return ltl_gemm_tc_check(g_stream);
 }
+int luaTL_gemm_bf16_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K, int ksplit)
+{
+    LTL_TRY(ltl_require_init("gemm_bf16_tc_xty"));
+    LTL_TRY(ltl_gemm_tc_xty(X, Y, C, M, N, K, ksplit, g_stream));
+    LTL_TRY(sync_stream("gemm_bf16_tc_xty"));
+    return ltl_gemm_tc_check(g_stream);
+}
 int luaTL_gemm_bf16_tc_time(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int tile_n,
                             int iters, float* ms_per_launch)
 {

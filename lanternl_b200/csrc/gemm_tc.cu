@@ -53,7 +53,9 @@ template <int BN> size_t smem_bytes(int stages) { return stages * stage_bytes<BN
 // N / 2 columns.  R is ignored.
 // EPI_ATOMIC: C (fp32) += the product, with red.global.add; every split-K slice adds into the same C.
 // This is the weight-gradient form (dW += X^T dY with a long reduction over the tokens).
-template <int BN, typename TC, int EPI>
+// MAJ = 1: both operands MN-major - A is X [K, M] and B is Y [K, N] in memory (the contraction runs down the
+// rows), i.e. C = X^T Y, the weight-gradient product of two token-major activations without a transpose.
+template <int BN, typename TC, int EPI, int MAJ = 0>
 __global__ void __launch_bounds__(192, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                TC* C, const TC* R, int M, int N, int K, int STAGES, int* __restrict__ err)
@@ -102,12 +104,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (round > 0) ok = mbar_wait(&sm.empty[s], (round - 1) & 1);
             if (!ok) break;
             mbar_expect_tx(&sm.full[s], STAGE_BYTES);
-            tma_load_2d(a_tile(s), &map_a, (kb0 + kb) * BK, m0, &sm.full[s]);
-            tma_load_2d(b_tile(s), &map_b, (kb0 + kb) * BK, n0, &sm.full[s]);
+            if (MAJ == 0) {
+                tma_load_2d(a_tile(s), &map_a, (kb0 + kb) * BK, m0, &sm.full[s]);
+                tma_load_2d(b_tile(s), &map_b, (kb0 + kb) * BK, n0, &sm.full[s]);
+            } else {
+                // column blocks of 64 features: BK token rows of 128 bytes each
+#pragma unroll
+                for (int cb = 0; cb < BM / 64; ++cb) tma_load_2d(a_tile(s) + cb * (BK * 128), &map_a, m0 + cb * 64, (kb0 + kb) * BK, &sm.full[s]);
+#pragma unroll
+                for (int cb = 0; cb < BN / 64; ++cb) tma_load_2d(b_tile(s) + cb * (BK * 128), &map_b, n0 + cb * 64, (kb0 + kb) * BK, &sm.full[s]);
+            }
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
-        constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+        constexpr uint32_t idesc = MAJ ? umma_idesc_bf16_mn(BM, BN) : umma_idesc_bf16(BM, BN);
         int s = 0;
         uint32_t round = 0;
         for (int kb = 0; kb < kblocks && ok; ++kb, ++s) {
@@ -115,11 +125,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             ok = mbar_wait(&sm.full[s], round & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t da = umma_desc_sw128(smem_u32(a_tile(s)));
-            const uint64_t db = umma_desc_sw128(smem_u32(b_tile(s)));
+            if (MAJ == 0) {
+                const uint64_t da = umma_desc_sw128(smem_u32(a_tile(s)));
+                const uint64_t db = umma_desc_sw128(smem_u32(b_tile(s)));
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)        // 32 bytes further along K per UMMA
-                umma_bf16(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+                for (int k = 0; k < BK / UMMA_K; ++k)        // 32 bytes further along K per UMMA
+                    umma_bf16(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+            } else {
+                // 16 token rows (2048 bytes) further per UMMA; column blocks BK * 128 bytes apart, 8-row groups 1024
+                constexpr uint32_t lbo = BK * 128, sbo = 1024;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint64_t da = umma_desc_sw128_mn(smem_u32(a_tile(s)) + k * 2048, lbo, sbo);
+                    const uint64_t db = umma_desc_sw128_mn(smem_u32(b_tile(s)) + k * 2048, lbo, sbo);
+                    umma_bf16(tmem, da, db, idesc, (kb | k) ? 1u : 0u);
+                }
+            }
             umma_commit(&sm.empty[s]);                    // frees the stage when these MMAs retire
         }
         umma_commit(&sm.acc_ready);
@@ -285,7 +306,42 @@ int launch(const void* A, const void* B, void* C, const void* R, int M, int N, i
     return ltl_check_launch("gemm_tc");
 }
 
+template <int BN>
+int launch_mn(const void* X, const void* Y, float* C, int M, int N, int K, int ksplit, cudaStream_t s)
+{
+    static_assert(BN % 64 == 0, "MN-major tiles are loaded in column blocks of 64");
+    CUtensorMap ma, mb;
+    LTL_TRY(tensor_map(X, K, M, M, 64, &ma));
+    LTL_TRY(tensor_map(Y, K, N, N, 64, &mb));
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, ksplit < 1 ? 1 : ksplit);
+    const int kb_all = (K + BK - 1) / BK;
+    const int kb_per = (kb_all + (int)grid.z - 1) / (int)grid.z;
+    int stages = BN == 128 ? 3 : 4;
+    if (stages > kb_per) stages = kb_per;
+    const size_t smem = smem_bytes<BN>(stages);
+    static bool attr_set = false;
+    if (!attr_set) {
+        LTL_CUDA("gemm_tc attr", cudaFuncSetAttribute(gemm_tc_kernel<BN, float, EPI_ATOMIC, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      (int)smem_bytes<BN>(4)));
+        attr_set = true;
+    }
+    gemm_tc_kernel<BN, float, EPI_ATOMIC, 1><<<grid, 192, smem, s>>>(ma, mb, C, nullptr, M, N, K, stages, g_err_flag);
+    return ltl_check_launch("gemm_tc_mn");
+}
+
 }  // namespace
+
+// C[M, N] (fp32) += X^T Y with X [K, M] and Y [K, N] bf16 row-major (both MN-major operands): the weight gradient
+// dW += X^T dY straight from the token-major activations.  M and N must be multiples of 8 (16-byte row pitch).
+int ltl_gemm_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K, int ksplit, cudaStream_t s)
+{
+    if (!X || !Y || !C) return ltl_fail(LTL_ERR_NULL, "gemm_tc_xty: null operand");
+    if (M <= 0 || N <= 0 || K <= 0 || M % 8 || N % 8 || (reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(Y) & 15))
+        return ltl_fail(LTL_ERR_UNSUPPORTED, "gemm_tc_xty: M and N must be multiples of 8 and the operands 16-byte aligned (M=%d N=%d K=%d)", M, N, K);
+    if (!ltl_tc_err_flag()) return ltl_fail(LTL_ERR_OOM, "gemm_tc_xty: error flag");
+    if (N >= 128) return launch_mn<128>(X, Y, C, M, N, K, ksplit, s);
+    return launch_mn<64>(X, Y, C, M, N, K, ksplit, s);
+}
 
 int ltl_tensor_map_bf16(const void* base, int rows, int cols, long long pitch, int box_rows, void* out_map)
 {

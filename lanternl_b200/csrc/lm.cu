@@ -67,9 +67,8 @@ struct luaTL_lm_s {
     int attn_tc = 1;             // tensor-core attention where the shape allows (LUATL_ATTN_TC=0 turns it off)
     bf16* att_scratch = nullptr; // head-major copies for the tensor-core attention (V; Q, K, dO in the backward)
     size_t att_scratch_elems = 0;
-    // mixed-precision backward scratch (bf16): activation gradients and token-major transposes
-    bf16 *b_dres = nullptr, *b_dhs = nullptr, *b_dh13 = nullptr, *b_dattn = nullptr, *b_dqkv = nullptr, *b_dl = nullptr,
-         *tX = nullptr, *tG = nullptr;
+    // mixed-precision backward scratch (bf16): activation gradients
+    bf16 *b_dres = nullptr, *b_dhs = nullptr, *b_dh13 = nullptr, *b_dattn = nullptr, *b_dqkv = nullptr, *b_dl = nullptr;
     cudaStream_t s = nullptr;
     float2* rope_tab = nullptr;
     Act train, infer, dec;
@@ -423,7 +422,7 @@ int backward(LM* m, Act& a, const int32_t* d_ids, int nseq, int T)
 // Every contraction runs on the tensor-core GEMM, which takes both operands with the contraction
 // dimension contiguous:
 //   dX[R, in]  = dY[R, out] . W[in, out]^T     B = the second weight mirror (Wm, master orientation)
-//   dW[in, out] += X^T[in, R] . dY^T[out, R]^T  both operands transposed to token-major copies (tX, tG),
+//   dW[in, out] += X[R, in]^T . dY[R, out]      both operands MN-major (read as they lie, no transpose),
 //                                               accumulated into G by the split-K atomic epilogue.
 int alloc_backward_tc(LM* m)
 {
@@ -436,20 +435,14 @@ int alloc_backward_tc(LM* m)
     DALLOC(m->b_dres, R * D * 2, "dres bf16"); DALLOC(m->b_dhs, R * F * 2, "dhs bf16");
     DALLOC(m->b_dh13, R * 2 * F * 2, "dh13 bf16"); DALLOC(m->b_dattn, R * D * 2, "dattn bf16");
     DALLOC(m->b_dqkv, R * 3 * D * 2, "dqkv bf16"); DALLOC(m->b_dl, R * V * 2, "dlogits bf16");
-    const size_t wx = std::max(std::max(F, D), V), wg = std::max(std::max(2 * F, 3 * D), D);
-    DALLOC(m->tX, R * wx * 2, "token-major activations"); DALLOC(m->tG, R * wg * 2, "token-major gradients");
     return LTL_OK;
 }
 
-// dW[wr, wc] += X^T . dY with X [R, wr] and dY [R, wc] given in the dtypes named.
-int dw_gemm(LM* m, const void* X, int x_dt, int wr, const void* dY, int dy_dt, int wc, float* dW, int R)
+// dW[wr, wc] += X^T . dY with X [R, wr] and dY [R, wc] bf16: both operands are read as they lie (MN-major).
+int dw_gemm(LM* m, const void* X, int wr, const void* dY, int wc, float* dW, int R)
 {
-    LTL_TRY(ltl_transpose_any_to_bf16(X, x_dt, m->tX, R, wr, m->s));
-    LTL_TRY(ltl_transpose_any_to_bf16(dY, dy_dt, m->tG, R, wc, m->s));
-    const int bn = 128;
-    LTL_TRY(ltl_gemm_tc(m->tX, m->tG, dW, nullptr, wr, wc, R, LTL_F32, bn, 2, ltl_gemm_tc_plan_accum(wr, wc, R, bn), m->s));
-    m->launches += 3;
-    return LTL_OK;
+    m->launches++;
+    return ltl_gemm_tc_xty(X, dY, dW, wr, wc, R, ltl_gemm_tc_plan_accum(wr, wc, R, 128), m->s);
 }
 // dX[R, n_in] = dY[R, n_out] . Wt^T with Wt = the mirror that holds the weight as [n_in, n_out].
 int dx_gemm(LM* m, const bf16* dY, int n_out, const bf16* Wt, int n_in, void* dX, int dx_dt, int R)
@@ -468,10 +461,10 @@ int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T)
     // head: dlogits (fp32, in a.logits) -> bf16
     LTL_TRY(ltl_cast(a.logits, LTL_F32, m->b_dl, LTL_BF16, (uint64_t)rows * V, m->s));
     if (m->c.tie) {
-        LTL_TRY(dw_gemm(m, m->b_dl, LTL_BF16, V, a.hf, LTL_BF16, D, G + m->off_emb, rows));         // dEmb += dl^T hf
+        LTL_TRY(dw_gemm(m, m->b_dl, V, a.hf, D, G + m->off_emb, rows));         // dEmb += dl^T hf
         LTL_TRY(dx_gemm(m, m->b_dl, V, m->Wm + m->off_emb, D, m->dhf, LTL_F32, rows));              // dhf = dl emb
     } else {
-        LTL_TRY(dw_gemm(m, a.hf, LTL_BF16, D, m->b_dl, LTL_BF16, V, G + m->off_head, rows));        // dHead += hf^T dl
+        LTL_TRY(dw_gemm(m, a.hf, D, m->b_dl, V, G + m->off_head, rows));        // dHead += hf^T dl
         LTL_TRY(dx_gemm(m, m->b_dl, V, m->Wm + m->off_head, D, m->dhf, LTL_F32, rows));             // dhf = dl head^T
     }
     LTL_TRY(ltl_rmsnorm_bwd(a.res + (size_t)L * RD, W + m->off_lnf, m->dhf, m->dres, G + m->off_lnf, rows, D,
@@ -492,16 +485,16 @@ int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T)
         // feed-forward
         LTL_TRY(ltl_cast(m->dres, LTL_F32, m->b_dres, LTL_BF16, (uint64_t)rows * D, m->s));
         LTL_TRY(dx_gemm(m, m->b_dres, D, m->Wm + o.w2, F, m->b_dhs, LTL_BF16, rows));               // dhs = dres W2^T
-        LTL_TRY(dw_gemm(m, hs, LTL_BF16, F, m->b_dres, LTL_BF16, D, G + o.w2, rows));               // dW2 += hs^T dres
+        LTL_TRY(dw_gemm(m, hs, F, m->b_dres, D, G + o.w2, rows));               // dW2 += hs^T dres
         LTL_TRY(ltl_swiglu_bwd(h13, h13 + F, m->b_dhs, m->b_dh13, m->b_dh13 + F, rows, F, 2 * F, 2 * F, F, LTL_BF16, m->s));
-        LTL_TRY(dw_gemm(m, h2, LTL_BF16, D, m->b_dh13, LTL_BF16, 2 * F, G + o.w13, rows));          // dW13 += h2^T dh13
+        LTL_TRY(dw_gemm(m, h2, D, m->b_dh13, 2 * F, G + o.w13, rows));          // dW13 += h2^T dh13
         LTL_TRY(dx_gemm(m, m->b_dh13, 2 * F, m->Wm + o.w13, D, m->dh2, LTL_F32, rows));             // dh2 = dh13 W13^T
         LTL_TRY(ltl_rmsnorm_bwd(mid, W + o.ln2, m->dh2, m->dbr, G + o.ln2, rows, D, m->c.eps, LTL_F32, m->ws, m->s));
         LTL_TRY(ltl_elementwise(m->dres, m->dbr, m->dres, (uint64_t)rows * D, LTL_F32, 6, 1.0f, 0.0f, m->s));
         // attention
         LTL_TRY(ltl_cast(m->dres, LTL_F32, m->b_dres, LTL_BF16, (uint64_t)rows * D, m->s));
         LTL_TRY(dx_gemm(m, m->b_dres, D, m->Wm + o.wo, D, m->b_dattn, LTL_BF16, rows));             // dattn = dres Wo^T
-        LTL_TRY(dw_gemm(m, attn, LTL_BF16, D, m->b_dres, LTL_BF16, D, G + o.wo, rows));             // dWo += attn^T dres
+        LTL_TRY(dw_gemm(m, attn, D, m->b_dres, D, G + o.wo, rows));             // dWo += attn^T dres
         if (use_attn_tc(m, T)) {
             LTL_TRY(ensure_att_scratch(m, (size_t)3 * rows * D));
             LTL_TRY(ltl_attn_bwd_tc(qkv, attn, m->b_dattn, lse, m->delta, m->att_scratch, m->b_dqkv, nseq, T, H, hd, m->scale, 1, m->s));
@@ -513,7 +506,7 @@ int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T)
         if (m->c.use_rope)
             LTL_TRY(ltl_rope(m->b_dqkv, a.posids, rows, 2 * H, hd, 3 * D, 0, m->c.rope_base, m->c.rope_interleaved, 1,
                              LTL_BF16, m->rope_tab, m->T, m->s));
-        LTL_TRY(dw_gemm(m, h1, LTL_BF16, D, m->b_dqkv, LTL_BF16, 3 * D, G + o.wqkv, rows));         // dWqkv += h1^T dqkv
+        LTL_TRY(dw_gemm(m, h1, D, m->b_dqkv, 3 * D, G + o.wqkv, rows));         // dWqkv += h1^T dqkv
         LTL_TRY(dx_gemm(m, m->b_dqkv, 3 * D, m->Wm + o.wqkv, D, m->dh1, LTL_F32, rows));            // dh1 = dqkv Wqkv^T
         LTL_TRY(ltl_rmsnorm_bwd(xin, W + o.ln1, m->dh1, m->dbr, G + o.ln1, rows, D, m->c.eps, LTL_F32, m->ws, m->s));
         LTL_TRY(ltl_elementwise(m->dres, m->dbr, m->dres, (uint64_t)rows * D, LTL_F32, 6, 1.0f, 0.0f, m->s));
@@ -582,9 +575,9 @@ int enter_train_tc(LM* m)
 {
     if (m->train_tc) return LTL_OK;
     if (!m->use_tc) return ltl_fail(LTL_ERR_UNSUPPORTED, "lm train_step: the bf16 training step needs the tensor-core GEMM");
-    if ((m->B * m->T) % 8 || m->D % 8 || m->F % 8 || m->V % 8)
-        return ltl_fail(LTL_ERR_SHAPE, "lm train_step: the bf16 training step needs batch x max_seq, dim, ffn and vocab to be "
-                        "multiples of 8 (got %d x %d, %d, %d, %d)", m->B, m->T, m->D, m->F, m->V);
+    if (m->D % 8 || m->F % 8 || m->V % 8)
+        return ltl_fail(LTL_ERR_SHAPE, "lm train_step: the bf16 training step needs dim, ffn and vocab to be multiples of 8 "
+                        "(got %d, %d, %d)", m->D, m->F, m->V);
     LTL_CUDA("sync", cudaStreamSynchronize(m->s));
     drop_graphs(m);
     DALLOC(m->Wm, (size_t)m->np * 2, "second bf16 weight mirror");
@@ -971,7 +964,7 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
     void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
                      m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
                      m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part,
-                     m->Wm, m->att_scratch, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl, m->tX, m->tG };
+                     m->Wm, m->att_scratch, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
     for (void* p : ptrs) if (p) cudaFree(p);
     for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
     cudaGetLastError();

@@ -124,6 +124,7 @@ int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int
 void ltl_gemm_tc_plan_split(int M, int N, int K, int* bn, int* ksplit);
 int ltl_gemm_tc_check(cudaStream_t s);
 int ltl_gemm_tc_plan_accum(int M, int N, int K, int bn);
+int ltl_gemm_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K, int ksplit, cudaStream_t s);
 // CUtensorMap (128 bytes, written to out_map) of a bf16 matrix [rows, cols] with rows `pitch` elements apart:
 // boxes of box_rows x 64 columns, 128-byte swizzle.  Cached per (base, shape).
 int ltl_tensor_map_bf16(const void* base, int rows, int cols, long long pitch, int box_rows, void* out_map);

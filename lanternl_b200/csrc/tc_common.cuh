@@ -53,11 +53,26 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr)
     d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
     return d;
 }
+// The same for an MN-major operand (the M or N dimension contiguous in memory, tiles loaded as rows of 64
+// elements = 128 bytes along M/N, one row per k): `lbo` bytes between 64-element column blocks along M/N,
+// `sbo` bytes between groups of 8 k-rows.
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t saddr, uint32_t lbo, uint32_t sbo)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
 // Instruction descriptor: D fp32, A and B bf16, both K-major, shape M x N.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N)
 {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+// Bits 15 / 16 select an MN-major A / B operand.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16_mn(int M, int N) { return umma_idesc_bf16(M, N) | (1u << 15) | (1u << 16); }
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile(

@@ -122,3 +122,27 @@ def test_many_tile_grid_uses_the_shallow_ring():
     assert rel_err(got, ref) < 1e-5
     got, ref = run(4096, 1536, 520, 64, c_dtype=_lib.BF16, seed=10)
     assert rel_err(got, ref) < 8e-3
+
+
+@pytest.mark.parametrize("M,N,K,ks", [(128, 128, 64, 1), (256, 384, 1000, 3), (64, 64, 128, 1), (2048, 5632, 4096, 1), (72, 200, 300, 2),
+                                      (2000, 128, 4096, 8)])
+def test_weight_gradient_product_of_token_major_operands(M, N, K, ks):
+    """C += X^T Y with X [K, M] and Y [K, N] as they lie in memory (both tensor-core operands MN-major): tails in
+    every dimension, split-K, a many-tile grid, two calls accumulate."""
+    x = bf16_round(synth.normal(31, 0, K * M).reshape(K, M).astype(np.float32))
+    y = bf16_round((synth.normal(32, 0, K * N) * 0.1).reshape(K, N).astype(np.float32))
+    c0 = synth.normal(33, 0, M * N).reshape(M, N).astype(np.float32)
+    X, Y = bf16_dev(x), bf16_dev(y)
+    Cc = ad.TensorView(M, N, _lib.F32)
+    Cc.upload(c0.ravel())
+    for _ in range(2):
+        _lib.call("luaTL_gemm_bf16_tc_xty", X.data, Y.data, Cc.data, M, N, K, ks)
+    ref = c0.astype(np.float64) + 2.0 * (x.astype(np.float64).T @ y.astype(np.float64))
+    assert rel_err(Cc.download().reshape(M, N), ref) < 1e-5
+
+
+def test_weight_gradient_product_rejects_unaligned_widths():
+    X, Y = ad.TensorView(64, 100, _lib.BF16), ad.TensorView(64, 64, _lib.BF16)
+    Cc = ad.TensorView(100, 64, _lib.F32)
+    with pytest.raises(_lib.LuaTLError, match="UNSUPPORT"):
+        _lib.call("luaTL_gemm_bf16_tc_xty", X.data, Y.data, Cc.data, 100, 64, 64, 1)
