@@ -13,12 +13,15 @@
 //
 // Forward, one CTA per (128 query rows, head, sequence), key tiles of 128, double-buffered:
 //   warp 0    TMA producer: Q once, then K_j (from qkv) and V^T_j (from the head-major copy) per tile
-//   warp 1    MMA issuer:   S = Q K_j^T  -> TMEM[0,128);  O_j = P V_j -> TMEM[128,128+hd)
-//   warps 2-5 softmax:      thread r owns query row r: reads S from TMEM, online max / sum, writes P (bf16)
-//                           into shared memory in the swizzled K-major layout, then folds O_j into its
-//                           fp32 output row held in registers (rescaled when the maximum moves).
+//   warp 1    MMA issuer:   S_j = Q K_j^T and O_j = P_j V_j into double-buffered tensor memory (S_{j+1} is issued
+//                           before P_j V_j, so it runs while the softmax threads work on S_j)
+//   warps 2-9 softmax:      two threads per query row, each owning 64 score columns and hd/2 output columns: S from
+//                           TMEM, online max / sum, P (bf16) into shared memory in the swizzled K-major layout,
+//                           O_j folded into the fp32 output row held in registers (rescaled when the maximum moves).
 // All waits are bounded; one that runs out raises the library's error flag and the CTA winds down.
 #include <cuda.h>
+
+#include <type_traits>
 
 #include "ops.h"
 #include "tc_common.cuh"
@@ -29,6 +32,14 @@ using namespace tc;
 
 constexpr int QT = 128, KT = 128;        // query rows and keys per tile
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+
+// 2^x on the special-function unit, one instruction (inputs here are <= 0 up to rounding; tiny results flush to 0).
+__device__ __forceinline__ float ex2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 // [R, 3D] -> head-major transposes: dst[((b*H + h)*HD + d) * T + t] = src[(b*T + t) * pitch + col0 + h*HD + d]
 __global__ void __launch_bounds__(256)
@@ -57,17 +68,27 @@ head_transpose_kernel(const bf16* __restrict__ src, bf16* __restrict__ dst, int 
 
 template <int HD>
 struct FwdSmem {
-    static constexpr int QB = QT * 128;                 // bytes of one 64-column k-block of a 128-row tile
     alignas(1024) uint8_t q[HD / 64][QT * 128];
     alignas(1024) uint8_t k[2][HD / 64][KT * 128];
     alignas(1024) uint8_t vt[2][KT / 64][HD * 128];
     alignas(1024) uint8_t p[KT / 64][QT * 128];
-    alignas(8) uint64_t q_full, kv_full[2], kv_free[2], s_ready, p_ready, o_ready;
+    float mx[2][2][QT];                                 // [tile parity][column half][row]: partial row maxima
+    float lsum[2][QT];                                  // final exchange of the partial denominators
+    int fail;
+    alignas(8) uint64_t q_full, kv_full[2], kv_free[2], s_ready[2], p_ready, o_ready[2];
     uint32_t tmem_base;
 };
 
+// Software pipeline: S and O_j are double-buffered in tensor memory (S0, S1, O0, O1 = 512 columns at hd 128), so the
+// tensor core computes S_{j+1} while the softmax threads work on S_j, and P_j V_j while they fold O_{j-1} into their
+// output rows (the fold of a tile is deferred by one tile; the rescale factor of each tile is kept until then).
+// Two threads per query row (eight softmax warps): thread (r, half) owns the 64 score columns and the hd/2 output
+// columns of its half; the two exchange their partial row maximum through shared memory once per tile and their
+// partial denominators once at the end.
+constexpr int FWD_THREADS = 320;
+
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_vt,
                    bf16* __restrict__ out, float* __restrict__ lse, int T, int H, float scale, int causal,
                    int* __restrict__ err)
@@ -75,7 +96,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
     extern __shared__ uint8_t smem_raw[];
     FwdSmem<HD>& sm = *reinterpret_cast<FwdSmem<HD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int KB = HD / 64;                         // k-blocks of the QK^T contraction
-    constexpr uint32_t TMEM_COLS = 256;
+    constexpr int HH = HD / 2;                          // output columns per thread
+    constexpr uint32_t TMEM_COLS = 512, COL_O = 256;    // S_b at 128 b, O_b at 256 + 128 b
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q0 = blockIdx.x * QT, h = blockIdx.y, b = blockIdx.z;
     const int D = H * HD;
@@ -83,8 +105,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.q_full, 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_free[s], 1); }
-        mbar_init(&sm.s_ready, 1); mbar_init(&sm.p_ready, 128); mbar_init(&sm.o_ready, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_free[s], 1);
+            mbar_init(&sm.s_ready[s], 1); mbar_init(&sm.o_ready[s], 1);
+        }
+        mbar_init(&sm.p_ready, 256);
+        sm.fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -113,19 +139,31 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
         constexpr uint32_t idesc_s = umma_idesc_bf16(QT, KT), idesc_o = umma_idesc_bf16(QT, HD);
-        ok = mbar_wait(&sm.q_full, 0);
-        for (int j = 0; j < ntiles && ok; ++j) {
+        auto issue_s = [&](int j) {
             const int s = j & 1;
-            ok = mbar_wait(&sm.kv_full[s], (j >> 1) & 1);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb) {
                 const uint64_t da = umma_desc_sw128(smem_u32(sm.q[kb])), db = umma_desc_sw128(smem_u32(sm.k[s][kb]));
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem + (uint32_t)(s * 128), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
             }
-            umma_commit(&sm.s_ready);
+            umma_commit(&sm.s_ready[s]);
+        };
+        ok = mbar_wait(&sm.q_full, 0) && mbar_wait(&sm.kv_full[0], 0);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_s(0);
+        }
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int s = j & 1;
+            if (j + 1 < ntiles) {
+                // S buffer (j+1)&1 was last read for tile j-1: its softmax finished before p_ready(j-1), waited below
+                ok = mbar_wait(&sm.kv_full[s ^ 1], ((j + 1) >> 1) & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_s(j + 1);
+            }
             ok = mbar_wait(&sm.p_ready, j & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -133,90 +171,123 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
             for (int kb = 0; kb < KT / 64; ++kb) {
                 const uint64_t da = umma_desc_sw128(smem_u32(sm.p[kb])), db = umma_desc_sw128(smem_u32(sm.vt[s][kb]));
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tmem + 128, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (kb | k) ? 1u : 0u);
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem + COL_O + (uint32_t)(s * 128), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (kb | k) ? 1u : 0u);
             }
-            umma_commit(&sm.o_ready);
+            umma_commit(&sm.o_ready[s]);
             umma_commit(&sm.kv_free[s]);
         }
     } else if (warp >= 2) {
-        // ---- softmax: one thread per query row ----
-        const int quad = warp & 3, r = quad * 32 + lane;
+        // ---- softmax: two threads per query row ----
+        const int quad = warp & 3, r = quad * 32 + lane, half = (warp - 2) >> 2;
         const int qi = q0 + r;
         const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
         const float sl2 = scale * LOG2E;
-        float m = -INFINITY, l = 0.0f;
-        float acc[HD];
+        volatile int* failp = &sm.fail;
+        float m = -INFINITY, l = 0.0f, corr_prev = 0.0f;
+        float acc[HH];
 #pragma unroll
-        for (int d = 0; d < HD; ++d) acc[d] = 0.0f;
+        for (int d = 0; d < HH; ++d) acc[d] = 0.0f;
+        // acc = acc * corr + (this thread's half of) O_t, the product in O buffer t & 1
+        auto fold = [&](int t, float corr) {
+            const uint32_t ocol = trow + COL_O + (uint32_t)((t & 1) * 128 + half * HH);
+            uint32_t v[HH];
+#pragma unroll
+            for (int c = 0; c < HH; c += 32) tmem_ld32(ocol + (uint32_t)c, *reinterpret_cast<uint32_t(*)[32]>(&v[c]));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < HH; ++i) acc[i] = fmaf(acc[i], corr, __uint_as_float(v[i]));
+        };
+        // A wait that runs out must not strand the other threads at the per-tile barrier: the thread raises sm.fail,
+        // keeps walking to the barrier, and everybody leaves together right after it.
         for (int j = 0; j < ntiles; ++j) {
-            if (!mbar_wait(&sm.s_ready, j & 1)) { ok = false; break; }
+            const uint32_t scol = trow + (uint32_t)((j & 1) * 128 + half * 64);
+            if (!mbar_wait(&sm.s_ready[j & 1], (j >> 1) & 1)) *failp = 1;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int kbase = j * KT;
-            const int klim = min(T, causal ? qi + 1 : T) - kbase;          // keys [0, klim) of this tile are visible
+            const int klim = min(T, causal ? qi + 1 : T) - j * KT - half * 64;   // visible columns among this thread's 64
+            uint32_t v[64];
+            tmem_ld32(scol, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+            tmem_ld32(scol + 32u, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // Only the tile on the diagonal (and a ragged last tile) needs the per-column mask.
+            const bool full = klim >= 64;
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < KT; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(trow + (uint32_t)c, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (full) {
+                float m0 = __uint_as_float(v[0]), m1 = __uint_as_float(v[1]), m2 = __uint_as_float(v[2]), m3 = __uint_as_float(v[3]);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) if (c + i < klim) mx = fmaxf(mx, __uint_as_float(v[i]));
+                for (int i = 4; i < 64; i += 4) {
+                    m0 = fmaxf(m0, __uint_as_float(v[i])); m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
+                    m2 = fmaxf(m2, __uint_as_float(v[i + 2])); m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+                }
+                mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) if (i < klim) mx = fmaxf(mx, __uint_as_float(v[i]));
             }
+            sm.mx[j & 1][half][r] = mx;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (*failp) { ok = false; break; }
+            mx = fmaxf(mx, sm.mx[j & 1][half ^ 1][r]);
             const float mn = fmaxf(m, mx * sl2);
             const float base = mn == -INFINITY ? 0.0f : mn;
-            const float corr = exp2f(m - base);                           // m = -inf -> 0
-            float sum = 0.0f;
-#pragma unroll 1
-            for (int c = 0; c < KT; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(trow + (uint32_t)c, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                uint32_t pk[16];
+            const float corr = ex2(m - base);                             // m = -inf -> 0
+            // P of the previous tile must have been consumed before it is overwritten (and O_{j-1} is then complete)
+            if (j > 0 && !mbar_wait(&sm.o_ready[(j - 1) & 1], ((j - 1) >> 1) & 1)) *failp = 1;
+            float sum0 = 0.0f, sum1 = 0.0f;
+            uint8_t* prow = sm.p[half] + r * 128;                        // k-block `half` holds this thread's 64 columns
+            auto probs = [&](auto full_c) {
+                constexpr bool FULL = decltype(full_c)::value;
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = c + i < klim ? exp2f(fmaf(__uint_as_float(v[i]), sl2, -base)) : 0.0f;
-                    const float p1 = c + i + 1 < klim ? exp2f(fmaf(__uint_as_float(v[i + 1]), sl2, -base)) : 0.0f;
-                    const __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
-                    // the sum uses the rounded probabilities, the values the second GEMM multiplies with
-                    sum += __low2float(t) + __high2float(t);
-                    pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&t);
-                }
-                // columns c .. c+31 of row r: four 16-byte chunks of k-block c / 64, swizzled by the row
-                uint8_t* prow = sm.p[c >> 6] + r * 128;
+                for (int c = 0; c < 64; c += 8) {
+                    uint32_t pk[4];
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = ((c & 63) >> 3) + q4;
-                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+                    for (int i = 0; i < 8; i += 2) {
+                        float p0 = ex2(fmaf(__uint_as_float(v[c + i]), sl2, -base));
+                        float p1 = ex2(fmaf(__uint_as_float(v[c + i + 1]), sl2, -base));
+                        if (!FULL) { p0 = c + i < klim ? p0 : 0.0f; p1 = c + i + 1 < klim ? p1 : 0.0f; }
+                        sum0 += p0; sum1 += p1;
+                        const __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+                        pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&t);
+                    }
+                    *reinterpret_cast<uint4*>(prow + (((c >> 3) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                 }
-            }
+            };
+            if (full) probs(std::true_type{}); else probs(std::false_type{});
+            const float sum = sum0 + sum1;
             l = fmaf(l, corr, sum);
             m = mn;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P visible to the tensor core's reads
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.p_ready)) : "memory");
-            if (!mbar_wait(&sm.o_ready, j & 1)) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int c = 0; c < HD; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(trow + 128u + (uint32_t)c, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(acc[c + i], corr, __uint_as_float(v[i]));
+            if (j > 0) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fold(j - 1, corr_prev);
             }
+            corr_prev = corr;
+        }
+        if (ok && ntiles > 0) {
+            if (!mbar_wait(&sm.o_ready[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1)) *failp = 1;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            fold(ntiles - 1, corr_prev);
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        if (ok) {                                        // uniform: `ok` only falls right after a barrier, for everybody
+            sm.lsum[half][r] = l;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (*failp) ok = false;
+            l += sm.lsum[half ^ 1][r];
+        }
         if (ok && qi < T) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            bf16* orow = out + ((size_t)b * T + qi) * D + h * HD;
+            bf16* orow = out + ((size_t)b * T + qi) * D + h * HD + half * HH;
 #pragma unroll
-            for (int d = 0; d < HD; d += 8) {
+            for (int d = 0; d < HH; d += 8) {
                 float o[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) o[i] = acc[d + i] * inv;
                 st16<bf16>(orow + d, o);
             }
-            if (lse) lse[((size_t)b * H + h) * T + qi] = (m == -INFINITY ? -INFINITY : m * LN2) + logf(fmaxf(l, 1e-30f));
+            if (lse && half == 0) lse[((size_t)b * H + h) * T + qi] = (m == -INFINITY ? -INFINITY : m * LN2) + logf(fmaxf(l, 1e-30f));
         }
     }
     if (!ok && err) atomicExch(err, 1);
@@ -244,47 +315,55 @@ int launch_fwd_tc(const bf16* qkv, bf16* vt, bf16* out, float* lse, int B, int T
         attr = true;
     }
     dim3 grid((T + QT - 1) / QT, H, B);
-    attn_fwd_tc_kernel<HD><<<grid, 192, smem, s>>>(mq, mv, out, lse, T, H, scale, causal, ltl_tc_err_flag());
+    attn_fwd_tc_kernel<HD><<<grid, FWD_THREADS, smem, s>>>(mq, mv, out, lse, T, H, scale, causal, ltl_tc_err_flag());
     return ltl_check_launch("attn_fwd_tc");
 }
 
 
 // ---------------------------------------------------------------------------------------------------
-// Backward, part 1: dQ.  One CTA per (128 query rows, head, sequence) walking the key tiles as the forward does.
-//   S = Q K_j^T and dP = dO V_j^T (tensor memory)  ->  thread r: P = exp(S*scale - lse_r), dS = P (dP - delta_r) scale
-//   -> dS (bf16) in shared memory, K-major  ->  dQ += dS K_j  with K_j^T read from the head-major copy of K.
+// Backward, part 1: dQ.  One CTA per (128 query rows, head, sequence) walking key tiles of 64.
+//   S = Q K_j^T and dP = dO V_j^T (tensor memory, double-buffered: the pair for tile j+1 is computed while the
+//   threads work on tile j)  ->  P = exp(S scale - lse_r), dS = P (dP - delta_r) scale  ->  dS (bf16) in shared
+//   memory, K-major  ->  dQ += dS K_j with K_j^T read from the head-major copy of K.
+// Two threads per query row (eight warps), 32 key columns each; nothing is exchanged between them.
 // ---------------------------------------------------------------------------------------------------
+constexpr int KS = 64;                   // keys per tile of the dQ walk
+constexpr int BWD_THREADS = 320;
+
 template <int HD>
 struct DqSmem {
     alignas(1024) uint8_t q[HD / 64][QT * 128];
     alignas(1024) uint8_t dout[HD / 64][QT * 128];
-    alignas(1024) uint8_t k[HD / 64][KT * 128];
-    alignas(1024) uint8_t v[HD / 64][KT * 128];
-    alignas(1024) uint8_t kt[KT / 64][HD * 128];
-    alignas(1024) uint8_t ds[KT / 64][QT * 128];
-    alignas(8) uint64_t q_full, kv_full, kv_free, s_ready, ds_ready, acc_ready;
+    alignas(1024) uint8_t k[2][HD / 64][KS * 128];
+    alignas(1024) uint8_t v[2][HD / 64][KS * 128];
+    alignas(1024) uint8_t kt[2][HD * 128];
+    alignas(1024) uint8_t ds[QT * 128];
+    alignas(8) uint64_t q_full, kv_full[2], kv_free[2], sd_ready[2], ds_ready, acc_ready;
     uint32_t tmem_base;
 };
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
-attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do,
-                      const __grid_constant__ CUtensorMap map_kt, const float* __restrict__ lse,
-                      const float* __restrict__ delta, bf16* __restrict__ dqkv, int T, int H, float scale, int causal,
-                      int* __restrict__ err)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,     // boxes of 128 rows (Q)
+                      const __grid_constant__ CUtensorMap map_qkv64,   // boxes of 64 rows (K_j, V_j)
+                      const __grid_constant__ CUtensorMap map_do,      // dO, boxes of 128 rows
+                      const __grid_constant__ CUtensorMap map_kt,      // head-major K^T, boxes hd x 64
+                      const float* __restrict__ lse, const float* __restrict__ delta, bf16* __restrict__ dqkv,
+                      int T, int H, float scale, int causal, int* __restrict__ err)
 {
     extern __shared__ uint8_t smem_raw[];
     DqSmem<HD>& sm = *reinterpret_cast<DqSmem<HD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int KB = HD / 64;
-    constexpr uint32_t TMEM_COLS = 512, COL_DP = 128, COL_DQ = 256;
+    constexpr uint32_t TMEM_COLS = 512, COL_DP = 128, COL_DQ = 256;      // S_b at 64 b, dP_b at 128 + 64 b
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q0 = blockIdx.x * QT, h = blockIdx.y, b = blockIdx.z;
     const int D = H * HD;
-    const int ntiles = causal ? min((q0 + QT - 1) / KT + 1, (T + KT - 1) / KT) : (T + KT - 1) / KT;
+    const int ntiles = causal ? min((q0 + QT - 1) / KS + 1, (T + KS - 1) / KS) : (T + KS - 1) / KS;
 
     if (threadIdx.x == 0) {
-        mbar_init(&sm.q_full, 1); mbar_init(&sm.kv_full, 1); mbar_init(&sm.kv_free, 1);
-        mbar_init(&sm.s_ready, 1); mbar_init(&sm.ds_ready, 128); mbar_init(&sm.acc_ready, 1);
+        mbar_init(&sm.q_full, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_free[s], 1); mbar_init(&sm.sd_ready[s], 1); }
+        mbar_init(&sm.ds_ready, 256); mbar_init(&sm.acc_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -304,79 +383,95 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_
             tma_load_2d(sm.dout[kb], &map_do, h * HD + kb * 64, b * T + q0, &sm.q_full);
         }
         for (int j = 0; j < ntiles && ok; ++j) {
-            if (j >= 1) ok = mbar_wait(&sm.kv_free, (j - 1) & 1);
+            const int s = j & 1;
+            if (j >= 2) ok = mbar_wait(&sm.kv_free[s], ((j >> 1) - 1) & 1);
             if (!ok) break;
-            mbar_expect_tx(&sm.kv_full, 3 * KT * HD * 2);
+            mbar_expect_tx(&sm.kv_full[s], 3 * KS * HD * 2);
             for (int kb = 0; kb < KB; ++kb) {
-                tma_load_2d(sm.k[kb], &map_qkv, D + h * HD + kb * 64, b * T + j * KT, &sm.kv_full);
-                tma_load_2d(sm.v[kb], &map_qkv, 2 * D + h * HD + kb * 64, b * T + j * KT, &sm.kv_full);
+                tma_load_2d(sm.k[s][kb], &map_qkv64, D + h * HD + kb * 64, b * T + j * KS, &sm.kv_full[s]);
+                tma_load_2d(sm.v[s][kb], &map_qkv64, 2 * D + h * HD + kb * 64, b * T + j * KS, &sm.kv_full[s]);
             }
-            for (int kb = 0; kb < KT / 64; ++kb) tma_load_2d(sm.kt[kb], &map_kt, j * KT + kb * 64, (b * H + h) * HD, &sm.kv_full);
+            tma_load_2d(sm.kt[s], &map_kt, j * KS, (b * H + h) * HD, &sm.kv_full[s]);
         }
     } else if (warp == 1 && lane == 0) {
-        constexpr uint32_t idesc_s = umma_idesc_bf16(QT, KT), idesc_o = umma_idesc_bf16(QT, HD);
-        ok = mbar_wait(&sm.q_full, 0);
-        for (int j = 0; j < ntiles && ok; ++j) {
-            ok = mbar_wait(&sm.kv_full, j & 1);
-            if (!ok) break;
+        constexpr uint32_t idesc_s = umma_idesc_bf16(QT, KS), idesc_o = umma_idesc_bf16(QT, HD);
+        auto issue_sd = [&](int j) {
+            const int s = j & 1;
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+                const uint64_t da = umma_desc_sw128(smem_u32(sm.q[kb])), db = umma_desc_sw128(smem_u32(sm.k[s][kb]));
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem + (uint32_t)(s * KS), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+            }
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+                const uint64_t da = umma_desc_sw128(smem_u32(sm.dout[kb])), db = umma_desc_sw128(smem_u32(sm.v[s][kb]));
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem + COL_DP + (uint32_t)(s * KS), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+            }
+            umma_commit(&sm.sd_ready[s]);
+        };
+        ok = mbar_wait(&sm.q_full, 0) && mbar_wait(&sm.kv_full[0], 0);
+        if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int kb = 0; kb < KB; ++kb) {
-                const uint64_t da = umma_desc_sw128(smem_u32(sm.q[kb])), db = umma_desc_sw128(smem_u32(sm.k[kb]));
-#pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+            issue_sd(0);
+        }
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int s = j & 1;
+            if (j + 1 < ntiles) {
+                ok = mbar_wait(&sm.kv_full[s ^ 1], ((j + 1) >> 1) & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_sd(j + 1);
             }
-#pragma unroll
-            for (int kb = 0; kb < KB; ++kb) {
-                const uint64_t da = umma_desc_sw128(smem_u32(sm.dout[kb])), db = umma_desc_sw128(smem_u32(sm.v[kb]));
-#pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tmem + COL_DP, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
-            }
-            umma_commit(&sm.s_ready);
             ok = mbar_wait(&sm.ds_ready, j & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t da = umma_desc_sw128(smem_u32(sm.ds)), db = umma_desc_sw128(smem_u32(sm.kt[s]));
 #pragma unroll
-            for (int kb = 0; kb < KT / 64; ++kb) {
-                const uint64_t da = umma_desc_sw128(smem_u32(sm.ds[kb])), db = umma_desc_sw128(smem_u32(sm.kt[kb]));
-#pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tmem + COL_DQ, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (j | kb | k) ? 1u : 0u);
-            }
-            umma_commit(&sm.kv_free);
+            for (int k = 0; k < 4; ++k)
+                umma_bf16(tmem + COL_DQ, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (j | k) ? 1u : 0u);
+            umma_commit(&sm.kv_free[s]);                 // also: dS of tile j has been consumed
         }
         if (ok) umma_commit(&sm.acc_ready);
     } else if (warp >= 2) {
-        const int quad = warp & 3, r = quad * 32 + lane;
+        const int quad = warp & 3, r = quad * 32 + lane, half = (warp - 2) >> 2;
         const int qi = q0 + r;
         const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
         const float sl2 = scale * LOG2E;
         const size_t li = ((size_t)b * H + h) * T + (qi < T ? qi : 0);
-        const float lse2 = lse[li] * LOG2E, dl = delta[li];
+        const float lse2 = lse[li] * LOG2E, dls = delta[li] * scale;
         for (int j = 0; j < ntiles; ++j) {
-            if (!mbar_wait(&sm.s_ready, j & 1)) { ok = false; break; }
+            const uint32_t col = (uint32_t)((j & 1) * KS + half * 32);
+            if (!mbar_wait(&sm.sd_ready[j & 1], (j >> 1) & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int klim = qi < T ? min(T, causal ? qi + 1 : T) - j * KT : 0;
-#pragma unroll 1
-            for (int c = 0; c < KT; c += 32) {
-                uint32_t sv[32], dv[32];
-                tmem_ld32(trow + (uint32_t)c, sv);
-                tmem_ld32(trow + COL_DP + (uint32_t)c, dv);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                uint32_t pk[16];
+            const int klim = qi < T ? min(T, causal ? qi + 1 : T) - j * KS - half * 32 : 0;
+            uint32_t sv[32], dv[32];
+            tmem_ld32(trow + col, sv);
+            tmem_ld32(trow + COL_DP + col, dv);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            uint32_t pk[16];
+            auto body = [&](auto full_c) {
+                constexpr bool FULL = decltype(full_c)::value;
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float d0 = 0.0f, d1 = 0.0f;
-                    if (c + i < klim) d0 = exp2f(fmaf(__uint_as_float(sv[i]), sl2, -lse2)) * (__uint_as_float(dv[i]) - dl) * scale;
-                    if (c + i + 1 < klim) d1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sl2, -lse2)) * (__uint_as_float(dv[i + 1]) - dl) * scale;
+                    float d0 = ex2(fmaf(__uint_as_float(sv[i]), sl2, -lse2)) * fmaf(__uint_as_float(dv[i]), scale, -dls);
+                    float d1 = ex2(fmaf(__uint_as_float(sv[i + 1]), sl2, -lse2)) * fmaf(__uint_as_float(dv[i + 1]), scale, -dls);
+                    if (!FULL) { d0 = i < klim ? d0 : 0.0f; d1 = i + 1 < klim ? d1 : 0.0f; }
                     const __nv_bfloat162 t = __floats2bfloat162_rn(d0, d1);
                     pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&t);
                 }
-                uint8_t* prow = sm.ds[c >> 6] + r * 128;
+            };
+            if (klim >= 32) body(std::true_type{}); else body(std::false_type{});
+            // dS of the previous tile must have been consumed by its dQ product before it is overwritten
+            if (j > 0 && !mbar_wait(&sm.kv_free[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
+            uint8_t* prow = sm.ds + r * 128;
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = ((c & 63) >> 3) + q4;
-                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-                }
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const int chunk = half * 4 + q4;
+                *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -385,11 +480,12 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_
         if (ok) ok = mbar_wait(&sm.acc_ready, 0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
-            bf16* orow = dqkv + ((size_t)b * T + qi) * 3 * D + h * HD;
+            constexpr int HH = HD / 2;
+            bf16* orow = dqkv + ((size_t)b * T + qi) * 3 * D + h * HD + half * HH;
 #pragma unroll 1
-            for (int c = 0; c < HD; c += 32) {
+            for (int c = 0; c < HH; c += 32) {
                 uint32_t v[32];
-                tmem_ld32(trow + COL_DQ + (uint32_t)c, v);
+                tmem_ld32(trow + COL_DQ + (uint32_t)(half * HH + c), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (qi < T) {
 #pragma unroll
@@ -412,14 +508,15 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_
     }
 }
 
-
 // ---------------------------------------------------------------------------------------------------
 // Backward, part 2: dK and dV.  One CTA per (128 keys, head, sequence) walking the query tiles (64 queries each)
-// that can see those keys.  Everything is computed transposed, so that thread r owns key row r:
-//   S^T = K Q_i^T and dP^T = V dO_i^T (tensor memory)
-//   -> P^T = exp(S^T scale - lse_q), dS^T = P^T (dP^T - delta_q) scale, both bf16 into shared memory (K-major)
-//   -> dV += P^T dO_i and dK += dS^T Q_i, with dO_i^T and Q_i^T read from the head-major copies, accumulated in
-//      tensor memory over the whole walk.
+// that can see those keys.  Everything is computed transposed, so that a thread owns a key row:
+//   S^T = K Q_i^T and dP^T = V dO_i^T (tensor memory, double-buffered: step i+1 is computed while the threads work
+//   on step i)  ->  P^T = exp(S^T scale - lse_q), dS^T = P^T (dP^T - delta_q) scale, both bf16 into shared memory
+//   (K-major)  ->  dV += P^T dO_i and dK += dS^T Q_i, with dO_i^T and Q_i^T read from the head-major copies,
+//   accumulated in tensor memory over the whole walk.
+// Two threads per key row (eight warps), 32 query columns each.  lse and delta of a step's 64 queries are staged in
+// shared memory by the producer warp.
 // ---------------------------------------------------------------------------------------------------
 constexpr int QS = 64;                   // queries per step of the dK / dV walk
 
@@ -427,18 +524,19 @@ template <int HD>
 struct DkvSmem {
     alignas(1024) uint8_t k[HD / 64][KT * 128];
     alignas(1024) uint8_t v[HD / 64][KT * 128];
-    alignas(1024) uint8_t q[HD / 64][QS * 128];         // Q_i   [64 queries x hd]   (B of S^T)
-    alignas(1024) uint8_t dout[HD / 64][QS * 128];      // dO_i  [64 queries x hd]   (B of dP^T)
-    alignas(1024) uint8_t qt[HD * 128];                 // Q_i^T [hd x 64 queries]   (B of dK)
-    alignas(1024) uint8_t dot[HD * 128];                // dO_i^T[hd x 64 queries]   (B of dV)
+    alignas(1024) uint8_t q[2][HD / 64][QS * 128];      // Q_i   [64 queries x hd]   (B of S^T)
+    alignas(1024) uint8_t dout[2][HD / 64][QS * 128];   // dO_i  [64 queries x hd]   (B of dP^T)
+    alignas(1024) uint8_t qt[2][HD * 128];              // Q_i^T [hd x 64 queries]   (B of dK)
+    alignas(1024) uint8_t dot[2][HD * 128];             // dO_i^T[hd x 64 queries]   (B of dV)
     alignas(1024) uint8_t pt[KT * 128];                 // P^T   [128 keys x 64 queries]
     alignas(1024) uint8_t dst[KT * 128];                // dS^T  [128 keys x 64 queries]
-    alignas(8) uint64_t kv_full, q_full, q_free, s_ready, p_ready, acc_ready;
+    float lse2[2][QS], dls[2][QS];                      // per step: lse * log2(e), delta * scale
+    alignas(8) uint64_t kv_full, q_full[2], q_free[2], aux_full[2], sd_ready[2], p_ready, acc_ready;
     uint32_t tmem_base;
 };
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes of 128 rows (K, V tiles)
                        const __grid_constant__ CUtensorMap map_qkv64,  // boxes of 64 rows (Q_i)
                        const __grid_constant__ CUtensorMap map_do64,   // dO [R, D], boxes of 64 rows
@@ -450,7 +548,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
     extern __shared__ uint8_t smem_raw[];
     DkvSmem<HD>& sm = *reinterpret_cast<DkvSmem<HD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int KB = HD / 64;
-    constexpr uint32_t TMEM_COLS = 512, COL_DP = 64, COL_DV = 128, COL_DK = 256;
+    constexpr uint32_t TMEM_COLS = 512, COL_DP = 128, COL_DV = 256, COL_DK = 384;   // S^T_b at 64 b, dP^T_b at 128 + 64 b
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k0 = blockIdx.x * KT, h = blockIdx.y, b = blockIdx.z;
     const int D = H * HD;
@@ -459,8 +557,10 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
     const int nsteps = nq - i0;
 
     if (threadIdx.x == 0) {
-        mbar_init(&sm.kv_full, 1); mbar_init(&sm.q_full, 1); mbar_init(&sm.q_free, 1);
-        mbar_init(&sm.s_ready, 1); mbar_init(&sm.p_ready, 128); mbar_init(&sm.acc_ready, 1);
+        mbar_init(&sm.kv_full, 1); mbar_init(&sm.p_ready, 256); mbar_init(&sm.acc_ready, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&sm.q_full[s], 1); mbar_init(&sm.q_free[s], 1); mbar_init(&sm.aux_full[s], 1); mbar_init(&sm.sd_ready[s], 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -473,106 +573,133 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
     const uint32_t tmem = sm.tmem_base;
     bool ok = true;
 
-    if (warp == 0 && lane == 0) {
-        mbar_expect_tx(&sm.kv_full, 2 * KT * HD * 2);
-        for (int kb = 0; kb < KB; ++kb) {
-            tma_load_2d(sm.k[kb], &map_qkv, D + h * HD + kb * 64, b * T + k0, &sm.kv_full);
-            tma_load_2d(sm.v[kb], &map_qkv, 2 * D + h * HD + kb * 64, b * T + k0, &sm.kv_full);
-        }
-        for (int st = 0; st < nsteps && ok; ++st) {
-            const int qrow = (i0 + st) * QS;
-            if (st >= 1) ok = mbar_wait(&sm.q_free, (st - 1) & 1);
-            if (!ok) break;
-            mbar_expect_tx(&sm.q_full, 4 * QS * HD * 2);
+    if (warp == 0) {
+        // ---- producer warp: lane 0 issues the TMA loads, all lanes stage lse / delta of the step's queries ----
+        if (lane == 0) {
+            mbar_expect_tx(&sm.kv_full, 2 * KT * HD * 2);
             for (int kb = 0; kb < KB; ++kb) {
-                tma_load_2d(sm.q[kb], &map_qkv64, h * HD + kb * 64, b * T + qrow, &sm.q_full);
-                tma_load_2d(sm.dout[kb], &map_do64, h * HD + kb * 64, b * T + qrow, &sm.q_full);
+                tma_load_2d(sm.k[kb], &map_qkv, D + h * HD + kb * 64, b * T + k0, &sm.kv_full);
+                tma_load_2d(sm.v[kb], &map_qkv, 2 * D + h * HD + kb * 64, b * T + k0, &sm.kv_full);
             }
-            tma_load_2d(sm.qt, &map_qt, qrow, (b * H + h) * HD, &sm.q_full);
-            tma_load_2d(sm.dot, &map_dot, qrow, (b * H + h) * HD, &sm.q_full);
+        }
+        const float* lse_h = lse + ((size_t)b * H + h) * T;
+        const float* delta_h = delta + ((size_t)b * H + h) * T;
+        for (int st = 0; st < nsteps; ++st) {
+            const int s = st & 1, qrow = (i0 + st) * QS;
+            // stage s (operands and lse / delta) was last used by step st - 2: free once its dV / dK products are done
+            if (st >= 2 && lane == 0) ok = mbar_wait(&sm.q_free[s], ((st >> 1) - 1) & 1);
+            ok = __shfl_sync(0xFFFFFFFFu, (int)ok, 0) != 0;
+            if (!ok) break;
+            if (lane == 0) {
+                mbar_expect_tx(&sm.q_full[s], 4 * QS * HD * 2);
+                for (int kb = 0; kb < KB; ++kb) {
+                    tma_load_2d(sm.q[s][kb], &map_qkv64, h * HD + kb * 64, b * T + qrow, &sm.q_full[s]);
+                    tma_load_2d(sm.dout[s][kb], &map_do64, h * HD + kb * 64, b * T + qrow, &sm.q_full[s]);
+                }
+                tma_load_2d(sm.qt[s], &map_qt, qrow, (b * H + h) * HD, &sm.q_full[s]);
+                tma_load_2d(sm.dot[s], &map_dot, qrow, (b * H + h) * HD, &sm.q_full[s]);
+            }
+#pragma unroll
+            for (int e = lane; e < QS; e += 32) {
+                const int qq = qrow + e;
+                sm.lse2[s][e] = qq < T ? lse_h[qq] * LOG2E : 0.0f;
+                sm.dls[s][e] = qq < T ? delta_h[qq] * scale : 0.0f;
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.aux_full[s])) : "memory");
         }
     } else if (warp == 1 && lane == 0) {
         constexpr uint32_t idesc_s = umma_idesc_bf16(KT, QS), idesc_o = umma_idesc_bf16(KT, HD);
-        ok = mbar_wait(&sm.kv_full, 0);
-        for (int st = 0; st < nsteps && ok; ++st) {
-            ok = mbar_wait(&sm.q_full, st & 1);
-            if (!ok) break;
+        auto issue_sd = [&](int st) {
+            const int s = st & 1;
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+                const uint64_t da = umma_desc_sw128(smem_u32(sm.k[kb])), db = umma_desc_sw128(smem_u32(sm.q[s][kb]));
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem + (uint32_t)(s * QS), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+            }
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+                const uint64_t da = umma_desc_sw128(smem_u32(sm.v[kb])), db = umma_desc_sw128(smem_u32(sm.dout[s][kb]));
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem + COL_DP + (uint32_t)(s * QS), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+            }
+            umma_commit(&sm.sd_ready[s]);
+        };
+        ok = mbar_wait(&sm.kv_full, 0) && mbar_wait(&sm.q_full[0], 0);
+        if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int kb = 0; kb < KB; ++kb) {
-                const uint64_t da = umma_desc_sw128(smem_u32(sm.k[kb])), db = umma_desc_sw128(smem_u32(sm.q[kb]));
-#pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+            issue_sd(0);
+        }
+        for (int st = 0; st < nsteps && ok; ++st) {
+            const int s = st & 1;
+            if (st + 1 < nsteps) {
+                ok = mbar_wait(&sm.q_full[s ^ 1], ((st + 1) >> 1) & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_sd(st + 1);
             }
-#pragma unroll
-            for (int kb = 0; kb < KB; ++kb) {
-                const uint64_t da = umma_desc_sw128(smem_u32(sm.v[kb])), db = umma_desc_sw128(smem_u32(sm.dout[kb]));
-#pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tmem + COL_DP, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
-            }
-            umma_commit(&sm.s_ready);
             ok = mbar_wait(&sm.p_ready, st & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             {
-                const uint64_t da = umma_desc_sw128(smem_u32(sm.pt)), db = umma_desc_sw128(smem_u32(sm.dot));
+                const uint64_t da = umma_desc_sw128(smem_u32(sm.pt)), db = umma_desc_sw128(smem_u32(sm.dot[s]));
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_bf16(tmem + COL_DV, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (st | k) ? 1u : 0u);
             }
             {
-                const uint64_t da = umma_desc_sw128(smem_u32(sm.dst)), db = umma_desc_sw128(smem_u32(sm.qt));
+                const uint64_t da = umma_desc_sw128(smem_u32(sm.dst)), db = umma_desc_sw128(smem_u32(sm.qt[s]));
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_bf16(tmem + COL_DK, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (st | k) ? 1u : 0u);
             }
-            umma_commit(&sm.q_free);
+            umma_commit(&sm.q_free[s]);                  // the step's operands, and P^T / dS^T, have been consumed
         }
         if (ok) umma_commit(&sm.acc_ready);
     } else if (warp >= 2) {
-        const int quad = warp & 3, r = quad * 32 + lane;     // key row of the tile
+        const int quad = warp & 3, r = quad * 32 + lane, half = (warp - 2) >> 2;     // key row, column half
         const int kj = k0 + r;
         const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
         const float sl2 = scale * LOG2E;
-        // lse and delta of the queries are read straight from global memory: every thread of the CTA reads the same
-        // 64 values per step (broadcast, L1 resident), and no CTA-wide barrier is needed inside the walk.
-        const float* lse_h = lse + ((size_t)b * H + h) * T;
-        const float* delta_h = delta + ((size_t)b * H + h) * T;
         for (int st = 0; st < nsteps; ++st) {
-            const int qrow = (i0 + st) * QS;
-            if (!mbar_wait(&sm.s_ready, st & 1)) { ok = false; break; }
+            const int s = st & 1, qbase = (i0 + st) * QS + half * 32;               // first query of this thread's columns
+            const uint32_t col = (uint32_t)(s * QS + half * 32);
+            if (!mbar_wait(&sm.sd_ready[s], (st >> 1) & 1) || !mbar_wait(&sm.aux_full[s], (st >> 1) & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // query q (column) sees key kj iff kj <= q (causal), q < T, kj < T
-            const int qmin = causal ? kj : 0;
-#pragma unroll 1
-            for (int c = 0; c < QS; c += 32) {
-                uint32_t sv[32], dv[32];
-                tmem_ld32(trow + (uint32_t)c, sv);
-                tmem_ld32(trow + COL_DP + (uint32_t)c, dv);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                uint32_t pp[16], pd[16];
+            uint32_t sv[32], dv[32];
+            tmem_ld32(trow + col, sv);
+            tmem_ld32(trow + COL_DP + col, dv);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // column i (query qbase + i) sees key kj iff kj <= query (causal), query < T, kj < T
+            const int lo = (causal ? kj : 0) - qbase, hi = (kj < T ? T : 0) - qbase;   // visible: lo <= i < hi
+            const float* l2p = sm.lse2[s] + half * 32;
+            const float* dlp = sm.dls[s] + half * 32;
+            uint32_t pp[16], pd[16];
+            auto body = [&](auto full_c) {
+                constexpr bool FULL = decltype(full_c)::value;
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = 0.0f, p1 = 0.0f, d0 = 0.0f, d1 = 0.0f;
-                    const int qa = qrow + c + i;
-                    if (kj < T && qa < T && qa >= qmin) {
-                        p0 = exp2f(fmaf(__uint_as_float(sv[i]), sl2, -__ldg(lse_h + qa) * LOG2E));
-                        d0 = p0 * (__uint_as_float(dv[i]) - __ldg(delta_h + qa)) * scale;
-                    }
-                    if (kj < T && qa + 1 < T && qa + 1 >= qmin) {
-                        p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sl2, -__ldg(lse_h + qa + 1) * LOG2E));
-                        d1 = p1 * (__uint_as_float(dv[i + 1]) - __ldg(delta_h + qa + 1)) * scale;
-                    }
+                    float p0 = ex2(fmaf(__uint_as_float(sv[i]), sl2, -l2p[i]));
+                    float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), sl2, -l2p[i + 1]));
+                    if (!FULL) { p0 = (i >= lo && i < hi) ? p0 : 0.0f; p1 = (i + 1 >= lo && i + 1 < hi) ? p1 : 0.0f; }
+                    const float d0 = p0 * fmaf(__uint_as_float(dv[i]), scale, -dlp[i]);
+                    const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), scale, -dlp[i + 1]);
                     const __nv_bfloat162 tp = __floats2bfloat162_rn(p0, p1), td = __floats2bfloat162_rn(d0, d1);
                     pp[i >> 1] = *reinterpret_cast<const uint32_t*>(&tp);
                     pd[i >> 1] = *reinterpret_cast<const uint32_t*>(&td);
                 }
-                uint8_t* prow = sm.pt + r * 128;
-                uint8_t* drow = sm.dst + r * 128;
+            };
+            if (lo <= 0 && hi >= 32) body(std::true_type{}); else body(std::false_type{});
+            // P^T / dS^T of the previous step must have been consumed before they are overwritten
+            if (st > 0 && !mbar_wait(&sm.q_free[(st - 1) & 1], ((st - 1) >> 1) & 1)) { ok = false; break; }
+            uint8_t* prow = sm.pt + r * 128;
+            uint8_t* drow = sm.dst + r * 128;
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = (c >> 3) + q4;
-                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pp[4 * q4], pp[4 * q4 + 1], pp[4 * q4 + 2], pp[4 * q4 + 3]);
-                    *reinterpret_cast<uint4*>(drow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pd[4 * q4], pd[4 * q4 + 1], pd[4 * q4 + 2], pd[4 * q4 + 3]);
-                }
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const int chunk = half * 4 + q4;
+                *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pp[4 * q4], pp[4 * q4 + 1], pp[4 * q4 + 2], pp[4 * q4 + 3]);
+                *reinterpret_cast<uint4*>(drow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pd[4 * q4], pd[4 * q4 + 1], pd[4 * q4 + 2], pd[4 * q4 + 3]);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -581,13 +708,14 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
         if (ok) ok = mbar_wait(&sm.acc_ready, 0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
-            bf16* krow = dqkv + ((size_t)b * T + kj) * 3 * D + D + h * HD;
+            constexpr int HH = HD / 2;
+            bf16* krow = dqkv + ((size_t)b * T + kj) * 3 * D + D + h * HD + half * HH;
             bf16* vrow = krow + D;
 #pragma unroll 1
-            for (int c = 0; c < HD; c += 32) {
+            for (int c = 0; c < HH; c += 32) {
                 uint32_t vk[32], vv[32];
-                tmem_ld32(trow + COL_DK + (uint32_t)c, vk);
-                tmem_ld32(trow + COL_DV + (uint32_t)c, vv);
+                tmem_ld32(trow + COL_DK + (uint32_t)(half * HH + c), vk);
+                tmem_ld32(trow + COL_DV + (uint32_t)(half * HH + c), vv);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (kj < T) {
 #pragma unroll
@@ -610,7 +738,6 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
 }
-
 
 template <int HD>
 int launch_bwd_tc(const bf16* qkv, const bf16* dout, const float* lse, const float* delta, bf16* scratch, bf16* dqkv,
@@ -640,9 +767,9 @@ int launch_bwd_tc(const bf16* qkv, const bf16* dout, const float* lse, const flo
         attr = true;
     }
     dim3 gq((T + QT - 1) / QT, H, B), gk((T + KT - 1) / KT, H, B);
-    attn_bwd_dq_tc_kernel<HD><<<gq, 192, smem_q, s>>>(mq128, mdo128, mkt, lse, delta, dqkv, T, H, scale, causal, ltl_tc_err_flag());
+    attn_bwd_dq_tc_kernel<HD><<<gq, BWD_THREADS, smem_q, s>>>(mq128, mq64, mdo128, mkt, lse, delta, dqkv, T, H, scale, causal, ltl_tc_err_flag());
     LTL_TRY(ltl_check_launch("attn_bwd_dq_tc"));
-    attn_bwd_dkv_tc_kernel<HD><<<gk, 192, smem_kv, s>>>(mq128, mq64, mdo64, mqt, mdot, lse, delta, dqkv, T, H, scale, causal,
+    attn_bwd_dkv_tc_kernel<HD><<<gk, BWD_THREADS, smem_kv, s>>>(mq128, mq64, mdo64, mqt, mdot, lse, delta, dqkv, T, H, scale, causal,
                                                         ltl_tc_err_flag());
     return ltl_check_launch("attn_bwd_dkv_tc");
 }
