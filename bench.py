@@ -461,6 +461,113 @@ def run_train4(args, dist):
     return line
 
 
+def run_sweep(args, dist):
+    """configs[3]: isolated kernels, fp32 and bf16, inputs ~N(0, 1) from a seed.  Every kernel is queued `iters` times
+    back to back on the library stream (immediate ops in deferred mode) between two CUDA events.  Operands larger
+    than L2 where the shape allows; the small GEMMs are latency cases by construction."""
+    from lanternl_b200 import _lib, luatl_adapter as ad, synth
+    _lib.init(dist.local)
+    pk = peaks()
+    rng_block = synth.normal(7, 0, 1 << 22).astype(np.float32)
+
+    def dev(rows, cols, dt):
+        t = ad.TensorView(rows, cols, dt)
+        n, blk = rows * cols, rng_block
+        host = np.resize(blk, n) if n > blk.size else blk[:n]
+        t.upload(host)
+        return t
+
+    def timed(fn, iters):
+        fn()
+        _lib.call("luaTL_sync")
+        _lib.load().luaTL_set_deferred(1)
+        try:
+            _lib.call("luaTL_timer_start")
+            for _ in range(iters):
+                fn()
+            ms = C.c_float()
+            _lib.call("luaTL_timer_stop", C.byref(ms))
+        finally:
+            _lib.load().luaTL_set_deferred(0)
+        return ms.value * 1e3 / iters                      # us per launch
+
+    rows_out = []
+
+    def record(kernel, shape, dt, us, nbytes=None, flops=None):
+        e = dict(kernel=kernel, shape=shape, dtype="bf16" if dt == _lib.BF16 else "f32", us=round(us, 2))
+        if nbytes is not None:
+            e["gbs"] = round(nbytes / us * 1e-3, 1)
+            e["hbm_frac"] = round(e["gbs"] / pk["hbm_gbs"], 3)
+        if flops is not None:
+            e["tflops"] = round(flops / us * 1e-6, 2)
+            if dt == _lib.BF16:
+                e["tensor_frac"] = round(e["tflops"] / pk["bf16_tflops"], 3)
+        rows_out.append(e)
+
+    it = args.sweep_iters
+    # GEMMs: fp32 on the CUDA cores (exact path), bf16 on the tensor cores (B stored [N, K])
+    for M in (1, 32, 256, 4096):
+        for N in (512, 1408, 8000):
+            for K in (512, 1408):
+                A, B, Cc = dev(M, K, _lib.F32), dev(K, N, _lib.F32), ad.TensorView(M, N, _lib.F32)
+                us = timed(lambda: _lib.call("luaTL_gemm_ex", A.data, B.data, Cc.data, None, None, None, M, N, K, _lib.F32,
+                                             K, 1, N, 1, N, 1, 0, 0, 0, 1, 1.0, 0.0, 0.0, 0, 0), it)
+                record("gemm_simt", f"{M}x{N}x{K}", _lib.F32, us, nbytes=4.0 * (M * K + K * N + M * N), flops=2.0 * M * N * K)
+                Ab, Bb, Cb = dev(M, K, _lib.BF16), dev(N, K, _lib.BF16), ad.TensorView(M, N, _lib.BF16)
+                us = timed(lambda: _lib.call("luaTL_gemm_bf16_tc", Ab.data, Bb.data, Cb.data, None, M, N, K, _lib.BF16, 0), it)
+                record("gemm_tc", f"{M}x{N}x{K}", _lib.BF16, us, nbytes=2.0 * (M * K + K * N + M * N), flops=2.0 * M * N * K)
+                for t in (A, B, Cc, Ab, Bb, Cb):
+                    t.free()
+    for dt, e in ((_lib.F32, 4), (_lib.BF16, 2)):
+        for cols in (128, 512, 2048):
+            rows = 65536
+            x, y, g = dev(rows, cols, dt), ad.TensorView(rows, cols, dt), dev(1, cols, dt)
+            us = timed(lambda: _lib.call("luaTL_rmsnorm", x.data, g.data, y.data, rows, cols, 1e-5, dt), it)
+            record("rmsnorm", f"{rows}x{cols}", dt, us, nbytes=2.0 * rows * cols * e)
+            us = timed(lambda: _lib.call("luaTL_softmax", x.data, None, y.data, rows, cols, 1.0, 0, 0, dt), it)
+            record("softmax", f"{rows}x{cols}", dt, us, nbytes=2.0 * rows * cols * e)
+            for t in (x, y, g):
+                t.free()
+        Bq, Hq, Tq, Dq = 64, 16, 1024, 64
+        x = dev(Bq * Tq, Hq * Dq, dt)
+        pos = ad.ids(Bq * Tq)
+        ad.upload_i32(pos, np.tile(np.arange(Tq, dtype=np.int32), Bq))
+        us = timed(lambda: _lib.call("luaTL_rope", x.data, pos.t.data, Bq * Tq, Hq, Dq, Hq * Dq, 0, 10000.0, 0, 0, dt), it)
+        record("rope", f"[{Bq},{Hq},{Tq},{Dq}]", dt, us, nbytes=2.0 * Bq * Tq * Hq * Dq * e)
+        x.free()
+        rows, F = 65536, 5632
+        a, b, o = dev(rows, F, dt), dev(rows, F, dt), ad.TensorView(rows, F, dt)
+        us = timed(lambda: _lib.call("luaTL_swiglu_fwd", a.data, b.data, o.data, rows, F, F, F, F, dt), it)
+        record("swiglu", f"{rows}x{F}", dt, us, nbytes=3.0 * rows * F * e)
+        for t in (a, b, o):
+            t.free()
+    rows, V = 16384, 32000
+    lg, dl = dev(rows, V, _lib.F32), ad.TensorView(rows, V, _lib.F32)
+    tg = ad.ids(rows)
+    ad.upload_i32(tg, synth.zipf_ids(3, rows, V))
+    losses = ad.TensorView(rows, 1, _lib.F32)
+    us = timed(lambda: _lib.call("luaTL_cross_entropy", lg.data, tg.t.data, losses.data, None, rows, V, -1, 1.0, _lib.F32), max(2, it // 4))
+    record("cross_entropy fwd", f"{rows}x{V}", _lib.F32, us, nbytes=4.0 * rows * V)
+    us = timed(lambda: _lib.call("luaTL_cross_entropy", lg.data, tg.t.data, losses.data, dl.data, rows, V, -1, 1.0, _lib.F32), max(2, it // 4))
+    record("cross_entropy fwd+bwd", f"{rows}x{V}", _lib.F32, us, nbytes=8.0 * rows * V)
+    hb = [r["hbm_frac"] for r in rows_out if r["kernel"] not in ("gemm_simt", "gemm_tc") and "hbm_frac" in r]
+    geo = float(np.exp(np.mean(np.log(hb))))
+    best_tc = max(r["tensor_frac"] for r in rows_out if r["kernel"] == "gemm_tc")
+    return dict(
+        metric="sweep_hbm_fraction_geomean", value=geo, unit="fraction of measured HBM copy bandwidth", n_gpus=1,
+        steps=args.sweep_iters, warmup=1, ms_per_step=sum(r["us"] for r in rows_out) * 1e-3, higher_is_better=True,
+        scaling="weak", vs_baseline=None, dtype="f32+bf16", data="synthetic",
+        config=dict(workload="configs[3] isolated kernel sweep (GEMM 4x3x2 shapes in fp32 and bf16; RMSNorm, softmax 65536 rows x "
+                             "{128,512,2048}; RoPE [64,16,1024,64]; SwiGLU 65536x5632; CE 16384x32000)",
+                    l2="row kernels, SwiGLU and CE operands are 32 MB .. 2.1 GB (most above L2); no flush between launches of the same "
+                       "kernel, so the 32 and 64 MB cases run from L2 and read above the HBM roof"),
+        gpu_launches=len(rows_out) * (args.sweep_iters + 1),
+        roofline=dict(bound="hbm", achieved=geo * pk["hbm_gbs"], peak=pk["hbm_gbs"], unit="GB/s", frac=geo, traffic=None,
+                      peak_source=pk["source"], kernel="geometric mean over the row-wise kernels of the sweep",
+                      best_gemm_tc_tensor_frac=best_tc),
+        kernels=rows_out)
+
+
 def host_threads():
     """Host threads this process may use (cgroup / affinity aware), at most 32 and at most one per sequence."""
     try:
@@ -556,7 +663,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "train", "train4"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "train", "train4", "sweep"])
+    ap.add_argument("--sweep-iters", type=int, default=20, help="sweep: launches per timed kernel")
     ap.add_argument("--micro-batch", type=int, default=8, help="train4: sequences per micro-batch")
     ap.add_argument("--global-batch", type=int, default=TRAIN4_GLOBAL_BATCH, help="train4: sequences per optimizer step over all GPUs")
     ap.add_argument("--layers", type=int, default=0, help="train4: layer count override (profiling aid; the metric uses 16)")
@@ -573,7 +681,7 @@ def main():
             print(json.dumps(run_reference(args, d)), flush=True)
         return
     dist = Dist(args.gpus)
-    line = {"decode": run_decode, "train": run_train, "train4": run_train4}[args.workload](args, dist)
+    line = {"decode": run_decode, "train": run_train, "train4": run_train4, "sweep": run_sweep}[args.workload](args, dist)
     if dist.rank == 0:
         if dist.world == 1 and not args.no_cpu_baseline:
             threads = host_threads()

@@ -229,6 +229,13 @@ int luaTL_attention_bwd(const void* qkv, const void* out, const void* dout, cons
  * token-major matrices (both tensor-core operands MN-major, nothing is transposed in memory).  M, N multiples
  * of 8.  ksplit: slices of K added with atomics (0/1 = one). */
 int luaTL_gemm_bf16_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K, int ksplit);
+/* New: device-side timing of immediate ops.  luaTL_set_deferred(1) makes the immediate entry points return
+ * without waiting for the stream (errors of queued kernels then surface at the next luaTL_sync / luaTL_timer_stop);
+ * luaTL_timer_start / luaTL_timer_stop bracket a stretch of the library stream with CUDA events and return the
+ * elapsed milliseconds.  The reference times from the host (ai/gpu/luaTL.lua); it has no counterpart. */
+void luaTL_set_deferred(int on);
+int  luaTL_timer_start(void);
+int  luaTL_timer_stop(float* ms);
 /* New: the same GEMM launched `iters` times back to back on the library stream and timed with CUDA events
  * (ms per launch), for roofline measurements without host gaps.  No residual operand. */
 int luaTL_gemm_bf16_tc_time(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int tile_n,

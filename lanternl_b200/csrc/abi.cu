@@ -57,9 +57,13 @@ bool ltl_pdl_enabled() { return g_pdl; }
 void ltl_pdl_set(bool on) { g_pdl = on; }
 int ltl_sm_count() { return g_sm_count; }
 
+static bool g_deferred = false;          // luaTL_set_deferred(1): immediate ops do not wait for the stream
+static cudaEvent_t g_timer[2] = { nullptr, nullptr };
+
 static int sync_stream(const char* ctx)
 {
     LTL_TRY(ltl_check_launch(ctx));
+    if (g_deferred) return LTL_OK;
     LTL_CUDA(ctx, cudaStreamSynchronize(g_stream));
     return LTL_OK;
 }
@@ -592,6 +596,27 @@ int luaTL_gemm_bf16_tc(const void* A, const void* B, void* C, const void* R, int
     LTL_TRY(ltl_require_init("gemm_bf16_tc"));
     LTL_TRY(ltl_gemm_tc(A, B, C, R, M, N, K, c_dtype, tile_n & 0xFFFF, (tile_n >> 16) & 3, (tile_n >> 20) & 0xFF, g_stream));
     LTL_TRY(sync_stream("gemm_bf16_tc"));
+    return g_deferred ? LTL_OK : ltl_gemm_tc_check(g_stream);      // deferred: luaTL_timer_stop reads the flag
+}
+// Immediate ops normally return after the stream has drained (the reference's contract).  Deferred mode lets a
+// caller queue many of them back to back; luaTL_sync or luaTL_timer_stop waits.  Errors of queued kernels then
+// surface at that wait.
+void luaTL_set_deferred(int on) { g_deferred = on != 0; }
+int luaTL_timer_start(void)
+{
+    LTL_TRY(ltl_require_init("timer_start"));
+    for (int i = 0; i < 2; ++i)
+        if (!g_timer[i]) LTL_CUDA("timer_start", cudaEventCreate(&g_timer[i]));
+    LTL_CUDA("timer_start", cudaEventRecord(g_timer[0], g_stream));
+    return LTL_OK;
+}
+int luaTL_timer_stop(float* ms)
+{
+    LTL_TRY(ltl_require_init("timer_stop"));
+    if (!ms || !g_timer[1]) return ltl_fail(LTL_ERR_ARG, "timer_stop: no result pointer, or timer_start was not called");
+    LTL_CUDA("timer_stop", cudaEventRecord(g_timer[1], g_stream));
+    LTL_CUDA("timer_stop", cudaStreamSynchronize(g_stream));
+    LTL_CUDA("timer_stop", cudaEventElapsedTime(ms, g_timer[0], g_timer[1]));
     return ltl_gemm_tc_check(g_stream);
 }
 int luaTL_gemm_bf16_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K, int ksplit)

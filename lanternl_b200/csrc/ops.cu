@@ -324,7 +324,7 @@ softmax_warp_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __re
         if (e < cols) {
 #pragma unroll
             for (int i = 0; i < N; ++i) {
-                v[c][i] = (e + i <= limit) ? expf(v[c][i] - base) : 0.0f;
+                v[c][i] = (e + i <= limit) ? __expf(v[c][i] - base) : 0.0f;
                 sum += v[c][i];
             }
         }
@@ -874,6 +874,71 @@ __global__ void ce_kernel(const T* __restrict__ logits, const int32_t* __restric
     }
 }
 
+// fp32 rows of up to 32768 logits (a multiple of 4): the row lives in registers (NV float4 per thread, 1024
+// threads), so the logits are read once with 16-byte loads, never staged in shared memory, and dlogits is written
+// from the registers.  Same results as ce_kernel up to the rounding of the fast exponential.
+template <int NV>
+__global__ void __launch_bounds__(1024)
+ce_reg_kernel(const float* __restrict__ logits, const int32_t* __restrict__ targets, float* __restrict__ losses,
+              float* __restrict__ dlogits, int32_t* __restrict__ pred, int rows, int V, int ignore_index, float gscale)
+{
+    __shared__ float red[33];
+    __shared__ float red_v[32];
+    __shared__ int red_i[32];
+    const int r = blockIdx.x;
+    const float* lr = logits + (size_t)r * V;
+    float* dr = dlogits ? dlogits + (size_t)r * V : nullptr;
+    const int t = targets[r];
+    const bool ignored = t < 0 || t >= V || t == ignore_index;
+    if (ignored && !pred) {
+        if (threadIdx.x == 0 && losses) losses[r] = 0.0f;
+        if (dr) for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) *reinterpret_cast<float4*>(dr + i) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        return;
+    }
+    float4 v[NV];
+    float best = -INFINITY;
+    int bi = 0x7FFFFFFF;
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
+        const int i = (c * 1024 + threadIdx.x) * 4;
+        v[c] = i < V ? *reinterpret_cast<const float4*>(lr + i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        if (v[c].x > best) { best = v[c].x; bi = i; }
+        if (v[c].y > best) { best = v[c].y; bi = i + 1; }
+        if (v[c].z > best) { best = v[c].z; bi = i + 2; }
+        if (v[c].w > best) { best = v[c].w; bi = i + 3; }
+    }
+    block_argmax(best, bi, red_v, red_i);
+    if (pred && threadIdx.x == 0) pred[r] = bi;
+    if (ignored) {
+        if (threadIdx.x == 0 && losses) losses[r] = 0.0f;
+        if (dr) for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) *reinterpret_cast<float4*>(dr + i) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        return;
+    }
+    const float mx = best;
+    float sum = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
+        v[c].x = __expf(v[c].x - mx); v[c].y = __expf(v[c].y - mx); v[c].z = __expf(v[c].z - mx); v[c].w = __expf(v[c].w - mx);
+        sum += (v[c].x + v[c].y) + (v[c].z + v[c].w);
+    }
+    const float xt = lr[t];               // read before dlogits may overwrite the row
+    sum = block_sum(sum, red);
+    const float ssum = fmaxf(sum, 1e-30f);
+    if (threadIdx.x == 0 && losses) losses[r] = logf(ssum) + mx - xt;
+    if (dr) {
+        const float k = gscale / ssum;
+#pragma unroll
+        for (int c = 0; c < NV; ++c) {
+            const int i = (c * 1024 + threadIdx.x) * 4;
+            if (i < V) {
+                float4 p = make_float4(v[c].x * k, v[c].y * k, v[c].z * k, v[c].w * k);
+                if (t == i) p.x -= gscale; else if (t == i + 1) p.y -= gscale; else if (t == i + 2) p.z -= gscale; else if (t == i + 3) p.w -= gscale;
+                *reinterpret_cast<float4*>(dr + i) = p;
+            }
+        }
+    }
+}
+
 int ltl_cross_entropy(const void* logits, const int32_t* targets, float* losses, void* dlogits,
                       int32_t* pred, int rows, int vocab, int ignore_index, float grad_scale,
                       int dtype, cudaStream_t s)
@@ -881,6 +946,13 @@ int ltl_cross_entropy(const void* logits, const int32_t* targets, float* losses,
     if (!logits || !targets) return ltl_fail(LTL_ERR_NULL, "cross_entropy: null pointer");
     if (rows < 0 || vocab <= 0) return ltl_fail(LTL_ERR_SHAPE, "cross_entropy: bad shape %dx%d", rows, vocab);
     if (rows == 0) return LTL_OK;
+    if (dtype == LTL_F32 && vocab % 4 == 0 && vocab >= 4096 && vocab <= 32768 && aligned16(logits) && (!dlogits || aligned16(dlogits))) {
+        const int nv = (vocab + 4095) / 4096;
+#define CE_REG(NVV) ce_reg_kernel<NVV><<<rows, 1024, 0, s>>>((const float*)logits, targets, losses, (float*)dlogits, pred, rows, vocab, ignore_index, grad_scale)
+        if (nv <= 2) CE_REG(2); else if (nv <= 4) CE_REG(4); else CE_REG(8);
+#undef CE_REG
+        return ltl_check_launch("cross_entropy");
+    }
     const bool cache = vocab <= CE_SMEM_MAX_V;
     const int threads = vocab >= 8192 ? 1024 : (vocab >= 1024 ? 512 : 256);
     const size_t smem = cache ? (size_t)vocab * sizeof(float) : 0;
