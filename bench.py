@@ -5,10 +5,13 @@ Default workload (BASELINE.json configs[2]): batched greedy decode - vocab 8000,
 8 layers, 8 heads, ffn 1408, ctx 1024, bf16 weights, fp32 accumulation; 256 independent
 sequences with 128-token Zipf(1.1) prompts, prefill then 512 generated tokens each, the
 sequences sharded over the GPUs (256/N per GPU, no communication).  One step = one full pass
-(prefill + 511 decode steps) over this rank's sequences.  `--workload train` times the
-configs[1] training step (fp32, forward + CE + backward + SGD) instead.
+(prefill + 511 decode steps) over this rank's sequences.  Other workloads:
+  --workload train    configs[1] training step (fp32, forward + CE + backward + SGD)
+  --workload train4   configs[4] data-parallel mixed-precision training (0.9 B parameters, global batch 64 x 2048
+                      split over the ranks, micro-batches accumulating into the flat gradient)
+  --workload sweep    configs[3] isolated kernel sweep (one GPU)
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|train]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|train|train4|sweep]
 
 Prints ONE JSON line (rank 0).  `value` is timed with the inputs resident in HBM; `e2e` goes
 through the host-facing call with host buffers (H2D of the prompts / ids, D2H of the result).
