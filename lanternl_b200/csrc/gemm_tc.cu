@@ -16,6 +16,7 @@
 // No cluster launch and no TMA multicast: the kernel is the same on 1 and on N GPUs.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <map>
 #include <tuple>
 
@@ -29,7 +30,7 @@ constexpr int BM = 128, BK = 64, UMMA_K = 16;
 // step are short (K = 512 ... 1408, 8 ... 22 k-blocks); with a deep ring most of a CTA's operand
 // bytes are requested at once and the kernel is bound by one memory round trip, not by one per
 // four k-blocks.
-template <int BN> struct Ring { static constexpr int STAGES = BN == 32 ? 10 : (BN == 64 ? 8 : 6); };
+template <int BN> struct Ring { static constexpr int STAGES = BN == 32 ? 10 : (BN == 64 ? 8 : (BN == 128 ? 6 : 4)); };
 enum { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ATOMIC = 2 };
 using namespace tc;
 
@@ -291,7 +292,7 @@ int launch(const void* A, const void* B, void* C, const void* R, int M, int N, i
     // Many tiles per SM: two CTAs per SM (about 100 KB of ring each).  Otherwise the allocation stays that of
     // the full ring whatever the depth used, which keeps one CTA per SM (each then has an SM's load path alone).
     const bool many = (long long)grid.x * grid.y * grid.z >= 2LL * ltl_sm_count();
-    if (many) stages = BN == 128 ? 3 : (BN == 64 ? 4 : 5);
+    if (many) stages = BN == 256 ? 2 : (BN == 128 ? 3 : (BN == 64 ? 4 : 5));
     if (stages > kb_per) stages = kb_per;
     if (stages < 1) stages = 1;
     const size_t smem = smem_bytes<BN>(many ? stages : Ring<BN>::STAGES);
@@ -316,13 +317,13 @@ int launch_mn(const void* X, const void* Y, float* C, int M, int N, int K, int k
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, ksplit < 1 ? 1 : ksplit);
     const int kb_all = (K + BK - 1) / BK;
     const int kb_per = (kb_all + (int)grid.z - 1) / (int)grid.z;
-    int stages = BN == 128 ? 3 : 4;
+    int stages = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
     if (stages > kb_per) stages = kb_per;
     const size_t smem = smem_bytes<BN>(stages);
     static bool attr_set = false;
     if (!attr_set) {
         LTL_CUDA("gemm_tc attr", cudaFuncSetAttribute(gemm_tc_kernel<BN, float, EPI_ATOMIC, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                      (int)smem_bytes<BN>(4)));
+                                                      (int)smem_bytes<BN>(BN == 256 ? 2 : 4)));
         attr_set = true;
     }
     gemm_tc_kernel<BN, float, EPI_ATOMIC, 1><<<grid, 192, smem, s>>>(ma, mb, C, nullptr, M, N, K, stages, g_err_flag);
@@ -339,6 +340,8 @@ int ltl_gemm_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K,
     if (M <= 0 || N <= 0 || K <= 0 || M % 8 || N % 8 || (reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(Y) & 15))
         return ltl_fail(LTL_ERR_UNSUPPORTED, "gemm_tc_xty: M and N must be multiples of 8 and the operands 16-byte aligned (M=%d N=%d K=%d)", M, N, K);
     if (!ltl_tc_err_flag()) return ltl_fail(LTL_ERR_OOM, "gemm_tc_xty: error flag");
+    if (N >= 256 && (long long)((M + BM - 1) / BM) * ((N + 255) / 256) * (ksplit < 1 ? 1 : ksplit) >= 4LL * ltl_sm_count())
+        return launch_mn<256>(X, Y, C, M, N, K, ksplit, s);
     if (N >= 128) return launch_mn<128>(X, Y, C, M, N, K, ksplit, s);
     return launch_mn<64>(X, Y, C, M, N, K, ksplit, s);
 }
@@ -374,6 +377,10 @@ static int pick_bn(int M, int N)
         const int ctas = mt * ((N + c - 1) / c);
         if (ctas <= sms && ctas > best_ctas) { best = c; best_ctas = ctas; }
     }
+    // Many tiles: the 128 x 256 tile (a third fewer L2 bytes per FLOP than 128 x 128; two CTAs per SM with a two-stage
+    // ring each) for grids of at least four such tiles per SM.  LUATL_GEMM_BN=128 keeps the narrower tile.
+    static const int wide = [] { const char* e = getenv("LUATL_GEMM_BN"); return e ? atoi(e) : 256; }();
+    if (best_ctas < 0 && wide == 256 && N >= 256 && (long long)mt * ((N + 255) / 256) >= 4LL * sms) best = 256;
     return best;
 }
 
@@ -431,9 +438,9 @@ int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int
         if (c_dtype == LTL_BF16) return launch<BNV, bf16, EPI_NONE>(A, B, C, R, M, N, K, 1, s);             \
         return ltl_fail(LTL_ERR_DTYPE, "gemm_tc: output dtype %d", c_dtype);                             \
     }
-    TC_CASE(32) TC_CASE(64) TC_CASE(128)
+    TC_CASE(32) TC_CASE(64) TC_CASE(128) TC_CASE(256)
 #undef TC_CASE
-    return ltl_fail(LTL_ERR_ARG, "gemm_tc: tile width %d not in {32, 64, 128}", bn);
+    return ltl_fail(LTL_ERR_ARG, "gemm_tc: tile width %d not in {32, 64, 128, 256}", bn);
 }
 
 // 1 when a bounded wait inside the kernel ran out since the last call (and clears the flag).

@@ -32,7 +32,7 @@ def run(M, N, K, tile, c_dtype=_lib.F32, residual=False, seed=0):
     return got, ref
 
 
-@pytest.mark.parametrize("tile", [32, 64, 128])
+@pytest.mark.parametrize("tile", [32, 64, 128, 256])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 512), (128, 64, 1408)])
 def test_exact_tiles(M, N, K, tile):
     got, ref = run(M, N, K, tile)
@@ -146,3 +146,10 @@ def test_weight_gradient_product_rejects_unaligned_widths():
     Cc = ad.TensorView(100, 64, _lib.F32)
     with pytest.raises(_lib.LuaTLError, match="UNSUPPORT"):
         _lib.call("luaTL_gemm_bf16_tc_xty", X.data, Y.data, Cc.data, 100, 64, 64, 1)
+
+
+def test_256_wide_tile_many_tile_grid_and_tails():
+    got, ref = run(4096, 5632, 520, 256, seed=12)              # 16 x 22 tiles: the two-stage two-CTA configuration
+    assert rel_err(got, ref) < 1e-5
+    got, ref = run(300, 700, 72, 256, c_dtype=_lib.BF16, residual=True, seed=13)
+    assert rel_err(got, ref) < 8e-3
