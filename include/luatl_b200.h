@@ -236,6 +236,11 @@ int luaTL_gemm_bf16_tc_xty(const void* X, const void* Y, float* C, int M, int N,
 void luaTL_set_deferred(int on);
 int  luaTL_timer_start(void);
 int  luaTL_timer_stop(float* ms);
+/* New: RMSNorm backward fused with the residual add of the backward pass: res += d(rmsnorm)/dx (fp32, in place),
+ * res_bf16 (optional) = bf16 copy of the updated res, dgamma (optional) += the gain gradient.  fp32 x / dy, cols a
+ * multiple of 4, at most 4096.  Equals luaTL_rmsnorm_bwd followed by an add and a cast. */
+int luaTL_rmsnorm_bwd_residual(const float* x, const float* gamma, const float* dy, float* res, void* res_bf16, float* dgamma,
+                               int rows, int cols, float eps);
 /* New: the same GEMM launched `iters` times back to back on the library stream and timed with CUDA events
  * (ms per launch), for roofline measurements without host gaps.  No residual operand. */
 int luaTL_gemm_bf16_tc_time(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int tile_n,

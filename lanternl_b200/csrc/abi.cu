@@ -619,6 +619,18 @@ int luaTL_timer_stop(float* ms)
     LTL_CUDA("timer_stop", cudaEventElapsedTime(ms, g_timer[0], g_timer[1]));
     return ltl_gemm_tc_check(g_stream);
 }
+int luaTL_rmsnorm_bwd_residual(const float* x, const float* gamma, const float* dy, float* res, void* res_bf16, float* dgamma,
+                               int rows, int cols, float eps)
+{
+    LTL_TRY(ltl_require_init("rmsnorm_bwd_residual"));
+    float* scratch = nullptr;
+    if (dgamma) {
+        scratch = workspace(ltl_rmsnorm_bwd_scratch_floats(cols));
+        if (!scratch) return LTL_ERR_OOM;
+    }
+    LTL_TRY(ltl_rmsnorm_bwd_residual(x, gamma, dy, res, (bf16*)res_bf16, dgamma, rows, cols, eps, scratch, g_stream));
+    return sync_stream("rmsnorm_bwd_residual");
+}
 int luaTL_gemm_bf16_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K, int ksplit)
 {
     LTL_TRY(ltl_require_init("gemm_bf16_tc_xty"));
@@ -659,12 +671,8 @@ int luaTL_attention_fwd(const void* qkv, void* out, float* lse, int B, int T, in
     const bool tc_ok = ltl_attn_tc_supported(T, H, hd, dtype);
     if (impl == 2 && !tc_ok) return ltl_fail(LTL_ERR_UNSUPPORTED, "attention_fwd: the tensor-core kernel needs bf16, head_dim 64 or 128 and T %% 8 == 0");
     if (impl == 2 || (impl == 0 && tc_ok)) {
-        void* vt = nullptr;
-        LTL_CUDA("attention_fwd scratch", cudaMalloc(&vt, (size_t)B * T * H * hd * 2));
-        int rc = ltl_attn_fwd_tc(qkv, vt, out, lse, B, T, H, hd, scale, causal, g_stream);
-        if (rc == LTL_OK) rc = sync_stream("attention_fwd");
-        cudaFree(vt);
-        LTL_TRY(rc);
+        LTL_TRY(ltl_attn_fwd_tc(qkv, out, lse, B, T, H, hd, scale, causal, g_stream));
+        LTL_TRY(sync_stream("attention_fwd"));
         return ltl_gemm_tc_check(g_stream);
     }
     ONE_SHOT("attention_fwd", ltl_attn_fwd(qkv, out, lse, B, T, H, hd, scale, causal, dtype, g_stream));
@@ -677,16 +685,12 @@ int luaTL_attention_bwd(const void* qkv, const void* out, const void* dout, cons
     const bool tc_ok = ltl_attn_tc_supported(T, H, hd, dtype);
     if (impl == 2 && !tc_ok) return ltl_fail(LTL_ERR_UNSUPPORTED, "attention_bwd: the tensor-core kernels need bf16, head_dim 64 or 128 and T %% 8 == 0");
     const bool tc = impl == 2 || (impl == 0 && tc_ok);
-    const size_t hm = (size_t)B * T * H * hd;
     float* delta = nullptr;
-    void* scratch = nullptr;
     LTL_CUDA("attention_bwd scratch", cudaMalloc(&delta, (size_t)B * H * T * 4));
-    if (tc && cudaMalloc(&scratch, 3 * hm * 2) != cudaSuccess) { cudaFree(delta); cudaGetLastError(); return ltl_fail(LTL_ERR_OOM, "attention_bwd: scratch"); }
-    int rc = tc ? ltl_attn_bwd_tc(qkv, out, dout, lse, delta, scratch, dqkv, B, T, H, hd, scale, causal, g_stream)
+    int rc = tc ? ltl_attn_bwd_tc(qkv, out, dout, lse, delta, dqkv, B, T, H, hd, scale, causal, g_stream)
                 : ltl_attn_bwd(qkv, out, dout, lse, delta, dqkv, B, T, H, hd, scale, causal, dtype, g_stream);
     if (rc == LTL_OK) rc = sync_stream("attention_bwd");
     cudaFree(delta);
-    if (scratch) cudaFree(scratch);
     LTL_TRY(rc);
     return tc ? ltl_gemm_tc_check(g_stream) : LTL_OK;
 }

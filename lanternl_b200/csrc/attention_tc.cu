@@ -6,13 +6,14 @@
 // [B*H*T, T] softmax and a second batched GEMM (ai/gpu/gpu_transformer.lua:333-352, backward :431-470),
 // materialising the T x T probabilities; here they never leave the SM.
 //
-// Every tensor-core operand is K-major (contraction dimension contiguous), the one layout the GEMM
-// kernel of this library already uses.  Operands whose natural layout has the other orientation are
-// transposed once per layer into head-major copies [B*H*hd, T] by a small kernel (V for the forward;
-// Q, K and dO for the backward) instead of being addressed through MN-major descriptors.
+// Every operand is read from the packed qkv / dO matrices as it lies.  Tiles whose contraction dimension is the
+// contiguous one (Q, K for the scores; V, dO for dP) are K-major operands; the same tiles serve as MN-major B
+// operands where the contraction runs over their rows (V in P V; K in dS K; Q in dS^T Q; dO in P^T dO) - one
+// shared-memory copy, two descriptors.  P, dS, P^T and dS^T are written by the softmax threads in the swizzled
+// K-major layout.
 //
 // Forward, one CTA per (128 query rows, head, sequence), key tiles of 128, double-buffered:
-//   warp 0    TMA producer: Q once, then K_j (from qkv) and V^T_j (from the head-major copy) per tile
+//   warp 0    TMA producer: Q once, then K_j and V_j per tile
 //   warp 1    MMA issuer:   S_j = Q K_j^T and O_j = P_j V_j into double-buffered tensor memory (S_{j+1} is issued
 //                           before P_j V_j, so it runs while the softmax threads work on S_j)
 //   warps 2-9 softmax:      two threads per query row, each owning 64 score columns and hd/2 output columns: S from
@@ -41,36 +42,11 @@ __device__ __forceinline__ float ex2(float x)
     return y;
 }
 
-// [R, 3D] -> head-major transposes: dst[((b*H + h)*HD + d) * T + t] = src[(b*T + t) * pitch + col0 + h*HD + d]
-__global__ void __launch_bounds__(256)
-head_transpose_kernel(const bf16* __restrict__ src, bf16* __restrict__ dst, int T, int H, int HD, long long pitch, int col0)
-{
-    __shared__ bf16 tile[64][66];
-    const int b = blockIdx.z / H, h = blockIdx.z % H;
-    const int t0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    for (int j = ty; j < 64; j += 8) {
-        const int t = t0 + j;
-        __nv_bfloat162 v = __floats2bfloat162_rn(0.0f, 0.0f);
-        if (t < T) v = *reinterpret_cast<const __nv_bfloat162*>(src + ((size_t)b * T + t) * pitch + col0 + h * HD + d0 + 2 * tx);
-        tile[j][2 * tx] = __low2bfloat16(v); tile[j][2 * tx + 1] = __high2bfloat16(v);
-    }
-    __syncthreads();
-    for (int j = ty; j < 64; j += 8) {
-        const int d = d0 + j, t = t0 + 2 * tx;
-        if (t < T) {
-            bf16* o = dst + ((size_t)(b * H + h) * HD + d) * T + t;
-            if (t + 1 < T) *reinterpret_cast<__nv_bfloat162*>(o) = __halves2bfloat162(tile[2 * tx][j], tile[2 * tx + 1][j]);
-            else o[0] = tile[2 * tx][j];
-        }
-    }
-}
-
 template <int HD>
 struct FwdSmem {
     alignas(1024) uint8_t q[HD / 64][QT * 128];
     alignas(1024) uint8_t k[2][HD / 64][KT * 128];
-    alignas(1024) uint8_t vt[2][KT / 64][HD * 128];
+    alignas(1024) uint8_t v[2][HD / 64][KT * 128];
     alignas(1024) uint8_t p[KT / 64][QT * 128];
     float mx[2][2][QT];                                 // [tile parity][column half][row]: partial row maxima
     float lsum[2][QT];                                  // final exchange of the partial denominators
@@ -89,8 +65,7 @@ constexpr int FWD_THREADS = 320;
 
 template <int HD>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
-attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_vt,
-                   bf16* __restrict__ out, float* __restrict__ lse, int T, int H, float scale, int causal,
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, bf16* __restrict__ out, float* __restrict__ lse, int T, int H, float scale, int causal,
                    int* __restrict__ err)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -133,12 +108,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
             if (j >= 2) ok = mbar_wait(&sm.kv_free[s], ((j >> 1) - 1) & 1);
             if (!ok) break;
             mbar_expect_tx(&sm.kv_full[s], 2 * KT * HD * 2);
-            for (int kb = 0; kb < KB; ++kb) tma_load_2d(sm.k[s][kb], &map_qkv, D + h * HD + kb * 64, b * T + j * KT, &sm.kv_full[s]);
-            for (int kb = 0; kb < KT / 64; ++kb) tma_load_2d(sm.vt[s][kb], &map_vt, j * KT + kb * 64, (b * H + h) * HD, &sm.kv_full[s]);
+            for (int kb = 0; kb < KB; ++kb) {
+                tma_load_2d(sm.k[s][kb], &map_qkv, D + h * HD + kb * 64, b * T + j * KT, &sm.kv_full[s]);
+                tma_load_2d(sm.v[s][kb], &map_qkv, 2 * D + h * HD + kb * 64, b * T + j * KT, &sm.kv_full[s]);
+            }
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
-        constexpr uint32_t idesc_s = umma_idesc_bf16(QT, KT), idesc_o = umma_idesc_bf16(QT, HD);
+        constexpr uint32_t idesc_s = umma_idesc_bf16(QT, KT), idesc_o = umma_idesc_bf16_bmn(QT, HD);
         auto issue_s = [&](int j) {
             const int s = j & 1;
 #pragma unroll
@@ -167,12 +144,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
             ok = mbar_wait(&sm.p_ready, j & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // O_j = P V_j: P is K-major (two blocks of 64 keys); V_j is read as it lies, [128 keys x hd] = an MN-major B
+            // operand: hd column blocks KT * 128 bytes apart, 16 key rows (2048 bytes) further per UMMA.
 #pragma unroll
-            for (int kb = 0; kb < KT / 64; ++kb) {
-                const uint64_t da = umma_desc_sw128(smem_u32(sm.p[kb])), db = umma_desc_sw128(smem_u32(sm.vt[s][kb]));
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem + COL_O + (uint32_t)(s * 128), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (kb | k) ? 1u : 0u);
+            for (int ks = 0; ks < KT / 16; ++ks) {
+                const uint64_t da = umma_desc_sw128(smem_u32(sm.p[ks >> 2])) + (uint64_t)((ks & 3) * 2);
+                const uint64_t db = umma_desc_sw128_mn(smem_u32(sm.v[s][0]) + ks * 2048, KT * 128, 1024);
+                umma_bf16(tmem + COL_O + (uint32_t)(s * 128), da, db, idesc_o, ks ? 1u : 0u);
             }
             umma_commit(&sm.o_ready[s]);
             umma_commit(&sm.kv_free[s]);
@@ -299,15 +277,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
 }
 
 template <int HD>
-int launch_fwd_tc(const bf16* qkv, bf16* vt, bf16* out, float* lse, int B, int T, int H, float scale, int causal, cudaStream_t s)
+int launch_fwd_tc(const bf16* qkv, bf16* out, float* lse, int B, int T, int H, float scale, int causal, cudaStream_t s)
 {
     const int D = H * HD;
-    dim3 tg((T + 63) / 64, HD / 64, B * H);
-    head_transpose_kernel<<<tg, 256, 0, s>>>(qkv, vt, T, H, HD, 3LL * D, 2 * D);
-    LTL_TRY(ltl_check_launch("attn head transpose"));
-    CUtensorMap mq, mv;
+    CUtensorMap mq;
     LTL_TRY(ltl_tensor_map_bf16(qkv, B * T, 3 * D, 3LL * D, 128, &mq));
-    LTL_TRY(ltl_tensor_map_bf16(vt, B * H * HD, T, T, HD, &mv));
     const size_t smem = sizeof(FwdSmem<HD>) + 1024;
     static bool attr = false;
     if (!attr) {
@@ -315,10 +289,9 @@ int launch_fwd_tc(const bf16* qkv, bf16* vt, bf16* out, float* lse, int B, int T
         attr = true;
     }
     dim3 grid((T + QT - 1) / QT, H, B);
-    attn_fwd_tc_kernel<HD><<<grid, FWD_THREADS, smem, s>>>(mq, mv, out, lse, T, H, scale, causal, ltl_tc_err_flag());
+    attn_fwd_tc_kernel<HD><<<grid, FWD_THREADS, smem, s>>>(mq, out, lse, T, H, scale, causal, ltl_tc_err_flag());
     return ltl_check_launch("attn_fwd_tc");
 }
-
 
 // ---------------------------------------------------------------------------------------------------
 // Backward, part 1: dQ.  One CTA per (128 query rows, head, sequence) walking key tiles of 64.
@@ -336,7 +309,6 @@ struct DqSmem {
     alignas(1024) uint8_t dout[HD / 64][QT * 128];
     alignas(1024) uint8_t k[2][HD / 64][KS * 128];
     alignas(1024) uint8_t v[2][HD / 64][KS * 128];
-    alignas(1024) uint8_t kt[2][HD * 128];
     alignas(1024) uint8_t ds[QT * 128];
     alignas(8) uint64_t q_full, kv_full[2], kv_free[2], sd_ready[2], ds_ready, acc_ready;
     uint32_t tmem_base;
@@ -347,7 +319,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,     // boxes of 128 rows (Q)
                       const __grid_constant__ CUtensorMap map_qkv64,   // boxes of 64 rows (K_j, V_j)
                       const __grid_constant__ CUtensorMap map_do,      // dO, boxes of 128 rows
-                      const __grid_constant__ CUtensorMap map_kt,      // head-major K^T, boxes hd x 64
                       const float* __restrict__ lse, const float* __restrict__ delta, bf16* __restrict__ dqkv,
                       int T, int H, float scale, int causal, int* __restrict__ err)
 {
@@ -386,15 +357,14 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,     // boxes 
             const int s = j & 1;
             if (j >= 2) ok = mbar_wait(&sm.kv_free[s], ((j >> 1) - 1) & 1);
             if (!ok) break;
-            mbar_expect_tx(&sm.kv_full[s], 3 * KS * HD * 2);
+            mbar_expect_tx(&sm.kv_full[s], 2 * KS * HD * 2);
             for (int kb = 0; kb < KB; ++kb) {
                 tma_load_2d(sm.k[s][kb], &map_qkv64, D + h * HD + kb * 64, b * T + j * KS, &sm.kv_full[s]);
                 tma_load_2d(sm.v[s][kb], &map_qkv64, 2 * D + h * HD + kb * 64, b * T + j * KS, &sm.kv_full[s]);
             }
-            tma_load_2d(sm.kt[s], &map_kt, j * KS, (b * H + h) * HD, &sm.kv_full[s]);
         }
     } else if (warp == 1 && lane == 0) {
-        constexpr uint32_t idesc_s = umma_idesc_bf16(QT, KS), idesc_o = umma_idesc_bf16(QT, HD);
+        constexpr uint32_t idesc_s = umma_idesc_bf16(QT, KS), idesc_o = umma_idesc_bf16_bmn(QT, HD);
         auto issue_sd = [&](int j) {
             const int s = j & 1;
 #pragma unroll
@@ -429,10 +399,12 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,     // boxes 
             ok = mbar_wait(&sm.ds_ready, j & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t da = umma_desc_sw128(smem_u32(sm.ds)), db = umma_desc_sw128(smem_u32(sm.kt[s]));
+            // dQ += dS K_j: K_j as it lies, [64 keys x hd] = an MN-major B operand (hd column blocks KS * 128 bytes apart)
+            const uint64_t da = umma_desc_sw128(smem_u32(sm.ds));
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-                umma_bf16(tmem + COL_DQ, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (j | k) ? 1u : 0u);
+                umma_bf16(tmem + COL_DQ, da + (uint64_t)(k * 2), umma_desc_sw128_mn(smem_u32(sm.k[s][0]) + k * 2048, KS * 128, 1024),
+                          idesc_o, (j | k) ? 1u : 0u);
             umma_commit(&sm.kv_free[s]);                 // also: dS of tile j has been consumed
         }
         if (ok) umma_commit(&sm.acc_ready);
@@ -524,10 +496,8 @@ template <int HD>
 struct DkvSmem {
     alignas(1024) uint8_t k[HD / 64][KT * 128];
     alignas(1024) uint8_t v[HD / 64][KT * 128];
-    alignas(1024) uint8_t q[2][HD / 64][QS * 128];      // Q_i   [64 queries x hd]   (B of S^T)
-    alignas(1024) uint8_t dout[2][HD / 64][QS * 128];   // dO_i  [64 queries x hd]   (B of dP^T)
-    alignas(1024) uint8_t qt[2][HD * 128];              // Q_i^T [hd x 64 queries]   (B of dK)
-    alignas(1024) uint8_t dot[2][HD * 128];             // dO_i^T[hd x 64 queries]   (B of dV)
+    alignas(1024) uint8_t q[2][HD / 64][QS * 128];      // Q_i  [64 queries x hd]: K-major B of S^T, MN-major B of dK
+    alignas(1024) uint8_t dout[2][HD / 64][QS * 128];   // dO_i [64 queries x hd]: K-major B of dP^T, MN-major B of dV
     alignas(1024) uint8_t pt[KT * 128];                 // P^T   [128 keys x 64 queries]
     alignas(1024) uint8_t dst[KT * 128];                // dS^T  [128 keys x 64 queries]
     float lse2[2][QS], dls[2][QS];                      // per step: lse * log2(e), delta * scale
@@ -540,8 +510,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes of 128 rows (K, V tiles)
                        const __grid_constant__ CUtensorMap map_qkv64,  // boxes of 64 rows (Q_i)
                        const __grid_constant__ CUtensorMap map_do64,   // dO [R, D], boxes of 64 rows
-                       const __grid_constant__ CUtensorMap map_qt,     // head-major Q^T, boxes hd x 64
-                       const __grid_constant__ CUtensorMap map_dot,    // head-major dO^T, boxes hd x 64
                        const float* __restrict__ lse, const float* __restrict__ delta, bf16* __restrict__ dqkv,
                        int T, int H, float scale, int causal, int* __restrict__ err)
 {
@@ -591,13 +559,11 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
             ok = __shfl_sync(0xFFFFFFFFu, (int)ok, 0) != 0;
             if (!ok) break;
             if (lane == 0) {
-                mbar_expect_tx(&sm.q_full[s], 4 * QS * HD * 2);
+                mbar_expect_tx(&sm.q_full[s], 2 * QS * HD * 2);
                 for (int kb = 0; kb < KB; ++kb) {
                     tma_load_2d(sm.q[s][kb], &map_qkv64, h * HD + kb * 64, b * T + qrow, &sm.q_full[s]);
                     tma_load_2d(sm.dout[s][kb], &map_do64, h * HD + kb * 64, b * T + qrow, &sm.q_full[s]);
                 }
-                tma_load_2d(sm.qt[s], &map_qt, qrow, (b * H + h) * HD, &sm.q_full[s]);
-                tma_load_2d(sm.dot[s], &map_dot, qrow, (b * H + h) * HD, &sm.q_full[s]);
             }
 #pragma unroll
             for (int e = lane; e < QS; e += 32) {
@@ -609,7 +575,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.aux_full[s])) : "memory");
         }
     } else if (warp == 1 && lane == 0) {
-        constexpr uint32_t idesc_s = umma_idesc_bf16(KT, QS), idesc_o = umma_idesc_bf16(KT, HD);
+        constexpr uint32_t idesc_s = umma_idesc_bf16(KT, QS), idesc_o = umma_idesc_bf16_bmn(KT, HD);
         auto issue_sd = [&](int st) {
             const int s = st & 1;
 #pragma unroll
@@ -644,15 +610,16 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
             ok = mbar_wait(&sm.p_ready, st & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            {
-                const uint64_t da = umma_desc_sw128(smem_u32(sm.pt)), db = umma_desc_sw128(smem_u32(sm.dot[s]));
+            {   // dV += P^T dO_i and dK += dS^T Q_i: dO_i and Q_i as they lie, [64 queries x hd] = MN-major B operands
+                const uint64_t dp = umma_desc_sw128(smem_u32(sm.pt)), dd = umma_desc_sw128(smem_u32(sm.dst));
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tmem + COL_DV, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (st | k) ? 1u : 0u);
-            }
-            {
-                const uint64_t da = umma_desc_sw128(smem_u32(sm.dst)), db = umma_desc_sw128(smem_u32(sm.qt[s]));
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem + COL_DV, dp + (uint64_t)(k * 2), umma_desc_sw128_mn(smem_u32(sm.dout[s][0]) + k * 2048, QS * 128, 1024),
+                              idesc_o, (st | k) ? 1u : 0u);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tmem + COL_DK, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (st | k) ? 1u : 0u);
+                for (int k = 0; k < 4; ++k)
+                    umma_bf16(tmem + COL_DK, dd + (uint64_t)(k * 2), umma_desc_sw128_mn(smem_u32(sm.q[s][0]) + k * 2048, QS * 128, 1024),
+                              idesc_o, (st | k) ? 1u : 0u);
             }
             umma_commit(&sm.q_free[s]);                  // the step's operands, and P^T / dS^T, have been consumed
         }
@@ -740,25 +707,15 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
 }
 
 template <int HD>
-int launch_bwd_tc(const bf16* qkv, const bf16* dout, const float* lse, const float* delta, bf16* scratch, bf16* dqkv,
+int launch_bwd_tc(const bf16* qkv, const bf16* dout, const float* lse, const float* delta, bf16* dqkv,
                   int B, int T, int H, float scale, int causal, cudaStream_t s)
 {
     const int D = H * HD;
-    const size_t hm = (size_t)B * H * HD * T;            // elements of one head-major copy
-    bf16 *qt = scratch, *kt = scratch + hm, *dot = scratch + 2 * hm;
-    dim3 tg((T + 63) / 64, HD / 64, B * H);
-    head_transpose_kernel<<<tg, 256, 0, s>>>(qkv, qt, T, H, HD, 3LL * D, 0);
-    head_transpose_kernel<<<tg, 256, 0, s>>>(qkv, kt, T, H, HD, 3LL * D, D);
-    head_transpose_kernel<<<tg, 256, 0, s>>>(dout, dot, T, H, HD, (long long)D, 0);
-    LTL_TRY(ltl_check_launch("attn head transpose"));
-    CUtensorMap mq128, mq64, mdo128, mdo64, mqt, mkt, mdot;
+    CUtensorMap mq128, mq64, mdo128, mdo64;
     LTL_TRY(ltl_tensor_map_bf16(qkv, B * T, 3 * D, 3LL * D, 128, &mq128));
     LTL_TRY(ltl_tensor_map_bf16(qkv, B * T, 3 * D, 3LL * D, 64, &mq64));
     LTL_TRY(ltl_tensor_map_bf16(dout, B * T, D, D, 128, &mdo128));
     LTL_TRY(ltl_tensor_map_bf16(dout, B * T, D, D, 64, &mdo64));
-    LTL_TRY(ltl_tensor_map_bf16(qt, B * H * HD, T, T, HD, &mqt));
-    LTL_TRY(ltl_tensor_map_bf16(kt, B * H * HD, T, T, HD, &mkt));
-    LTL_TRY(ltl_tensor_map_bf16(dot, B * H * HD, T, T, HD, &mdot));
     static bool attr = false;
     const size_t smem_q = sizeof(DqSmem<HD>) + 1024, smem_kv = sizeof(DkvSmem<HD>) + 1024;
     if (!attr) {
@@ -767,10 +724,9 @@ int launch_bwd_tc(const bf16* qkv, const bf16* dout, const float* lse, const flo
         attr = true;
     }
     dim3 gq((T + QT - 1) / QT, H, B), gk((T + KT - 1) / KT, H, B);
-    attn_bwd_dq_tc_kernel<HD><<<gq, BWD_THREADS, smem_q, s>>>(mq128, mq64, mdo128, mkt, lse, delta, dqkv, T, H, scale, causal, ltl_tc_err_flag());
+    attn_bwd_dq_tc_kernel<HD><<<gq, BWD_THREADS, smem_q, s>>>(mq128, mq64, mdo128, lse, delta, dqkv, T, H, scale, causal, ltl_tc_err_flag());
     LTL_TRY(ltl_check_launch("attn_bwd_dq_tc"));
-    attn_bwd_dkv_tc_kernel<HD><<<gk, BWD_THREADS, smem_kv, s>>>(mq128, mq64, mdo64, mqt, mdot, lse, delta, dqkv, T, H, scale, causal,
-                                                        ltl_tc_err_flag());
+    attn_bwd_dkv_tc_kernel<HD><<<gk, BWD_THREADS, smem_kv, s>>>(mq128, mq64, mdo64, lse, delta, dqkv, T, H, scale, causal, ltl_tc_err_flag());
     return ltl_check_launch("attn_bwd_dkv_tc");
 }
 
@@ -781,25 +737,23 @@ bool ltl_attn_tc_supported(int T, int H, int hd, int dtype)
     return dtype == LTL_BF16 && (hd == 64 || hd == 128) && T % 8 == 0 && T >= 64;
 }
 
-// vt: scratch of B*H*hd*T bf16 elements (the head-major copy of V).
-int ltl_attn_fwd_tc(const void* qkv, void* vt, void* out, float* lse, int B, int T, int H, int hd, float scale, int causal,
-                    cudaStream_t s)
+int ltl_attn_fwd_tc(const void* qkv, void* out, float* lse, int B, int T, int H, int hd, float scale, int causal, cudaStream_t s)
 {
-    if (!qkv || !vt || !out) return ltl_fail(LTL_ERR_NULL, "attn_fwd_tc: null pointer");
+    if (!qkv || !out) return ltl_fail(LTL_ERR_NULL, "attn_fwd_tc: null pointer");
     if (!ltl_attn_tc_supported(T, H, hd, LTL_BF16)) return ltl_fail(LTL_ERR_UNSUPPORTED, "attn_fwd_tc: head_dim %d, T %d", hd, T);
-    if (B <= 0 || H <= 0 || B > 65535 || (long long)B * H > 65535) return ltl_fail(LTL_ERR_SHAPE, "attn_fwd_tc: grid too large");
-    if (hd == 64) return launch_fwd_tc<64>((const bf16*)qkv, (bf16*)vt, (bf16*)out, lse, B, T, H, scale, causal, s);
-    return launch_fwd_tc<128>((const bf16*)qkv, (bf16*)vt, (bf16*)out, lse, B, T, H, scale, causal, s);
+    if (B <= 0 || H <= 0 || B > 65535 || H > 65535) return ltl_fail(LTL_ERR_SHAPE, "attn_fwd_tc: grid too large");
+    if (hd == 64) return launch_fwd_tc<64>((const bf16*)qkv, (bf16*)out, lse, B, T, H, scale, causal, s);
+    return launch_fwd_tc<128>((const bf16*)qkv, (bf16*)out, lse, B, T, H, scale, causal, s);
 }
 
-// scratch: 3 * B*H*hd*T bf16 elements (head-major copies of Q, K and dO).  delta [B*H*T] is written here too.
-int ltl_attn_bwd_tc(const void* qkv, const void* out, const void* dout, const float* lse, float* delta, void* scratch,
-                    void* dqkv, int B, int T, int H, int hd, float scale, int causal, cudaStream_t s)
+// delta [B*H*T] (fp32 scratch) is written here.
+int ltl_attn_bwd_tc(const void* qkv, const void* out, const void* dout, const float* lse, float* delta, void* dqkv,
+                    int B, int T, int H, int hd, float scale, int causal, cudaStream_t s)
 {
-    if (!qkv || !out || !dout || !lse || !delta || !scratch || !dqkv) return ltl_fail(LTL_ERR_NULL, "attn_bwd_tc: null pointer");
+    if (!qkv || !out || !dout || !lse || !delta || !dqkv) return ltl_fail(LTL_ERR_NULL, "attn_bwd_tc: null pointer");
     if (!ltl_attn_tc_supported(T, H, hd, LTL_BF16)) return ltl_fail(LTL_ERR_UNSUPPORTED, "attn_bwd_tc: head_dim %d, T %d", hd, T);
-    if (B <= 0 || H <= 0 || B > 65535 || (long long)B * H > 65535) return ltl_fail(LTL_ERR_SHAPE, "attn_bwd_tc: grid too large");
+    if (B <= 0 || H <= 0 || B > 65535 || H > 65535) return ltl_fail(LTL_ERR_SHAPE, "attn_bwd_tc: grid too large");
     LTL_TRY(ltl_attn_delta(out, dout, delta, B, T, H, hd, LTL_BF16, s));
-    if (hd == 64) return launch_bwd_tc<64>((const bf16*)qkv, (const bf16*)dout, lse, delta, (bf16*)scratch, (bf16*)dqkv, B, T, H, scale, causal, s);
-    return launch_bwd_tc<128>((const bf16*)qkv, (const bf16*)dout, lse, delta, (bf16*)scratch, (bf16*)dqkv, B, T, H, scale, causal, s);
+    if (hd == 64) return launch_bwd_tc<64>((const bf16*)qkv, (const bf16*)dout, lse, delta, (bf16*)dqkv, B, T, H, scale, causal, s);
+    return launch_bwd_tc<128>((const bf16*)qkv, (const bf16*)dout, lse, delta, (bf16*)dqkv, B, T, H, scale, causal, s);
 }

@@ -65,8 +65,6 @@ struct luaTL_lm_s {
     int mirror_dirty = 1;
     int train_tc = 0;            // bf16 model that has been asked to train: mixed-precision step
     int attn_tc = 1;             // tensor-core attention where the shape allows (LUATL_ATTN_TC=0 turns it off)
-    bf16* att_scratch = nullptr; // head-major copies for the tensor-core attention (V; Q, K, dO in the backward)
-    size_t att_scratch_elems = 0;
     // mixed-precision backward scratch (bf16): activation gradients
     bf16 *b_dres = nullptr, *b_dhs = nullptr, *b_dh13 = nullptr, *b_dattn = nullptr, *b_dqkv = nullptr, *b_dl = nullptr;
     cudaStream_t s = nullptr;
@@ -190,14 +188,6 @@ int ensure_ws(LM* m, size_t floats)
     return LTL_OK;
 }
 
-int ensure_att_scratch(LM* m, size_t elems)
-{
-    if (m->att_scratch_elems >= elems) return LTL_OK;
-    if (m->att_scratch) { LTL_CUDA("sync", cudaStreamSynchronize(m->s)); cudaFree(m->att_scratch); m->att_scratch = nullptr; }
-    DALLOC(m->att_scratch, elems * 2, "attention scratch");
-    m->att_scratch_elems = elems;
-    return LTL_OK;
-}
 bool use_attn_tc(const LM* m, int T)
 {
     return m->attn_tc && m->use_tc && m->adt == LTL_BF16 && m->c.causal && ltl_attn_tc_supported(T, m->H, m->hd, LTL_BF16);
@@ -309,8 +299,7 @@ int forward(LM* m, Act& a, const int32_t* d_ids, int nseq, int T, int mode)
             LTL_TRY(ltl_rope(qkv, a.posids, rows, 2 * H, hd, 3 * D, 0, m->c.rope_base, m->c.rope_interleaved, 0,
                              adt, m->rope_tab, m->T, m->s));
         if (use_attn_tc(m, T)) {
-            LTL_TRY(ensure_att_scratch(m, (size_t)rows * D));
-            LTL_TRY(ltl_attn_fwd_tc(qkv, m->att_scratch, attn, lse, nseq, T, H, hd, m->scale, 1, m->s));
+            LTL_TRY(ltl_attn_fwd_tc(qkv, attn, lse, nseq, T, H, hd, m->scale, 1, m->s));
             m->launches++;
         } else {
             LTL_TRY(ltl_attn_fwd(qkv, attn, lse, nseq, T, H, hd, m->scale, m->c.causal, adt, m->s));
@@ -451,15 +440,15 @@ int dx_gemm(LM* m, const bf16* dY, int n_out, const bf16* Wt, int n_in, void* dX
     return ltl_gemm_tc(dY, Wt, dX, nullptr, R, n_in, n_out, dx_dt, 0, 0, 1, m->s);
 }
 
-int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T)
+int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T, bool dl_in_bf16)
 {
     const int D = m->D, F = m->F, V = m->V, L = m->L, H = m->H, hd = m->hd;
     const int rows = nseq * T;
     const size_t RD = (size_t)a.rows_cap * D;
     float* W = m->W; float* G = m->G;
     LTL_TRY(ensure_ws(m, ltl_rmsnorm_bwd_scratch_floats(D)));
-    // head: dlogits (fp32, in a.logits) -> bf16
-    LTL_TRY(ltl_cast(a.logits, LTL_F32, m->b_dl, LTL_BF16, (uint64_t)rows * V, m->s));
+    // head: dlogits (fp32, in a.logits) -> bf16, unless the loss kernel already wrote it there
+    if (!dl_in_bf16) LTL_TRY(ltl_cast(a.logits, LTL_F32, m->b_dl, LTL_BF16, (uint64_t)rows * V, m->s));
     if (m->c.tie) {
         LTL_TRY(dw_gemm(m, m->b_dl, V, a.hf, D, G + m->off_emb, rows));         // dEmb += dl^T hf
         LTL_TRY(dx_gemm(m, m->b_dl, V, m->Wm + m->off_emb, D, m->dhf, LTL_F32, rows));              // dhf = dl emb
@@ -482,22 +471,27 @@ int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T)
         const bf16* hs = (const bf16*)a.hs + (size_t)l * a.rows_cap * F;
         const float* lse = a.lse + (size_t)l * a.rows_cap * H;
 
-        // feed-forward
-        LTL_TRY(ltl_cast(m->dres, LTL_F32, m->b_dres, LTL_BF16, (uint64_t)rows * D, m->s));
+        // feed-forward (the bf16 copy of dres is left by the previous layer's last kernel)
+        if (l == L - 1) LTL_TRY(ltl_cast(m->dres, LTL_F32, m->b_dres, LTL_BF16, (uint64_t)rows * D, m->s));
         LTL_TRY(dx_gemm(m, m->b_dres, D, m->Wm + o.w2, F, m->b_dhs, LTL_BF16, rows));               // dhs = dres W2^T
         LTL_TRY(dw_gemm(m, hs, F, m->b_dres, D, G + o.w2, rows));               // dW2 += hs^T dres
         LTL_TRY(ltl_swiglu_bwd(h13, h13 + F, m->b_dhs, m->b_dh13, m->b_dh13 + F, rows, F, 2 * F, 2 * F, F, LTL_BF16, m->s));
         LTL_TRY(dw_gemm(m, h2, D, m->b_dh13, 2 * F, G + o.w13, rows));          // dW13 += h2^T dh13
         LTL_TRY(dx_gemm(m, m->b_dh13, 2 * F, m->Wm + o.w13, D, m->dh2, LTL_F32, rows));             // dh2 = dh13 W13^T
-        LTL_TRY(ltl_rmsnorm_bwd(mid, W + o.ln2, m->dh2, m->dbr, G + o.ln2, rows, D, m->c.eps, LTL_F32, m->ws, m->s));
-        LTL_TRY(ltl_elementwise(m->dres, m->dbr, m->dres, (uint64_t)rows * D, LTL_F32, 6, 1.0f, 0.0f, m->s));
+        // dres += rmsnorm_bwd(...) and its bf16 copy for the GEMMs below, in one kernel when the row width allows
+        const bool fused_norm = D % 4 == 0 && D <= 4096;
+        if (fused_norm) {
+            LTL_TRY(ltl_rmsnorm_bwd_residual(mid, W + o.ln2, m->dh2, m->dres, m->b_dres, G + o.ln2, rows, D, m->c.eps, m->ws, m->s));
+        } else {
+            LTL_TRY(ltl_rmsnorm_bwd(mid, W + o.ln2, m->dh2, m->dbr, G + o.ln2, rows, D, m->c.eps, LTL_F32, m->ws, m->s));
+            LTL_TRY(ltl_elementwise(m->dres, m->dbr, m->dres, (uint64_t)rows * D, LTL_F32, 6, 1.0f, 0.0f, m->s));
+            LTL_TRY(ltl_cast(m->dres, LTL_F32, m->b_dres, LTL_BF16, (uint64_t)rows * D, m->s));
+        }
         // attention
-        LTL_TRY(ltl_cast(m->dres, LTL_F32, m->b_dres, LTL_BF16, (uint64_t)rows * D, m->s));
         LTL_TRY(dx_gemm(m, m->b_dres, D, m->Wm + o.wo, D, m->b_dattn, LTL_BF16, rows));             // dattn = dres Wo^T
         LTL_TRY(dw_gemm(m, attn, D, m->b_dres, D, G + o.wo, rows));             // dWo += attn^T dres
         if (use_attn_tc(m, T)) {
-            LTL_TRY(ensure_att_scratch(m, (size_t)3 * rows * D));
-            LTL_TRY(ltl_attn_bwd_tc(qkv, attn, m->b_dattn, lse, m->delta, m->att_scratch, m->b_dqkv, nseq, T, H, hd, m->scale, 1, m->s));
+            LTL_TRY(ltl_attn_bwd_tc(qkv, attn, m->b_dattn, lse, m->delta, m->b_dqkv, nseq, T, H, hd, m->scale, 1, m->s));
             m->launches += 3;
         } else {
             LTL_TRY(ltl_attn_bwd(qkv, attn, m->b_dattn, lse, m->delta, m->b_dqkv, nseq, T, H, hd, m->scale, m->c.causal,
@@ -508,8 +502,14 @@ int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T)
                              LTL_BF16, m->rope_tab, m->T, m->s));
         LTL_TRY(dw_gemm(m, h1, D, m->b_dqkv, 3 * D, G + o.wqkv, rows));         // dWqkv += h1^T dqkv
         LTL_TRY(dx_gemm(m, m->b_dqkv, 3 * D, m->Wm + o.wqkv, D, m->dh1, LTL_F32, rows));            // dh1 = dqkv Wqkv^T
-        LTL_TRY(ltl_rmsnorm_bwd(xin, W + o.ln1, m->dh1, m->dbr, G + o.ln1, rows, D, m->c.eps, LTL_F32, m->ws, m->s));
-        LTL_TRY(ltl_elementwise(m->dres, m->dbr, m->dres, (uint64_t)rows * D, LTL_F32, 6, 1.0f, 0.0f, m->s));
+        if (fused_norm) {
+            LTL_TRY(ltl_rmsnorm_bwd_residual(xin, W + o.ln1, m->dh1, m->dres, l > 0 ? m->b_dres : nullptr, G + o.ln1, rows, D,
+                                             m->c.eps, m->ws, m->s));
+        } else {
+            LTL_TRY(ltl_rmsnorm_bwd(xin, W + o.ln1, m->dh1, m->dbr, G + o.ln1, rows, D, m->c.eps, LTL_F32, m->ws, m->s));
+            LTL_TRY(ltl_elementwise(m->dres, m->dbr, m->dres, (uint64_t)rows * D, LTL_F32, 6, 1.0f, 0.0f, m->s));
+            if (l > 0) LTL_TRY(ltl_cast(m->dres, LTL_F32, m->b_dres, LTL_BF16, (uint64_t)rows * D, m->s));
+        }
         m->launches += 10;
     }
     LTL_TRY(ltl_embed_bwd(d_ids, m->dres, G + m->off_emb, rows, D, V, 1.0f, LTL_F32, m->s));
@@ -545,14 +545,21 @@ int loss_and_grad(LM* m, const int32_t* d_ids, const int32_t* d_tgt, int valid_g
     const float gs = 1.0f / (float)(valid_global < 1 ? 1 : valid_global);
     if (!accumulate) LTL_CUDA("zero gradients", cudaMemsetAsync(m->G, 0, (size_t)(m->np + 4) * 4, m->s));
     LTL_TRY(forward(m, a, d_ids, m->B, m->T, MODE_TRAIN));
-    LTL_TRY(ltl_cross_entropy(a.logits, d_tgt, m->losses, want_grad ? a.logits : nullptr, m->d_pred, rows, m->V,
-                              -1, gs, LTL_F32, m->s));
+    // Mixed precision: the gradient of the logits is only ever read as a bf16 GEMM operand, so CE writes it as such.
+    const bool dl_bf16 = want_grad && m->adt == LTL_BF16 && ltl_cross_entropy_bf16_grad_supported(a.logits, m->V);
+    if (dl_bf16) {
+        LTL_TRY(alloc_backward_tc(m));
+        LTL_TRY(ltl_cross_entropy_bf16_grad(a.logits, d_tgt, m->losses, m->b_dl, m->d_pred, rows, m->V, -1, gs, m->s));
+    } else {
+        LTL_TRY(ltl_cross_entropy(a.logits, d_tgt, m->losses, want_grad ? a.logits : nullptr, m->d_pred, rows, m->V,
+                                  -1, gs, LTL_F32, m->s));
+    }
     LTL_TRY(ltl_sum_f32(m->losses, rows, m->G + m->np, gs, m->s));
     LTL_TRY(ltl_count_correct(m->d_pred, d_tgt, rows, m->G + m->np + 1, m->s));
     m->launches += 4;
     if (want_grad && m->adt == LTL_BF16) {
         LTL_TRY(alloc_backward_tc(m));
-        LTL_TRY(backward_tc(m, a, d_ids, m->B, m->T));
+        LTL_TRY(backward_tc(m, a, d_ids, m->B, m->T, dl_bf16));
     } else if (want_grad) {
         LTL_TRY(alloc_backward(m));
         LTL_TRY(backward(m, a, d_ids, m->B, m->T));
@@ -964,7 +971,7 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
     void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
                      m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
                      m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part,
-                     m->Wm, m->att_scratch, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
+                     m->Wm, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
     for (void* p : ptrs) if (p) cudaFree(p);
     for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
     cudaGetLastError();

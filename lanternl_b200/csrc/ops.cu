@@ -283,6 +283,107 @@ int ltl_rmsnorm_bwd(const void* x, const void* gamma, const void* dy, void* dx, 
     return ltl_check_launch("rmsnorm_bwd");
 }
 
+// RMSNorm backward for wide fp32 rows fused with what follows it in the mixed-precision backward: the input
+// gradient is ADDED to the residual-stream gradient (res += dx, in place) and the updated row is also written as
+// bf16 (the next GEMMs' operand).  A persistent grid of 256-thread CTAs walks the rows; a thread owns CHT 16-byte
+// chunks of every row (x, dy, gamma and its share of dgamma stay in registers: 32 floats at 2048 columns against
+// 256 in the warp-per-row kernel), the two row sums cross the CTA through shared memory, and every CTA leaves one
+// partial dgamma row in scratch for colsum_partials_kernel.
+template <int CHT>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_res_kernel(const float* __restrict__ x, const float* __restrict__ g, const float* __restrict__ dy,
+                       float* __restrict__ res, bf16* __restrict__ res_bf16, float* __restrict__ partial,
+                       int rows, int cols, float eps)
+{
+    __shared__ float red[2][8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float4 gam[CHT], dg[CHT];
+#pragma unroll
+    for (int c = 0; c < CHT; ++c) {
+        const int e = (c * 256 + tid) * 4;
+        gam[c] = (g && e < cols) ? *reinterpret_cast<const float4*>(g + e) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        dg[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const size_t base = (size_t)row * cols;
+        float4 xv[CHT], dv[CHT], rv[CHT];
+        float ss = 0.0f, dot = 0.0f;
+#pragma unroll
+        for (int c = 0; c < CHT; ++c) {
+            const int e = (c * 256 + tid) * 4;
+            xv[c] = dv[c] = rv[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (e < cols) {
+                xv[c] = *reinterpret_cast<const float4*>(x + base + e);
+                dv[c] = *reinterpret_cast<const float4*>(dy + base + e);
+                rv[c] = *reinterpret_cast<const float4*>(res + base + e);
+            }
+            ss += xv[c].x * xv[c].x + xv[c].y * xv[c].y + xv[c].z * xv[c].z + xv[c].w * xv[c].w;
+            dot += dv[c].x * gam[c].x * xv[c].x + dv[c].y * gam[c].y * xv[c].y + dv[c].z * gam[c].z * xv[c].z + dv[c].w * gam[c].w * xv[c].w;
+        }
+        ss = warp_sum(ss);
+        dot = warp_sum(dot);
+        __syncthreads();                                  // the previous row's sums have been read
+        if (lane == 0) { red[0][warp] = ss; red[1][warp] = dot; }
+        __syncthreads();
+        ss = 0.0f; dot = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) { ss += red[0][w]; dot += red[1][w]; }
+        const float sc = 1.0f / sqrtf(ss / (float)cols + eps);
+        const float coef = sc * sc * sc / (float)cols * dot;
+#pragma unroll
+        for (int c = 0; c < CHT; ++c) {
+            const int e = (c * 256 + tid) * 4;
+            if (e < cols) {
+                float4 o;
+                o.x = rv[c].x + (sc * gam[c].x * dv[c].x - coef * xv[c].x);
+                o.y = rv[c].y + (sc * gam[c].y * dv[c].y - coef * xv[c].y);
+                o.z = rv[c].z + (sc * gam[c].z * dv[c].z - coef * xv[c].z);
+                o.w = rv[c].w + (sc * gam[c].w * dv[c].w - coef * xv[c].w);
+                dg[c].x = fmaf(dv[c].x * xv[c].x, sc, dg[c].x); dg[c].y = fmaf(dv[c].y * xv[c].y, sc, dg[c].y);
+                dg[c].z = fmaf(dv[c].z * xv[c].z, sc, dg[c].z); dg[c].w = fmaf(dv[c].w * xv[c].w, sc, dg[c].w);
+                *reinterpret_cast<float4*>(res + base + e) = o;
+                if (res_bf16) {
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                    pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(res_bf16 + base + e) = pk;
+                }
+            }
+        }
+    }
+    if (partial) {
+        float* pr = partial + (size_t)blockIdx.x * cols;
+#pragma unroll
+        for (int c = 0; c < CHT; ++c) {
+            const int e = (c * 256 + tid) * 4;
+            if (e < cols) *reinterpret_cast<float4*>(pr + e) = dg[c];
+        }
+    }
+}
+
+// res += rmsnorm_bwd(x, gamma, dy); res_bf16 = bf16(res) (optional); dgamma += ... (optional, needs scratch of
+// ltl_rmsnorm_bwd_scratch_floats(cols)).  fp32, cols a multiple of 4 and at most 4096.
+int ltl_rmsnorm_bwd_residual(const float* x, const float* gamma, const float* dy, float* res, bf16* res_bf16, float* dgamma,
+                             int rows, int cols, float eps, float* scratch, cudaStream_t s)
+{
+    if (!x || !dy || !res) return ltl_fail(LTL_ERR_NULL, "rmsnorm_bwd_residual: null pointer");
+    if (rows < 0 || cols <= 0 || cols % 4 || cols > 4096) return ltl_fail(LTL_ERR_SHAPE, "rmsnorm_bwd_residual: bad shape %dx%d", rows, cols);
+    if (!aligned16(x) || !aligned16(dy) || !aligned16(res) || (gamma && !aligned16(gamma)) || (res_bf16 && !aligned16(res_bf16)) ||
+        (dgamma && (!scratch || !aligned16(scratch))))
+        return ltl_fail(LTL_ERR_ARG, "rmsnorm_bwd_residual: operands must be 16-byte aligned (and scratch given with dgamma)");
+    if (rows == 0) return LTL_OK;
+    int grid = 2 * ltl_sm_count();
+    if (grid > rows) grid = rows;
+    float* partial = dgamma ? scratch : nullptr;
+    const int cht = (cols + 1023) / 1024;
+    if (cht <= 1) rmsnorm_bwd_res_kernel<1><<<grid, 256, 0, s>>>(x, gamma, dy, res, res_bf16, partial, rows, cols, eps);
+    else if (cht == 2) rmsnorm_bwd_res_kernel<2><<<grid, 256, 0, s>>>(x, gamma, dy, res, res_bf16, partial, rows, cols, eps);
+    else rmsnorm_bwd_res_kernel<4><<<grid, 256, 0, s>>>(x, gamma, dy, res, res_bf16, partial, rows, cols, eps);
+    if (dgamma) colsum_partials_kernel<<<(cols + 31) / 32, 256, 0, s>>>(scratch, grid, cols, dgamma);
+    return ltl_check_launch("rmsnorm_bwd_residual");
+}
+
 // ------------------------------------------------------------------------------------------
 // Masked softmax forward / backward (reference: cuda/luaTL_train.cu:545,589).
 //   v = x*scale + bias ; columns > (row % group) + mask_offset are masked when causal.
@@ -880,7 +981,8 @@ __global__ void ce_kernel(const T* __restrict__ logits, const int32_t* __restric
 template <int NV>
 __global__ void __launch_bounds__(1024)
 ce_reg_kernel(const float* __restrict__ logits, const int32_t* __restrict__ targets, float* __restrict__ losses,
-              float* __restrict__ dlogits, int32_t* __restrict__ pred, int rows, int V, int ignore_index, float gscale)
+              float* __restrict__ dlogits, bf16* __restrict__ dlogits_bf16, int32_t* __restrict__ pred, int rows, int V,
+              int ignore_index, float gscale)
 {
     __shared__ float red[33];
     __shared__ float red_v[32];
@@ -888,11 +990,13 @@ ce_reg_kernel(const float* __restrict__ logits, const int32_t* __restrict__ targ
     const int r = blockIdx.x;
     const float* lr = logits + (size_t)r * V;
     float* dr = dlogits ? dlogits + (size_t)r * V : nullptr;
+    bf16* db = dlogits_bf16 ? dlogits_bf16 + (size_t)r * V : nullptr;
     const int t = targets[r];
     const bool ignored = t < 0 || t >= V || t == ignore_index;
     if (ignored && !pred) {
         if (threadIdx.x == 0 && losses) losses[r] = 0.0f;
         if (dr) for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) *reinterpret_cast<float4*>(dr + i) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (db) for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) *reinterpret_cast<uint2*>(db + i) = make_uint2(0u, 0u);
         return;
     }
     float4 v[NV];
@@ -912,6 +1016,7 @@ ce_reg_kernel(const float* __restrict__ logits, const int32_t* __restrict__ targ
     if (ignored) {
         if (threadIdx.x == 0 && losses) losses[r] = 0.0f;
         if (dr) for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) *reinterpret_cast<float4*>(dr + i) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (db) for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) *reinterpret_cast<uint2*>(db + i) = make_uint2(0u, 0u);
         return;
     }
     const float mx = best;
@@ -925,7 +1030,7 @@ ce_reg_kernel(const float* __restrict__ logits, const int32_t* __restrict__ targ
     sum = block_sum(sum, red);
     const float ssum = fmaxf(sum, 1e-30f);
     if (threadIdx.x == 0 && losses) losses[r] = logf(ssum) + mx - xt;
-    if (dr) {
+    if (dr || db) {
         const float k = gscale / ssum;
 #pragma unroll
         for (int c = 0; c < NV; ++c) {
@@ -933,10 +1038,36 @@ ce_reg_kernel(const float* __restrict__ logits, const int32_t* __restrict__ targ
             if (i < V) {
                 float4 p = make_float4(v[c].x * k, v[c].y * k, v[c].z * k, v[c].w * k);
                 if (t == i) p.x -= gscale; else if (t == i + 1) p.y -= gscale; else if (t == i + 2) p.z -= gscale; else if (t == i + 3) p.w -= gscale;
-                *reinterpret_cast<float4*>(dr + i) = p;
+                if (dr) *reinterpret_cast<float4*>(dr + i) = p;
+                if (db) {
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(p.x, p.y), hi = __floats2bfloat162_rn(p.z, p.w);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                    pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(db + i) = pk;
+                }
             }
         }
     }
+}
+
+bool ltl_cross_entropy_bf16_grad_supported(const void* logits, int vocab)
+{
+    return vocab % 4 == 0 && vocab >= 4096 && vocab <= 32768 && aligned16(logits);
+}
+// fp32 logits in, loss / argmax out, the gradient written as bf16 only (the operand of the backward's GEMMs).
+int ltl_cross_entropy_bf16_grad(const float* logits, const int32_t* targets, float* losses, bf16* dlogits_bf16, int32_t* pred,
+                                int rows, int vocab, int ignore_index, float grad_scale, cudaStream_t s)
+{
+    if (!logits || !targets || !dlogits_bf16) return ltl_fail(LTL_ERR_NULL, "cross_entropy: null pointer");
+    if (!ltl_cross_entropy_bf16_grad_supported(logits, vocab) || (reinterpret_cast<uintptr_t>(dlogits_bf16) & 7))
+        return ltl_fail(LTL_ERR_UNSUPPORTED, "cross_entropy: bf16 gradient output needs a vocabulary of 4096 .. 32768, a multiple of 4");
+    if (rows <= 0) return LTL_OK;
+    const int nv = (vocab + 4095) / 4096;
+#define CE_REG(NVV) ce_reg_kernel<NVV><<<rows, 1024, 0, s>>>(logits, targets, losses, nullptr, dlogits_bf16, pred, rows, vocab, ignore_index, grad_scale)
+    if (nv <= 2) CE_REG(2); else if (nv <= 4) CE_REG(4); else CE_REG(8);
+#undef CE_REG
+    return ltl_check_launch("cross_entropy");
 }
 
 int ltl_cross_entropy(const void* logits, const int32_t* targets, float* losses, void* dlogits,
@@ -948,7 +1079,7 @@ int ltl_cross_entropy(const void* logits, const int32_t* targets, float* losses,
     if (rows == 0) return LTL_OK;
     if (dtype == LTL_F32 && vocab % 4 == 0 && vocab >= 4096 && vocab <= 32768 && aligned16(logits) && (!dlogits || aligned16(dlogits))) {
         const int nv = (vocab + 4095) / 4096;
-#define CE_REG(NVV) ce_reg_kernel<NVV><<<rows, 1024, 0, s>>>((const float*)logits, targets, losses, (float*)dlogits, pred, rows, vocab, ignore_index, grad_scale)
+#define CE_REG(NVV) ce_reg_kernel<NVV><<<rows, 1024, 0, s>>>((const float*)logits, targets, losses, (float*)dlogits, nullptr, pred, rows, vocab, ignore_index, grad_scale)
         if (nv <= 2) CE_REG(2); else if (nv <= 4) CE_REG(4); else CE_REG(8);
 #undef CE_REG
         return ltl_check_launch("cross_entropy");

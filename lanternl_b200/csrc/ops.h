@@ -8,6 +8,8 @@ int ltl_rmsnorm(const void* x, const void* w, void* out, int rows, int cols, flo
                 int dtype, cudaStream_t s);
 // `scratch` holds rmsnorm_bwd_scratch_floats(cols) floats (per-CTA dgamma partials).
 size_t ltl_rmsnorm_bwd_scratch_floats(int cols);
+int ltl_rmsnorm_bwd_residual(const float* x, const float* gamma, const float* dy, float* res, bf16* res_bf16, float* dgamma,
+                             int rows, int cols, float eps, float* scratch, cudaStream_t s);
 int ltl_rmsnorm_bwd(const void* x, const void* gamma, const void* dy, void* dx, float* dgamma,
                     int rows, int cols, float eps, int dtype, float* scratch, cudaStream_t s);
 int ltl_softmax(const void* x, const void* bias, void* out, int rows, int cols, float scale,
@@ -28,6 +30,9 @@ int ltl_embed_fwd(const int32_t* ids, const void* table, void* out, int rows, in
 int ltl_embed_bwd(const int32_t* ids, const void* dout, float* dtable, int rows, int dim,
                   int vocab, float scale, int dtype, cudaStream_t s);
 // pred (optional): row argmax of the logits (ties -> lowest index), written before dlogits.
+bool ltl_cross_entropy_bf16_grad_supported(const void* logits, int vocab);
+int ltl_cross_entropy_bf16_grad(const float* logits, const int32_t* targets, float* losses, bf16* dlogits_bf16, int32_t* pred,
+                                int rows, int vocab, int ignore_index, float grad_scale, cudaStream_t s);
 int ltl_cross_entropy(const void* logits, const int32_t* targets, float* losses, void* dlogits,
                       int32_t* pred, int rows, int vocab, int ignore_index, float grad_scale,
                       int dtype, cudaStream_t s);
@@ -130,9 +135,8 @@ int ltl_gemm_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K,
 int ltl_tensor_map_bf16(const void* base, int rows, int cols, long long pitch, int box_rows, void* out_map);
 // Tensor-core flash attention (attention_tc.cu): bf16, head_dim 64 / 128, T a multiple of 8.
 bool ltl_attn_tc_supported(int T, int H, int hd, int dtype);
-int ltl_attn_fwd_tc(const void* qkv, void* vt_scratch, void* out, float* lse, int B, int T, int H, int hd, float scale,
-                    int causal, cudaStream_t s);
-int ltl_attn_bwd_tc(const void* qkv, const void* out, const void* dout, const float* lse, float* delta, void* scratch,
-                    void* dqkv, int B, int T, int H, int hd, float scale, int causal, cudaStream_t s);
+int ltl_attn_fwd_tc(const void* qkv, void* out, float* lse, int B, int T, int H, int hd, float scale, int causal, cudaStream_t s);
+int ltl_attn_bwd_tc(const void* qkv, const void* out, const void* dout, const float* lse, float* delta, void* dqkv,
+                    int B, int T, int H, int hd, float scale, int causal, cudaStream_t s);
 int ltl_attn_delta(const void* out, const void* dout, float* delta, int B, int T, int H, int hd, int dtype, cudaStream_t s);
 int* ltl_tc_err_flag();        // device flag raised by a bounded wait that ran out (read by ltl_gemm_tc_check)

@@ -371,7 +371,12 @@ def test_bulk_staged_decode_attention_long_context(dtype, heads):
 MIXED_LOSS_TOL, MIXED_GRAD_TOL = 2e-3, 3e-2
 
 
-@pytest.mark.parametrize("cfg,B", [(CFG0, 2), (CFG1, 32)])
+# vocabulary of 4096: the loss kernel that keeps the row in registers and writes the gradient as bf16; head_dim 64 and
+# 128 tokens: the tensor-core attention forward and backward inside the model
+CFG_WIDE_VOCAB = dict(vocab=4096, dim=128, layers=2, heads=2, ffn=256, max_seq=128)
+
+
+@pytest.mark.parametrize("cfg,B", [(CFG0, 2), (CFG1, 32), (CFG_WIDE_VOCAB, 3)])
 def test_mixed_precision_training_step_loss_and_gradients(cfg, B):
     T = cfg["max_seq"]
     w = bf16_round(params_for(cfg, seed=0, gain_jitter=0.1))

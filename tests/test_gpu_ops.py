@@ -157,6 +157,26 @@ def test_rmsnorm_bwd_against_analytic_and_central_differences(rows, cols):
         assert abs((f(xp) - f(xm)) / (2 * h) - host(DX)[r, c]) < 2e-2
 
 
+@pytest.mark.parametrize("rows,cols", [(7, 64), (300, 2048), (5, 1000), (33, 4096)])
+def test_rmsnorm_bwd_fused_with_residual_add_and_bf16_copy(rows, cols):
+    """res += d(rmsnorm)/dx, bf16 copy of the sum, dgamma accumulation: one, two and four chunks per thread, a ragged
+    width, more rows than CTAs."""
+    x, g, dy, r0 = rnd(25, rows, cols), 1.0 + 0.1 * rnd(26, 1, cols), rnd(27, rows, cols), rnd(28, rows, cols)
+    X, G, DY, R, DG = dev(x), dev(g), dev(dy), dev(r0), ad.alloc(1, cols)
+    RB = ad.TensorView(rows, cols, _lib.BF16)
+    x64, g64, d64 = x.astype(np.float64), g.astype(np.float64).ravel(), dy.astype(np.float64)
+    s = 1.0 / np.sqrt((x64 * x64).mean(1, keepdims=True) + 1e-5)
+    dot = (d64 * g64 * x64).sum(1, keepdims=True)
+    ref = r0.astype(np.float64) + s * g64 * d64 - x64 * s ** 3 / cols * dot
+    ref_dg = (d64 * x64 * s).sum(0)
+    _lib.call("luaTL_rmsnorm_bwd_residual", X.t.data, G.t.data, DY.t.data, R.t.data, RB.data, DG.t.data, rows, cols, 1e-5)
+    assert rel_err(host(R), ref) < 1e-5
+    assert rel_err(RB.download().reshape(rows, cols), ref) < 8e-3            # one bf16 rounding
+    assert rel_err(host(DG).ravel(), ref_dg) < 1e-5
+    with pytest.raises(_lib.LuaTLError, match="SHAPE"):
+        _lib.call("luaTL_rmsnorm_bwd_residual", X.t.data, G.t.data, DY.t.data, R.t.data, None, None, rows, 4100, 1e-5)
+
+
 # [6] SwiGLU -----------------------------------------------------------------------------------
 @pytest.mark.parametrize("rows,F,dtype,tol", [(9, 64, _lib.F32, 1e-5), (5, 30, _lib.F32, 1e-5), (17, 256, _lib.BF16, 3e-2)])
 def test_swiglu_forward_backward_packed_layout(rows, F, dtype, tol):
