@@ -16,6 +16,7 @@
 // No cluster launch and no TMA multicast: the kernel is the same on 1 and on N GPUs.
 #include <cuda.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <map>
 #include <tuple>
@@ -235,6 +236,178 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Persistent form for many-tile problems (training, prefill): one CTA per SM walks 128 x 256 output tiles.
+//   - the TMA ring (4 stages of 48 KB) never drains between tiles;
+//   - two accumulators of 256 columns in tensor memory: the MMA warp fills one while the four epilogue warps
+//     read the other, so the epilogue of tile i runs under the main loop of tile i + 1;
+//   - consecutive CTAs take consecutive M tiles of the same N tile, so the wide B (weight) tile is shared in L2.
+// MAJ = 0: C = A B^T (+ R), K-major operands, TC = bf16 or fp32.  MAJ = 1: C (fp32) += X^T Y, MN-major operands,
+// work items = (K slice, tile), atomic accumulation.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int PBN = 256, PSTAGES = 4;
+struct PBars {
+    uint64_t full[PSTAGES], empty[PSTAGES], acc_full[2], acc_empty[2];
+    uint32_t tmem_base;
+};
+constexpr size_t PSMEM = (size_t)PSTAGES * (BM + PBN) * BK * 2 + sizeof(PBars) + 1024;
+
+template <typename TC, int MAJ>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       TC* C, const TC* R, int M, int N, int K, int ksplit, int* __restrict__ err)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* const tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* const tiles_b = tiles + (size_t)PSTAGES * (BM * BK * 2);
+    PBars& sm = *reinterpret_cast<PBars*>(tiles_b + (size_t)PSTAGES * (PBN * BK * 2));
+    auto a_tile = [&](int st) { return tiles + (size_t)st * (BM * BK * 2); };
+    auto b_tile = [&](int st) { return tiles_b + (size_t)st * (PBN * BK * 2); };
+    constexpr uint32_t STAGE_BYTES = (BM + PBN) * BK * 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + PBN - 1) / PBN, ntiles = tiles_m * tiles_n;
+    const int kb_all = (K + BK - 1) / BK;
+    const int kb_per = (kb_all + ksplit - 1) / ksplit;
+    const int nitems = ntiles * ksplit;                  // item = slice * ntiles + tile; tile = nt * tiles_m + mt
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PSTAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&sm.acc_full[s], 1); mbar_init(&sm.acc_empty[s], 128); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;
+    bool ok = true;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer ----
+        int s = 0;
+        uint32_t round = 0;
+        for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x) {
+            const int tile = it % ntiles, slice = it / ntiles;
+            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * PBN;
+            const int kb0 = slice * kb_per, kb1 = min(kb_all, kb0 + kb_per);
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (round > 0) ok = mbar_wait(&sm.empty[s], (round - 1) & 1);
+                if (!ok) break;
+                mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+                if (MAJ == 0) {
+                    tma_load_2d(a_tile(s), &map_a, kb * BK, m0, &sm.full[s]);
+                    tma_load_2d(b_tile(s), &map_b, kb * BK, n0, &sm.full[s]);
+                } else {
+#pragma unroll
+                    for (int cb = 0; cb < BM / 64; ++cb) tma_load_2d(a_tile(s) + cb * (BK * 128), &map_a, m0 + cb * 64, kb * BK, &sm.full[s]);
+#pragma unroll
+                    for (int cb = 0; cb < PBN / 64; ++cb) tma_load_2d(b_tile(s) + cb * (BK * 128), &map_b, n0 + cb * 64, kb * BK, &sm.full[s]);
+                }
+                if (++s == PSTAGES) { s = 0; ++round; }
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        constexpr uint32_t idesc = MAJ ? umma_idesc_bf16_mn(BM, PBN) : umma_idesc_bf16(BM, PBN);
+        int s = 0;
+        uint32_t round = 0, i = 0;
+        for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x, ++i) {
+            const int slice = it / ntiles;
+            const int kb0 = slice * kb_per, kb1 = min(kb_all, kb0 + kb_per);
+            const uint32_t buf = i & 1, acc = tmem + buf * PBN;
+            if (i >= 2) ok = mbar_wait(&sm.acc_empty[buf], ((i >> 1) - 1) & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int kb = kb0; kb < kb1; ++kb) {
+                ok = mbar_wait(&sm.full[s], round & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (MAJ == 0) {
+                    const uint64_t da = umma_desc_sw128(smem_u32(a_tile(s))), db = umma_desc_sw128(smem_u32(b_tile(s)));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > kb0 || k) ? 1u : 0u);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16(acc, umma_desc_sw128_mn(smem_u32(a_tile(s)) + k * 2048, BK * 128, 1024),
+                                  umma_desc_sw128_mn(smem_u32(b_tile(s)) + k * 2048, BK * 128, 1024), idesc, (kb > kb0 || k) ? 1u : 0u);
+                }
+                umma_commit(&sm.empty[s]);
+                if (++s == PSTAGES) { s = 0; ++round; }
+            }
+            if (ok) umma_commit(&sm.acc_full[buf]);
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue ----
+        const int quad = warp & 3;
+        uint32_t i = 0;
+        for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++i) {
+            const int tile = it % ntiles, slice = it / ntiles;
+            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * PBN;
+            const bool empty_slice = slice * kb_per >= kb_all;
+            const uint32_t buf = i & 1;
+            if (!mbar_wait(&sm.acc_full[buf], (i >> 1) & 1)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + quad * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < PBN; c0 += 32) {
+                if (n0 + c0 >= N) break;
+                uint32_t v[32];
+                tmem_ld32(tmem + buf * PBN + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row >= M || empty_slice) continue;
+                const size_t base = (size_t)row * N + n0 + c0;
+                const int ncols = min(32, N - (n0 + c0));
+                if (MAJ == 1) {
+                    float* dst = reinterpret_cast<float*>(C) + base;
+                    if (ncols == 32 && (N & 3) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j),
+                                         "f"(__uint_as_float(v[j])), "f"(__uint_as_float(v[j + 1])),
+                                         "f"(__uint_as_float(v[j + 2])), "f"(__uint_as_float(v[j + 3])) : "memory");
+                    } else {
+                        for (int j = 0; j < ncols; ++j) atomicAdd(dst + j, __uint_as_float(v[j]));
+                    }
+                } else if (ncols == 32 && (N % Vec16<TC>::N) == 0) {
+                    constexpr int NV = Vec16<TC>::N;
+#pragma unroll
+                    for (int j = 0; j < 32; j += NV) {
+                        float o[NV];
+#pragma unroll
+                        for (int e = 0; e < NV; ++e) o[e] = __uint_as_float(v[j + e]);
+                        if (R) {
+                            float rr[NV];
+                            ld16<TC>(R + base + j, rr);
+#pragma unroll
+                            for (int e = 0; e < NV; ++e) o[e] += rr[e];
+                        }
+                        st16<TC>(C + base + j, o);
+                    }
+                } else {
+                    for (int j = 0; j < ncols; ++j) {
+                        float o = __uint_as_float(v[j]);
+                        if (R) o += Cvt<TC>::ld(R, base + j);
+                        Cvt<TC>::st(C, base + j, o);
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.acc_empty[buf])) : "memory");
+        }
+    }
+    if (!ok && err) atomicExch(err, 1);
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
 typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -279,12 +452,39 @@ int tensor_map(const void* base, int rows, int cols, long long pitch, int box_ro
 
 int* g_err_flag = nullptr;
 
+// LUATL_GEMM_PERSIST: 0 = never, 1 = K-major only, 2 (default) = K-major and the weight-gradient (MN-major) form
+int persist_mode()
+{
+    static const int mode = [] { const char* e = getenv("LUATL_GEMM_PERSIST"); return e ? atoi(e) : 2; }();
+    return mode;
+}
+bool persist_enabled() { return persist_mode() >= 1; }
+
+template <typename TC, int MAJ>
+int launch_persist(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const void* R, int M, int N, int K, int ksplit, cudaStream_t s)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        LTL_CUDA("gemm_tc attr", cudaFuncSetAttribute(gemm_tc_persist_kernel<TC, MAJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PSMEM));
+        attr_set = true;
+    }
+    if (ksplit < 1) ksplit = 1;
+    const long long items = (long long)((M + BM - 1) / BM) * ((N + PBN - 1) / PBN) * ksplit;
+    const int grid = (int)std::min<long long>(items, ltl_sm_count());
+    gemm_tc_persist_kernel<TC, MAJ><<<grid, 192, PSMEM, s>>>(ma, mb, (TC*)C, (const TC*)R, M, N, K, ksplit, g_err_flag);
+    return ltl_check_launch("gemm_tc_persist");
+}
+
 template <int BN, typename TC, int EPI>
 int launch(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int ksplit, cudaStream_t s)
 {
     CUtensorMap ma, mb;
     LTL_TRY(tensor_map(A, M, K, K, BM, &ma));
     LTL_TRY(tensor_map(B, N, K, K, BN, &mb));
+    if constexpr (BN == 256 && EPI == EPI_NONE) {
+        // long reductions run a little faster as two co-resident CTAs (measured: K = 5632 .. 11264, fp32 output)
+        if (persist_enabled() && ksplit <= 1 && K <= 4096) return launch_persist<TC, 0>(ma, mb, C, R, M, N, K, 1, s);
+    }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, ksplit < 1 ? 1 : ksplit);
     const int kb_all = (K + BK - 1) / BK;
     const int kb_per = (kb_all + (int)grid.z - 1) / (int)grid.z;
@@ -314,6 +514,9 @@ int launch_mn(const void* X, const void* Y, float* C, int M, int N, int K, int k
     CUtensorMap ma, mb;
     LTL_TRY(tensor_map(X, K, M, M, 64, &ma));
     LTL_TRY(tensor_map(Y, K, N, N, 64, &mb));
+    if constexpr (BN == 256) {
+        if (persist_mode() >= 2) return launch_persist<float, 1>(ma, mb, C, nullptr, M, N, K, ksplit, s);
+    }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, ksplit < 1 ? 1 : ksplit);
     const int kb_all = (K + BK - 1) / BK;
     const int kb_per = (kb_all + (int)grid.z - 1) / (int)grid.z;

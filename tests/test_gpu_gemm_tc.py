@@ -125,7 +125,7 @@ def test_many_tile_grid_uses_the_shallow_ring():
 
 
 @pytest.mark.parametrize("M,N,K,ks", [(128, 128, 64, 1), (256, 384, 1000, 3), (64, 64, 128, 1), (2048, 5632, 4096, 1), (72, 200, 300, 2),
-                                      (2000, 128, 4096, 8)])
+                                      (2000, 128, 4096, 8), (4096, 5632, 512, 1), (2048, 5640, 1000, 2), (4000, 2824, 200, 5)])
 def test_weight_gradient_product_of_token_major_operands(M, N, K, ks):
     """C += X^T Y with X [K, M] and Y [K, N] as they lie in memory (both tensor-core operands MN-major): tails in
     every dimension, split-K, a many-tile grid, two calls accumulate."""
@@ -152,4 +152,13 @@ def test_256_wide_tile_many_tile_grid_and_tails():
     got, ref = run(4096, 5632, 520, 256, seed=12)              # 16 x 22 tiles: the two-stage two-CTA configuration
     assert rel_err(got, ref) < 1e-5
     got, ref = run(300, 700, 72, 256, c_dtype=_lib.BF16, residual=True, seed=13)
+    assert rel_err(got, ref) < 8e-3
+
+
+def test_persistent_kernel_many_items_per_cta_tails_and_residual():
+    """More than two 128 x 256 tiles per SM: every CTA of the persistent kernel walks several tiles (ring and
+    accumulator parities wrap), with tails in M, N and K, fp32 + residual and bf16 outputs."""
+    got, ref = run(8200, 5000, 328, 256, residual=True, seed=14)
+    assert rel_err(got, ref) < 1e-5
+    got, ref = run(16384, 2048, 136, 256, c_dtype=_lib.BF16, seed=15)
     assert rel_err(got, ref) < 8e-3
