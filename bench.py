@@ -46,8 +46,9 @@ def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
-    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
 class Clocks:
@@ -457,8 +458,11 @@ def run_train4(args, dist):
                       kernel=f"gemm_tc_kernel<128,bf16>: feed-forward up projection of one micro-batch, {R} x {F2} x {D}, "
                              "10 launches back to back, CUDA events on the launching stream",
                       flops_per_launch=2.0 * R * F2 * D, us_per_launch=gms.value * 1e3,
-                      whole_step=dict(note="model FLOPs (6 x matrix parameters x tokens + causal attention) over the step time, per GPU",
-                                      achieved=step_tf, frac=step_tf / pk["bf16_tflops"])),
+                      whole_step=dict(note="model FLOPs (6 x matrix parameters x tokens + causal attention) over the step time, per GPU; "
+                                           "frac is of the sustained cuBLAS figure (a seconds-long step under the power cap), "
+                                           "frac_of_burst of the burst figure the isolated GEMM above is compared with",
+                                      achieved=step_tf, peak=pk["bf16_tflops_sustained"], frac=step_tf / pk["bf16_tflops_sustained"],
+                                      frac_of_burst=step_tf / pk["bf16_tflops"])),
         final_loss=loss, wall_ms_per_step=wall_ms / args.steps, clocks=clk)
     m.free()
     return line
