@@ -72,6 +72,12 @@ class Clocks:
         for line in self.proc.stdout:
             self.rows.append([x.strip() for x in line.split(",")])
 
+    def mark(self):
+        """Call where the timed region starts (the sampler itself is started before the warm-up, because nvidia-smi takes
+        a few hundred ms to print its first line): only samples after the mark count, unless the region was too short
+        to hold two of them, in which case the warm-up's samples (same work) are used and the window says so."""
+        self.mark_at = len(self.rows)
+
     def stop(self):
         if self.proc:
             self.proc.terminate()
@@ -80,7 +86,12 @@ class Clocks:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
         sm, mx, reasons = [], 0.0, set()
-        for r in self.rows:
+        mark = getattr(self, "mark_at", 0)
+        window = "timed region"
+        rows = self.rows[mark:]
+        if len(rows) < 2:
+            rows, window = self.rows, "warm-up + timed region (timed region shorter than two samples)"
+        for r in rows:
             try:
                 sm.append(float(r[1]))
                 mx = max(mx, float(r[2]))
@@ -91,7 +102,7 @@ class Clocks:
                     reasons.add(name)
         busy = [x for x in sm if x > 0.5 * mx] or sm
         return dict(sm_mhz=float(np.median(busy)) if busy else None, sm_max_mhz=mx or None,
-                    reasons=sorted(reasons), samples=len(sm))
+                    reasons=sorted(reasons), samples=len(sm), window=window)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -193,11 +204,12 @@ def run_decode(args, dist):
         _lib.call("luaTL_lm_generate_dev", m._h, d_prompts.t.data, nseq, N_PROMPT, N_NEW, d_out.t.data, C.byref(res))
         return res.step_ms
 
-    for _ in range(args.warmup):
-        step_dev()
     clocks = Clocks(dist.local)
     clocks.start()
+    for _ in range(args.warmup):
+        step_dev()
     dist.barrier()
+    clocks.mark()
     t0 = time.perf_counter()
     dev_ms, pre_ms, dec_ms, launches = 0.0, 0.0, 0.0, 0
     for _ in range(args.steps):
@@ -291,11 +303,12 @@ def run_train(args, dist):
         _lib.call("luaTL_lm_train_step_dev", m._h, d_ids.t.data, d_tgt.t.data, C.byref(a), C.byref(res))
         return res.step_ms
 
-    for _ in range(args.warmup):
-        step_dev()
     clocks = Clocks(dist.local)
     clocks.start()
+    for _ in range(args.warmup):
+        step_dev()
     dist.barrier()
+    clocks.mark()
     dev_ms, launches = 0.0, 0
     for _ in range(args.steps):
         dev_ms += step_dev()
@@ -400,11 +413,12 @@ def run_train4(args, dist):
             launches += m.last_timing()["launches"]
         return ms, launches
 
-    for w in range(args.warmup):
-        step_dev(w + 1)
     clocks = Clocks(dist.local)
     clocks.start()
+    for w in range(args.warmup):
+        step_dev(w + 1)
     dist.barrier()
+    clocks.mark()
     dev_ms, launches = 0.0, 0
     t0 = time.perf_counter()
     for s in range(args.steps):
