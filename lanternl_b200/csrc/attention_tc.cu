@@ -303,14 +303,16 @@ int launch_fwd_tc(const bf16* qkv, bf16* out, float* lse, int B, int T, int H, f
 constexpr int KS = 64;                   // keys per tile of the dQ walk
 constexpr int BWD_THREADS = 320;
 
+constexpr int DQ_ST = 4;                 // K / V ring depth of the dQ walk (S / dP stay double-buffered in tensor memory)
+
 template <int HD>
 struct DqSmem {
     alignas(1024) uint8_t q[HD / 64][QT * 128];
     alignas(1024) uint8_t dout[HD / 64][QT * 128];
-    alignas(1024) uint8_t k[2][HD / 64][KS * 128];
-    alignas(1024) uint8_t v[2][HD / 64][KS * 128];
+    alignas(1024) uint8_t k[DQ_ST][HD / 64][KS * 128];
+    alignas(1024) uint8_t v[DQ_ST][HD / 64][KS * 128];
     alignas(1024) uint8_t ds[QT * 128];
-    alignas(8) uint64_t q_full, kv_full[2], kv_free[2], sd_ready[2], ds_ready, acc_ready;
+    alignas(8) uint64_t q_full, kv_full[DQ_ST], kv_free[DQ_ST], sd_ready[2], ds_ready, acc_ready;
     uint32_t tmem_base;
 };
 
@@ -333,7 +335,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,     // boxes 
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.q_full, 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_free[s], 1); mbar_init(&sm.sd_ready[s], 1); }
+        for (int s = 0; s < DQ_ST; ++s) { mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_free[s], 1); }
+        for (int s = 0; s < 2; ++s) mbar_init(&sm.sd_ready[s], 1);
         mbar_init(&sm.ds_ready, 256); mbar_init(&sm.acc_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -354,8 +357,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,     // boxes 
             tma_load_2d(sm.dout[kb], &map_do, h * HD + kb * 64, b * T + q0, &sm.q_full);
         }
         for (int j = 0; j < ntiles && ok; ++j) {
-            const int s = j & 1;
-            if (j >= 2) ok = mbar_wait(&sm.kv_free[s], ((j >> 1) - 1) & 1);
+            const int s = j % DQ_ST;
+            if (j >= DQ_ST) ok = mbar_wait(&sm.kv_free[s], ((j / DQ_ST) - 1) & 1);
             if (!ok) break;
             mbar_expect_tx(&sm.kv_full[s], 2 * KS * HD * 2);
             for (int kb = 0; kb < KB; ++kb) {
@@ -366,22 +369,22 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,     // boxes 
     } else if (warp == 1 && lane == 0) {
         constexpr uint32_t idesc_s = umma_idesc_bf16(QT, KS), idesc_o = umma_idesc_bf16_bmn(QT, HD);
         auto issue_sd = [&](int j) {
-            const int s = j & 1;
+            const int s = j % DQ_ST, tb = j & 1;        // shared-memory stage, tensor-memory buffer
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb) {
                 const uint64_t da = umma_desc_sw128(smem_u32(sm.q[kb])), db = umma_desc_sw128(smem_u32(sm.k[s][kb]));
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem + (uint32_t)(s * KS), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+                    umma_bf16(tmem + (uint32_t)(tb * KS), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
             }
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb) {
                 const uint64_t da = umma_desc_sw128(smem_u32(sm.dout[kb])), db = umma_desc_sw128(smem_u32(sm.v[s][kb]));
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem + COL_DP + (uint32_t)(s * KS), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+                    umma_bf16(tmem + COL_DP + (uint32_t)(tb * KS), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
             }
-            umma_commit(&sm.sd_ready[s]);
+            umma_commit(&sm.sd_ready[tb]);
         };
         ok = mbar_wait(&sm.q_full, 0) && mbar_wait(&sm.kv_full[0], 0);
         if (ok) {
@@ -389,9 +392,9 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,     // boxes 
             issue_sd(0);
         }
         for (int j = 0; j < ntiles && ok; ++j) {
-            const int s = j & 1;
+            const int s = j % DQ_ST;
             if (j + 1 < ntiles) {
-                ok = mbar_wait(&sm.kv_full[s ^ 1], ((j + 1) >> 1) & 1);
+                ok = mbar_wait(&sm.kv_full[(j + 1) % DQ_ST], ((j + 1) / DQ_ST) & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 issue_sd(j + 1);
@@ -438,7 +441,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,     // boxes 
             };
             if (klim >= 32) body(std::true_type{}); else body(std::false_type{});
             // dS of the previous tile must have been consumed by its dQ product before it is overwritten
-            if (j > 0 && !mbar_wait(&sm.kv_free[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
+            if (j > 0 && !mbar_wait(&sm.kv_free[(j - 1) % DQ_ST], ((j - 1) / DQ_ST) & 1)) { ok = false; break; }
             uint8_t* prow = sm.ds + r * 128;
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
@@ -492,16 +495,18 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,     // boxes 
 // ---------------------------------------------------------------------------------------------------
 constexpr int QS = 64;                   // queries per step of the dK / dV walk
 
+constexpr int KV_ST = 3;                 // Q / dO ring depth of the dK / dV walk
+
 template <int HD>
 struct DkvSmem {
     alignas(1024) uint8_t k[HD / 64][KT * 128];
     alignas(1024) uint8_t v[HD / 64][KT * 128];
-    alignas(1024) uint8_t q[2][HD / 64][QS * 128];      // Q_i  [64 queries x hd]: K-major B of S^T, MN-major B of dK
-    alignas(1024) uint8_t dout[2][HD / 64][QS * 128];   // dO_i [64 queries x hd]: K-major B of dP^T, MN-major B of dV
+    alignas(1024) uint8_t q[KV_ST][HD / 64][QS * 128];      // Q_i  [64 queries x hd]: K-major B of S^T, MN-major B of dK
+    alignas(1024) uint8_t dout[KV_ST][HD / 64][QS * 128];   // dO_i [64 queries x hd]: K-major B of dP^T, MN-major B of dV
     alignas(1024) uint8_t pt[KT * 128];                 // P^T   [128 keys x 64 queries]
     alignas(1024) uint8_t dst[KT * 128];                // dS^T  [128 keys x 64 queries]
-    float lse2[2][QS], dls[2][QS];                      // per step: lse * log2(e), delta * scale
-    alignas(8) uint64_t kv_full, q_full[2], q_free[2], aux_full[2], sd_ready[2], p_ready, acc_ready;
+    float lse2[KV_ST][QS], dls[KV_ST][QS];                      // per step: lse * log2(e), delta * scale
+    alignas(8) uint64_t kv_full, q_full[KV_ST], q_free[KV_ST], aux_full[KV_ST], sd_ready[2], p_ready, acc_ready;
     uint32_t tmem_base;
 };
 
@@ -526,9 +531,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.kv_full, 1); mbar_init(&sm.p_ready, 256); mbar_init(&sm.acc_ready, 1);
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&sm.q_full[s], 1); mbar_init(&sm.q_free[s], 1); mbar_init(&sm.aux_full[s], 1); mbar_init(&sm.sd_ready[s], 1);
-        }
+        for (int s = 0; s < KV_ST; ++s) { mbar_init(&sm.q_full[s], 1); mbar_init(&sm.q_free[s], 1); mbar_init(&sm.aux_full[s], 1); }
+        for (int s = 0; s < 2; ++s) mbar_init(&sm.sd_ready[s], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -553,9 +557,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
         const float* lse_h = lse + ((size_t)b * H + h) * T;
         const float* delta_h = delta + ((size_t)b * H + h) * T;
         for (int st = 0; st < nsteps; ++st) {
-            const int s = st & 1, qrow = (i0 + st) * QS;
-            // stage s (operands and lse / delta) was last used by step st - 2: free once its dV / dK products are done
-            if (st >= 2 && lane == 0) ok = mbar_wait(&sm.q_free[s], ((st >> 1) - 1) & 1);
+            const int s = st % KV_ST, qrow = (i0 + st) * QS;
+            // stage s (operands and lse / delta) was last used by step st - KV_ST: free once its dV / dK products are done
+            if (st >= KV_ST && lane == 0) ok = mbar_wait(&sm.q_free[s], ((st / KV_ST) - 1) & 1);
             ok = __shfl_sync(0xFFFFFFFFu, (int)ok, 0) != 0;
             if (!ok) break;
             if (lane == 0) {
@@ -577,22 +581,22 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
     } else if (warp == 1 && lane == 0) {
         constexpr uint32_t idesc_s = umma_idesc_bf16(KT, QS), idesc_o = umma_idesc_bf16_bmn(KT, HD);
         auto issue_sd = [&](int st) {
-            const int s = st & 1;
+            const int s = st % KV_ST, tb = st & 1;      // shared-memory stage, tensor-memory buffer
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb) {
                 const uint64_t da = umma_desc_sw128(smem_u32(sm.k[kb])), db = umma_desc_sw128(smem_u32(sm.q[s][kb]));
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem + (uint32_t)(s * QS), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+                    umma_bf16(tmem + (uint32_t)(tb * QS), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
             }
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb) {
                 const uint64_t da = umma_desc_sw128(smem_u32(sm.v[kb])), db = umma_desc_sw128(smem_u32(sm.dout[s][kb]));
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem + COL_DP + (uint32_t)(s * QS), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+                    umma_bf16(tmem + COL_DP + (uint32_t)(tb * QS), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
             }
-            umma_commit(&sm.sd_ready[s]);
+            umma_commit(&sm.sd_ready[tb]);
         };
         ok = mbar_wait(&sm.kv_full, 0) && mbar_wait(&sm.q_full[0], 0);
         if (ok) {
@@ -600,9 +604,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
             issue_sd(0);
         }
         for (int st = 0; st < nsteps && ok; ++st) {
-            const int s = st & 1;
+            const int s = st % KV_ST;
             if (st + 1 < nsteps) {
-                ok = mbar_wait(&sm.q_full[s ^ 1], ((st + 1) >> 1) & 1);
+                ok = mbar_wait(&sm.q_full[(st + 1) % KV_ST], ((st + 1) / KV_ST) & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 issue_sd(st + 1);
@@ -630,9 +634,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
         const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
         const float sl2 = scale * LOG2E;
         for (int st = 0; st < nsteps; ++st) {
-            const int s = st & 1, qbase = (i0 + st) * QS + half * 32;               // first query of this thread's columns
-            const uint32_t col = (uint32_t)(s * QS + half * 32);
-            if (!mbar_wait(&sm.sd_ready[s], (st >> 1) & 1) || !mbar_wait(&sm.aux_full[s], (st >> 1) & 1)) { ok = false; break; }
+            const int s = st % KV_ST, tb = st & 1, qbase = (i0 + st) * QS + half * 32;   // first query of this thread's columns
+            const uint32_t col = (uint32_t)(tb * QS + half * 32);
+            if (!mbar_wait(&sm.sd_ready[tb], (st >> 1) & 1) || !mbar_wait(&sm.aux_full[s], (st / KV_ST) & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t sv[32], dv[32];
             tmem_ld32(trow + col, sv);
@@ -659,7 +663,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_qkv,    // boxes 
             };
             if (lo <= 0 && hi >= 32) body(std::true_type{}); else body(std::false_type{});
             // P^T / dS^T of the previous step must have been consumed before they are overwritten
-            if (st > 0 && !mbar_wait(&sm.q_free[(st - 1) & 1], ((st - 1) >> 1) & 1)) { ok = false; break; }
+            if (st > 0 && !mbar_wait(&sm.q_free[(st - 1) % KV_ST], ((st - 1) / KV_ST) & 1)) { ok = false; break; }
             uint8_t* prow = sm.pt + r * 128;
             uint8_t* drow = sm.dst + r * 128;
 #pragma unroll
