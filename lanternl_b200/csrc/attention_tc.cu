@@ -51,7 +51,7 @@ struct FwdSmem {
     float mx[2][2][QT];                                 // [tile parity][column half][row]: partial row maxima
     float lsum[2][QT];                                  // final exchange of the partial denominators
     int fail;
-    alignas(8) uint64_t q_full, kv_full[2], kv_free[2], s_ready[2], p_ready, o_ready[2];
+    alignas(8) uint64_t q_full, k_full[2], k_free[2], v_full[2], v_free[2], s_ready[2], p_ready, o_ready[2];
     uint32_t tmem_base;
 };
 
@@ -81,7 +81,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, bf16* __restrict
     if (threadIdx.x == 0) {
         mbar_init(&sm.q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_free[s], 1);
+            mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_free[s], 1); mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_free[s], 1);
             mbar_init(&sm.s_ready[s], 1); mbar_init(&sm.o_ready[s], 1);
         }
         mbar_init(&sm.p_ready, 256);
@@ -99,19 +99,26 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, bf16* __restrict
     bool ok = true;
 
     if (warp == 0 && lane == 0) {
-        // ---- TMA producer ----
+        // ---- TMA producer, K side: a K stage is free as soon as the scores that read it are done, one tile before
+        //      the matching V stage, so K_{j+2} is requested early enough to hide its latency ----
         const int row_q = b * T + q0;
         mbar_expect_tx(&sm.q_full, QT * HD * 2);
         for (int kb = 0; kb < KB; ++kb) tma_load_2d(sm.q[kb], &map_qkv, h * HD + kb * 64, row_q, &sm.q_full);
         for (int j = 0; j < ntiles && ok; ++j) {
             const int s = j & 1;
-            if (j >= 2) ok = mbar_wait(&sm.kv_free[s], ((j >> 1) - 1) & 1);
+            if (j >= 2) ok = mbar_wait(&sm.k_free[s], ((j >> 1) - 1) & 1);
             if (!ok) break;
-            mbar_expect_tx(&sm.kv_full[s], 2 * KT * HD * 2);
-            for (int kb = 0; kb < KB; ++kb) {
-                tma_load_2d(sm.k[s][kb], &map_qkv, D + h * HD + kb * 64, b * T + j * KT, &sm.kv_full[s]);
-                tma_load_2d(sm.v[s][kb], &map_qkv, 2 * D + h * HD + kb * 64, b * T + j * KT, &sm.kv_full[s]);
-            }
+            mbar_expect_tx(&sm.k_full[s], KT * HD * 2);
+            for (int kb = 0; kb < KB; ++kb) tma_load_2d(sm.k[s][kb], &map_qkv, D + h * HD + kb * 64, b * T + j * KT, &sm.k_full[s]);
+        }
+    } else if (warp == 0 && lane == 16) {
+        // ---- TMA producer, V side ----
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int s = j & 1;
+            if (j >= 2) ok = mbar_wait(&sm.v_free[s], ((j >> 1) - 1) & 1);
+            if (!ok) break;
+            mbar_expect_tx(&sm.v_full[s], KT * HD * 2);
+            for (int kb = 0; kb < KB; ++kb) tma_load_2d(sm.v[s][kb], &map_qkv, 2 * D + h * HD + kb * 64, b * T + j * KT, &sm.v_full[s]);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
@@ -126,8 +133,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, bf16* __restrict
                     umma_bf16(tmem + (uint32_t)(s * 128), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
             }
             umma_commit(&sm.s_ready[s]);
+            umma_commit(&sm.k_free[s]);
         };
-        ok = mbar_wait(&sm.q_full, 0) && mbar_wait(&sm.kv_full[0], 0);
+        ok = mbar_wait(&sm.q_full, 0) && mbar_wait(&sm.k_full[0], 0);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_s(0);
@@ -136,12 +144,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, bf16* __restrict
             const int s = j & 1;
             if (j + 1 < ntiles) {
                 // S buffer (j+1)&1 was last read for tile j-1: its softmax finished before p_ready(j-1), waited below
-                ok = mbar_wait(&sm.kv_full[s ^ 1], ((j + 1) >> 1) & 1);
+                ok = mbar_wait(&sm.k_full[s ^ 1], ((j + 1) >> 1) & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 issue_s(j + 1);
             }
-            ok = mbar_wait(&sm.p_ready, j & 1);
+            ok = mbar_wait(&sm.p_ready, j & 1) && mbar_wait(&sm.v_full[s], (j >> 1) & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // O_j = P V_j: P is K-major (two blocks of 64 keys); V_j is read as it lies, [128 keys x hd] = an MN-major B
@@ -153,7 +161,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_qkv, bf16* __restrict
                 umma_bf16(tmem + COL_O + (uint32_t)(s * 128), da, db, idesc_o, ks ? 1u : 0u);
             }
             umma_commit(&sm.o_ready[s]);
-            umma_commit(&sm.kv_free[s]);
+            umma_commit(&sm.v_free[s]);
         }
     } else if (warp >= 2) {
         // ---- softmax: two threads per query row ----
