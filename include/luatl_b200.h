@@ -241,6 +241,16 @@ int  luaTL_timer_stop(float* ms);
  * multiple of 4, at most 4096.  Equals luaTL_rmsnorm_bwd followed by an add and a cast. */
 int luaTL_rmsnorm_bwd_residual(const float* x, const float* gamma, const float* dy, float* res, void* res_bf16, float* dgamma,
                                int rows, int cols, float eps);
+/* New: sampling beyond greedy on the device, the rule of pick_token (ai/optim/lmtrain.lua:1364-1436): temperature
+ * <= 0 is the argmax; top_k in 1..128 keeps the k largest logits (descending, ties by lower index), top_p in (0, 1)
+ * cuts the nucleus inside that set (top_p without top_k is not supported); top_k = 0 walks the whole row in index
+ * order.  The uniform draw is a 24-bit counter-based hash of (seed, row, counter), so results are reproducible.
+ * luaTL_sample_rows: one index per row of fp32 logits [rows, vocab], counters[r] = position of row r (NULL: 0).
+ * luaTL_lm_set_sampling: the same rule inside luaTL_lm_generate*, counter = the sequence's position; stop_id >= 0:
+ * a sequence that emitted it keeps emitting it (stop_id = -1: none).  The reference samples on the host from
+ * downloaded logits with math.random. */
+int luaTL_sample_rows(const float* logits, int rows, int vocab, float temperature, int top_k, float top_p, uint64_t seed,
+                      const int32_t* counters, int32_t* out);
 /* New: the same GEMM launched `iters` times back to back on the library stream and timed with CUDA events
  * (ms per launch), for roofline measurements without host gaps.  No residual operand. */
 int luaTL_gemm_bf16_tc_time(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int tile_n,
@@ -337,6 +347,8 @@ int luaTL_lm_generate_dev(luaTL_lm_t* m, const int32_t* d_prompts, int nseq, int
  * launch per layer, each over its own layer of the cache (inputs larger than L2).  Leaves the
  * generation state reset. */
 int luaTL_lm_time_decode_attn(luaTL_lm_t* m, int nseq, int cache_len, int iters, float* ms_per_launch);
+/* Sampling rule of luaTL_lm_generate* (see luaTL_sample_rows); temperature <= 0 restores the greedy pick. */
+int luaTL_lm_set_sampling(luaTL_lm_t* m, float temperature, int top_k, float top_p, uint64_t seed, int stop_id);
 /* Device time (ms) and kernel launches of the last prefill and decode phases. */
 int luaTL_lm_last_timing(luaTL_lm_t* m, float* prefill_ms, float* decode_ms, int64_t* launches);
 

@@ -138,6 +138,8 @@ SIGNATURES = {
     "luaTL_gemm_bf16_tc_xty": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
     "luaTL_set_deferred": (None, [_i]), "luaTL_timer_start": (_i, []), "luaTL_timer_stop": (_i, [C.POINTER(C.c_float)]),
     "luaTL_rmsnorm_bwd_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f]),
+    "luaTL_sample_rows": (_i, [_vp, _i, _i, _f, _i, _f, _u64, _vp, _vp]),
+    "luaTL_lm_set_sampling": (_i, [_vp, _f, _i, _f, _u64, _i]),
     "luaTL_gemm_bf16_tc_time": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, C.POINTER(C.c_float)]),
     "luaTL_prog_create": (C.POINTER(Prog), [_i, _i]), "luaTL_prog_destroy": (None, [C.POINTER(Prog)]),
     "luaTL_prog_reset": (None, [C.POINTER(Prog)]), "luaTL_prog_push": (_i, [C.POINTER(Prog), C.POINTER(Op)]),

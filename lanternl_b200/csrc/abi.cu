@@ -631,6 +631,11 @@ int luaTL_rmsnorm_bwd_residual(const float* x, const float* gamma, const float* 
     LTL_TRY(ltl_rmsnorm_bwd_residual(x, gamma, dy, res, (bf16*)res_bf16, dgamma, rows, cols, eps, scratch, g_stream));
     return sync_stream("rmsnorm_bwd_residual");
 }
+int luaTL_sample_rows(const float* logits, int rows, int vocab, float temperature, int top_k, float top_p, uint64_t seed,
+                      const int32_t* counters, int32_t* out)
+{
+    ONE_SHOT("sample_rows", ltl_sample_rows(logits, rows, vocab, temperature, top_k, top_p, seed, counters, out, g_stream));
+}
 int luaTL_gemm_bf16_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K, int ksplit)
 {
     LTL_TRY(ltl_require_init("gemm_bf16_tc_xty"));

@@ -64,6 +64,9 @@ struct luaTL_lm_s {
     bf16* Wm = nullptr;          // second bf16 mirror for the backward: the other orientation of every matrix
     int mirror_dirty = 1;
     int train_tc = 0;            // bf16 model that has been asked to train: mixed-precision step
+    // sampling of the generation loop (temperature <= 0: greedy); captured decode graphs are specific to these values
+    struct Sampling { float temperature = 0.0f; int top_k = 0; float top_p = 0.0f; uint64_t seed = 0; int stop_id = -1; } samp;
+    int32_t* d_done = nullptr;   // per sequence: the stop token has been emitted
     int attn_tc = 1;             // tensor-core attention where the shape allows (LUATL_ATTN_TC=0 turns it off)
     // mixed-precision backward scratch (bf16): activation gradients
     bf16 *b_dres = nullptr, *b_dhs = nullptr, *b_dh13 = nullptr, *b_dattn = nullptr, *b_dqkv = nullptr, *b_dl = nullptr;
@@ -671,6 +674,7 @@ int ensure_decode(LM* m, int nseq, int n_prompt, int n_new)
         DALLOC(m->kc, cache, "K cache"); DALLOC(m->vc, cache, "V cache");
         DALLOC(m->d_pos, (size_t)m->nseq_cap * 4, "positions"); DALLOC(m->d_count, (size_t)m->nseq_cap * 4, "counts");
         DALLOC(m->d_next, (size_t)m->nseq_cap * 4, "next tokens"); DALLOC(m->d_err, 4, "error flag");
+        DALLOC(m->d_done, (size_t)m->nseq_cap * 4, "stop flags");
         DALLOC(m->d_win, (size_t)m->nseq_cap * m->T * 4, "window ids");
         DALLOC(m->xlast, (size_t)m->nseq_cap * m->D * 4, "last rows");
         DALLOC(m->part, (size_t)8 * m->nseq_cap * m->D * 4, "split-K partial sums");
@@ -704,6 +708,18 @@ int ensure_decode(LM* m, int nseq, int n_prompt, int n_new)
         }
     }
     return LTL_OK;
+}
+
+// Greedy pick, or the sampled one when a temperature is set; both advance the sequence state on the device.
+int pick_next(LM* m, const float* logits, int nseq, int slot0, int32_t* d_out, int out_stride, int32_t* hist, int hist_stride,
+              int hist_base, cudaStream_t st)
+{
+    if (m->samp.temperature > 0.0f)
+        return ltl_sample_advance(logits, nseq, m->V, m->d_next + slot0, d_out, out_stride, m->d_count + slot0, m->d_pos + slot0,
+                                  hist, hist_stride, hist_base, m->samp.temperature, m->samp.top_k, m->samp.top_p, m->samp.seed,
+                                  m->samp.stop_id, m->d_done ? m->d_done + slot0 : nullptr, slot0, st);
+    return ltl_pick_advance(logits, nseq, m->V, m->d_next + slot0, d_out, out_stride, m->d_count + slot0, m->d_pos + slot0,
+                            hist, hist_stride, hist_base, st);
 }
 
 // Decode step of the bf16 tensor-core path.  The two residual GEMMs of a layer (attention output
@@ -748,8 +764,7 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
     LTL_TRY(ltl_gemm_tc(a.hf, m->Wb + (m->c.tie ? m->off_emb : m->off_head), a.logits, nullptr, nseq, V, D, LTL_F32, 0, 0, 1, m->s));
     m->launches++;
     if (pick) {
-        LTL_TRY(ltl_pick_advance(a.logits, nseq, V, m->d_next + slot0, d_out, out_stride, m->d_count + slot0,
-                                 m->d_pos + slot0, hist, hist_stride, hist_base, m->s));
+        LTL_TRY(pick_next(m, a.logits, nseq, slot0, d_out, out_stride, hist, hist_stride, hist_base, m->s));
         m->launches++;
     }
     return LTL_OK;
@@ -798,8 +813,7 @@ int decode_step(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t* d_out
     else LTL_TRY(wgemm(m, a.hf, nseq, D, m->off_head, V, a.logits, LTL_F32, nullptr, 0));
     m->launches++;
     if (pick) {
-        LTL_TRY(ltl_pick_advance(a.logits, nseq, V, m->d_next + slot0, d_out, out_stride, m->d_count + slot0,
-                                 m->d_pos + slot0, hist, hist_stride, hist_base, m->s));
+        LTL_TRY(pick_next(m, a.logits, nseq, slot0, d_out, out_stride, hist, hist_stride, hist_base, m->s));
         m->launches++;
     }
     return LTL_OK;
@@ -830,8 +844,7 @@ int prefill_and_pick(LM* m, int nseq, int len, int hist_stride, int hist_base, i
     LTL_TRY(ltl_check_launch("window"));
     LTL_TRY(forward(m, m->infer, m->d_win, nseq, Wn, MODE_PREFILL));
     LTL_TRY(ltl_fill_i32(m->d_pos, nseq, Wn - 1, m->s));
-    LTL_TRY(ltl_pick_advance(m->infer.logits, nseq, m->V, m->d_next, d_out, out_stride, m->d_count, m->d_pos,
-                             m->d_hist, hist_stride, hist_base, m->s));
+    LTL_TRY(pick_next(m, m->infer.logits, nseq, 0, d_out, out_stride, m->d_hist, hist_stride, hist_base, m->s));
     m->launches += 3;
     return LTL_OK;
 }
@@ -847,6 +860,7 @@ int generate_dev(LM* m, const int32_t* d_prompts, int nseq, int n_prompt, int n_
     LTL_CUDA("event", cudaEventRecord(m->ev[0], m->s));
     LTL_CUDA("memset", cudaMemsetAsync(m->d_count, 0, (size_t)nseq * 4, m->s));
     LTL_CUDA("memset", cudaMemsetAsync(m->d_err, 0, 4, m->s));
+    LTL_CUDA("memset", cudaMemsetAsync(m->d_done, 0, (size_t)nseq * 4, m->s));
     copy_prompt_kernel<<<(nseq * n_prompt + 255) / 256, 256, 0, m->s>>>(d_prompts, n_prompt, m->d_hist, hs, nseq);
     LTL_TRY(ltl_check_launch("copy_prompt"));
     LTL_TRY(prefill_and_pick(m, nseq, n_prompt, hs, n_prompt, d_out, n_new));
@@ -971,7 +985,7 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
     void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
                      m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
                      m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part,
-                     m->Wm, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
+                     m->Wm, m->d_done, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
     for (void* p : ptrs) if (p) cudaFree(p);
     for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
     cudaGetLastError();
@@ -1178,6 +1192,26 @@ int luaTL_lm_generate(luaTL_lm_t* m, const int32_t* prompts, int nseq, int n_pro
     LTL_TRY(generate_dev(m, m->d_prompt, nseq, n_prompt, n_new, m->d_out, timing));
     LTL_CUDA("ids download", cudaMemcpyAsync(out, m->d_out, (size_t)nseq * n_new * 4, cudaMemcpyDeviceToHost, m->s));
     LTL_CUDA("generate sync", cudaStreamSynchronize(m->s));
+    return LTL_OK;
+}
+
+int luaTL_lm_set_sampling(luaTL_lm_t* m, float temperature, int top_k, float top_p, uint64_t seed, int stop_id)
+{
+    if (!m) return ltl_fail(LTL_ERR_NULL, "lm_set_sampling: null model");
+    if (temperature > 0.0f) {
+        if (top_k < 0 || top_k > 128) return ltl_fail(LTL_ERR_UNSUPPORTED, "lm_set_sampling: top_k %d outside 0..128", top_k);
+        if (top_p > 0.0f && top_p < 1.0f && !(top_k > 0 && top_k < m->V))
+            return ltl_fail(LTL_ERR_UNSUPPORTED, "lm_set_sampling: top_p needs top_k in 1..128 on this backend (the nucleus is cut inside the top-k set)");
+    }
+    if (stop_id >= m->V) return ltl_fail(LTL_ERR_ARG, "lm_set_sampling: stop token %d outside the vocabulary", stop_id);
+    LM::Sampling n;
+    n.temperature = temperature > 0.0f ? temperature : 0.0f; n.top_k = top_k; n.top_p = top_p; n.seed = seed; n.stop_id = stop_id;
+    const LM::Sampling& o = m->samp;
+    if (n.temperature != o.temperature || n.top_k != o.top_k || n.top_p != o.top_p || n.seed != o.seed || n.stop_id != o.stop_id) {
+        LTL_CUDA("sync", cudaStreamSynchronize(m->s));
+        drop_graphs(m);                                  // captured decode steps carry the old values as kernel arguments
+        m->samp = n;
+    }
     return LTL_OK;
 }
 

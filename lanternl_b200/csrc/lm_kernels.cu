@@ -887,6 +887,220 @@ int ltl_pick_advance(const float* logits, int B, int V, int32_t* next, int32_t* 
     return ltl_check_launch("pick_advance");
 }
 
+// ------------------------------------------------------------------------------------------
+// Sampling beyond greedy on the device (rule: ai/optim/lmtrain.lua:1364-1436).
+//   temperature <= 0            -> argmax (pick_advance_kernel)
+//   top_k in [1, 128]           -> the k largest logits in descending order (ties: lower index first), softmax at the
+//                                  temperature over them, optional nucleus cut-off top_p inside that set, then the
+//                                  first candidate whose cumulative weight reaches u * norm
+//   top_k = 0 and top_p = 0     -> the same walk over the whole row in index order
+// u is a counter-based uniform in [0, 1) with 24 bits: splitmix64(seed, sequence, position), so a generation is
+// reproducible and independent of launch geometry.  One CTA per row.
+// ------------------------------------------------------------------------------------------
+namespace samp {
+constexpr int MAXK = 128, EQCAP = 1024;
+__host__ __device__ inline uint64_t mix64(uint64_t z)
+{
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__host__ __device__ inline float uniform24(uint64_t seed, uint32_t row, uint32_t counter)
+{
+    const uint64_t h = mix64(mix64(seed ^ ((uint64_t)row << 32)) ^ counter);
+    return (float)(h >> 40) * (1.0f / 16777216.0f);
+}
+__device__ __forceinline__ uint32_t order_key(float x)       // larger float -> larger unsigned
+{
+    const uint32_t u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+}  // namespace samp
+
+// Returns the sampled index of one row (valid in thread 0).  blockDim.x threads, a multiple of 32, at most 1024.
+__device__ int sample_row(const float* __restrict__ row, int V, float temperature, int top_k, float top_p, float u)
+{
+    using namespace samp;
+    __shared__ unsigned hist[256];
+    __shared__ float cand_v[MAXK];
+    __shared__ int cand_i[MAXK];
+    __shared__ int eq_i[EQCAP];
+    __shared__ float sorted_v[MAXK];
+    __shared__ int sorted_i[MAXK];
+    __shared__ unsigned s_prefix, s_need, s_ngt, s_neq;
+    __shared__ float red[33];
+    __shared__ float scan[1024];
+    __shared__ int s_pick;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const float invT = 1.0f / temperature;
+    if (top_k > 0 && top_k < V) {
+        const int k = top_k < MAXK ? top_k : MAXK;
+        // radix select, most significant byte first: key of the k-th largest element
+        if (tid == 0) { s_prefix = 0; s_need = (unsigned)k; }
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            for (int i = tid; i < 256; i += nt) hist[i] = 0;
+            __syncthreads();
+            const unsigned prefix = s_prefix, himask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+            for (int i = tid; i < V; i += nt) {
+                const unsigned key = order_key(row[i]);
+                if ((key & himask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned need = s_need;
+                int bkt = 255;
+                for (; bkt > 0; --bkt) { if (hist[bkt] >= need) break; need -= hist[bkt]; }
+                s_prefix = prefix | ((unsigned)bkt << shift);
+                s_need = need;                           // how many of the bucket's elements are still wanted
+            }
+            __syncthreads();
+        }
+        const unsigned kth = s_prefix;
+        if (tid == 0) { s_ngt = 0; s_neq = 0; }
+        __syncthreads();
+        for (int i = tid; i < V; i += nt) {
+            const float x = row[i];
+            const unsigned key = order_key(x);
+            if (key > kth) { const unsigned slot = atomicAdd(&s_ngt, 1u); if (slot < (unsigned)MAXK) { cand_v[slot] = x; cand_i[slot] = i; } }
+            else if (key == kth) { const unsigned slot = atomicAdd(&s_neq, 1u); if (slot < (unsigned)EQCAP) eq_i[slot] = i; }
+        }
+        __syncthreads();
+        const int ngt = min((int)s_ngt, k), neq = min((int)s_neq, EQCAP), want_eq = min(k - ngt, neq);
+        // the elements equal to the k-th value with the lowest indices complete the set
+        for (int e = tid; e < neq; e += nt) {
+            int rank = 0;
+            for (int o = 0; o < neq; ++o) rank += eq_i[o] < eq_i[e];
+            if (rank < want_eq) { cand_v[ngt + rank] = row[eq_i[e]]; cand_i[ngt + rank] = eq_i[e]; }
+        }
+        __syncthreads();
+        const int n = ngt + want_eq;
+        // order: value descending, index ascending (rank sort over at most 128 candidates)
+        for (int e = tid; e < n; e += nt) {
+            int rank = 0;
+            for (int o = 0; o < n; ++o) rank += (cand_v[o] > cand_v[e]) || (cand_v[o] == cand_v[e] && cand_i[o] < cand_i[e]);
+            sorted_v[rank] = cand_v[e]; sorted_i[rank] = cand_i[e];
+        }
+        __syncthreads();
+        if (tid == 0) {
+            const float mx = sorted_v[0];
+            float sum = 0.0f;
+            for (int r = 0; r < n; ++r) { cand_v[r] = expf((sorted_v[r] - mx) * invT); sum += cand_v[r]; }
+            int limit = n;
+            if (top_p > 0.0f && top_p < 1.0f) {
+                float acc = 0.0f;
+                for (int r = 0; r < n; ++r) { acc += cand_v[r] / sum; if (acc >= top_p) { limit = r + 1; break; } }
+            }
+            float norm = 0.0f;
+            for (int r = 0; r < limit; ++r) norm += cand_v[r];
+            const float target = u * norm;
+            float acc = 0.0f;
+            int pick = sorted_i[limit - 1];
+            for (int r = 0; r < limit; ++r) { acc += cand_v[r]; if (acc >= target) { pick = sorted_i[r]; break; } }
+            s_pick = pick;
+        }
+        __syncthreads();
+        return s_pick;
+    }
+    // whole row in index order: contiguous chunk per thread, block scan of the chunk sums
+    const int chunk = (V + nt - 1) / nt, i0 = tid * chunk, i1 = min(V, i0 + chunk);
+    float mx = -INFINITY;
+    for (int i = i0; i < i1; ++i) mx = fmaxf(mx, row[i]);
+    mx = block_max(mx, red);
+    float local = 0.0f;
+    for (int i = i0; i < i1; ++i) local += expf((row[i] - mx) * invT);
+    scan[tid] = local;
+    __syncthreads();
+    if (tid == 0) {
+        float total = 0.0f;
+        for (int t = 0; t < nt; ++t) total += scan[t];
+        const float target = u * total;
+        float acc = 0.0f;
+        int owner = nt - 1;
+        for (int t = 0; t < nt; ++t) { if (acc + scan[t] >= target) { owner = t; break; } acc += scan[t]; }
+        while (owner > 0 && owner * chunk >= V) --owner;
+        int pick = min(V, (owner + 1) * chunk) - 1;
+        for (int i = owner * chunk; i < min(V, (owner + 1) * chunk); ++i) {
+            acc += expf((row[i] - mx) * invT);
+            if (acc >= target) { pick = i; break; }
+        }
+        s_pick = pick;
+    }
+    __syncthreads();
+    return s_pick;
+}
+
+__global__ void __launch_bounds__(1024)
+sample_advance_kernel(const float* __restrict__ logits, int V, int32_t* __restrict__ next, int32_t* __restrict__ out_ids,
+                      int out_stride, int32_t* __restrict__ count, int32_t* __restrict__ pos, int32_t* __restrict__ hist,
+                      int hist_stride, int hist_base, float temperature, int top_k, float top_p, unsigned long long seed,
+                      int stop_id, int32_t* __restrict__ done, int slot0)
+{
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const float u = samp::uniform24(seed, (uint32_t)(slot0 + b), (uint32_t)pos[b]);
+    int pick = sample_row(logits + (size_t)b * V, V, temperature, top_k, top_p, u);
+    if (threadIdx.x == 0) {
+        if (done && stop_id >= 0) {
+            if (done[b]) pick = stop_id;                 // a finished sequence keeps emitting its stop token
+            else if (pick == stop_id) done[b] = 1;
+        }
+        next[b] = pick;
+        const int c = count[b];
+        if (out_ids && c < out_stride) out_ids[(size_t)b * out_stride + c] = pick;
+        if (hist && hist_base + c < hist_stride) hist[(size_t)b * hist_stride + hist_base + c] = pick;
+        count[b] = c + 1;
+        pos[b] += 1;
+    }
+}
+
+// One sampled index per row with explicit counters (the position of the row in its sequence): the rule of the
+// generation loop as an immediate op.
+__global__ void __launch_bounds__(1024)
+sample_rows_kernel(const float* __restrict__ logits, int V, float temperature, int top_k, float top_p,
+                   unsigned long long seed, const int32_t* __restrict__ counters, int32_t* __restrict__ out)
+{
+    const int b = blockIdx.x;
+    const float u = samp::uniform24(seed, (uint32_t)b, (uint32_t)(counters ? counters[b] : 0));
+    const int pick = sample_row(logits + (size_t)b * V, V, temperature, top_k, top_p, u);
+    if (threadIdx.x == 0) out[b] = pick;
+}
+
+static int check_sampling(float temperature, int top_k, float top_p, int V)
+{
+    if (!(temperature > 0.0f)) return ltl_fail(LTL_ERR_ARG, "sample: temperature must be positive (use the greedy pick otherwise)");
+    if (top_k < 0 || top_k > samp::MAXK) return ltl_fail(LTL_ERR_UNSUPPORTED, "sample: top_k %d outside 0..%d", top_k, samp::MAXK);
+    if (top_p > 0.0f && top_p < 1.0f && !(top_k > 0 && top_k < V))
+        return ltl_fail(LTL_ERR_UNSUPPORTED, "sample: top_p needs top_k in 1..%d on this backend (the nucleus is cut inside the top-k set)", samp::MAXK);
+    return LTL_OK;
+}
+
+int ltl_sample_advance(const float* logits, int B, int V, int32_t* next, int32_t* out_ids, int out_stride, int32_t* count,
+                       int32_t* pos, int32_t* hist, int hist_stride, int hist_base, float temperature, int top_k, float top_p,
+                       uint64_t seed, int stop_id, int32_t* done, int slot0, cudaStream_t s)
+{
+    if (!logits || !next || !count || !pos) return ltl_fail(LTL_ERR_NULL, "sample_advance: null pointer");
+    LTL_TRY(check_sampling(temperature, top_k, top_p, V));
+    if (B <= 0) return LTL_OK;
+    LTL_CUDA("sample_advance launch", ltl_launch(sample_advance_kernel, dim3(B), dim3(V >= 4096 ? 1024 : 256), 0, s, ltl_pdl_enabled(),
+                                                 logits, V, next, out_ids, out_stride, count, pos, hist, hist_stride, hist_base,
+                                                 temperature, top_k, top_p, (unsigned long long)seed, stop_id, done, slot0));
+    return ltl_check_launch("sample_advance");
+}
+
+int ltl_sample_rows(const float* logits, int rows, int V, float temperature, int top_k, float top_p, uint64_t seed,
+                    const int32_t* counters, int32_t* out, cudaStream_t s)
+{
+    if (!logits || !out) return ltl_fail(LTL_ERR_NULL, "sample_rows: null pointer");
+    if (rows < 0 || V <= 0) return ltl_fail(LTL_ERR_SHAPE, "sample_rows: bad shape %dx%d", rows, V);
+    LTL_TRY(check_sampling(temperature, top_k, top_p, V));
+    if (rows == 0) return LTL_OK;
+    sample_rows_kernel<<<rows, V >= 4096 ? 1024 : 256, 0, s>>>(logits, V, temperature, top_k, top_p, (unsigned long long)seed, counters, out);
+    return ltl_check_launch("sample_rows");
+}
+
 __global__ void fill_i32_kernel(int32_t* p, int n, int32_t v)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;

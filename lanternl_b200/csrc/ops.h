@@ -114,6 +114,11 @@ int ltl_decode_attn(const void* qkv, void* kcache, void* vcache, void* out,
 int ltl_pick_advance(const float* logits, int B, int V, int32_t* next, int32_t* out_ids,
                      int out_stride, int32_t* count, int32_t* pos, int32_t* hist, int hist_stride,
                      int hist_base, cudaStream_t s);
+int ltl_sample_advance(const float* logits, int B, int V, int32_t* next, int32_t* out_ids, int out_stride, int32_t* count,
+                       int32_t* pos, int32_t* hist, int hist_stride, int hist_base, float temperature, int top_k, float top_p,
+                       uint64_t seed, int stop_id, int32_t* done, int slot0, cudaStream_t s);
+int ltl_sample_rows(const float* logits, int rows, int V, float temperature, int top_k, float top_p, uint64_t seed,
+                    const int32_t* counters, int32_t* out, cudaStream_t s);
 int ltl_fill_i32(int32_t* p, int n, int32_t value, cudaStream_t s);
 // correct[0] += #{r : tgt[r] >= 0 and pred[r] == tgt[r]}  (as float)
 int ltl_count_correct(const int32_t* pred, const int32_t* tgt, int n, float* correct, cudaStream_t s);

@@ -303,8 +303,16 @@ class Model:
             logits = self.step(t, state)
         return logits
 
+    def set_sampling(self, temperature=0.0, top_k=0, top_p=0.0, seed=0, stop_id=None, zero_indexed=False):
+        """Sampling rule of the generation loop (opts.temperature / top_k / top_p of LMTrain:generate,
+        lmtrain.lua:1364-1436); temperature <= 0 is greedy.  stop_id: the sequence keeps emitting it once drawn."""
+        self._alive("set_sampling")
+        stop = -1 if stop_id is None else int(stop_id) - (0 if zero_indexed else 1)
+        _lib.call("luaTL_lm_set_sampling", self._h, float(temperature), int(top_k), float(top_p), int(seed), stop)
+
     def generate_batch(self, prompts, n_new, zero_indexed=False):
-        """Greedy generation for [nseq, n_prompt] prompts -> [nseq, n_new] ids, all on the device."""
+        """Generation for [nseq, n_prompt] prompts -> [nseq, n_new] ids, all on the device: greedy, or sampled when
+        set_sampling gave a temperature."""
         self._alive("generate_batch")
         p = np.ascontiguousarray(prompts, dtype=np.int32)
         if p.ndim == 1:

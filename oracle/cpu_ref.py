@@ -189,3 +189,56 @@ def rope(x, heads, hd, pos0=0, base=10000.0, interleaved=False, inverse=False):
     y = _f64(x).copy()
     lib().ora_rope(_d(y), y.shape[0], heads, hd, pos0, base, int(interleaved), int(inverse))
     return y
+
+
+# ---- sampling beyond greedy: restatement of pick_token (ai/optim/lmtrain.lua:1364-1436) -------------------------
+def sampling_uniform(seed, row, counter):
+    """The 24-bit counter-based uniform the device kernels draw (splitmix64 of seed, row, counter); the reference
+    calls math.random() here, which no other implementation can reproduce."""
+    M = (1 << 64) - 1
+
+    def mix(z):
+        z = (z + 0x9E3779B97F4A7C15) & M
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M
+        return z ^ (z >> 31)
+    h = mix(mix((seed ^ ((row & 0xFFFFFFFF) << 32)) & M) ^ (counter & 0xFFFFFFFF))
+    return (h >> 40) / 16777216.0
+
+
+def pick_token(row, temperature, top_k=0, top_p=0.0, u=0.0):
+    """Index (0-based) the reference's pick_token returns for uniform draw u.  Candidates: all columns in index order,
+    or the top_k largest in descending order (ties: lower index first, the order its insertion pass produces), or -
+    with top_p - all columns sorted descending (cut to top_k when given); softmax at the temperature over the
+    candidates; nucleus cut; first candidate whose cumulative weight reaches u * norm.  Also returns the distance of
+    the target to the nearest cumulative boundary, relative to norm (how robust the pick is to rounding)."""
+    row = np.asarray(row, dtype=np.float64)
+    cols = row.size
+    if not temperature or temperature <= 0:
+        return int(np.argmax(row)), 1.0
+    if 0 < top_p < 1:
+        idx = np.argsort(-row, kind="stable")
+        n = top_k if 0 < top_k < cols else cols
+    elif 0 < top_k < cols:
+        idx = np.argsort(-row, kind="stable")
+        n = top_k
+    else:
+        idx = np.arange(cols)
+        n = cols
+    idx = idx[:n]
+    vals = row[idx]
+    probs = np.exp((vals - vals.max()) / temperature)
+    total = probs.sum()
+    limit = n
+    if 0 < top_p < 1:
+        acc = np.cumsum(probs / total)
+        hit = np.nonzero(acc >= top_p)[0]
+        if hit.size:
+            limit = int(hit[0]) + 1
+    cum = np.cumsum(probs[:limit])
+    norm = cum[-1]
+    target = u * norm
+    r = int(np.searchsorted(cum, target, side="left"))
+    r = min(r, limit - 1)
+    margin = float(np.min(np.abs(cum - target)) / norm)
+    return int(idx[r]), margin

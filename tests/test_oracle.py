@@ -179,3 +179,24 @@ def test_greedy_reprefills_when_context_is_full():
         lg = o.forward(p, np.array(win)[None, :])[0, -1]
         assert int(np.argmax(lg)) == out[0, s]
         seq.append(int(out[0, s]))
+
+
+def test_pick_token_restatement_rules():
+    """pick_token (ai/optim/lmtrain.lua:1364-1436): greedy at temperature 0, top-1 = argmax, u = 0 takes the first
+    candidate of the walk order, the nucleus cut keeps the smallest prefix reaching top_p, frequencies follow the
+    softmax."""
+    row = np.array([0.1, 2.0, -1.0, 2.0, 0.5, 1.5])
+    assert cpu_ref.pick_token(row, 0.0)[0] == 1                            # first maximum
+    assert cpu_ref.pick_token(row, 1.0, top_k=1, u=0.73)[0] == 1
+    assert cpu_ref.pick_token(row, 1.0, u=0.0)[0] == 0                     # whole row: index order
+    assert cpu_ref.pick_token(row, 1.0, top_k=3, u=0.0)[0] == 1            # top-k: descending, ties by lower index
+    assert cpu_ref.pick_token(row, 1.0, top_k=3, u=0.999999)[0] == 5
+    p = np.exp(row - row.max()); p /= p.sum()
+    order = np.argsort(-row, kind="stable")
+    assert cpu_ref.pick_token(row, 1.0, top_k=5, top_p=p[order][:2].sum() - 1e-9, u=0.999999)[0] == order[1]
+    us = (np.arange(4000) + 0.5) / 4000
+    picks = np.array([cpu_ref.pick_token(row, 0.8, u=u)[0] for u in us])
+    q = np.exp((row - row.max()) / 0.8); q /= q.sum()
+    assert np.abs(np.bincount(picks, minlength=6) / 4000 - q).max() < 1e-3
+    us24 = [cpu_ref.sampling_uniform(9, r, c) for r in range(50) for c in range(50)]
+    assert 0.0 <= min(us24) and max(us24) < 1.0 and abs(np.mean(us24) - 0.5) < 0.02 and len(set(us24)) > 2400
