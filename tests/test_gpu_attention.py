@@ -102,7 +102,8 @@ TOL_GRAD = 1.5e-2
 
 
 @pytest.mark.parametrize("impl", [1, 2])
-@pytest.mark.parametrize("B,T,H,hd", [(2, 128, 2, 64), (1, 256, 2, 128), (2, 200, 1, 64), (1, 520, 2, 128), (2, 64, 2, 64)])
+@pytest.mark.parametrize("B,T,H,hd", [(2, 128, 2, 64), (1, 256, 2, 128), (2, 200, 1, 64), (1, 520, 2, 128), (2, 64, 2, 64),
+                                     (1, 2048, 1, 128), (1, 1032, 2, 64)])
 def test_attention_backward_matches_float64(B, T, H, hd, impl):
     got, ref = run_bwd(B, T, H, hd, impl, seed=7 * T + hd)
     D = H * hd
