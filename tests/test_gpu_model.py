@@ -455,3 +455,24 @@ def test_config4_width_one_layer_accumulation_property():
     # the optimizer acted on the fp32 master weights
     assert np.allclose(m1.flat_params(), w - 1e-3 * g1, rtol=0, atol=1e-7)
     m1.free()
+
+
+def test_config4_width_mixed_precision_against_the_fp32_path():
+    """Same widths, one sequence: the mixed-precision step (tensor-core GEMMs and attention, bf16 activations) against
+    this library's exact fp32 path (CUDA-core kernels, the one pinned to the oracle and to the reference's CUDA kernels
+    at small sizes) on the same bf16-valued weights: loss within 2e-3, every gradient tensor within 3e-2 in L2."""
+    cfg = dict(vocab=32000, dim=2048, layers=1, heads=16, ffn=5632, max_seq=2048)
+    T = cfg["max_seq"]
+    w = bf16_round(synth.init_params(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], seed=0))
+    ids = synth.zipf_ids(10, T, cfg["vocab"]).reshape(1, T)
+    tgt = shifted_targets(ids)
+    res = {}
+    for dt in ("f32", "bf16"):
+        m = make(cfg, 1, w, dtype=dt, optimizer="sgd", decode_batch=0, init=False)
+        loss, _, valid, _, finite = m.train_step_ids(ids, tgt, lr=0.0, no_update=True)
+        assert finite and valid == T - 1
+        res[dt] = (loss, split_params(m.flat_grads(), cfg))
+        m.free()
+    assert abs(res["bf16"][0] - res["f32"][0]) < MIXED_LOSS_TOL * res["f32"][0]
+    worst = max((l2_err(res["bf16"][1][n], res["f32"][1][n]), n) for n in res["f32"][1])
+    assert worst[0] < MIXED_GRAD_TOL, worst
