@@ -67,6 +67,11 @@ struct luaTL_lm_s {
     // sampling of the generation loop (temperature <= 0: greedy); captured decode graphs are specific to these values
     struct Sampling { float temperature = 0.0f; int top_k = 0; float top_p = 0.0f; uint64_t seed = 0; int stop_id = -1; } samp;
     int32_t* d_done = nullptr;   // per sequence: the stop token has been emitted
+    // data-parallel gradient exchange overlapped with the backward: a layer's slice of the flat gradient is reduced
+    // on its own stream as soon as that layer's backward has finished
+    cudaStream_t comm_s = nullptr;
+    cudaEvent_t ev_grad = nullptr, ev_comm = nullptr;
+    int overlap_comm = 1;        // LUATL_OVERLAP_COMM=0: one all-reduce after the backward
     int attn_tc = 1;             // tensor-core attention where the shape allows (LUATL_ATTN_TC=0 turns it off)
     // mixed-precision backward scratch (bf16): activation gradients
     bf16 *b_dres = nullptr, *b_dhs = nullptr, *b_dh13 = nullptr, *b_dattn = nullptr, *b_dqkv = nullptr, *b_dl = nullptr;
@@ -443,7 +448,21 @@ int dx_gemm(LM* m, const bf16* dY, int n_out, const bf16* Wt, int n_in, void* dX
     return ltl_gemm_tc(dY, Wt, dX, nullptr, R, n_in, n_out, dx_dt, 0, 0, 1, m->s);
 }
 
-int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T, bool dl_in_bf16)
+// Queues an all-reduce of G[off, off + count) on the communication stream, after everything queued so far on the
+// compute stream (the kernels that produced that slice).
+int reduce_slice(LM* m, int64_t off, int64_t count)
+{
+    if (!m->comm_s) {
+        LTL_CUDA("comm stream", cudaStreamCreateWithFlags(&m->comm_s, cudaStreamNonBlocking));
+        LTL_CUDA("comm event", cudaEventCreateWithFlags(&m->ev_grad, cudaEventDisableTiming));
+        LTL_CUDA("comm event", cudaEventCreateWithFlags(&m->ev_comm, cudaEventDisableTiming));
+    }
+    LTL_CUDA("comm record", cudaEventRecord(m->ev_grad, m->s));
+    LTL_CUDA("comm wait", cudaStreamWaitEvent(m->comm_s, m->ev_grad, 0));
+    return ltl_comm_allreduce(m->G + off, (uint64_t)count, m->comm_s);
+}
+
+int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T, bool dl_in_bf16, bool overlap_allreduce)
 {
     const int D = m->D, F = m->F, V = m->V, L = m->L, H = m->H, hd = m->hd;
     const int rows = nseq * T;
@@ -462,6 +481,7 @@ int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T, bool dl_in
     LTL_TRY(ltl_rmsnorm_bwd(a.res + (size_t)L * RD, W + m->off_lnf, m->dhf, m->dres, G + m->off_lnf, rows, D,
                             m->c.eps, LTL_F32, m->ws, m->s));
     m->launches += 2;
+    if (overlap_allreduce) LTL_TRY(reduce_slice(m, m->off_lnf, m->np - m->off_lnf));      // lnf (and an untied head): final
     for (int l = L - 1; l >= 0; --l) {
         const LayerOff& o = m->lo[l];
         const float* xin = a.res + (size_t)l * RD;
@@ -514,9 +534,21 @@ int backward_tc(LM* m, Act& a, const int32_t* d_ids, int nseq, int T, bool dl_in
             if (l > 0) LTL_TRY(ltl_cast(m->dres, LTL_F32, m->b_dres, LTL_BF16, (uint64_t)rows * D, m->s));
         }
         m->launches += 10;
+        if (overlap_allreduce) {                         // this layer's slice [ln1 .. end of w2] is final
+            const int64_t end = l + 1 < L ? m->lo[l + 1].ln1 : m->off_lnf;
+            LTL_TRY(reduce_slice(m, o.ln1, end - o.ln1));
+        }
     }
     LTL_TRY(ltl_embed_bwd(d_ids, m->dres, G + m->off_emb, rows, D, V, 1.0f, LTL_F32, m->s));
     m->launches++;
+    if (overlap_allreduce) {
+        // the embedding (it also holds the tied head's gradient) and the loss / accuracy tail come last; the compute
+        // stream then waits for the communication stream before the optimizer reads G
+        LTL_TRY(reduce_slice(m, m->off_emb, m->lo[0].ln1 - m->off_emb));
+        LTL_TRY(reduce_slice(m, m->np, 2));
+        LTL_CUDA("comm record", cudaEventRecord(m->ev_comm, m->comm_s));
+        LTL_CUDA("comm wait", cudaStreamWaitEvent(m->s, m->ev_comm, 0));
+    }
     return LTL_OK;
 }
 
@@ -541,7 +573,8 @@ int ensure_train(LM* m)
 }
 
 // tail of G: [np] loss accumulator, [np+1] correct count, [np+2] grad norm^2, [np+3] spare
-int loss_and_grad(LM* m, const int32_t* d_ids, const int32_t* d_tgt, int valid_global, int want_grad, int accumulate = 0)
+int loss_and_grad(LM* m, const int32_t* d_ids, const int32_t* d_tgt, int valid_global, int want_grad, int accumulate = 0,
+                  bool overlap_allreduce = false)
 {
     const int rows = m->B * m->T;
     Act& a = m->train;
@@ -562,7 +595,7 @@ int loss_and_grad(LM* m, const int32_t* d_ids, const int32_t* d_tgt, int valid_g
     m->launches += 4;
     if (want_grad && m->adt == LTL_BF16) {
         LTL_TRY(alloc_backward_tc(m));
-        LTL_TRY(backward_tc(m, a, d_ids, m->B, m->T, dl_bf16));
+        LTL_TRY(backward_tc(m, a, d_ids, m->B, m->T, dl_bf16, overlap_allreduce));
     } else if (want_grad) {
         LTL_TRY(alloc_backward(m));
         LTL_TRY(backward(m, a, d_ids, m->B, m->T));
@@ -606,8 +639,12 @@ int train_step_dev(LM* m, const int32_t* d_ids, const int32_t* d_tgt, const luaT
     const int valid = a->valid_global > 0 ? a->valid_global : valid_local;
     m->launches = 0;
     LTL_CUDA("event", cudaEventRecord(m->ev[0], m->s));
-    LTL_TRY(loss_and_grad(m, d_ids, d_tgt, valid, 1, a->accumulate));
-    if (world > 1 && !a->skip_allreduce) LTL_TRY(ltl_comm_allreduce(m->G, (uint64_t)m->np + 2, m->s));
+    // Mixed-precision models exchange the gradient slice by slice under the backward of the step's last micro-batch
+    // (a layer's slice is final once that backward has passed the layer).
+    const bool exchange = world > 1 && !a->skip_allreduce;
+    const bool overlap = exchange && m->adt == LTL_BF16 && m->overlap_comm;
+    LTL_TRY(loss_and_grad(m, d_ids, d_tgt, valid, 1, a->accumulate, overlap));
+    if (exchange && !overlap) LTL_TRY(ltl_comm_allreduce(m->G, (uint64_t)m->np + 2, m->s));
     float tail[4] = { 0, 0, 0, 0 };
     LTL_CUDA("loss download", cudaMemcpyAsync(tail, m->G + m->np, 8, cudaMemcpyDeviceToHost, m->s));
     LTL_CUDA("loss sync", cudaStreamSynchronize(m->s));
@@ -958,6 +995,8 @@ luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
         m->use_pdl = !(p && p[0] == '0');
         const char* at = getenv("LUATL_ATTN_TC");
         m->attn_tc = !(at && at[0] == '0');
+        const char* oc = getenv("LUATL_OVERLAP_COMM");
+        m->overlap_comm = !(oc && oc[0] == '0');
     }
     layout_params(m);
     int rc = LTL_OK;
@@ -988,6 +1027,9 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
                      m->Wm, m->d_done, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
     for (void* p : ptrs) if (p) cudaFree(p);
     for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
+    if (m->ev_grad) cudaEventDestroy(m->ev_grad);
+    if (m->ev_comm) cudaEventDestroy(m->ev_comm);
+    if (m->comm_s) cudaStreamDestroy(m->comm_s);
     cudaGetLastError();
     delete m;
 }
