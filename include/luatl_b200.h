@@ -229,6 +229,11 @@ int luaTL_attention_bwd(const void* qkv, const void* out, const void* dout, cons
  * token-major matrices (both tensor-core operands MN-major, nothing is transposed in memory).  M, N multiples
  * of 8.  ksplit: slices of K added with atomics (0/1 = one). */
 int luaTL_gemm_bf16_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K, int ksplit);
+/* New: few-row GEMM of the decode step (mma.sync, weights read straight into fragments): C = A[M,K] B[N,K]^T for
+ * 1 <= M <= 64 and K a multiple of 32, bf16 operands, fp32 accumulate.  c_dtype 0 (f32) or 2 (bf16); epilogue 1 =
+ * SwiGLU over interleaved (gate, up) rows of B, C [M, N/2] bf16; ksplit > 1: C receives ksplit fp32 partial
+ * matrices [ksplit][M][N].  The product of the reference's matmul op (cuda/luaTL_core.cu:1506) on a transposed weight. */
+int luaTL_gemm_bf16_rows(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int epilogue, int ksplit);
 /* New: device-side timing of immediate ops.  luaTL_set_deferred(1) makes the immediate entry points return
  * without waiting for the stream (errors of queued kernels then surface at the next luaTL_sync / luaTL_timer_stop);
  * luaTL_timer_start / luaTL_timer_stop bracket a stretch of the library stream with CUDA events and return the

@@ -643,6 +643,10 @@ int luaTL_gemm_bf16_tc_xty(const void* X, const void* Y, float* C, int M, int N,
     LTL_TRY(sync_stream("gemm_bf16_tc_xty"));
     return ltl_gemm_tc_check(g_stream);
 }
+int luaTL_gemm_bf16_rows(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int epilogue, int ksplit)
+{
+    ONE_SHOT("gemm_bf16_rows", ltl_gemm_rows(A, B, C, M, N, K, c_dtype, epilogue, ksplit, g_stream));
+}
 int luaTL_gemm_bf16_tc_time(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int tile_n,
                             int iters, float* ms_per_launch)
 {

@@ -165,6 +165,13 @@ __device__ __forceinline__ float block_max(float v, float* red)
     return warp_max(t);
 }
 
+// Two floats rounded to bf16, the first in the low half (the lower address).
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&t);
+}
+
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float silu_grad_f(float x)
 {

@@ -99,7 +99,7 @@ struct luaTL_lm_s {
     float prefill_ms = 0, decode_ms = 0;
     int64_t launches = 0;
     int adam_alloc = 0;
-    int use_tc = 1, fuse_swiglu = 0, use_pdl = 1;
+    int use_tc = 1, fuse_swiglu = 0, use_pdl = 1, rows_gemm = 1;
 };
 
 namespace {
@@ -721,8 +721,11 @@ int ensure_decode(LM* m, int nseq, int n_prompt, int n_new)
         LTL_TRY(alloc_act(m, m->dec, m->nseq_cap, 0, m->nseq_cap));
         int sp = m->c.kv_splits;
         if (sp <= 0) {
-            const int ctas = m->nseq_cap * m->H;
-            sp = (2 * ltl_sm_count() + ctas - 1) / ctas;
+            // One CTA per (sequence, head) once that gives every SM one: a second slice would add the combine
+            // launch to every layer of a step that is bound by launch latency.  Fewer: slice the cache to two CTAs per SM.
+            const int ctas = m->nseq_cap * m->H, sms = ltl_sm_count();
+            const char* e = getenv("LUATL_KV_SPLITS");
+            sp = e ? atoi(e) : (ctas >= sms ? 1 : (2 * sms + ctas - 1) / ctas);
             if (sp > 16) sp = 16;
             if (sp < 1) sp = 1;
         }
@@ -774,11 +777,26 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
     const size_t cl = (size_t)m->nseq_cap * H * m->T * hd * e;
     const size_t cslot = (size_t)slot0 * H * m->T * hd * e;
     // Every kernel of the step is launched with programmatic stream serialization: each calls
-    // griddepcontrol.wait before touching its inputs, so only launch latency and prologues overlap.
+    // griddepcontrol.wait before touching anything a kernel of the step writes, so only launch latency and
+    // prologues overlap (the few-row GEMM also reads its weights ahead of the wait: no kernel of the step writes them).
     struct PdlScope { bool prev; PdlScope(bool on) : prev(ltl_pdl_enabled()) { ltl_pdl_set(on); } ~PdlScope() { ltl_pdl_set(prev); } } pdl(m->use_pdl);
     int bn_o, s_o, bn_d, s_d;
     ltl_gemm_tc_plan_split(nseq, D, D, &bn_o, &s_o);
     ltl_gemm_tc_plan_split(nseq, D, F, &bn_d, &s_d);
+    // Up to 32 sequences the step uses the few-row mma.sync kernel (weights prefetched ahead of the dependency wait):
+    // a 128-row tcgen05 tile would be at most a quarter full and every GEMM is bound by the latency of its launch.
+    // Measured per pass of 512 steps: 8 sequences 126 -> 103 ms, 16: 130 -> 112 ms, 32: 134 -> 131 ms; at 64 the
+    // tcgen05 tiles win (152 vs 176 ms: four row tiles per warp and a 64 KB activation stage per CTA).
+    const bool rows = m->rows_gemm && nseq <= 32 && ltl_gemm_rows_supported(a.h1, m->Wb, nseq, D, D, 1) &&
+                      ltl_gemm_rows_supported(a.hs, m->Wb, nseq, D, F, 8);
+    if (rows) {
+        s_o = ltl_gemm_rows_plan_split(D, D, 8);
+        s_d = ltl_gemm_rows_plan_split(D, F, 8);
+    }
+    auto gemm = [&](const void* A, const bf16* Wt, void* C, int N, int K, int c_dt, int bn, int epi, int ks) -> int {
+        if (rows) return ltl_gemm_rows(A, Wt, C, nseq, N, K, c_dt, epi, ks, m->s);
+        return ltl_gemm_tc(A, Wt, C, nullptr, nseq, N, K, c_dt, bn, epi, ks, m->s);
+    };
     LTL_TRY(ltl_lm_embed_rmsnorm(d_tok, m->Wb + m->off_emb, LTL_BF16, x, m->W + m->lo[0].ln1, a.h1, LTL_BF16, nseq, D, V,
                                  m->c.eps, m->s));
     m->launches++;
@@ -786,19 +804,19 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
         const LayerOff& o = m->lo[l];
         void* kcl = (char*)m->kc + l * cl + cslot;
         void* vcl = (char*)m->vc + l * cl + cslot;
-        LTL_TRY(ltl_gemm_tc(a.h1, m->Wb + o.wqkv, a.qkv, nullptr, nseq, 3 * D, D, LTL_BF16, 0, 0, 1, m->s));
+        LTL_TRY(gemm(a.h1, m->Wb + o.wqkv, a.qkv, 3 * D, D, LTL_BF16, 0, 0, 1));
         LTL_TRY(ltl_decode_attn(a.qkv, kcl, vcl, a.attn, pos, nseq, H, hd, m->T, m->scale, LTL_BF16, m->splits, m->ws,
                                 m->rope_tab, m->c.rope_interleaved, m->c.use_rope, m->d_err, m->s));
-        LTL_TRY(ltl_gemm_tc(a.attn, m->Wb + o.wo, m->part, nullptr, nseq, D, D, LTL_F32, bn_o, 0, s_o, m->s));
+        LTL_TRY(gemm(a.attn, m->Wb + o.wo, m->part, D, D, LTL_F32, bn_o, 0, s_o));
         LTL_TRY(ltl_lm_residual_rmsnorm(x, m->part, s_o, m->W + o.ln2, a.h2, LTL_BF16, nseq, D, m->c.eps, m->s));
-        LTL_TRY(ltl_gemm_tc(a.h2, m->Wb + o.w13, a.hs, nullptr, nseq, 2 * F, D, LTL_BF16, 0, 1, 1, m->s));
-        LTL_TRY(ltl_gemm_tc(a.hs, m->Wb + o.w2, m->part, nullptr, nseq, D, F, LTL_F32, bn_d, 0, s_d, m->s));
+        LTL_TRY(gemm(a.h2, m->Wb + o.w13, a.hs, 2 * F, D, LTL_BF16, 0, 1, 1));
+        LTL_TRY(gemm(a.hs, m->Wb + o.w2, m->part, D, F, LTL_F32, bn_d, 0, s_d));
         const bool last = l + 1 == L;
         LTL_TRY(ltl_lm_residual_rmsnorm(x, m->part, s_d, m->W + (last ? m->off_lnf : m->lo[l + 1].ln1),
                                         last ? a.hf : a.h1, LTL_BF16, nseq, D, m->c.eps, m->s));
         m->launches += 7 + (m->splits > 1 ? 1 : 0);
     }
-    LTL_TRY(ltl_gemm_tc(a.hf, m->Wb + (m->c.tie ? m->off_emb : m->off_head), a.logits, nullptr, nseq, V, D, LTL_F32, 0, 0, 1, m->s));
+    LTL_TRY(gemm(a.hf, m->Wb + (m->c.tie ? m->off_emb : m->off_head), a.logits, V, D, LTL_F32, 0, 0, 1));
     m->launches++;
     if (pick) {
         LTL_TRY(pick_next(m, a.logits, nseq, slot0, d_out, out_stride, hist, hist_stride, hist_base, m->s));
@@ -995,6 +1013,8 @@ luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
         m->use_pdl = !(p && p[0] == '0');
         const char* at = getenv("LUATL_ATTN_TC");
         m->attn_tc = !(at && at[0] == '0');
+        const char* rg = getenv("LUATL_DECODE_ROWS_GEMM");          // 0: tcgen05 tiles at every batch size (A/B comparison)
+        m->rows_gemm = !(rg && rg[0] == '0');
         const char* oc = getenv("LUATL_OVERLAP_COMM");
         m->overlap_comm = !(oc && oc[0] == '0');
     }

@@ -86,12 +86,6 @@ int ltl_lm_rmsnorm(const float* x, const float* gain, void* out, int out_dtype, 
 }
 
 
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
-{
-    const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&t);
-}
-
 // Consumer of the split-K GEMMs: x += partial[0] + partial[1] + ... (fixed order, so the result
 // does not depend on scheduling), then RMSNorm of the updated row.  One warp per row.
 template <typename TO>

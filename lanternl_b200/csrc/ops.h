@@ -135,6 +135,10 @@ void ltl_gemm_tc_plan_split(int M, int N, int K, int* bn, int* ksplit);
 int ltl_gemm_tc_check(cudaStream_t s);
 int ltl_gemm_tc_plan_accum(int M, int N, int K, int bn);
 int ltl_gemm_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K, int ksplit, cudaStream_t s);
+// Few-row GEMM (gemm_rows.cu, mma.sync): 1 <= M <= 64, K a multiple of 32; same epi / ksplit meaning as above.
+bool ltl_gemm_rows_supported(const void* A, const void* B, int M, int N, int K, int ksplit);
+int ltl_gemm_rows_plan_split(int N, int K, int max_parts);
+int ltl_gemm_rows(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int epi, int ksplit, cudaStream_t s);
 // CUtensorMap (128 bytes, written to out_map) of a bf16 matrix [rows, cols] with rows `pitch` elements apart:
 // boxes of box_rows x 64 columns, 128-byte swizzle.  Cached per (base, shape).
 int ltl_tensor_map_bf16(const void* base, int rows, int cols, long long pitch, int box_rows, void* out_map);

@@ -236,7 +236,13 @@ def assert_tokens_consistent(o, w, prompts, got, tol):
     return near
 
 
-def test_bf16_decode_small_model_logits_and_tokens():
+# Decode GEMMs: "1" = the few-row mma.sync kernel (up to 64 sequences), "0" = tcgen05 tiles at every batch size.
+ROWS_GEMM = pytest.mark.parametrize("rows_gemm", ["1", "0"])
+
+
+@ROWS_GEMM
+def test_bf16_decode_small_model_logits_and_tokens(rows_gemm, monkeypatch):
+    monkeypatch.setenv("LUATL_DECODE_ROWS_GEMM", rows_gemm)
     cfg = dict(vocab=512, dim=128, layers=2, heads=2, ffn=192, max_seq=96)
     w = bf16_round(params_for(cfg, seed=0, std=0.05))                 # the weights ARE bf16 values
     nseq, npr, n_new = 6, 16, 64
@@ -253,10 +259,12 @@ def test_bf16_decode_small_model_logits_and_tokens():
     assert near <= 2
 
 
-def test_config2_shapes_bf16_prefill_and_decode_agree_with_single_steps():
+@ROWS_GEMM
+def test_config2_shapes_bf16_prefill_and_decode_agree_with_single_steps(rows_gemm, monkeypatch):
     """Configuration 2 architecture (bf16, head_dim 64, ffn 1408), reduced batch: the batched
     prefill + graph-replayed decode must produce the tokens the one-token-at-a-time path gives,
     and its first logits must match the oracle within the bf16 tolerance."""
+    monkeypatch.setenv("LUATL_DECODE_ROWS_GEMM", rows_gemm)
     cfg = dict(CFG2, max_seq=160, layers=2)
     w = bf16_round(params_for(cfg, seed=0))
     nseq, npr, n_new = 4, 128, 24
