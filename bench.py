@@ -527,8 +527,10 @@ def run_sweep(args, dist):
         rows_out.append(e)
 
     it = args.sweep_iters
+    only = set(args.sweep_only.split(",")) if args.sweep_only else None
+    want = lambda k: only is None or k in only             # noqa: E731
     # GEMMs: fp32 on the CUDA cores (exact path), bf16 on the tensor cores (B stored [N, K])
-    for M in (1, 32, 256, 4096):
+    for M in ((1, 32, 256, 4096) if want("gemm") else ()):
         for N in (512, 1408, 8000):
             for K in (512, 1408):
                 A, B, Cc = dev(M, K, _lib.F32), dev(K, N, _lib.F32), ad.TensorView(M, N, _lib.F32)
@@ -541,7 +543,7 @@ def run_sweep(args, dist):
                 for t in (A, B, Cc, Ab, Bb, Cb):
                     t.free()
     for dt, e in ((_lib.F32, 4), (_lib.BF16, 2)):
-        for cols in (128, 512, 2048):
+        for cols in ((128, 512, 2048) if want("row") else ()):
             rows = 65536
             x, y, g = dev(rows, cols, dt), ad.TensorView(rows, cols, dt), dev(1, cols, dt)
             us = timed(lambda: _lib.call("luaTL_rmsnorm", x.data, g.data, y.data, rows, cols, 1e-5, dt), it)
@@ -550,31 +552,34 @@ def run_sweep(args, dist):
             record("softmax", f"{rows}x{cols}", dt, us, nbytes=2.0 * rows * cols * e)
             for t in (x, y, g):
                 t.free()
-        Bq, Hq, Tq, Dq = 64, 16, 1024, 64
-        x = dev(Bq * Tq, Hq * Dq, dt)
-        pos = ad.ids(Bq * Tq)
-        ad.upload_i32(pos, np.tile(np.arange(Tq, dtype=np.int32), Bq))
-        us = timed(lambda: _lib.call("luaTL_rope", x.data, pos.t.data, Bq * Tq, Hq, Dq, Hq * Dq, 0, 10000.0, 0, 0, dt), it)
-        record("rope", f"[{Bq},{Hq},{Tq},{Dq}]", dt, us, nbytes=2.0 * Bq * Tq * Hq * Dq * e)
-        x.free()
-        rows, F = 65536, 5632
-        a, b, o = dev(rows, F, dt), dev(rows, F, dt), ad.TensorView(rows, F, dt)
-        us = timed(lambda: _lib.call("luaTL_swiglu_fwd", a.data, b.data, o.data, rows, F, F, F, F, dt), it)
-        record("swiglu", f"{rows}x{F}", dt, us, nbytes=3.0 * rows * F * e)
-        for t in (a, b, o):
-            t.free()
-    rows, V = 16384, 32000
-    lg, dl = dev(rows, V, _lib.F32), ad.TensorView(rows, V, _lib.F32)
-    tg = ad.ids(rows)
-    ad.upload_i32(tg, synth.zipf_ids(3, rows, V))
-    losses = ad.TensorView(rows, 1, _lib.F32)
-    us = timed(lambda: _lib.call("luaTL_cross_entropy", lg.data, tg.t.data, losses.data, None, rows, V, -1, 1.0, _lib.F32), max(2, it // 4))
-    record("cross_entropy fwd", f"{rows}x{V}", _lib.F32, us, nbytes=4.0 * rows * V)
-    us = timed(lambda: _lib.call("luaTL_cross_entropy", lg.data, tg.t.data, losses.data, dl.data, rows, V, -1, 1.0, _lib.F32), max(2, it // 4))
-    record("cross_entropy fwd+bwd", f"{rows}x{V}", _lib.F32, us, nbytes=8.0 * rows * V)
+        if want("rope"):
+            Bq, Hq, Tq, Dq = 64, 16, 1024, 64
+            x = dev(Bq * Tq, Hq * Dq, dt)
+            pos = ad.ids(Bq * Tq)
+            ad.upload_i32(pos, np.tile(np.arange(Tq, dtype=np.int32), Bq))
+            us = timed(lambda: _lib.call("luaTL_rope", x.data, pos.t.data, Bq * Tq, Hq, Dq, Hq * Dq, 0, 10000.0, 0, 0, dt), it)
+            record("rope", f"[{Bq},{Hq},{Tq},{Dq}]", dt, us, nbytes=2.0 * Bq * Tq * Hq * Dq * e)
+            x.free()
+        if want("swiglu"):
+            rows, F = 65536, 5632
+            a, b, o = dev(rows, F, dt), dev(rows, F, dt), ad.TensorView(rows, F, dt)
+            us = timed(lambda: _lib.call("luaTL_swiglu_fwd", a.data, b.data, o.data, rows, F, F, F, F, dt), it)
+            record("swiglu", f"{rows}x{F}", dt, us, nbytes=3.0 * rows * F * e)
+            for t in (a, b, o):
+                t.free()
+    if want("ce"):
+        rows, V = 16384, 32000
+        lg, dl = dev(rows, V, _lib.F32), ad.TensorView(rows, V, _lib.F32)
+        tg = ad.ids(rows)
+        ad.upload_i32(tg, synth.zipf_ids(3, rows, V))
+        losses = ad.TensorView(rows, 1, _lib.F32)
+        us = timed(lambda: _lib.call("luaTL_cross_entropy", lg.data, tg.t.data, losses.data, None, rows, V, -1, 1.0, _lib.F32), max(2, it // 4))
+        record("cross_entropy fwd", f"{rows}x{V}", _lib.F32, us, nbytes=4.0 * rows * V)
+        us = timed(lambda: _lib.call("luaTL_cross_entropy", lg.data, tg.t.data, losses.data, dl.data, rows, V, -1, 1.0, _lib.F32), max(2, it // 4))
+        record("cross_entropy fwd+bwd", f"{rows}x{V}", _lib.F32, us, nbytes=8.0 * rows * V)
     hb = [r["hbm_frac"] for r in rows_out if r["kernel"] not in ("gemm_simt", "gemm_tc") and "hbm_frac" in r]
-    geo = float(np.exp(np.mean(np.log(hb))))
-    best_tc = max(r["tensor_frac"] for r in rows_out if r["kernel"] == "gemm_tc")
+    geo = float(np.exp(np.mean(np.log(hb)))) if hb else 0.0
+    best_tc = max([r["tensor_frac"] for r in rows_out if r["kernel"] == "gemm_tc"], default=None)
     return dict(
         metric="sweep_hbm_fraction_geomean", value=geo, unit="fraction of measured HBM copy bandwidth", n_gpus=1,
         steps=args.sweep_iters, warmup=1, ms_per_step=sum(r["us"] for r in rows_out) * 1e-3, higher_is_better=True,
@@ -687,6 +692,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "train", "train4", "sweep"])
     ap.add_argument("--sweep-iters", type=int, default=20, help="sweep: launches per timed kernel")
+    ap.add_argument("--sweep-only", default="", help="sweep: comma list of gemm,row,rope,swiglu,ce (profiling aid; the metric runs all)")
     ap.add_argument("--micro-batch", type=int, default=8, help="train4: sequences per micro-batch")
     ap.add_argument("--global-batch", type=int, default=TRAIN4_GLOBAL_BATCH, help="train4: sequences per optimizer step over all GPUs")
     ap.add_argument("--layers", type=int, default=0, help="train4: layer count override (profiling aid; the metric uses 16)")

@@ -60,8 +60,11 @@ template <int BN> size_t smem_bytes(int stages) { return stages * stage_bytes<BN
 template <int BN, typename TC, int EPI, int MAJ = 0>
 __global__ void __launch_bounds__(192, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               TC* C, const TC* R, int M, int N, int K, int STAGES, int* __restrict__ err)
+               TC* C, const TC* R, int M, int N, int K, int STAGES, int b_early, int* __restrict__ err)
 {
+    // b_early: B holds weights that no kernel of the surrounding programmatic-launch chain writes (the decode
+    // step), so the first ring of B tiles is requested before griddepcontrol.wait and lands under the tail of
+    // the predecessor; only the A tiles wait for it.
     // gridDim.z > 1: split-K.  Slice z covers a contiguous range of k-blocks and writes its partial
     // sums to C + z * M * N (the consumer adds the slices in a fixed order).
     extern __shared__ uint8_t smem_raw[];
@@ -94,6 +97,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = sm.tmem_base;
     bool ok = true;
+    int npre = 0;                                         // stages whose B tile is already on its way
+    if (MAJ == 0 && b_early && warp == 0 && lane == 0) {
+        npre = min(STAGES, kblocks);
+        for (int s = 0; s < npre; ++s) {
+            mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+            tma_load_2d(b_tile(s), &map_b, (kb0 + s) * BK, n0, &sm.full[s]);
+        }
+    }
     pdl_trigger();          // the next kernel may set itself up
     pdl_wait();             // barriers and TMEM are ready; now the predecessor's output may be read
 
@@ -103,6 +114,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t round = 0;                               // kb / STAGES, kept without a division
         for (int kb = 0; kb < kblocks && ok; ++kb, ++s) {
             if (s == STAGES) { s = 0; ++round; }
+            if (MAJ == 0 && kb < npre) {                  // first ring: expect_tx and the B tile were issued above
+                tma_load_2d(a_tile(s), &map_a, (kb0 + kb) * BK, m0, &sm.full[s]);
+                continue;
+            }
             if (round > 0) ok = mbar_wait(&sm.empty[s], (round - 1) & 1);
             if (!ok) break;
             mbar_expect_tx(&sm.full[s], STAGE_BYTES);
@@ -459,6 +474,12 @@ int persist_mode()
     return mode;
 }
 bool persist_enabled() { return persist_mode() >= 1; }
+// LUATL_GEMM_B_EARLY=0: weights of a decode-step GEMM wait for the predecessor like the activations (A/B comparison).
+bool b_early_enabled()
+{
+    static const bool on = [] { const char* e = getenv("LUATL_GEMM_B_EARLY"); return !(e && e[0] == '0'); }();
+    return on;
+}
 
 template <typename TC, int MAJ>
 int launch_persist(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const void* R, int M, int N, int K, int ksplit, cudaStream_t s)
@@ -503,7 +524,8 @@ int launch(const void* A, const void* B, void* C, const void* R, int M, int N, i
         attr_set = true;
     }
     LTL_CUDA("gemm_tc launch", ltl_launch(gemm_tc_kernel<BN, TC, EPI>, grid, dim3(192), smem, s, ltl_pdl_enabled(),
-                                          ma, mb, (TC*)C, (const TC*)R, M, N, K, stages, g_err_flag));
+                                          ma, mb, (TC*)C, (const TC*)R, M, N, K, stages, b_early_enabled() && ltl_pdl_enabled() ? 1 : 0,
+                                          g_err_flag));
     return ltl_check_launch("gemm_tc");
 }
 
@@ -529,7 +551,7 @@ int launch_mn(const void* X, const void* Y, float* C, int M, int N, int K, int k
                                                       (int)smem_bytes<BN>(BN == 256 ? 2 : 4)));
         attr_set = true;
     }
-    gemm_tc_kernel<BN, float, EPI_ATOMIC, 1><<<grid, 192, smem, s>>>(ma, mb, C, nullptr, M, N, K, stages, g_err_flag);
+    gemm_tc_kernel<BN, float, EPI_ATOMIC, 1><<<grid, 192, smem, s>>>(ma, mb, C, nullptr, M, N, K, stages, 0, g_err_flag);
     return ltl_check_launch("gemm_tc_mn");
 }
 

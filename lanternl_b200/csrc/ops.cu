@@ -444,6 +444,64 @@ softmax_warp_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __re
     }
 }
 
+// Wide rows (more than four 16-byte packets per lane of a warp): one CTA of TH threads per row, PT packets per
+// thread (two, so that a thread has 32 bytes in flight).  The warp-per-row form keeps 64 values per lane in registers there, which leaves 16 warps per SM and
+// the loads of a row exposed (34 % of DRAM throughput at 2048 columns); this form runs at full occupancy.
+template <typename T, int PT, int TH>
+__global__ void __launch_bounds__(TH)
+softmax_cta_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __restrict__ out,
+                   int rows, int cols, float scale, int causal, int group, int mask_offset)
+{
+    constexpr int N = Vec16<T>::N;
+    __shared__ float red[33];
+    const int row = blockIdx.x;
+    const int lrow = group > 0 ? row % group : row;
+    const int limit = causal ? lrow + mask_offset : cols - 1;
+    const T* xr = x + (size_t)row * cols;
+    float v[PT][N];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < PT; ++c) {
+        const int e = (c * TH + threadIdx.x) * N;
+        if (e < cols) {
+            ld16<T>(xr + e, v[c]);
+            float b[N];
+            if (bias) ld16<T>(bias + e, b);
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                v[c][i] = (e + i <= limit) ? v[c][i] * scale + (bias ? b[i] : 0.0f) : -INFINITY;
+                mx = fmaxf(mx, v[c][i]);
+            }
+        }
+    }
+    mx = block_max(mx, red);
+    const float base = (mx == -INFINITY) ? 0.0f : mx;
+    float sum = 0.0f;
+#pragma unroll
+    for (int c = 0; c < PT; ++c) {
+        const int e = (c * TH + threadIdx.x) * N;
+        if (e < cols) {
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                v[c][i] = (e + i <= limit) ? __expf(v[c][i] - base) : 0.0f;
+                sum += v[c][i];
+            }
+        }
+    }
+    sum = block_sum(sum, red);
+    const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+    T* orow = out + (size_t)row * cols;
+#pragma unroll
+    for (int c = 0; c < PT; ++c) {
+        const int e = (c * TH + threadIdx.x) * N;
+        if (e < cols) {
+#pragma unroll
+            for (int i = 0; i < N; ++i) v[c][i] *= inv;
+            st16<T>(orow + e, v[c]);
+        }
+    }
+}
+
 template <typename T>
 __global__ void softmax_block_kernel(const T* __restrict__ x, const T* __restrict__ bias,
                                      T* __restrict__ out, int rows, int cols, float scale,
@@ -483,7 +541,11 @@ int ltl_softmax(const void* x, const void* bias, void* out, int rows, int cols, 
     const int ch = row_chunks(cols, ltl_dtype_size(dtype));
     const bool vec = ch && aligned16(x) && aligned16(out) && (!bias || aligned16(bias));
     DISPATCH_T(dtype, {
-        if (vec) {
+        if (vec && ch > 4) {
+            // ch packets per lane of a warp = 32 ch packets per row: two per thread of a 128- or 256-thread CTA
+            if (ch <= 8) softmax_cta_kernel<T, 2, 128><<<rows, 128, 0, s>>>((const T*)x, (const T*)bias, (T*)out, rows, cols, scale, causal, group, mask_offset);
+            else softmax_cta_kernel<T, 2, 256><<<rows, 256, 0, s>>>((const T*)x, (const T*)bias, (T*)out, rows, cols, scale, causal, group, mask_offset);
+        } else if (vec) {
             DISPATCH_CH(ch, softmax_warp_kernel<T, CH><<<(rows + ROW_WARPS - 1) / ROW_WARPS,
                 ROW_WARPS * 32, 0, s>>>((const T*)x, (const T*)bias, (T*)out, rows, cols, scale,
                                         causal, group, mask_offset));
@@ -758,6 +820,45 @@ __global__ void rope_kernel(T* __restrict__ x, const int32_t* __restrict__ pos_i
     }
 }
 
+// Half-split layout without a table: the angle depends on (position, pair) only, so one thread computes
+// the sines and cosines of Vec16<T>::N pairs once and rotates those pairs in every head of its row
+// (the per-element powf + sincosf made the per-head form bound by the SM, not by memory).
+template <typename T>
+__global__ void rope_heads_kernel(T* __restrict__ x, const int32_t* __restrict__ pos_ids, int rows,
+                                  int heads, int hd, int row_stride, int pos_offset, float theta, int inverse)
+{
+    constexpr int N = Vec16<T>::N;
+    const int pairs = hd >> 1;
+    const int ppr = pairs / N;                       // packets per row (of one head)
+    const uint64_t n = (uint64_t)rows * ppr;
+    for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+         idx += (uint64_t)gridDim.x * blockDim.x) {
+        const int p = (int)(idx % ppr) * N;
+        const int r = (int)(idx / ppr);
+        const int pos = pos_ids ? pos_ids[r] : r + pos_offset;
+        float c[N], sn[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            rope_angle(pos, p + i, hd, theta, nullptr, 0, c[i], sn[i]);
+            if (inverse) sn[i] = -sn[i];
+        }
+        T* xr = x + (size_t)r * row_stride + p;
+#pragma unroll 4
+        for (int hh = 0; hh < heads; ++hh) {
+            float x0[N], x1[N], y0[N], y1[N];
+            ld16<T>(xr + (size_t)hh * hd, x0);
+            ld16<T>(xr + (size_t)hh * hd + pairs, x1);
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                y0[i] = x0[i] * c[i] - x1[i] * sn[i];
+                y1[i] = x1[i] * c[i] + x0[i] * sn[i];
+            }
+            st16<T>(xr + (size_t)hh * hd, y0);
+            st16<T>(xr + (size_t)hh * hd + pairs, y1);
+        }
+    }
+}
+
 int ltl_rope(void* x, const int32_t* pos_ids, int rows, int heads, int head_dim, int row_stride,
              int pos_offset, float theta, int interleaved, int inverse, int dtype,
              const float2* cs_table, int table_rows, cudaStream_t s)
@@ -772,7 +873,9 @@ int ltl_rope(void* x, const int32_t* pos_ids, int rows, int heads, int head_dim,
     const bool vec = !interleaved && pairs % n == 0 && row_stride % n == 0 && aligned16(x);
     const uint64_t work = (uint64_t)rows * heads * (vec ? pairs / n : pairs);
     DISPATCH_T(dtype, {
-        if (vec) rope_kernel<T, true><<<grid1d(work, 256), 256, 0, s>>>((T*)x, pos_ids, rows, heads, head_dim, row_stride, pos_offset, theta, interleaved, inverse, cs_table, table_rows);
+        if (vec && !cs_table && heads >= 4 && (uint64_t)rows * (pairs / n) >= 4096)
+            rope_heads_kernel<T><<<grid1d((uint64_t)rows * (pairs / n), 128), 128, 0, s>>>((T*)x, pos_ids, rows, heads, head_dim, row_stride, pos_offset, theta, inverse);
+        else if (vec) rope_kernel<T, true><<<grid1d(work, 256), 256, 0, s>>>((T*)x, pos_ids, rows, heads, head_dim, row_stride, pos_offset, theta, interleaved, inverse, cs_table, table_rows);
         else rope_kernel<T, false><<<grid1d(work, 256), 256, 0, s>>>((T*)x, pos_ids, rows, heads, head_dim, row_stride, pos_offset, theta, interleaved, inverse, cs_table, table_rows);
     });
     return ltl_check_launch("rope");

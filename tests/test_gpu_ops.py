@@ -76,7 +76,9 @@ def test_batched_head_view_gemm():
 
 # [4] group-causal softmax and its backward ----------------------------------------------------
 @pytest.mark.parametrize("cols,dtype,tol", [(8, _lib.F32, 1e-6), (128, _lib.F32, 1e-6), (2048, _lib.F32, 1e-6),
-                                             (37, _lib.F32, 1e-6), (4096, _lib.F32, 1e-6), (128, _lib.BF16, 1e-2)])
+                                             (37, _lib.F32, 1e-6), (4096, _lib.F32, 1e-6), (128, _lib.BF16, 1e-2),
+                                             (1024, _lib.F32, 1e-6), (2048, _lib.BF16, 1e-2), (4096, _lib.BF16, 1e-2),
+                                             (1000, _lib.F32, 1e-6)])
 def test_softmax_group_causal(cols, dtype, tol):
     group, heads = min(cols, 16), 3
     rows = group * heads
@@ -221,6 +223,22 @@ def test_rope_with_position_ids_on_a_column_slice():
     for b in range(rows // T):
         ref = cpu_ref.rope(qkv[b * T:(b + 1) * T, D:2 * D], H, hd, pos0=0)
         assert np.abs(got[b * T:(b + 1) * T, D:2 * D] - ref).max() < 1e-5
+
+
+@pytest.mark.parametrize("dtype,tol", [(_lib.F32, 1e-5), (_lib.BF16, 3e-2)])
+def test_rope_many_rows_shares_the_angles_across_heads(dtype, tol):
+    """Large inputs take the kernel that computes each (position, pair) angle once for all heads."""
+    rows, H, hd, T = 2048, 4, 64, 32
+    x = rnd(24, rows, H * hd)
+    X, pos = dev(x, dtype), i32dev(np.arange(rows) % T)
+    _lib.call("luaTL_rope", X.t.data, pos.t.data, rows, H, hd, H * hd, 0, 10000.0, 0, 0, dtype)
+    got = host(X)
+    xin = bf16_round(x) if dtype == _lib.BF16 else x
+    for b in (0, 17, rows // T - 1):
+        ref = cpu_ref.rope(xin[b * T:(b + 1) * T], H, hd, pos0=0)
+        assert np.abs(got[b * T:(b + 1) * T] - ref).max() < tol
+    _lib.call("luaTL_rope", X.t.data, pos.t.data, rows, H, hd, H * hd, 0, 10000.0, 0, 1, dtype)
+    assert np.abs(host(X) - xin).max() < (1e-5 if dtype == _lib.F32 else 6e-2)
 
 
 def test_rope_rejects_odd_head_dim():
