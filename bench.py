@@ -540,6 +540,9 @@ def run_sweep(args, dist):
                 Ab, Bb, Cb = dev(M, K, _lib.BF16), dev(N, K, _lib.BF16), ad.TensorView(M, N, _lib.BF16)
                 us = timed(lambda: _lib.call("luaTL_gemm_bf16_tc", Ab.data, Bb.data, Cb.data, None, M, N, K, _lib.BF16, 0), it)
                 record("gemm_tc", f"{M}x{N}x{K}", _lib.BF16, us, nbytes=2.0 * (M * K + K * N + M * N), flops=2.0 * M * N * K)
+                if M <= 32:                                # the decode step's kernel for small shards
+                    us = timed(lambda: _lib.call("luaTL_gemm_bf16_rows", Ab.data, Bb.data, Cb.data, M, N, K, _lib.BF16, 0, 1), it)
+                    record("gemm_rows", f"{M}x{N}x{K}", _lib.BF16, us, nbytes=2.0 * (M * K + K * N + M * N), flops=2.0 * M * N * K)
                 for t in (A, B, Cc, Ab, Bb, Cb):
                     t.free()
     for dt, e in ((_lib.F32, 4), (_lib.BF16, 2)):
@@ -577,7 +580,7 @@ def run_sweep(args, dist):
         record("cross_entropy fwd", f"{rows}x{V}", _lib.F32, us, nbytes=4.0 * rows * V)
         us = timed(lambda: _lib.call("luaTL_cross_entropy", lg.data, tg.t.data, losses.data, dl.data, rows, V, -1, 1.0, _lib.F32), max(2, it // 4))
         record("cross_entropy fwd+bwd", f"{rows}x{V}", _lib.F32, us, nbytes=8.0 * rows * V)
-    hb = [r["hbm_frac"] for r in rows_out if r["kernel"] not in ("gemm_simt", "gemm_tc") and "hbm_frac" in r]
+    hb = [r["hbm_frac"] for r in rows_out if r["kernel"] not in ("gemm_simt", "gemm_tc", "gemm_rows") and "hbm_frac" in r]
     geo = float(np.exp(np.mean(np.log(hb)))) if hb else 0.0
     best_tc = max([r["tensor_frac"] for r in rows_out if r["kernel"] == "gemm_tc"], default=None)
     return dict(
