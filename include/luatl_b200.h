@@ -234,6 +234,17 @@ int luaTL_gemm_bf16_tc_xty(const void* X, const void* Y, float* C, int M, int N,
  * SwiGLU over interleaved (gate, up) rows of B, C [M, N/2] bf16; ksplit > 1: C receives ksplit fp32 partial
  * matrices [ksplit][M][N].  The product of the reference's matmul op (cuda/luaTL_core.cu:1506) on a transposed weight. */
 int luaTL_gemm_bf16_rows(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int epilogue, int ksplit);
+/* New: the two fused forms of the decode-step GEMMs (impl 0 = tcgen05 tiles, 1 = the few-row kernel).  The reference
+ * runs matmul, add and rmsnorm as three ops (ai/gpu/gpu_transformer.lua:354-372); these have no counterpart there.
+ *  resid: split-K product A[M,K] B[N,K]^T into `slices` [ksplit][M][N]; the CTA that finishes an output tile last adds
+ *    the slices in slice order and the residual, x[M,N] += product, and writes h = bf16(x * gain) and, per row, the
+ *    sum of x^2 over each 32-column tile to ssq [M][N/32].  N a multiple of 32.
+ *  rowscale: C = diag(s) A B^T with s_r = 1 / sqrt(sum_t ssq[r][t] / K + eps): the RMSNorm factor of the activation
+ *    that produced A (A holds x * gain), applied in the epilogue; epilogue / c_dtype as in luaTL_gemm_bf16_rows. */
+int luaTL_gemm_bf16_resid(const void* A, const void* B, float* slices, float* x, const float* gain, void* h, float* ssq,
+                          int M, int N, int K, int ksplit, int impl);
+int luaTL_gemm_bf16_rowscale(const void* A, const void* B, void* C, const float* ssq, int ssq_tiles, float eps, int M, int N,
+                             int K, int c_dtype, int epilogue, int impl);
 /* New: device-side timing of immediate ops.  luaTL_set_deferred(1) makes the immediate entry points return
  * without waiting for the stream (errors of queued kernels then surface at the next luaTL_sync / luaTL_timer_stop);
  * luaTL_timer_start / luaTL_timer_stop bracket a stretch of the library stream with CUDA events and return the

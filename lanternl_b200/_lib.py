@@ -137,6 +137,8 @@ SIGNATURES = {
     "luaTL_attention_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i]),
     "luaTL_gemm_bf16_tc_xty": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
     "luaTL_gemm_bf16_rows": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i]),
+    "luaTL_gemm_bf16_resid": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i]),
+    "luaTL_gemm_bf16_rowscale": (_i, [_vp, _vp, _vp, _vp, _i, _f, _i, _i, _i, _i, _i, _i]),
     "luaTL_set_deferred": (None, [_i]), "luaTL_timer_start": (_i, []), "luaTL_timer_stop": (_i, [C.POINTER(C.c_float)]),
     "luaTL_rmsnorm_bwd_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f]),
     "luaTL_sample_rows": (_i, [_vp, _i, _i, _f, _i, _f, _u64, _vp, _vp]),

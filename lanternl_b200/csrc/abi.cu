@@ -647,6 +647,46 @@ int luaTL_gemm_bf16_rows(const void* A, const void* B, void* C, int M, int N, in
 {
     ONE_SHOT("gemm_bf16_rows", ltl_gemm_rows(A, B, C, M, N, K, c_dtype, epilogue, ksplit, g_stream));
 }
+// Arrival counters of the fused residual GEMMs for the immediate entry point: one per output tile, zero at rest.
+static int* abi_tickets(size_t n)
+{
+    static int* buf = nullptr;
+    static size_t cap = 0;
+    if (n > cap) {
+        if (buf) cudaFree(buf);
+        buf = nullptr; cap = 0;
+        if (cudaMalloc(&buf, n * sizeof(int)) != cudaSuccess) return nullptr;
+        cudaMemset(buf, 0, n * sizeof(int));
+        cap = n;
+    }
+    return buf;
+}
+int luaTL_gemm_bf16_resid(const void* A, const void* B, float* slices, float* x, const float* gain, void* h, float* ssq,
+                          int M, int N, int K, int ksplit, int impl)
+{
+    LTL_TRY(ltl_require_init("gemm_bf16_resid"));
+    if (N <= 0 || M <= 0) return ltl_fail(LTL_ERR_SHAPE, "gemm_bf16_resid: bad shape %dx%d", M, N);
+    int* tickets = abi_tickets((size_t)((M + 127) / 128) * ((N + 31) / 32));
+    if (!tickets) return ltl_fail(LTL_ERR_OOM, "gemm_bf16_resid: tile tickets");
+    LtlGemmFuse f = {};
+    f.x = x; f.gain = gain; f.h = h; f.ssq_out = ssq; f.counters = tickets;
+    if (impl == 1) LTL_TRY(ltl_gemm_rows(A, B, slices, M, N, K, LTL_F32, 3, ksplit < 1 ? 1 : ksplit, g_stream, &f));
+    else LTL_TRY(ltl_gemm_tc(A, B, slices, nullptr, M, N, K, LTL_F32, 32, 3, ksplit < 1 ? 1 : ksplit, g_stream, &f));
+    LTL_TRY(sync_stream("gemm_bf16_resid"));
+    return impl == 1 ? LTL_OK : ltl_gemm_tc_check(g_stream);
+}
+int luaTL_gemm_bf16_rowscale(const void* A, const void* B, void* C, const float* ssq, int ssq_tiles, float eps, int M, int N, int K,
+                             int c_dtype, int epilogue, int impl)
+{
+    LTL_TRY(ltl_require_init("gemm_bf16_rowscale"));
+    if (!ssq || ssq_tiles < 1) return ltl_fail(LTL_ERR_ARG, "gemm_bf16_rowscale: ssq [M][ssq_tiles] is needed");
+    LtlGemmFuse f = {};
+    f.ssq_in = ssq; f.ssq_tiles = ssq_tiles; f.inv_dim = 1.0f / (float)K; f.eps = eps;
+    if (impl == 1) LTL_TRY(ltl_gemm_rows(A, B, C, M, N, K, c_dtype, epilogue, 1, g_stream, &f));
+    else LTL_TRY(ltl_gemm_tc(A, B, C, nullptr, M, N, K, c_dtype, 0, epilogue, 1, g_stream, &f));
+    LTL_TRY(sync_stream("gemm_bf16_rowscale"));
+    return impl == 1 ? LTL_OK : ltl_gemm_tc_check(g_stream);
+}
 int luaTL_gemm_bf16_tc_time(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int tile_n,
                             int iters, float* ms_per_launch)
 {

@@ -19,7 +19,7 @@
 
 namespace {
 
-enum { ROWS_EPI_NONE = 0, ROWS_EPI_SWIGLU = 1 };
+enum { ROWS_EPI_NONE = 0, ROWS_EPI_SWIGLU = 1, ROWS_EPI_RESID = 3 };
 constexpr int ROWS_NC = 32;          // columns of C per CTA (one n8 tile per warp)
 constexpr int ROWS_BATCH = 16;       // 32-wide k chunks whose weights are in registers at once
 constexpr int ROWS_MAX_SMEM = 200 * 1024;
@@ -44,11 +44,17 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 __host__ __device__ inline int rows_pitch(int cps) { return cps * 64 + ((cps & 1) ? 0 : 64); }
 
 // grid (ceil(N / 32), ksplit), 128 threads.  cps = 32-wide k chunks per slice.
+// fz.ssq_in: rows are scaled by the deferred RMSNorm factor.  ROWS_EPI_RESID (N a multiple of 32): the CTA that
+// draws the last ticket of its 32-column group adds the slices in slice order and the residual (see LtlGemmFuse);
+// no CTA waits for another.
 template <int MT, typename TC, int EPI>
 __global__ void __launch_bounds__(128)
-gemm_rows_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, TC* __restrict__ C, int M, int N, int K, int cps)
+gemm_rows_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, TC* __restrict__ C, int M, int N, int K, int cps,
+                 const LtlGemmFuse fz)
 {
     extern __shared__ __align__(16) unsigned char rows_smem[];
+    __shared__ float rsc[MT * 16];
+    __shared__ int ticket;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * ROWS_NC + warp * 8;
     const int c_begin = blockIdx.y * cps;
@@ -64,6 +70,16 @@ gemm_rows_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, TC* __r
         if (j < nch) bv[j] = __ldg(bp + j * 4);
     pdl_trigger();
     pdl_wait();
+    const bool scaled = EPI != ROWS_EPI_RESID && fz.ssq_in != nullptr;
+    if (scaled && threadIdx.x < MT * 16) {
+        float sc = 1.0f;
+        if ((int)threadIdx.x < M) {
+            float ss = 0.0f;
+            for (int q = 0; q < fz.ssq_tiles; ++q) ss += fz.ssq_in[(size_t)threadIdx.x * fz.ssq_tiles + q];
+            sc = 1.0f / sqrtf(ss * fz.inv_dim + fz.eps);
+        }
+        rsc[threadIdx.x] = sc;                                // visible after the barrier below
+    }
     {
         const int per_row = nch * 4;                          // 16-byte pieces per activation row
         for (int i = threadIdx.x; i < MT * 16 * per_row; i += 128) {
@@ -108,8 +124,9 @@ gemm_rows_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, TC* __r
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int row = mt * 16 + g + 8 * h;
-            const float v0 = acc[mt][2 * h], v1 = acc[mt][2 * h + 1];
+            float v0 = acc[mt][2 * h], v1 = acc[mt][2 * h + 1];
             if (row >= M || n >= N) continue;
+            if (scaled) { v0 *= rsc[row]; v1 *= rsc[row]; }
             if (EPI == ROWS_EPI_SWIGLU) {
                 // interleaved (gate, up) columns; both rounded to bf16 first, as a stored gate|up tensor would be
                 const float gt = __bfloat162float(__float2bfloat16_rn(v0)), up = __bfloat162float(__float2bfloat16_rn(v1));
@@ -126,10 +143,51 @@ gemm_rows_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, TC* __r
             }
         }
     }
+    if (EPI == ROWS_EPI_RESID) {
+        __threadfence();                                      // this CTA's slice is visible before its ticket is drawn
+        __syncthreads();
+        if (threadIdx.x == 0) ticket = atomicAdd(fz.counters + blockIdx.x, 1);
+        __syncthreads();
+        if (ticket != (int)gridDim.y - 1) return;
+        __threadfence();
+        const int c4 = threadIdx.x & 7, col = blockIdx.x * ROWS_NC + c4 * 4;
+        for (int base = 0; base < M * 8; base += 128) {       // 8 threads per row, 4 columns each; uniform trip count
+            const int r = (base + (int)threadIdx.x) >> 3;
+            float ss = 0.0f;
+            if (r < M) {
+                const float* pr = reinterpret_cast<const float*>(C) + (size_t)r * N + col;
+                float* xr = fz.x + (size_t)r * N + col;
+                float4 xv = *reinterpret_cast<const float4*>(xr);
+                const float4 g = *reinterpret_cast<const float4*>(fz.gain + col);
+                float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int p0 = 0; p0 < (int)gridDim.y; p0 += 8) {          // eight slices in flight at a time
+                    float4 q[8];
+#pragma unroll
+                    for (int p = 0; p < 8; ++p)
+                        if (p0 + p < (int)gridDim.y) q[p] = __ldcg(reinterpret_cast<const float4*>(pr + (size_t)(p0 + p) * M * N));
+#pragma unroll
+                    for (int p = 0; p < 8; ++p)                            // slice order: the sum does not depend on arrival order
+                        if (p0 + p < (int)gridDim.y) { a.x += q[p].x; a.y += q[p].y; a.z += q[p].z; a.w += q[p].w; }
+                }
+                xv.x += a.x; xv.y += a.y; xv.z += a.z; xv.w += a.w;
+                *reinterpret_cast<float4*>(xr) = xv;
+                ss = fmaf(xv.x, xv.x, fmaf(xv.y, xv.y, fmaf(xv.z, xv.z, xv.w * xv.w)));
+                uint2 pk;
+                pk.x = pack_bf16x2(xv.x * g.x, xv.y * g.y);
+                pk.y = pack_bf16x2(xv.z * g.z, xv.w * g.w);
+                *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(fz.h) + (size_t)r * N + col) = pk;
+            }
+            ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 1);
+            ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 2);
+            ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 4);
+            if (r < M && c4 == 0) fz.ssq_out[(size_t)r * gridDim.x + blockIdx.x] = ss;
+        }
+        if (threadIdx.x == 0) fz.counters[blockIdx.x] = 0;    // ready for the next launch
+    }
 }
 
 template <int MT, typename TC, int EPI>
-int launch_rows(const void* A, const void* B, void* C, int M, int N, int K, int ksplit, cudaStream_t s)
+int launch_rows(const void* A, const void* B, void* C, int M, int N, int K, int ksplit, cudaStream_t s, const LtlGemmFuse& fz)
 {
     const int kc = K / 32, cps = (kc + ksplit - 1) / ksplit;
     const size_t smem = (size_t)MT * 16 * rows_pitch(cps);
@@ -139,18 +197,18 @@ int launch_rows(const void* A, const void* B, void* C, int M, int N, int K, int 
         attr_set = true;
     }
     LTL_CUDA("gemm_rows launch", ltl_launch(gemm_rows_kernel<MT, TC, EPI>, dim3((N + ROWS_NC - 1) / ROWS_NC, ksplit), dim3(128), smem, s,
-                                            ltl_pdl_enabled(), (const bf16*)A, (const bf16*)B, (TC*)C, M, N, K, cps));
+                                            ltl_pdl_enabled(), (const bf16*)A, (const bf16*)B, (TC*)C, M, N, K, cps, fz));
     return ltl_check_launch("gemm_rows");
 }
 
 template <typename TC, int EPI>
-int launch_rows_mt(const void* A, const void* B, void* C, int M, int N, int K, int ksplit, cudaStream_t s)
+int launch_rows_mt(const void* A, const void* B, void* C, int M, int N, int K, int ksplit, cudaStream_t s, const LtlGemmFuse& fz)
 {
     switch ((M + 15) / 16) {
-    case 1: return launch_rows<1, TC, EPI>(A, B, C, M, N, K, ksplit, s);
-    case 2: return launch_rows<2, TC, EPI>(A, B, C, M, N, K, ksplit, s);
-    case 3: return launch_rows<3, TC, EPI>(A, B, C, M, N, K, ksplit, s);
-    default: return launch_rows<4, TC, EPI>(A, B, C, M, N, K, ksplit, s);
+    case 1: return launch_rows<1, TC, EPI>(A, B, C, M, N, K, ksplit, s, fz);
+    case 2: return launch_rows<2, TC, EPI>(A, B, C, M, N, K, ksplit, s, fz);
+    case 3: return launch_rows<3, TC, EPI>(A, B, C, M, N, K, ksplit, s, fz);
+    default: return launch_rows<4, TC, EPI>(A, B, C, M, N, K, ksplit, s, fz);
     }
 }
 
@@ -180,19 +238,26 @@ int ltl_gemm_rows_plan_split(int N, int K, int max_parts)
 
 // C (c_dtype f32 or bf16) = A[M,K] B[N,K]^T.  epi = 1: SwiGLU over interleaved (gate, up) rows of B, C is
 // [M, N/2] bf16.  ksplit > 1: C receives ksplit fp32 partial matrices [ksplit][M][N].
-int ltl_gemm_rows(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int epi, int ksplit, cudaStream_t s)
+int ltl_gemm_rows(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int epi, int ksplit, cudaStream_t s,
+                  const LtlGemmFuse* fuse)
 {
+    const LtlGemmFuse fz = fuse ? *fuse : LtlGemmFuse{};
     if (!A || !B || !C) return ltl_fail(LTL_ERR_NULL, "gemm_rows: null operand");
     if (!ltl_gemm_rows_supported(A, B, M, N, K, ksplit))
         return ltl_fail(LTL_ERR_UNSUPPORTED, "gemm_rows: needs 1 <= M <= 64, K %% 32 == 0, 16-byte aligned operands (M=%d N=%d K=%d ksplit=%d)", M, N, K, ksplit);
-    if (ksplit > 1 && (c_dtype != LTL_F32 || epi))
+    if (epi == ROWS_EPI_RESID) {
+        if (c_dtype != LTL_F32 || (N % 32) || !fz.x || !fz.gain || !fz.h || !fz.ssq_out || !fz.counters)
+            return ltl_fail(LTL_ERR_ARG, "gemm_rows: the residual form needs fp32 slices, N %% 32 == 0 and all of x, gain, h, ssq_out, counters");
+        return launch_rows_mt<float, ROWS_EPI_RESID>(A, B, C, M, N, K, ksplit, s, fz);
+    }
+    if (ksplit > 1 && (c_dtype != LTL_F32 || epi || fz.ssq_in))
         return ltl_fail(LTL_ERR_ARG, "gemm_rows: split-K writes fp32 partial sums and takes no epilogue");
     if (epi == ROWS_EPI_SWIGLU) {
         if (c_dtype != LTL_BF16 || (N & 1)) return ltl_fail(LTL_ERR_ARG, "gemm_rows: the SwiGLU epilogue writes bf16 and needs an even N");
-        return launch_rows_mt<bf16, ROWS_EPI_SWIGLU>(A, B, C, M, N, K, 1, s);
+        return launch_rows_mt<bf16, ROWS_EPI_SWIGLU>(A, B, C, M, N, K, 1, s, fz);
     }
     if (epi != ROWS_EPI_NONE) return ltl_fail(LTL_ERR_ARG, "gemm_rows: epilogue %d", epi);
-    if (c_dtype == LTL_F32) return launch_rows_mt<float, ROWS_EPI_NONE>(A, B, C, M, N, K, ksplit, s);
-    if (c_dtype == LTL_BF16) return launch_rows_mt<bf16, ROWS_EPI_NONE>(A, B, C, M, N, K, 1, s);
+    if (c_dtype == LTL_F32) return launch_rows_mt<float, ROWS_EPI_NONE>(A, B, C, M, N, K, ksplit, s, fz);
+    if (c_dtype == LTL_BF16) return launch_rows_mt<bf16, ROWS_EPI_NONE>(A, B, C, M, N, K, 1, s, fz);
     return ltl_fail(LTL_ERR_DTYPE, "gemm_rows: output dtype %d", c_dtype);
 }

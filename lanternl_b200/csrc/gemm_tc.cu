@@ -32,7 +32,7 @@ constexpr int BM = 128, BK = 64, UMMA_K = 16;
 // bytes are requested at once and the kernel is bound by one memory round trip, not by one per
 // four k-blocks.
 template <int BN> struct Ring { static constexpr int STAGES = BN == 32 ? 10 : (BN == 64 ? 8 : (BN == 128 ? 6 : 4)); };
-enum { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ATOMIC = 2 };
+enum { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ATOMIC = 2, EPI_RESID = 3 };
 using namespace tc;
 
 // Shared memory of one CTA, carved from the dynamic allocation (1024-byte aligned for the 128-byte
@@ -46,6 +46,7 @@ struct Bars {
     uint64_t empty[MAX_STAGES];
     uint64_t acc_ready;
     uint32_t tmem_base;
+    int ticket;                    // EPI_RESID: arrival order of this CTA at its output tile
 };
 template <int BN> constexpr size_t stage_bytes() { return (size_t)(BM + BN) * BK * 2; }
 template <int BN> size_t smem_bytes(int stages) { return stages * stage_bytes<BN>() + sizeof(Bars) + 1024; }
@@ -55,12 +56,15 @@ template <int BN> size_t smem_bytes(int stages) { return stages * stage_bytes<BN
 // N / 2 columns.  R is ignored.
 // EPI_ATOMIC: C (fp32) += the product, with red.global.add; every split-K slice adds into the same C.
 // This is the weight-gradient form (dW += X^T dY with a long reduction over the tokens).
+// EPI_RESID (BN = 32, fp32 slices, N a multiple of 32): split-K whose last-arriving CTA per output tile finishes the
+// tile - see LtlGemmFuse.  No CTA waits for another: every CTA publishes its slice (fence, then a ticket from an
+// atomic counter) and only the one that draws the last ticket reads the others' slices.
 // MAJ = 1: both operands MN-major - A is X [K, M] and B is Y [K, N] in memory (the contraction runs down the
 // rows), i.e. C = X^T Y, the weight-gradient product of two token-major activations without a transpose.
 template <int BN, typename TC, int EPI, int MAJ = 0>
 __global__ void __launch_bounds__(192, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               TC* C, const TC* R, int M, int N, int K, int STAGES, int b_early, int* __restrict__ err)
+               TC* C, const TC* R, int M, int N, int K, int STAGES, int b_early, const LtlGemmFuse fz, int* __restrict__ err)
 {
     // b_early: B holds weights that no kernel of the surrounding programmatic-launch chain writes (the decode
     // step), so the first ring of B tiles is requested before griddepcontrol.wait and lands under the tail of
@@ -81,6 +85,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int kb_per = (kb_all + gridDim.z - 1) / gridDim.z;
     const int kb0 = blockIdx.z * kb_per;
     const int kblocks = max(0, min(kb_all, kb0 + kb_per) - kb0);
+    TC* const Cbase = C;
     if (EPI != EPI_ATOMIC) C += (size_t)blockIdx.z * M * N;
 
     if (threadIdx.x == 0) {
@@ -167,6 +172,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int quad = warp & 3;                        // TMEM lane quadrant this warp may read
         const int row = m0 + quad * 32 + lane;
+        float rscale = 1.0f;                              // deferred RMSNorm factor of this row
+        const bool scaled = (EPI == EPI_NONE || EPI == EPI_SWIGLU) && fz.ssq_in != nullptr;
+        if (scaled && row < M) {
+            float ss = 0.0f;
+            for (int t = 0; t < fz.ssq_tiles; ++t) ss += fz.ssq_in[(size_t)row * fz.ssq_tiles + t];
+            rscale = 1.0f / sqrtf(ss * fz.inv_dim + fz.eps);
+        }
         if (ok) {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -176,6 +188,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (kblocks == 0) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = 0u;
+                }
+                if (scaled) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * rscale);
                 }
                 if (EPI == EPI_SWIGLU) {
                     if (row < M) {
@@ -239,6 +255,64 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                     }
                 }
+            }
+        }
+        if (EPI == EPI_RESID) {
+            // Every epilogue thread gets here whatever its wait returned, so the named barrier always completes.
+            __threadfence();                                              // this CTA's slice is visible ...
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+            if (threadIdx.x == 64) sm.ticket = atomicAdd(fz.counters + tile, 1);   // ... before its ticket is drawn
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (sm.ticket == (int)gridDim.z - 1) {
+                __threadfence();
+                // 8 threads per row (4 columns each), 16 rows per pass; two passes and all their slices in flight at once
+                const int te = threadIdx.x - 64, c4 = te & 7, col = n0 + c4 * 4;
+                const int ks = (int)gridDim.z;
+                const float* part = reinterpret_cast<const float*>(Cbase);
+                const float4 g = *reinterpret_cast<const float4*>(fz.gain + col);
+#pragma unroll 1
+                for (int i0 = 0; i0 < 8; i0 += 2) {
+                    float4 q[2][8], xv[2];
+                    int rr[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        rr[u] = m0 + (te >> 3) + 16 * (i0 + u);
+                        if (rr[u] < M) {
+                            xv[u] = *reinterpret_cast<const float4*>(fz.x + (size_t)rr[u] * N + col);
+#pragma unroll
+                            for (int p = 0; p < 8; ++p)
+                                if (p < ks) q[u][p] = __ldcg(reinterpret_cast<const float4*>(part + (size_t)p * M * N + (size_t)rr[u] * N + col));
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        float ss = 0.0f;
+                        if (rr[u] < M) {
+                            float4 a4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                            for (int p = 0; p < 8; ++p)                  // slice order: the sum does not depend on arrival order
+                                if (p < ks) { a4.x += q[u][p].x; a4.y += q[u][p].y; a4.z += q[u][p].z; a4.w += q[u][p].w; }
+                            for (int p = 8; p < ks; ++p) {               // more than eight slices: the rest one by one
+                                const float4 e = __ldcg(reinterpret_cast<const float4*>(part + (size_t)p * M * N + (size_t)rr[u] * N + col));
+                                a4.x += e.x; a4.y += e.y; a4.z += e.z; a4.w += e.w;
+                            }
+                            float4 v4 = xv[u];
+                            v4.x += a4.x; v4.y += a4.y; v4.z += a4.z; v4.w += a4.w;
+                            *reinterpret_cast<float4*>(fz.x + (size_t)rr[u] * N + col) = v4;
+                            ss = fmaf(v4.x, v4.x, fmaf(v4.y, v4.y, fmaf(v4.z, v4.z, v4.w * v4.w)));
+                            uint2 pk;
+                            pk.x = pack_bf16x2(v4.x * g.x, v4.y * g.y);
+                            pk.y = pack_bf16x2(v4.z * g.z, v4.w * g.w);
+                            *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(fz.h) + (size_t)rr[u] * N + col) = pk;
+                        }
+                        ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 1);
+                        ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 2);
+                        ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 4);
+                        if (rr[u] < M && c4 == 0) fz.ssq_out[(size_t)rr[u] * gridDim.x + blockIdx.x] = ss;
+                    }
+                }
+                if (threadIdx.x == 64) fz.counters[tile] = 0;             // ready for the next launch
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -497,14 +571,15 @@ int launch_persist(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const 
 }
 
 template <int BN, typename TC, int EPI>
-int launch(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int ksplit, cudaStream_t s)
+int launch(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int ksplit, cudaStream_t s,
+           const LtlGemmFuse& fz = LtlGemmFuse{})
 {
     CUtensorMap ma, mb;
     LTL_TRY(tensor_map(A, M, K, K, BM, &ma));
     LTL_TRY(tensor_map(B, N, K, K, BN, &mb));
     if constexpr (BN == 256 && EPI == EPI_NONE) {
         // long reductions run a little faster as two co-resident CTAs (measured: K = 5632 .. 11264, fp32 output)
-        if (persist_enabled() && ksplit <= 1 && K <= 4096) return launch_persist<TC, 0>(ma, mb, C, R, M, N, K, 1, s);
+        if (persist_enabled() && ksplit <= 1 && K <= 4096 && !fz.ssq_in) return launch_persist<TC, 0>(ma, mb, C, R, M, N, K, 1, s);
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, ksplit < 1 ? 1 : ksplit);
     const int kb_all = (K + BK - 1) / BK;
@@ -525,7 +600,7 @@ int launch(const void* A, const void* B, void* C, const void* R, int M, int N, i
     }
     LTL_CUDA("gemm_tc launch", ltl_launch(gemm_tc_kernel<BN, TC, EPI>, grid, dim3(192), smem, s, ltl_pdl_enabled(),
                                           ma, mb, (TC*)C, (const TC*)R, M, N, K, stages, b_early_enabled() && ltl_pdl_enabled() ? 1 : 0,
-                                          g_err_flag));
+                                          fz, g_err_flag));
     return ltl_check_launch("gemm_tc");
 }
 
@@ -551,7 +626,7 @@ int launch_mn(const void* X, const void* Y, float* C, int M, int N, int K, int k
                                                       (int)smem_bytes<BN>(BN == 256 ? 2 : 4)));
         attr_set = true;
     }
-    gemm_tc_kernel<BN, float, EPI_ATOMIC, 1><<<grid, 192, smem, s>>>(ma, mb, C, nullptr, M, N, K, stages, 0, g_err_flag);
+    gemm_tc_kernel<BN, float, EPI_ATOMIC, 1><<<grid, 192, smem, s>>>(ma, mb, C, nullptr, M, N, K, stages, 0, LtlGemmFuse{}, g_err_flag);
     return ltl_check_launch("gemm_tc_mn");
 }
 
@@ -639,8 +714,20 @@ int ltl_gemm_tc_plan_accum(int M, int N, int K, int bn)
 // ksplit > 1: split-K, C receives ksplit fp32 partial matrices [ksplit][M][N] (bn should then be the
 // width the caller sized the grid for; see ltl_gemm_tc_plan_split).
 int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int c_dtype, int bn,
-                int epi, int ksplit, cudaStream_t s)
+                int epi, int ksplit, cudaStream_t s, const LtlGemmFuse* fuse)
 {
+    const LtlGemmFuse fz = fuse ? *fuse : LtlGemmFuse{};
+    if (epi == EPI_RESID) {
+        if (c_dtype != LTL_F32 || R || (N % 32) || (bn != 0 && bn != 32) || !fz.x || !fz.gain || !fz.h || !fz.ssq_out || !fz.counters)
+            return ltl_fail(LTL_ERR_ARG, "gemm_tc: the residual form needs fp32 slices, N %% 32 == 0, tiles of 32 columns and all of x, gain, h, ssq_out, counters");
+        if (!A || !B || !C) return ltl_fail(LTL_ERR_NULL, "gemm_tc: null operand");
+        if (!ltl_gemm_tc_supported(A, B, M, N, K))
+            return ltl_fail(LTL_ERR_UNSUPPORTED, "gemm_tc: needs K %% 8 == 0 and 16-byte aligned operands (M=%d N=%d K=%d)", M, N, K);
+        if (!ltl_tc_err_flag()) return ltl_fail(LTL_ERR_OOM, "gemm_tc: error flag");
+        return launch<32, float, EPI_RESID>(A, B, C, nullptr, M, N, K, ksplit < 1 ? 1 : ksplit, s, fz);
+    }
+    if (fz.ssq_in && (epi == EPI_ATOMIC || ksplit > 1 || R))
+        return ltl_fail(LTL_ERR_ARG, "gemm_tc: the row-scale epilogue takes no residual, split-K or accumulation");
     if (epi == EPI_ATOMIC && (c_dtype != LTL_F32 || R))
         return ltl_fail(LTL_ERR_ARG, "gemm_tc: the accumulating epilogue adds into an fp32 C and takes no residual");
     if (epi != EPI_ATOMIC && ksplit > 1 && (c_dtype != LTL_F32 || R || epi))
@@ -657,10 +744,10 @@ int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int
     if (bn == 0) bn = pick_bn(M, N);
 #define TC_CASE(BNV)                                                                                     \
     if (bn == BNV) {                                                                                     \
-        if (epi == EPI_SWIGLU) return launch<BNV, bf16, EPI_SWIGLU>(A, B, C, nullptr, M, N, K, 1, s);       \
+        if (epi == EPI_SWIGLU) return launch<BNV, bf16, EPI_SWIGLU>(A, B, C, nullptr, M, N, K, 1, s, fz);   \
         if (epi == EPI_ATOMIC) return launch<BNV, float, EPI_ATOMIC>(A, B, C, nullptr, M, N, K, ksplit, s);    \
-        if (c_dtype == LTL_F32) return launch<BNV, float, EPI_NONE>(A, B, C, R, M, N, K, ksplit, s);             \
-        if (c_dtype == LTL_BF16) return launch<BNV, bf16, EPI_NONE>(A, B, C, R, M, N, K, 1, s);             \
+        if (c_dtype == LTL_F32) return launch<BNV, float, EPI_NONE>(A, B, C, R, M, N, K, ksplit, s, fz);         \
+        if (c_dtype == LTL_BF16) return launch<BNV, bf16, EPI_NONE>(A, B, C, R, M, N, K, 1, s, fz);         \
         return ltl_fail(LTL_ERR_DTYPE, "gemm_tc: output dtype %d", c_dtype);                             \
     }
     TC_CASE(32) TC_CASE(64) TC_CASE(128) TC_CASE(256)

@@ -94,12 +94,14 @@ struct luaTL_lm_s {
     int* d_err = nullptr;
     float* xlast = nullptr;
     float* part = nullptr;       // split-K partial sums of the decode GEMMs [8][nseq_cap][D]
+    float* ssq[2] = { nullptr, nullptr };   // per-row sums of squares by 32-column tile [nseq_cap][D / 32] (fused residual GEMMs)
+    int* tile_tickets = nullptr; // arrival counters of the fused residual GEMMs, one per output tile, zero between launches
     std::map<int, GraphEntry> graphs;
     cudaEvent_t ev[4] = { nullptr, nullptr, nullptr, nullptr };
     float prefill_ms = 0, decode_ms = 0;
     int64_t launches = 0;
     int adam_alloc = 0;
-    int use_tc = 1, fuse_swiglu = 0, use_pdl = 1, rows_gemm = 1;
+    int use_tc = 1, fuse_swiglu = 0, use_pdl = 1, rows_gemm = 1, fuse_norm = 0;
 };
 
 namespace {
@@ -715,6 +717,13 @@ int ensure_decode(LM* m, int nseq, int n_prompt, int n_new)
         DALLOC(m->d_win, (size_t)m->nseq_cap * m->T * 4, "window ids");
         DALLOC(m->xlast, (size_t)m->nseq_cap * m->D * 4, "last rows");
         DALLOC(m->part, (size_t)8 * m->nseq_cap * m->D * 4, "split-K partial sums");
+        {
+            const size_t tiles = (size_t)(m->D + 31) / 32, ntick = ((size_t)m->nseq_cap / 128 + 1) * tiles;
+            DALLOC(m->ssq[0], (size_t)m->nseq_cap * tiles * 4, "row sums of squares");
+            DALLOC(m->ssq[1], (size_t)m->nseq_cap * tiles * 4, "row sums of squares");
+            DALLOC(m->tile_tickets, ntick * 4, "tile tickets");
+            LTL_CUDA("memset", cudaMemsetAsync(m->tile_tickets, 0, ntick * 4, m->s));
+        }
         LTL_CUDA("memset", cudaMemsetAsync(m->d_pos, 0, (size_t)m->nseq_cap * 4, m->s));
         LTL_CUDA("memset", cudaMemsetAsync(m->d_count, 0, (size_t)m->nseq_cap * 4, m->s));
         LTL_CUDA("memset", cudaMemsetAsync(m->d_err, 0, 4, m->s));
@@ -765,7 +774,8 @@ int pick_next(LM* m, const float* logits, int nseq, int slot0, int32_t* d_out, i
 // Decode step of the bf16 tensor-core path.  The two residual GEMMs of a layer (attention output
 // and FFN down projection: N = D, few tiles) run split-K so that every SM pulls weights; their
 // fp32 partial sums are added to the residual stream, in a fixed order, by the RMSNorm kernel that
-// follows anyway.  Launches per step: 2 + 6 L.
+// follows anyway (2 + 7 L launches per step; the default), or - fused form, LUATL_DECODE_FUSE_NORM=1 - by the
+// last-arriving CTA of the GEMM itself, with the normalisation factor applied by the next GEMM's epilogue (2 + 5 L).
 int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t* d_out, int out_stride, int pick,
                       int32_t* hist, int hist_stride, int hist_base)
 {
@@ -793,17 +803,48 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
         s_o = ltl_gemm_rows_plan_split(D, D, 8);
         s_d = ltl_gemm_rows_plan_split(D, F, 8);
     }
-    auto gemm = [&](const void* A, const bf16* Wt, void* C, int N, int K, int c_dt, int bn, int epi, int ks) -> int {
-        if (rows) return ltl_gemm_rows(A, Wt, C, nseq, N, K, c_dt, epi, ks, m->s);
-        return ltl_gemm_tc(A, Wt, C, nullptr, nseq, N, K, c_dt, bn, epi, ks, m->s);
+    auto gemm = [&](const void* A, const bf16* Wt, void* C, int N, int K, int c_dt, int bn, int epi, int ks,
+                    const LtlGemmFuse* fz = nullptr) -> int {
+        if (rows) return ltl_gemm_rows(A, Wt, C, nseq, N, K, c_dt, epi, ks, m->s, fz);
+        return ltl_gemm_tc(A, Wt, C, nullptr, nseq, N, K, c_dt, bn, epi, ks, m->s, fz);
     };
     LTL_TRY(ltl_lm_embed_rmsnorm(d_tok, m->Wb + m->off_emb, LTL_BF16, x, m->W + m->lo[0].ln1, a.h1, LTL_BF16, nseq, D, V,
                                  m->c.eps, m->s));
     m->launches++;
+    // Fused form: the split-K reduce, the residual add and the gain of the next RMSNorm ride in the residual GEMM
+    // (its last-arriving CTA per tile), the normalisation factor of a row is applied by the epilogue of the GEMM that
+    // consumes it (a per-row scale commutes with the product): 5 launches per layer instead of 7.  Optional, see create.
+    const bool fuse = m->fuse_norm && D % 32 == 0 && m->ssq[0] && m->tile_tickets;
+    const int tiles = D / 32;
+    auto resid = [&](const float* gain, void* h, int which) {
+        LtlGemmFuse f = {};
+        f.x = x; f.gain = gain; f.h = h; f.ssq_out = m->ssq[which]; f.counters = m->tile_tickets;
+        return f;
+    };
+    auto scale_by = [&](int which) {
+        LtlGemmFuse f = {};
+        f.ssq_in = m->ssq[which]; f.ssq_tiles = tiles; f.inv_dim = 1.0f / (float)D; f.eps = m->c.eps;
+        return f;
+    };
     for (int l = 0; l < L; ++l) {
         const LayerOff& o = m->lo[l];
         void* kcl = (char*)m->kc + l * cl + cslot;
         void* vcl = (char*)m->vc + l * cl + cslot;
+        const bool last = l + 1 == L;
+        const float* next_gain = m->W + (last ? m->off_lnf : m->lo[l + 1].ln1);
+        void* next_h = last ? a.hf : a.h1;
+        if (fuse) {
+            const LtlGemmFuse in1 = scale_by(1), in0 = scale_by(0);
+            const LtlGemmFuse ro = resid(m->W + o.ln2, a.h2, 0), rd = resid(next_gain, next_h, 1);
+            LTL_TRY(gemm(a.h1, m->Wb + o.wqkv, a.qkv, 3 * D, D, LTL_BF16, 0, 0, 1, l > 0 ? &in1 : nullptr));
+            LTL_TRY(ltl_decode_attn(a.qkv, kcl, vcl, a.attn, pos, nseq, H, hd, m->T, m->scale, LTL_BF16, m->splits, m->ws,
+                                    m->rope_tab, m->c.rope_interleaved, m->c.use_rope, m->d_err, m->s));
+            LTL_TRY(gemm(a.attn, m->Wb + o.wo, m->part, D, D, LTL_F32, bn_o, 3, s_o, &ro));
+            LTL_TRY(gemm(a.h2, m->Wb + o.w13, a.hs, 2 * F, D, LTL_BF16, 0, 1, 1, &in0));
+            LTL_TRY(gemm(a.hs, m->Wb + o.w2, m->part, D, F, LTL_F32, bn_d, 3, s_d, &rd));
+            m->launches += 5 + (m->splits > 1 ? 1 : 0);
+            continue;
+        }
         LTL_TRY(gemm(a.h1, m->Wb + o.wqkv, a.qkv, 3 * D, D, LTL_BF16, 0, 0, 1));
         LTL_TRY(ltl_decode_attn(a.qkv, kcl, vcl, a.attn, pos, nseq, H, hd, m->T, m->scale, LTL_BF16, m->splits, m->ws,
                                 m->rope_tab, m->c.rope_interleaved, m->c.use_rope, m->d_err, m->s));
@@ -811,12 +852,13 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
         LTL_TRY(ltl_lm_residual_rmsnorm(x, m->part, s_o, m->W + o.ln2, a.h2, LTL_BF16, nseq, D, m->c.eps, m->s));
         LTL_TRY(gemm(a.h2, m->Wb + o.w13, a.hs, 2 * F, D, LTL_BF16, 0, 1, 1));
         LTL_TRY(gemm(a.hs, m->Wb + o.w2, m->part, D, F, LTL_F32, bn_d, 0, s_d));
-        const bool last = l + 1 == L;
-        LTL_TRY(ltl_lm_residual_rmsnorm(x, m->part, s_d, m->W + (last ? m->off_lnf : m->lo[l + 1].ln1),
-                                        last ? a.hf : a.h1, LTL_BF16, nseq, D, m->c.eps, m->s));
+        LTL_TRY(ltl_lm_residual_rmsnorm(x, m->part, s_d, next_gain, next_h, LTL_BF16, nseq, D, m->c.eps, m->s));
         m->launches += 7 + (m->splits > 1 ? 1 : 0);
     }
-    LTL_TRY(gemm(a.hf, m->Wb + (m->c.tie ? m->off_emb : m->off_head), a.logits, V, D, LTL_F32, 0, 0, 1));
+    {
+        const LtlGemmFuse in1 = scale_by(1);
+        LTL_TRY(gemm(a.hf, m->Wb + (m->c.tie ? m->off_emb : m->off_head), a.logits, V, D, LTL_F32, 0, 0, 1, fuse ? &in1 : nullptr));
+    }
     m->launches++;
     if (pick) {
         LTL_TRY(pick_next(m, a.logits, nseq, slot0, d_out, out_stride, hist, hist_stride, hist_base, m->s));
@@ -1015,6 +1057,13 @@ luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
         m->attn_tc = !(at && at[0] == '0');
         const char* rg = getenv("LUATL_DECODE_ROWS_GEMM");          // 0: tcgen05 tiles at every batch size (A/B comparison)
         m->rows_gemm = !(rg && rg[0] == '0');
+        // LUATL_DECODE_FUSE_NORM=1: split-K reduce + residual inside the GEMM (last-arriving CTA per tile), RMSNorm factor
+        // in the next GEMM's epilogue.  Off by default: measured slower than the reduce + RMSNorm kernel of its own
+        // (256 sequences 263.6 -> 302.4 ms per pass, 32: 136.9 -> 153.7, 8: 102.9 -> 107.7) - with programmatic
+        // dependent launch that kernel is already resident when its input lands, so it costs one memory round trip,
+        // while the fence + ticket + reduction of the fused form add three to the GEMM's critical path.
+        const char* fn = getenv("LUATL_DECODE_FUSE_NORM");
+        m->fuse_norm = fn && fn[0] == '1';
         const char* oc = getenv("LUATL_OVERLAP_COMM");
         m->overlap_comm = !(oc && oc[0] == '0');
     }
@@ -1044,7 +1093,7 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
     void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
                      m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
                      m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part,
-                     m->Wm, m->d_done, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
+                     m->Wm, m->d_done, m->ssq[0], m->ssq[1], m->tile_tickets, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
     for (void* p : ptrs) if (p) cudaFree(p);
     for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
     if (m->ev_grad) cudaEventDestroy(m->ev_grad);

@@ -125,12 +125,28 @@ int ltl_count_correct(const int32_t* pred, const int32_t* tgt, int n, float* cor
 // Gather row (b * T + last) of x [B*T, cols] into out [B, cols].
 int ltl_gather_last_rows(const float* x, float* out, int B, int T, int cols, int last, cudaStream_t s);
 
+// Fusions of the decode step around a GEMM (both GEMM kernels take it by value; all-null = none).
+//  * residual form (epi = 3, split-K): the CTA that arrives last at an output tile adds the slices (in slice order)
+//    and the residual x, writes x back, h = bf16(x * gain) and the tile's share of sum(x^2) per row to ssq_out
+//    [M][tiles]; the RMSNorm factor itself is left to the consumer;
+//  * row-scale form (ssq_in != null): the epilogue multiplies row r by 1 / sqrt(sum_t ssq_in[r][t] * inv_dim + eps).
+struct LtlGemmFuse {
+    float* x;
+    const float* gain;
+    void* h;
+    float* ssq_out;
+    int* counters;
+    const float* ssq_in;
+    int ssq_tiles;
+    float inv_dim, eps;
+};
+
 // ---- tcgen05 / TMA GEMM (gemm_tc.cu): C[M,N] = A[M,K] B[N,K]^T + R, bf16 in, fp32 accumulate ----
 bool ltl_gemm_tc_supported(const void* A, const void* B, int M, int N, int K);
 // epi = 1: B rows interleave gate/up, C [M, N/2] bf16 = silu(gate) * up (R ignored).
 // ksplit > 1: C receives ksplit fp32 partial matrices [ksplit][M][N] (no residual, no epilogue).
 int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int c_dtype,
-                int bn, int epi, int ksplit, cudaStream_t s);
+                int bn, int epi, int ksplit, cudaStream_t s, const LtlGemmFuse* fuse = nullptr);
 void ltl_gemm_tc_plan_split(int M, int N, int K, int* bn, int* ksplit);
 int ltl_gemm_tc_check(cudaStream_t s);
 int ltl_gemm_tc_plan_accum(int M, int N, int K, int bn);
@@ -138,7 +154,8 @@ int ltl_gemm_tc_xty(const void* X, const void* Y, float* C, int M, int N, int K,
 // Few-row GEMM (gemm_rows.cu, mma.sync): 1 <= M <= 64, K a multiple of 32; same epi / ksplit meaning as above.
 bool ltl_gemm_rows_supported(const void* A, const void* B, int M, int N, int K, int ksplit);
 int ltl_gemm_rows_plan_split(int N, int K, int max_parts);
-int ltl_gemm_rows(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int epi, int ksplit, cudaStream_t s);
+int ltl_gemm_rows(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int epi, int ksplit, cudaStream_t s,
+                  const LtlGemmFuse* fuse = nullptr);
 // CUtensorMap (128 bytes, written to out_map) of a bf16 matrix [rows, cols] with rows `pitch` elements apart:
 // boxes of box_rows x 64 columns, 128-byte swizzle.  Cached per (base, shape).
 int ltl_tensor_map_bf16(const void* base, int rows, int cols, long long pitch, int box_rows, void* out_map);

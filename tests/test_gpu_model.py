@@ -236,13 +236,16 @@ def assert_tokens_consistent(o, w, prompts, got, tol):
     return near
 
 
-# Decode GEMMs: "1" = the few-row mma.sync kernel (up to 64 sequences), "0" = tcgen05 tiles at every batch size.
-ROWS_GEMM = pytest.mark.parametrize("rows_gemm", ["1", "0"])
+# Decode GEMMs: rows_gemm "1" = the few-row mma.sync kernel (up to 32 sequences), "0" = tcgen05 tiles at every batch
+# size; fuse_norm "1" = split-K reduce + residual inside the GEMM and the RMSNorm factor in the next GEMM's epilogue,
+# "0" = the reduce + RMSNorm kernel of its own.
+ROWS_GEMM = pytest.mark.parametrize("rows_gemm,fuse_norm", [("1", "1"), ("0", "1"), ("1", "0"), ("0", "0")])
 
 
 @ROWS_GEMM
-def test_bf16_decode_small_model_logits_and_tokens(rows_gemm, monkeypatch):
+def test_bf16_decode_small_model_logits_and_tokens(rows_gemm, fuse_norm, monkeypatch):
     monkeypatch.setenv("LUATL_DECODE_ROWS_GEMM", rows_gemm)
+    monkeypatch.setenv("LUATL_DECODE_FUSE_NORM", fuse_norm)
     cfg = dict(vocab=512, dim=128, layers=2, heads=2, ffn=192, max_seq=96)
     w = bf16_round(params_for(cfg, seed=0, std=0.05))                 # the weights ARE bf16 values
     nseq, npr, n_new = 6, 16, 64
@@ -260,11 +263,12 @@ def test_bf16_decode_small_model_logits_and_tokens(rows_gemm, monkeypatch):
 
 
 @ROWS_GEMM
-def test_config2_shapes_bf16_prefill_and_decode_agree_with_single_steps(rows_gemm, monkeypatch):
+def test_config2_shapes_bf16_prefill_and_decode_agree_with_single_steps(rows_gemm, fuse_norm, monkeypatch):
     """Configuration 2 architecture (bf16, head_dim 64, ffn 1408), reduced batch: the batched
     prefill + graph-replayed decode must produce the tokens the one-token-at-a-time path gives,
     and its first logits must match the oracle within the bf16 tolerance."""
     monkeypatch.setenv("LUATL_DECODE_ROWS_GEMM", rows_gemm)
+    monkeypatch.setenv("LUATL_DECODE_FUSE_NORM", fuse_norm)
     cfg = dict(CFG2, max_seq=160, layers=2)
     w = bf16_round(params_for(cfg, seed=0))
     nseq, npr, n_new = 4, 128, 24
