@@ -47,13 +47,18 @@ __host__ __device__ inline int rows_pitch(int cps) { return cps * 64 + ((cps & 1
 // fz.ssq_in: rows are scaled by the deferred RMSNorm factor.  ROWS_EPI_RESID (N a multiple of 32): the CTA that
 // draws the last ticket of its 32-column group adds the slices in slice order and the residual (see LtlGemmFuse);
 // no CTA waits for another.
-template <int MT, typename TC, int EPI>
+// FZ selects the instantiations that take the fusion arguments; the plain ones keep an empty parameter and none of the code.
+struct NoFuse {};
+template <bool FZ> struct FuseArg { typedef NoFuse type; };
+template <> struct FuseArg<true> { typedef LtlGemmFuse type; };
+
+template <int MT, typename TC, int EPI, bool FZ>
 __global__ void __launch_bounds__(128)
 gemm_rows_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, TC* __restrict__ C, int M, int N, int K, int cps,
-                 const LtlGemmFuse fz)
+                 const typename FuseArg<FZ>::type fz)
 {
     extern __shared__ __align__(16) unsigned char rows_smem[];
-    __shared__ float rsc[MT * 16];
+    __shared__ float rsc[FZ ? MT * 16 : 1];
     __shared__ int ticket;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * ROWS_NC + warp * 8;
@@ -70,15 +75,17 @@ gemm_rows_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, TC* __r
         if (j < nch) bv[j] = __ldg(bp + j * 4);
     pdl_trigger();
     pdl_wait();
-    const bool scaled = EPI != ROWS_EPI_RESID && fz.ssq_in != nullptr;
-    if (scaled && threadIdx.x < MT * 16) {
-        float sc = 1.0f;
-        if ((int)threadIdx.x < M) {
-            float ss = 0.0f;
-            for (int q = 0; q < fz.ssq_tiles; ++q) ss += fz.ssq_in[(size_t)threadIdx.x * fz.ssq_tiles + q];
-            sc = 1.0f / sqrtf(ss * fz.inv_dim + fz.eps);
+    constexpr bool scaled = FZ && EPI != ROWS_EPI_RESID;
+    if constexpr (scaled) {
+        if (threadIdx.x < MT * 16) {
+            float sc = 1.0f;
+            if ((int)threadIdx.x < M) {
+                float ss = 0.0f;
+                for (int q = 0; q < fz.ssq_tiles; ++q) ss += fz.ssq_in[(size_t)threadIdx.x * fz.ssq_tiles + q];
+                sc = 1.0f / sqrtf(ss * fz.inv_dim + fz.eps);
+            }
+            rsc[threadIdx.x] = sc;                            // visible after the barrier below
         }
-        rsc[threadIdx.x] = sc;                                // visible after the barrier below
     }
     {
         const int per_row = nch * 4;                          // 16-byte pieces per activation row
@@ -143,7 +150,7 @@ gemm_rows_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, TC* __r
             }
         }
     }
-    if (EPI == ROWS_EPI_RESID) {
+    if constexpr (EPI == ROWS_EPI_RESID && FZ) {
         __threadfence();                                      // this CTA's slice is visible before its ticket is drawn
         __syncthreads();
         if (threadIdx.x == 0) ticket = atomicAdd(fz.counters + blockIdx.x, 1);
@@ -186,19 +193,27 @@ gemm_rows_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, TC* __r
     }
 }
 
-template <int MT, typename TC, int EPI>
-int launch_rows(const void* A, const void* B, void* C, int M, int N, int K, int ksplit, cudaStream_t s, const LtlGemmFuse& fz)
+template <int MT, typename TC, int EPI, bool FZ, typename FA>
+int launch_rows_fz(const void* A, const void* B, void* C, int M, int N, int K, int ksplit, cudaStream_t s, const FA& fa)
 {
     const int kc = K / 32, cps = (kc + ksplit - 1) / ksplit;
     const size_t smem = (size_t)MT * 16 * rows_pitch(cps);
     static bool attr_set = false;
     if (!attr_set) {
-        LTL_CUDA("gemm_rows smem attribute", cudaFuncSetAttribute(gemm_rows_kernel<MT, TC, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_MAX_SMEM));
+        LTL_CUDA("gemm_rows smem attribute", cudaFuncSetAttribute(gemm_rows_kernel<MT, TC, EPI, FZ>, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS_MAX_SMEM));
         attr_set = true;
     }
-    LTL_CUDA("gemm_rows launch", ltl_launch(gemm_rows_kernel<MT, TC, EPI>, dim3((N + ROWS_NC - 1) / ROWS_NC, ksplit), dim3(128), smem, s,
-                                            ltl_pdl_enabled(), (const bf16*)A, (const bf16*)B, (TC*)C, M, N, K, cps, fz));
+    LTL_CUDA("gemm_rows launch", ltl_launch(gemm_rows_kernel<MT, TC, EPI, FZ>, dim3((N + ROWS_NC - 1) / ROWS_NC, ksplit), dim3(128), smem, s,
+                                            ltl_pdl_enabled(), (const bf16*)A, (const bf16*)B, (TC*)C, M, N, K, cps, fa));
     return ltl_check_launch("gemm_rows");
+}
+
+template <int MT, typename TC, int EPI>
+int launch_rows(const void* A, const void* B, void* C, int M, int N, int K, int ksplit, cudaStream_t s, const LtlGemmFuse& fz)
+{
+    if (EPI == ROWS_EPI_RESID || fz.ssq_in) return launch_rows_fz<MT, TC, EPI, true>(A, B, C, M, N, K, ksplit, s, fz);
+    if constexpr (EPI == ROWS_EPI_RESID) return ltl_fail(LTL_ERR_ARG, "gemm_rows: the residual form needs its fusion arguments");
+    else return launch_rows_fz<MT, TC, EPI, false>(A, B, C, M, N, K, ksplit, s, NoFuse{});
 }
 
 template <typename TC, int EPI>

@@ -61,10 +61,16 @@ template <int BN> size_t smem_bytes(int stages) { return stages * stage_bytes<BN
 // atomic counter) and only the one that draws the last ticket reads the others' slices.
 // MAJ = 1: both operands MN-major - A is X [K, M] and B is Y [K, N] in memory (the contraction runs down the
 // rows), i.e. C = X^T Y, the weight-gradient product of two token-major activations without a transpose.
-template <int BN, typename TC, int EPI, int MAJ = 0>
+// FZ selects the instantiations that take the fusion arguments; the others keep an empty parameter, so the kernels of
+// the plain paths are exactly what they were without the fused forms (their presence alone cost 1 - 2 % of a decode pass).
+struct NoFuse {};
+template <bool FZ> struct FuseArg { typedef NoFuse type; };
+template <> struct FuseArg<true> { typedef LtlGemmFuse type; };
+
+template <int BN, typename TC, int EPI, int MAJ = 0, bool FZ = false>
 __global__ void __launch_bounds__(192, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               TC* C, const TC* R, int M, int N, int K, int STAGES, int b_early, const LtlGemmFuse fz, int* __restrict__ err)
+               TC* C, const TC* R, int M, int N, int K, int STAGES, int b_early, const typename FuseArg<FZ>::type fz, int* __restrict__ err)
 {
     // b_early: B holds weights that no kernel of the surrounding programmatic-launch chain writes (the decode
     // step), so the first ring of B tiles is requested before griddepcontrol.wait and lands under the tail of
@@ -173,11 +179,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quad = warp & 3;                        // TMEM lane quadrant this warp may read
         const int row = m0 + quad * 32 + lane;
         float rscale = 1.0f;                              // deferred RMSNorm factor of this row
-        const bool scaled = (EPI == EPI_NONE || EPI == EPI_SWIGLU) && fz.ssq_in != nullptr;
-        if (scaled && row < M) {
-            float ss = 0.0f;
-            for (int t = 0; t < fz.ssq_tiles; ++t) ss += fz.ssq_in[(size_t)row * fz.ssq_tiles + t];
-            rscale = 1.0f / sqrtf(ss * fz.inv_dim + fz.eps);
+        constexpr bool scaled = FZ && (EPI == EPI_NONE || EPI == EPI_SWIGLU);
+        if constexpr (scaled) {
+            if (row < M) {
+                float ss = 0.0f;
+                for (int t = 0; t < fz.ssq_tiles; ++t) ss += fz.ssq_in[(size_t)row * fz.ssq_tiles + t];
+                rscale = 1.0f / sqrtf(ss * fz.inv_dim + fz.eps);
+            }
         }
         if (ok) {
 #pragma unroll 1
@@ -257,7 +265,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
         }
-        if (EPI == EPI_RESID) {
+        if constexpr (EPI == EPI_RESID && FZ) {
             // Every epilogue thread gets here whatever its wait returned, so the named barrier always completes.
             __threadfence();                                              // this CTA's slice is visible ...
             asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -598,10 +606,29 @@ int launch(const void* A, const void* B, void* C, const void* R, int M, int N, i
                                                       (int)smem_bytes<BN>(Ring<BN>::STAGES)));
         attr_set = true;
     }
-    LTL_CUDA("gemm_tc launch", ltl_launch(gemm_tc_kernel<BN, TC, EPI>, grid, dim3(192), smem, s, ltl_pdl_enabled(),
-                                          ma, mb, (TC*)C, (const TC*)R, M, N, K, stages, b_early_enabled() && ltl_pdl_enabled() ? 1 : 0,
-                                          fz, g_err_flag));
-    return ltl_check_launch("gemm_tc");
+    const int early = b_early_enabled() && ltl_pdl_enabled() ? 1 : 0;
+    if (EPI == EPI_RESID || fz.ssq_in) {
+        if constexpr (EPI == EPI_ATOMIC) {
+            return ltl_fail(LTL_ERR_ARG, "gemm_tc: the accumulating epilogue takes no fusion");
+        } else {
+            static bool fz_attr_set = false;
+            if (!fz_attr_set) {
+                LTL_CUDA("gemm_tc attr", cudaFuncSetAttribute(gemm_tc_kernel<BN, TC, EPI, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                              (int)smem_bytes<BN>(Ring<BN>::STAGES)));
+                fz_attr_set = true;
+            }
+            LTL_CUDA("gemm_tc launch", ltl_launch(gemm_tc_kernel<BN, TC, EPI, 0, true>, grid, dim3(192), smem, s, ltl_pdl_enabled(),
+                                                  ma, mb, (TC*)C, (const TC*)R, M, N, K, stages, early, fz, g_err_flag));
+            return ltl_check_launch("gemm_tc");
+        }
+    }
+    if constexpr (EPI == EPI_RESID) {
+        return ltl_fail(LTL_ERR_ARG, "gemm_tc: the residual form needs its fusion arguments");
+    } else {
+        LTL_CUDA("gemm_tc launch", ltl_launch(gemm_tc_kernel<BN, TC, EPI>, grid, dim3(192), smem, s, ltl_pdl_enabled(),
+                                              ma, mb, (TC*)C, (const TC*)R, M, N, K, stages, early, NoFuse{}, g_err_flag));
+        return ltl_check_launch("gemm_tc");
+    }
 }
 
 template <int BN>
@@ -626,7 +653,7 @@ int launch_mn(const void* X, const void* Y, float* C, int M, int N, int K, int k
                                                       (int)smem_bytes<BN>(BN == 256 ? 2 : 4)));
         attr_set = true;
     }
-    gemm_tc_kernel<BN, float, EPI_ATOMIC, 1><<<grid, 192, smem, s>>>(ma, mb, C, nullptr, M, N, K, stages, 0, LtlGemmFuse{}, g_err_flag);
+    gemm_tc_kernel<BN, float, EPI_ATOMIC, 1><<<grid, 192, smem, s>>>(ma, mb, C, nullptr, M, N, K, stages, 0, NoFuse{}, g_err_flag);
     return ltl_check_launch("gemm_tc_mn");
 }
 
