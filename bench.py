@@ -250,7 +250,7 @@ def run_decode(args, dist):
     line = dict(
         metric="decode_tokens_per_s", value=tokens / (dev_ms * 1e-3), unit="tokens/s", n_gpus=dist.world,
         steps=args.steps, warmup=args.warmup, ms_per_step=dev_ms / args.steps, higher_is_better=True,
-        scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
+        scaling=args.decode_scaling, vs_baseline=None, dtype="bf16", data="synthetic",
         config=dict(workload=f"configs[2] batched greedy decode: V8000 D512 L8 H8 F1408 ctx1024, {NSEQ_TOTAL} seqs x "
                              f"({N_PROMPT} prompt + {N_NEW} generated), sequences sharded over GPUs",
                     nseq_per_gpu=nseq, n_prompt=N_PROMPT, n_new=N_NEW, parallelism=f"dp{dist.world} (no collective)",
@@ -701,10 +701,15 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="train4: layer count override (profiling aid; the metric uses 16)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--nseq", type=int, default=NSEQ_TOTAL, help="sequences over all GPUs (profiling aid; the metric uses 256)")
+    ap.add_argument("--decode-scaling", default="strong", choices=["strong", "weak"],
+                    help="decode: strong = the configuration's sequences split over the GPUs (configs[2]: 32/64/128/256 per GPU at "
+                         "8/4/2/1 GPUs; the metric); weak = --nseq sequences on EVERY GPU")
     ap.add_argument("--n-prompt", type=int, default=N_PROMPT, help="prompt length (profiling aid; the metric uses 128)")
     ap.add_argument("--n-new", type=int, default=N_NEW, help="generated tokens per sequence (profiling aid; the metric uses 512)")
     args = ap.parse_args()
     NSEQ_TOTAL, N_PROMPT, N_NEW = args.nseq, args.n_prompt, args.n_new
+    if args.decode_scaling == "weak":
+        NSEQ_TOTAL = args.nseq * int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
         if rank == 0:
