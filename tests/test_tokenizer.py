@@ -204,3 +204,28 @@ def test_id_batches_layout_and_range_check():
         if torch.cuda.is_available():
             raise T.TokenizerError("IdBatches: page-locked memory needs a CUDA device")
         T.IdBatches(w, 2, 3, 10, pinned=True)
+
+
+@pytest.mark.gpu
+def test_text_to_device_steps_through_page_locked_batches():
+    """Text -> BPE ids -> windows -> page-locked [B, T] blocks -> the device training step."""
+    from lanternl_b200 import gpu_transformer as GT
+    text = corpus(11, 1500)
+    tok = T.Tokenizer(text=text, vocab_size=320).train()
+    ids = tok.encode(text)
+    assert tok.decode(ids) == text
+    w = T.build_windows([ids], 32)
+    m = GT.new(dict(vocab=tok.vocab_size, dim=32, layers=1, heads=2, ffn=64, max_seq=32, batch_size=8, optimizer="sgd"))
+    ib = T.IdBatches(w, batch=8, seq_len=32, vocab=tok.vocab_size)
+    assert ib.pinned and len(ib) >= 4
+    losses = []
+    for epoch in range(3):
+        for blk_ids, blk_tgt, valid in ib:
+            loss, correct, n, gnorm, finite = m.train_step_ids(blk_ids, blk_tgt, 0.5, m.steps + 1)
+            assert finite and n == valid
+            losses.append(loss)
+    assert losses[-1] < losses[0]
+    # the packed blocks are what the window path packs itself
+    a, b, _ = m._pack(w[:8], 8)
+    i0, t0, _ = ib.fill(0)
+    assert np.array_equal(a, i0) and np.array_equal(b, t0)
