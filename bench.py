@@ -170,6 +170,12 @@ def shard_rows(rows, world, rank):
     return np.ascontiguousarray(rows[rank * n:(rank + 1) * n])
 
 
+# DRAM bytes per algorithmic byte of the decode attention kernel: 101.08 MB read + 3.16 MB written for 100.9 MB of K/V
+# rows in the committed ncu summary of a 128-sequence launch (profiles/decode_attn_bulk_ncu_full.md).  Every K/V byte
+# crosses HBM once whatever the batch, so the traffic of a full-size launch is this ratio times its algorithmic bytes.
+ATTN_TRAFFIC_PER_ALGORITHMIC_BYTE = 104.24 / 100.9
+
+
 def decode_bytes(cfg, nparams, nseq, n_prompt, n_new):
     """Algorithmic HBM bytes of the decode phase on one GPU: per step the bf16 weights once, the
     K/V of every cached position of every sequence once, and the appended K/V."""
@@ -259,7 +265,10 @@ def run_decode(args, dist):
                  d2h_bytes_per_step=int(out_host.nbytes) * dist.world),
         gpu_launches=int(launches),
         roofline=dict(bound="hbm", achieved=achieved, peak=pk["hbm_gbs"], unit="GB/s", frac=achieved / pk["hbm_gbs"],
-                      traffic=None, peak_source=pk["source"],
+                      traffic=int(ATTN_TRAFFIC_PER_ALGORITHMIC_BYTE * attn[n_mid]["bytes"]),
+                      traffic_source="dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of this kernel at 128 sequences x "
+                                     "cache length 385 (104.2 MB for 100.9 MB algorithmic), scaled by the bytes one launch streams here",
+                      peak_source=pk["source"],
                       kernel=f"decode_attn_bulk_kernel<bf16,64>, {nseq} sequences at cache length {n_mid} (mean of the run), "
                              "one launch per layer, CUDA events on the launching stream",
                       algorithmic_bytes_per_launch=attn[n_mid]["bytes"], us_per_launch=attn[n_mid]["us"],
