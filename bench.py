@@ -479,7 +479,7 @@ def run_train4(args, dist):
         gpu_launches=int(launches),
         roofline=dict(bound="tensor", achieved=gemm_tf, peak=pk["bf16_tflops"], unit="TFLOP/s", frac=gemm_tf / pk["bf16_tflops"],
                       traffic=None, peak_source=pk["source"],
-                      kernel=f"gemm_tc_kernel<128,bf16>: feed-forward up projection of one micro-batch, {R} x {F2} x {D}, "
+                      kernel=f"gemm_tc_persist_kernel<bf16> (128 x 256 tiles): feed-forward up projection of one micro-batch, {R} x {F2} x {D}, "
                              "10 launches back to back, CUDA events on the launching stream",
                       flops_per_launch=2.0 * R * F2 * D, us_per_launch=gms.value * 1e3,
                       whole_step=dict(note="model FLOPs (6 x matrix parameters x tokens + causal attention) over the step time, per GPU; "
