@@ -788,7 +788,9 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
     const size_t cslot = (size_t)slot0 * H * m->T * hd * e;
     // Every kernel of the step is launched with programmatic stream serialization: each calls
     // griddepcontrol.wait before touching anything a kernel of the step writes, so only launch latency and
-    // prologues overlap (the few-row GEMM also reads its weights ahead of the wait: no kernel of the step writes them).
+    // prologues overlap (the GEMMs also request their weights ahead of the wait: no kernel of the step writes them, and
+    // what does write them - the mirror kernels after an optimizer step or a parameter upload - is separated from this
+    // chain by a fully ordered operation: the token upload of a single step, or the prefill of a generation).
     struct PdlScope { bool prev; PdlScope(bool on) : prev(ltl_pdl_enabled()) { ltl_pdl_set(on); } ~PdlScope() { ltl_pdl_set(prev); } } pdl(m->use_pdl);
     int bn_o, s_o, bn_d, s_d;
     ltl_gemm_tc_plan_split(nseq, D, D, &bn_o, &s_o);
