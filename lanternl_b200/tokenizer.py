@@ -97,6 +97,8 @@ class Tokenizer:
         self.min_frequency = cfg.get("min_frequency", 2)
         sp = cfg.get("special_tokens")
         self.special_tokens = [_b(t) for t in (["<pad>", "<s>", "</s>", "<unk>"] if sp is None else sp)]
+        self.log_every = cfg.get("log_every", 50)
+        self.verbose = bool(cfg.get("verbose", False))          # the reference prints by default; a library does not
         self.merges = []
         self.trained = False
         self._memo = {}
@@ -224,7 +226,12 @@ class Tokenizer:
                     heapq.heappush(heap, (-bump(p, fq, widx), _key(*p), p[0], p[1]))
             counts.pop((a, b), None)
             where.pop((a, b), None)
-        return self._rebuild_vocab()
+            if self.verbose and len(self.merges) % self.log_every == 0:
+                print("Merge #%d: %r + %r (count=%d)" % (len(self.merges), a, b, top[0]))
+        self._rebuild_vocab()
+        if self.verbose:
+            print("Vocabulary: %d tokens from %d merges" % (self.vocab_size, len(self.merges)))
+        return self
 
     # ---- encode / decode ----------------------------------------------------------------------------------
     def _bpe(self, chunk):

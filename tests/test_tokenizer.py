@@ -31,6 +31,15 @@ def test_reference_round_trip_case():
     assert [tok.vocab[t] for t in (b"<pad>", b"<s>", b"</s>", b"<unk>")] == [1, 2, 3, 4] and tok.unk_id == 4
 
 
+def test_reference_example_script_case():
+    """examples/train_tokenizer.lua: the same vocab_size 100 on a longer text - still no merges; the saved file is the header alone."""
+    tok = T.Tokenizer.new(dict(text="hello world, this is a test of the lanternl tokenizer. it learns words and subwords.",
+                               vocab_size=100, verbose=False)).train()
+    ids = tok.encode("hello world")
+    assert ids == [b + 5 for b in b"hello world"] and tok.decode(ids) == b"hello world"
+    assert tok.dumps() == b"bpe\t2\nspecials\t4\n<pad>\n<s>\n</s>\n<unk>\nmerges\t0\n"
+
+
 @pytest.mark.parametrize("text,chunks", [
     (b"hello world", [b"hello", b" world"]),
     (b"a  b", [b"a", b"  ", b"b"]),                           # two blanks: the run of blanks wins over ' ?%a+'
