@@ -1,7 +1,7 @@
 // Few-row GEMM for the decode step of a small shard: C[M <= 64, N] = A[M,K] B[N,K]^T, bf16 in, fp32
-// accumulate.  With 1 ... 64 sequences a decode GEMM moves a few hundred KB of weights and is bound by
+// accumulate.  With a few dozen sequences a decode GEMM moves a few hundred KB of weights and is bound by
 // the latency of one dependent launch, not by bytes or flops: a 128-row tcgen05 tile would spend
-// its time on barrier, TMA and TMEM round trips for a tile that is at most half full.  This kernel
+// its time on barrier, TMA and TMEM round trips for a tile that is at most a quarter full.  This kernel
 // keeps the whole chain to one memory round trip:
 //   * every thread reads its slice of the WEIGHTS straight into mma.sync B fragments with 128-bit
 //     loads, issued before griddepcontrol.wait - weights do not change inside a decode step, so the
@@ -14,6 +14,8 @@
 // leaves the sum unchanged.
 // Split-K writes fp32 partial matrices [ksplit][M][N] that the residual + RMSNorm kernel adds in a
 // fixed order, exactly like the tcgen05 path (reference op: luaTL_matmul, cuda/luaTL_core.cu:1506).
+// The decode step uses it up to 32 sequences (measured faster than tcgen05 tiles there, slower at 64,
+// where four row tiles per warp and a 64 KB activation stage per CTA weigh more than the tile set-up).
 #include "common.cuh"
 #include "ops.h"
 
