@@ -68,6 +68,38 @@ typedef struct {
 
 typedef struct luaTL_pool_s luaTL_pool_t;
 
+/* cuda/luaTL_core.cu:199-212: what the GEMM planner reports */
+typedef struct {
+    int32_t tm, tn, tk, block_x, block_y, grid_x, grid_y;
+    int32_t shmem_bytes, kernel_id, unroll, use_tensor_core, from_cache;
+    double  measured_ms;
+} luaTL_plan_t;
+
+/* cuda/luaTL_core.cu:251-257: bump arena over one pool block; the host bumps offset / peak itself
+ * (ai/gpu/luaTL.lua:345-356) */
+typedef struct {
+    char*    base;
+    uint64_t capacity, offset, peak, alignment;
+    void*    pool;
+} luaTL_arena_t;
+
+/* cuda/luaTL_core.cu:259-277: command and queue of the v1 Pipeline (ai/gpu/luaTL.lua:48-63, :797-819) */
+typedef struct {
+    int32_t  op, dtype, act, flags;
+    int32_t  i0, i1, i2, i3;
+    float    f0, f1, f2, f3, f4, f5;
+    uint64_t n;
+    void    *p0, *p1, *p2, *p3, *p4, *p5;
+} luaTL_cmd_t;
+typedef struct {
+    luaTL_cmd_t* cmds;
+    int32_t      count, capacity, flags, status;
+    void        *stream, *ev_start, *ev_stop;
+    double       last_ms;
+    uint64_t     total_runs, total_ops;
+    int32_t      owns_stream, timing;
+} luaTL_pipeline_t;
+
 /* cuda/luaTL_core.cu:238-249 (56 bytes; Lua reads and writes the fields directly) */
 typedef struct {
     void*    data;
@@ -127,7 +159,25 @@ int         luaTL_sync(void);                            /* core.cu:1749 */
 int         luaTL_get_devinfo(int device, luaTL_devinfo_t* out);     /* core.cu:1755 */
 int         luaTL_mem_info(uint64_t* freeb, uint64_t* totalb);       /* core.cu:1765 */
 
-/* ---------------- pool and tensors (cuda/luaTL_core.cu:585-886,1839-2159) ---------------- */
+/* ---------------- streams and page-locked host memory (cuda/luaTL_core.cu:1776-1813) ------ */
+void* luaTL_stream_create(int nonblocking);              /* core.cu:1776 */
+void  luaTL_stream_destroy(void* s);                     /* core.cu:1786 */
+int   luaTL_stream_sync(void* s);                        /* core.cu:1793 */
+void* luaTL_host_alloc_pinned(uint64_t bytes);           /* core.cu:1801 */
+void  luaTL_host_free_pinned(void* p);                   /* core.cu:1809 */
+
+/* ---------------- pool and tensors (cuda/luaTL_core.cu:585-886,1818-2159) ---------------- */
+luaTL_pool_t* luaTL_pool_create(int device);             /* core.cu:1818; device < 0: the bound device */
+void          luaTL_pool_destroy(luaTL_pool_t* P);       /* core.cu:1826; the default pool is left alone */
+luaTL_arena_t* luaTL_arena_create(luaTL_pool_t* P, uint64_t bytes);   /* core.cu:1880 */
+void           luaTL_arena_destroy(luaTL_arena_t* A);                 /* core.cu:1901 */
+void*          luaTL_arena_alloc(luaTL_arena_t* A, uint64_t bytes);   /* core.cu:1908: 256-byte aligned bump */
+void           luaTL_arena_reset(luaTL_arena_t* A);                   /* core.cu:1924 */
+/* legacy raw-pointer calls, cuda/luaTL_core.cu:2147-2153 */
+float* luaTL_gpu_malloc(uint64_t nelem);
+void   luaTL_gpu_free(float* p);
+int    luaTL_to_gpu(const float* host, float* dev, uint64_t nelem);
+int    luaTL_to_cpu(const float* dev, float* host, uint64_t nelem);
 luaTL_pool_t* luaTL_default_pool(void);
 void*         luaTL_tensor_alloc(luaTL_pool_t* P, uint64_t bytes);
 void          luaTL_tensor_free(luaTL_pool_t* P, void* ptr);
@@ -151,8 +201,9 @@ int  luaTL_download_i32(const void* dev, int32_t* host, uint64_t n);     /* trai
 int  luaTL_download_f32(const void* dev, float* host, uint64_t n);       /* train.cu:1290 */
 
 /* ---------------- one-shot math on the path (synchronous) ------------------------------- */
-/* cuda/luaTL_train.cu:1075: C = post(alpha * A B + bias) + beta * C with explicit strides.
- * pre_op other than 0 is not supported here (LUATL_ERR_UNSUPPORT). */
+/* cuda/luaTL_train.cu:1075: C = post(alpha * pre(A) B + bias) + beta * C with explicit strides.
+ * pre_op (cuda/luaTL_core.cu:84-90): 0 none; 1 RMSNorm prologue - A(m,k) * rowscale[m] * gamma[k], rowscale computed
+ * from A with eps when NULL (cuda/luaTL_train.cu:159-204); 2 gelu, 3 silu, 4 relu on A. */
 int luaTL_gemm_ex(const void* A, const void* B, void* C, const void* bias, const void* gamma,
                   const float* rowscale, int M, int N, int K, int dtype,
                   long long a_rs, long long a_cs, long long b_rs, long long b_cs,
@@ -200,6 +251,33 @@ int luaTL_elementwise(const void* A, const void* B, void* C, uint64_t n, int dty
                       float alpha, float beta);                                                           /* core.cu:2308 */
 int luaTL_adamw(float* w, const void* g, float* m, float* v, void* w_lp, uint64_t n, int grad_dtype,
                 float lr, float beta1, float beta2, float eps, float wd, int step, float clip);           /* core.cu:2412 */
+/* cuda/luaTL_core.cu:2373-2410, cuda/luaTL_train.cu:1203-1270: small ops the model itself does not queue */
+int luaTL_bcast_add(const void* x, const void* v, void* out, int rows, int cols, float alpha, int dtype);   /* out = x + alpha * v[c] */
+int luaTL_transpose(const void* in, void* out, int rows, int cols, int dtype);
+int luaTL_rms_rowscale(const void* x, float* scale, int rows, int cols, float eps, int dtype);             /* 1/sqrt(mean x^2 + eps) */
+int luaTL_reduce_cols(const void* x, float* out, int rows, int cols, long long row_stride, float alpha,
+                      float beta, int dtype);                                                             /* train.cu:1203 */
+int luaTL_gather_rows(const void* src, const void* idx, void* dst, int n, int cols, int src_rows, int dtype);  /* train.cu:1251 */
+int luaTL_row_rms(const void* x, float* out, int rows, int cols, long long rs, long long cs, float eps, int dtype); /* train.cu:1261 */
+/* GEMM planner, cuda/luaTL_core.cu:2163-2266.  One fixed plan per shape here: plan_gemm reports it, the override is
+ * accepted and has no effect, autotune_benchmark times that plan. */
+int  luaTL_plan_gemm(int M, int N, int K, int dtype, int allow_tc, luaTL_plan_t* out);
+void luaTL_set_tile_override(int kernel_id);
+void luaTL_tune_reset(void);
+int  luaTL_autotune_benchmark(int M, int N, int K, int dtype, int iters, luaTL_plan_t* out);
+/* legacy float-only wrappers, cuda/luaTL_core.cu:2289-2371 */
+int matmul_cuda(const float* A, const float* B, float* C, int M, int N, int K);
+int fused_rmsnorm_matmul_cuda(const float* x, const float* gamma, const float* W, float* out, const float* bias,
+                              int M, int N, int K, float eps);
+int fused_gelu_matmul_cuda(const float* x, const float* W, float* out, const float* bias, int M, int N, int K);
+int fused_silu_matmul_cuda(const float* x, const float* W, float* out, const float* bias, int M, int N, int K);
+int fused_matmul_gelu_cuda(const float* A, const float* B, float* C, const float* bias, int M, int N, int K);
+int add_cuda(const float* A, const float* B, float* C, uint64_t n);
+int add_inplace_cuda(float* A, const float* B, uint64_t n, float alpha);
+int rmsnorm_cuda(const float* x, const float* w, float* out, int rows, int cols, float eps);
+int rmsnorm_inplace_cuda(float* x, const float* w, int rows, int cols, float eps);
+int softmax_cuda(const float* x, float* out, int rows, int cols);
+int fused_add_bias_softmax_cuda(const float* x, const float* bias, float* out, int rows, int cols, float scale, int causal);
 /* New: w -= lr * (f * g + wd * w) with f = min(1, max_norm / (sqrt(*nsq) + 1e-6)) when nsq != NULL
  * and max_norm > 0 (rule: ai/optim/optim2.lua:93-99; clip factor: cuda/luaTL_train.cu:950-952). */
 int luaTL_sgd(float* w, const float* g, uint64_t n, float lr, float wd, const float* nsq, float max_norm);
@@ -258,9 +336,10 @@ int  luaTL_timer_stop(float* ms);
 int luaTL_rmsnorm_bwd_residual(const float* x, const float* gamma, const float* dy, float* res, void* res_bf16, float* dgamma,
                                int rows, int cols, float eps);
 /* New: sampling beyond greedy on the device, the rule of pick_token (ai/optim/lmtrain.lua:1364-1436): temperature
- * <= 0 is the argmax; top_k in 1..128 keeps the k largest logits (descending, ties by lower index), top_p in (0, 1)
- * cuts the nucleus inside that set (top_p without top_k is not supported); top_k = 0 walks the whole row in index
- * order.  The uniform draw is a 24-bit counter-based hash of (seed, row, counter), so results are reproducible.
+ * <= 0 is the argmax; top_k in 1..vocab-1 keeps the k largest logits (descending, ties by lower index); top_p in (0, 1)
+ * cuts the nucleus inside that set, or inside the whole row sorted descending when no top_k is given; top_k = 0 without
+ * top_p walks the whole row in index order.  The uniform draw is a 24-bit counter-based hash of (seed, row, counter),
+ * so results are reproducible.
  * luaTL_sample_rows: one index per row of fp32 logits [rows, vocab], counters[r] = position of row r (NULL: 0).
  * luaTL_lm_set_sampling: the same rule inside luaTL_lm_generate*, counter = the sequence's position; stop_id >= 0:
  * a sequence that emitted it keeps emitting it (stop_id = -1: none).  The reference samples on the host from
@@ -282,6 +361,14 @@ int           luaTL_prog_capture(luaTL_prog_t* P);
 int           luaTL_prog_replay(luaTL_prog_t* P);
 int           luaTL_prog_wait(luaTL_prog_t* P);
 void          luaTL_prog_graph_free(luaTL_prog_t* P);
+
+/* ---------------- v1 Pipeline (cuda/luaTL_core.cu:2431-2686) ---------------------------------- */
+luaTL_pipeline_t* luaTL_pipeline_create(int capacity, int timing);
+void              luaTL_pipeline_destroy(luaTL_pipeline_t* P);
+void              luaTL_pipeline_reset(luaTL_pipeline_t* P);
+int               luaTL_pipeline_push(luaTL_pipeline_t* P, const luaTL_cmd_t* cmd);
+int               luaTL_pipeline_run(luaTL_pipeline_t* P);
+int               luaTL_pipeline_wait(luaTL_pipeline_t* P);
 
 /* ---------------- fused device-resident model (new) ------------------------------------- */
 typedef struct {
@@ -340,6 +427,14 @@ int luaTL_lm_train_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* target
 /* Same with ids/targets already on the device. */
 int luaTL_lm_train_step_dev(luaTL_lm_t* m, const int32_t* d_ids, const int32_t* d_targets,
                             const luaTL_lm_train_args_t* a, luaTL_lm_result_t* out);
+/* The captured training step (ai/gpu/gpu_transformer.lua:714-733 capture / maybe_capture, :643 replay rule): with
+ * on = 1, the forward + loss + backward of luaTL_lm_train_step* is captured as one CUDA graph on the third step and
+ * replayed on every later step whose valid-target count, accumulate flag and id / target buffers are those of the
+ * capture (otherwise it is captured again); the optimizer launches stay outside, their scalars change per step.
+ * Steps whose gradient exchange overlaps the backward (bf16 model, more than one rank) are not captured.
+ * luaTL_lm_graph_ready: 1 while a captured step exists. */
+int luaTL_lm_set_graph(luaTL_lm_t* m, int on);
+int luaTL_lm_graph_ready(const luaTL_lm_t* m);
 /* Forward only: loss / accuracy, optionally the logits [rows_out, vocab] to the host
  * (last_only = 1: only row n_tokens - 1 of sequence 0, what generate reads). */
 int luaTL_lm_eval_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* targets, luaTL_lm_result_t* out);
@@ -374,6 +469,16 @@ int luaTL_comm_init(const char* id128, int world, int rank);
 int luaTL_comm_world(void);
 int luaTL_comm_allreduce_f32(float* dev, uint64_t n);
 void luaTL_comm_destroy(void);
+/* Failure handling of the exchange.  No entry point blocks on a collective without a limit: the host polls the stream
+ * and the communicator's asynchronous error state; on an error, or when `ms` milliseconds pass (default 120000, or
+ * LUATL_COMM_TIMEOUT_MS), the communicator is aborted and the call returns LUATL_ERR_CUDA ("... did not finish within
+ * ... ms (a rank did not arrive?)").  After that luaTL_comm_world() is 1 until luaTL_comm_init is called again. */
+void luaTL_comm_set_timeout(int ms);
+/* The same wait loop run against fakes, usable without a GPU: the fake collective finishes when the file `arrive_path`
+ * exists (NULL: never), the fake communicator reports `async_error` from the `error_after`-th poll on (0: never).
+ * *aborted receives 1 when the loop tore the communicator down.  Neither has a counterpart in the reference, which has
+ * no collective. */
+int luaTL_comm_selftest_wait(const char* arrive_path, int timeout_ms, int async_error, int error_after, int* aborted);
 
 #ifdef __cplusplus
 }

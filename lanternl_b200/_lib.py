@@ -66,6 +66,32 @@ class DevInfo(C.Structure):
         + [("name", C.c_char * 256)])
 
 
+class Plan(C.Structure):
+    _fields_ = ([(n, C.c_int32) for n in ("tm", "tn", "tk", "block_x", "block_y", "grid_x", "grid_y", "shmem_bytes",
+                                          "kernel_id", "unroll", "use_tensor_core", "from_cache")]
+                + [("measured_ms", C.c_double)])
+
+
+class Arena(C.Structure):
+    _fields_ = [("base", C.c_void_p), ("capacity", C.c_uint64), ("offset", C.c_uint64), ("peak", C.c_uint64),
+                ("alignment", C.c_uint64), ("pool", C.c_void_p)]
+
+
+class Cmd(C.Structure):
+    _fields_ = ([("op", C.c_int32), ("dtype", C.c_int32), ("act", C.c_int32), ("flags", C.c_int32)]
+                + [(f"i{k}", C.c_int32) for k in range(4)]
+                + [(f"f{k}", C.c_float) for k in range(6)]
+                + [("n", C.c_uint64)]
+                + [(f"p{k}", C.c_void_p) for k in range(6)])
+
+
+class Pipeline(C.Structure):
+    _fields_ = [("cmds", C.POINTER(Cmd)), ("count", C.c_int32), ("capacity", C.c_int32), ("flags", C.c_int32),
+                ("status", C.c_int32), ("stream", C.c_void_p), ("ev_start", C.c_void_p), ("ev_stop", C.c_void_p),
+                ("last_ms", C.c_double), ("total_runs", C.c_uint64), ("total_ops", C.c_uint64),
+                ("owns_stream", C.c_int32), ("timing", C.c_int32)]
+
+
 class LmConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("vocab", "dim", "layers", "heads", "ffn", "max_seq", "batch",
                                          "decode_batch", "tie", "dtype", "use_rope", "rope_interleaved",
@@ -95,6 +121,33 @@ SIGNATURES = {
     "luaTL_get_last_error": (_cp, []), "luaTL_has_error": (_i, []), "luaTL_clear_error": (None, []),
     "luaTL_sync": (_i, []), "luaTL_get_devinfo": (_i, [_i, C.POINTER(DevInfo)]),
     "luaTL_mem_info": (_i, [C.POINTER(_u64), C.POINTER(_u64)]),
+    "luaTL_stream_create": (_vp, [_i]), "luaTL_stream_destroy": (None, [_vp]), "luaTL_stream_sync": (_i, [_vp]),
+    "luaTL_host_alloc_pinned": (_vp, [_u64]), "luaTL_host_free_pinned": (None, [_vp]),
+    "luaTL_pool_create": (_vp, [_i]), "luaTL_pool_destroy": (None, [_vp]),
+    "luaTL_arena_create": (C.POINTER(Arena), [_vp, _u64]), "luaTL_arena_destroy": (None, [C.POINTER(Arena)]),
+    "luaTL_arena_alloc": (_vp, [C.POINTER(Arena), _u64]), "luaTL_arena_reset": (None, [C.POINTER(Arena)]),
+    "luaTL_gpu_malloc": (_vp, [_u64]), "luaTL_gpu_free": (None, [_vp]),
+    "luaTL_to_gpu": (_i, [_vp, _vp, _u64]), "luaTL_to_cpu": (_i, [_vp, _vp, _u64]),
+    "luaTL_plan_gemm": (_i, [_i, _i, _i, _i, _i, C.POINTER(Plan)]), "luaTL_set_tile_override": (None, [_i]),
+    "luaTL_tune_reset": (None, []), "luaTL_autotune_benchmark": (_i, [_i, _i, _i, _i, _i, C.POINTER(Plan)]),
+    "luaTL_bcast_add": (_i, [_vp, _vp, _vp, _i, _i, _f, _i]), "luaTL_transpose": (_i, [_vp, _vp, _i, _i, _i]),
+    "luaTL_rms_rowscale": (_i, [_vp, _vp, _i, _i, _f, _i]),
+    "luaTL_reduce_cols": (_i, [_vp, _vp, _i, _i, _ll, _f, _f, _i]),
+    "luaTL_gather_rows": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
+    "luaTL_row_rms": (_i, [_vp, _vp, _i, _i, _ll, _ll, _f, _i]),
+    "matmul_cuda": (_i, [_vp, _vp, _vp, _i, _i, _i]),
+    "fused_rmsnorm_matmul_cuda": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f]),
+    "fused_gelu_matmul_cuda": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
+    "fused_silu_matmul_cuda": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
+    "fused_matmul_gelu_cuda": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
+    "add_cuda": (_i, [_vp, _vp, _vp, _u64]), "add_inplace_cuda": (_i, [_vp, _vp, _u64, _f]),
+    "rmsnorm_cuda": (_i, [_vp, _vp, _vp, _i, _i, _f]), "rmsnorm_inplace_cuda": (_i, [_vp, _vp, _i, _i, _f]),
+    "softmax_cuda": (_i, [_vp, _vp, _i, _i]),
+    "fused_add_bias_softmax_cuda": (_i, [_vp, _vp, _vp, _i, _i, _f, _i]),
+    "luaTL_pipeline_create": (C.POINTER(Pipeline), [_i, _i]), "luaTL_pipeline_destroy": (None, [C.POINTER(Pipeline)]),
+    "luaTL_pipeline_reset": (None, [C.POINTER(Pipeline)]),
+    "luaTL_pipeline_push": (_i, [C.POINTER(Pipeline), C.POINTER(Cmd)]),
+    "luaTL_pipeline_run": (_i, [C.POINTER(Pipeline)]), "luaTL_pipeline_wait": (_i, [C.POINTER(Pipeline)]),
     "luaTL_default_pool": (_vp, []), "luaTL_tensor_alloc": (_vp, [_vp, _u64]),
     "luaTL_tensor_free": (None, [_vp, _vp]), "luaTL_pool_trim": (None, [_vp]),
     "luaTL_pool_get_stats": (_i, [_vp, C.POINTER(PoolStats)]), "luaTL_pool_owns": (_i, [_vp, _vp]),
@@ -158,6 +211,7 @@ SIGNATURES = {
     "luaTL_lm_params_device": (_vp, [_vp]), "luaTL_lm_grads_device": (_vp, [_vp]),
     "luaTL_lm_train_step": (_i, [_vp, _vp, _vp, C.POINTER(LmTrainArgs), C.POINTER(LmResult)]),
     "luaTL_lm_train_step_dev": (_i, [_vp, _vp, _vp, C.POINTER(LmTrainArgs), C.POINTER(LmResult)]),
+    "luaTL_lm_set_graph": (_i, [_vp, _i]), "luaTL_lm_graph_ready": (_i, [_vp]),
     "luaTL_lm_eval_step": (_i, [_vp, _vp, _vp, C.POINTER(LmResult)]),
     "luaTL_lm_forward": (_i, [_vp, _vp, _i, _i, _vp, _i]),
     "luaTL_lm_state_reset": (_i, [_vp]), "luaTL_lm_slot_reset": (_i, [_vp, _i]), "luaTL_lm_step": (_i, [_vp, _i, C.c_int32, _vp]),
@@ -168,11 +222,12 @@ SIGNATURES = {
     "luaTL_lm_last_timing": (_i, [_vp, C.POINTER(_f), C.POINTER(_f), C.POINTER(_i64)]),
     "luaTL_comm_unique_id": (_i, [_cp]), "luaTL_comm_init": (_i, [_cp, _i, _i]),
     "luaTL_comm_world": (_i, []), "luaTL_comm_allreduce_f32": (_i, [_vp, _u64]),
-    "luaTL_comm_destroy": (None, []),
+    "luaTL_comm_destroy": (None, []), "luaTL_comm_set_timeout": (None, [_i]),
+    "luaTL_comm_selftest_wait": (_i, [_cp, _i, _i, _i, C.POINTER(C.c_int)]),
 }
 
 # int-returning functions whose value is not a status
-_NOT_STATUS = {"luaTL_init", "luaTL_has_error", "luaTL_pool_owns", "luaTL_lm_ntensors", "luaTL_lm_state_len",
+_NOT_STATUS = {"luaTL_init", "luaTL_has_error", "luaTL_pool_owns", "luaTL_lm_ntensors", "luaTL_lm_state_len", "luaTL_lm_graph_ready",
                "luaTL_comm_world"}
 
 _lib = None

@@ -20,6 +20,7 @@ static int g_has_err = 0;
 static int g_verbose = 0;
 static int g_initialized = 0;
 static int g_device = 0;
+static int g_bound_once = 0;
 static int g_sm_count = 148;
 static uint64_t g_epoch = 1;
 static char g_devname[320] = { 0 };
@@ -52,6 +53,7 @@ int ltl_require_init(const char* ctx)
                     "this backend has no CPU fallback", ctx);
 }
 cudaStream_t ltl_default_stream() { return g_stream; }
+int ltl_bound_device() { return g_device; }
 static bool g_pdl = false;
 bool ltl_pdl_enabled() { return g_pdl; }
 void ltl_pdl_set(bool on) { g_pdl = on; }
@@ -67,6 +69,7 @@ static int sync_stream(const char* ctx)
     LTL_CUDA(ctx, cudaStreamSynchronize(g_stream));
     return LTL_OK;
 }
+int ltl_sync_stream(const char* ctx) { return sync_stream(ctx); }
 
 // ------------------------------------------------------------------------------------------
 // caching device pool: power-of-two classes below 1 MiB, 1 MiB granules above
@@ -79,6 +82,7 @@ struct luaTL_pool_s {
     luaTL_pool_stats_t st = {};
 };
 static luaTL_pool_t* g_pool = nullptr;
+static std::vector<luaTL_pool_t*> g_extra_pools;      // made by luaTL_pool_create, freed with the library
 
 static size_t size_class(size_t bytes)
 {
@@ -157,6 +161,8 @@ static void pool_free(luaTL_pool_t* P, void* p)
 // Library workspace for kernels that need scratch (grown outside of any graph capture).
 static float* g_ws = nullptr;
 static size_t g_ws_floats = 0;
+static int* g_tickets = nullptr;         // tile tickets of luaTL_gemm_bf16_resid
+static size_t g_tickets_cap = 0;
 static float* workspace(size_t floats)
 {
     if (floats <= g_ws_floats) return g_ws;
@@ -200,7 +206,13 @@ int luaTL_init(int device)
         return 0;
     }
     if (g_initialized && device == g_device) return count;
-    if (g_initialized) luaTL_shutdown();
+    // One device per process: kernel attributes, cached tensor maps and the streams held by live models and Programs
+    // all belong to the device bound first (the reference binds device 0 once, ai/gpu/luatl_adapter.lua:12).
+    if (g_bound_once && device != g_device) {
+        ltl_fail(LTL_ERR_UNSUPPORTED, "luaTL_init: this process is bound to device %d; one device per process "
+                 "(start one process per GPU)", g_device);
+        return 0;
+    }
     if ((e = cudaSetDevice(device)) != cudaSuccess) { ltl_cuda_fail("cudaSetDevice", e); return 0; }
     if ((e = cudaFree(0)) != cudaSuccess) { ltl_cuda_fail("context creation", e); return 0; }
     cudaDeviceProp prop;
@@ -214,6 +226,7 @@ int luaTL_init(int device)
     g_sm_count = prop.multiProcessorCount > 0 ? prop.multiProcessorCount : 148;
     if ((e = cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking)) != cudaSuccess) { ltl_cuda_fail("cudaStreamCreate", e); return 0; }
     g_device = device;
+    g_bound_once = 1;
     g_pool = new luaTL_pool_s();
     g_pool->device = device;
     g_initialized = 1;
@@ -229,7 +242,13 @@ void luaTL_shutdown(void)
         delete g_pool;
         g_pool = nullptr;
     }
+    for (luaTL_pool_t* P : g_extra_pools) {
+        for (auto& kv : P->owned) cudaFree(kv.first);
+        delete P;
+    }
+    g_extra_pools.clear();
     if (g_ws) { cudaFree(g_ws); g_ws = nullptr; g_ws_floats = 0; }
+    if (g_tickets) { cudaFree(g_tickets); g_tickets = nullptr; g_tickets_cap = 0; }
     if (g_stream) { cudaStreamDestroy(g_stream); g_stream = nullptr; }
     g_initialized = 0;
 }
@@ -286,6 +305,32 @@ int luaTL_mem_info(uint64_t* freeb, uint64_t* totalb)
 // pool and tensors
 // ------------------------------------------------------------------------------------------
 luaTL_pool_t* luaTL_default_pool(void) { return g_pool; }
+
+// cuda/luaTL_core.cu:1818-1838: a second caching pool with its own statistics; the default pool cannot be destroyed.
+luaTL_pool_t* luaTL_pool_create(int device)
+{
+    if (ltl_require_init("pool_create") != LTL_OK) return nullptr;
+    if (device >= 0 && device != g_device) {
+        ltl_fail(LTL_ERR_ARG, "pool_create: device %d is not the device this process is bound to (%d)", device, g_device);
+        return nullptr;
+    }
+    luaTL_pool_t* P = new luaTL_pool_s();
+    P->device = g_device;
+    g_extra_pools.push_back(P);
+    return P;
+}
+void luaTL_pool_destroy(luaTL_pool_t* P)
+{
+    if (!P || P == g_pool) return;
+    for (size_t i = 0; i < g_extra_pools.size(); ++i)
+        if (g_extra_pools[i] == P) {
+            g_extra_pools.erase(g_extra_pools.begin() + i);
+            if (g_initialized) { cudaDeviceSynchronize(); for (auto& kv : P->owned) cudaFree(kv.first); }
+            delete P;
+            cudaGetLastError();
+            return;
+        }
+}
 
 void* luaTL_tensor_alloc(luaTL_pool_t* P, uint64_t bytes)
 {
@@ -350,7 +395,12 @@ int luaTL_tensor_wrap(luaTL_tensor_t* t, void* data, int rows, int cols, int dty
 void luaTL_tensor_release(luaTL_tensor_t* t)
 {
     if (!t) return;
-    if (t->owns && t->data && g_initialized && g_pool) pool_free((luaTL_pool_t*)(t->pool ? t->pool : g_pool), t->data);
+    if (t->owns && t->data && g_initialized && g_pool) {
+        luaTL_pool_t* P = (luaTL_pool_t*)(t->pool ? t->pool : g_pool);
+        bool alive = P == g_pool;
+        for (luaTL_pool_t* q : g_extra_pools) alive = alive || q == P;
+        if (alive) pool_free(P, t->data);
+    }
     t->data = nullptr; t->owns = 0; t->nelem = 0; t->nbytes = 0;
 }
 void luaTL_tensor_release_safe(luaTL_tensor_t* t)
@@ -493,10 +543,8 @@ int luaTL_gemm_ex(const void* A, const void* B, void* C, const void* bias, const
                   long long c_rs, long long c_cs, long long a_bs, long long b_bs, long long c_bs,
                   int batch, float alpha, float beta, float eps, int pre_op, int post_op)
 {
-    (void)gamma; (void)rowscale; (void)eps;
-    if (pre_op != 0) return ltl_fail(LTL_ERR_UNSUPPORTED, "gemm_ex: pre_op %d is not part of this backend", pre_op);
     GemmDesc g = { A, B, C, bias, nullptr, M, N, K, batch < 1 ? 1 : batch, a_rs, a_cs, b_rs, b_cs, c_rs, c_cs,
-                   a_bs, b_bs, c_bs, alpha, beta, post_op, dtype, dtype, dtype };
+                   a_bs, b_bs, c_bs, alpha, beta, post_op, dtype, dtype, dtype, pre_op, gamma, rowscale, eps };
     ONE_SHOT("gemm_ex", ltl_gemm_simt(g, g_stream));
 }
 int luaTL_gemm(const void* A, const void* B, void* C, const void* bias, const void* gamma,
@@ -650,16 +698,16 @@ int luaTL_gemm_bf16_rows(const void* A, const void* B, void* C, int M, int N, in
 // Arrival counters of the fused residual GEMMs for the immediate entry point: one per output tile, zero at rest.
 static int* abi_tickets(size_t n)
 {
-    static int* buf = nullptr;
-    static size_t cap = 0;
-    if (n > cap) {
-        if (buf) cudaFree(buf);
-        buf = nullptr; cap = 0;
-        if (cudaMalloc(&buf, n * sizeof(int)) != cudaSuccess) return nullptr;
-        cudaMemset(buf, 0, n * sizeof(int));
-        cap = n;
+    if (n > g_tickets_cap) {
+        cudaStreamSynchronize(g_stream);
+        if (g_tickets) cudaFree(g_tickets);
+        g_tickets = nullptr; g_tickets_cap = 0;
+        if (cudaMalloc(&g_tickets, n * sizeof(int)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        // on the library stream (a non-blocking stream is not ordered after the legacy stream's memset)
+        if (cudaMemsetAsync(g_tickets, 0, n * sizeof(int), g_stream) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        g_tickets_cap = n;
     }
-    return buf;
+    return g_tickets;
 }
 int luaTL_gemm_bf16_resid(const void* A, const void* B, float* slices, float* x, const float* gain, void* h, float* ssq,
                           int M, int N, int K, int ksplit, int impl)
@@ -749,6 +797,3 @@ int luaTL_sgd(float* w, const float* g, uint64_t n, float lr, float wd, const fl
 }
 
 }  // extern "C"
-
-// Scratch for Program ops that need it (rmsnorm_bwd); sized before the op list runs.
-float* ltl_library_workspace(size_t floats) { return workspace(floats); }

@@ -19,6 +19,8 @@ int  ltl_cuda_fail(const char* ctx, cudaError_t e);
 int  ltl_check_launch(const char* ctx);            // cudaGetLastError -> status
 int  ltl_require_init(const char* ctx);            // LTL_ERR_CUDA unless luaTL_init succeeded
 cudaStream_t ltl_default_stream();
+int  ltl_bound_device();              // the device luaTL_init bound
+int  ltl_sync_stream(const char* ctx);   // launch check + wait for the library stream (no wait in deferred mode)
 bool ltl_pdl_enabled();               // programmatic dependent launch for the decode-step kernels
 void ltl_pdl_set(bool on);
 int  ltl_sm_count();

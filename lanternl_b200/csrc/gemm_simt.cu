@@ -34,10 +34,12 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
                  const TI* __restrict__ bias, const TC* R, int M, int N, int K,
                  long long a_rs, long long a_cs, long long b_rs, long long b_cs,
                  long long c_rs, long long c_cs, long long a_bs, long long b_bs, long long c_bs,
-                 float alpha, float beta, int post_op, int ksplit)
+                 float alpha, float beta, int post_op, int ksplit,
+                 int pre_op, const TI* __restrict__ gamma, const float* __restrict__ rowscale, float eps)
 {
     __shared__ __align__(16) float As[BK][BM + PAD];
     __shared__ __align__(16) float Bs[BK][BN + PAD];
+    __shared__ float rowsc[BM];
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     // ksplit > 1 (batch == 1 only): blockIdx.z selects a slice of K and the partial product is
@@ -54,6 +56,21 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
         if (R) R += (long long)blockIdx.z * c_bs;
     }
     const int tx = tid & 15, ty = tid >> 4;
+    if (pre_op == 1) {
+        // RMSNorm prologue: the factor of each of the tile's 64 rows - taken from rowscale, or computed here over the
+        // whole of K (four threads per row; every CTA of a row block repeats it, which keeps the op free of scratch).
+        const int r = tid >> 2, q = tid & 3, gm = m0 + r;
+        float part = 0.0f;
+        if (!rowscale && gm < M)
+            for (int k = q; k < K; k += 4) {
+                const float a = Cvt<TI>::ld(A, (size_t)(gm * a_rs + k * a_cs));
+                part = fmaf(a, a, part);
+            }
+        part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
+        part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
+        if (q == 0) rowsc[r] = gm < M ? (rowscale ? rowscale[gm] : rsqrtf(part / (float)K + eps)) : 0.0f;
+        __syncthreads();
+    }
     const bool a_kfast = (a_cs == 1);      // k contiguous in memory
     const bool b_nfast = (b_cs == 1);      // n contiguous in memory
 
@@ -70,7 +87,12 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
             if (a_kfast) { kk = tid & 15; mm = (tid >> 4) + 16 * p; }
             else         { mm = tid & 63; kk = (tid >> 6) + 4 * p; }
             const int gm = m0 + mm, gk = k0 + kk;
-            As[kk][mm] = (gm < M && gk < k_end) ? Cvt<TI>::ld(A, (size_t)(gm * a_rs + gk * a_cs)) : 0.0f;
+            float av = (gm < M && gk < k_end) ? Cvt<TI>::ld(A, (size_t)(gm * a_rs + gk * a_cs)) : 0.0f;
+            if (pre_op == 1) av = av * rowsc[mm] * ((gamma && gk < k_end) ? Cvt<TI>::ld(gamma, gk) : 1.0f);
+            else if (pre_op == 2) av = act_apply(2, av);
+            else if (pre_op == 3) av = act_apply(3, av);
+            else if (pre_op == 4) av = fmaxf(av, 0.0f);
+            As[kk][mm] = av;
             int nn, kb;
             if (b_nfast) { nn = tid & 63; kb = (tid >> 6) + 4 * p; }
             else         { kb = tid & 15; nn = (tid >> 4) + 16 * p; }
@@ -120,7 +142,7 @@ int launch(const GemmDesc& g, cudaStream_t s)
     // handful of CTAs; spread K over the SMs and accumulate with fp32 atomics instead.
     int ksplit = 1;
     const int tiles = ((g.N + BN - 1) / BN) * ((g.M + BM - 1) / BM);
-    if (g.batch == 1 && g.beta == 1.0f && !g.bias && !g.R && g.post_op == 0 && sizeof(TC) == 4 &&
+    if (g.batch == 1 && g.beta == 1.0f && !g.bias && !g.R && g.post_op == 0 && g.pre_op == 0 && sizeof(TC) == 4 &&
         tiles * 2 <= ltl_sm_count() && g.K >= 8 * BK) {
         ksplit = (2 * ltl_sm_count() + tiles - 1) / tiles;
         if (ksplit > g.K / (2 * BK)) ksplit = g.K / (2 * BK);
@@ -131,7 +153,7 @@ int launch(const GemmDesc& g, cudaStream_t s)
     gemm_simt_kernel<TI, TC><<<grid, 256, 0, s>>>(
         (const TI*)g.A, (const TI*)g.B, (TC*)g.C, (const TI*)g.bias, (const TC*)g.R, g.M, g.N, g.K,
         g.a_rs, g.a_cs, g.b_rs, g.b_cs, g.c_rs, g.c_cs, g.a_bs, g.b_bs, g.c_bs, g.alpha, g.beta,
-        g.post_op, ksplit);
+        g.post_op, ksplit, g.pre_op, (const TI*)g.gamma, g.rowscale, g.eps);
     return ltl_check_launch("gemm");
 }
 
@@ -147,6 +169,7 @@ int ltl_gemm_simt(const GemmDesc& g, cudaStream_t s)
         return ltl_fail(LTL_ERR_SHAPE, "gemm: grid too large (M=%d batch=%d)", g.M, g.batch);
     if (g.a_dtype != g.b_dtype) return ltl_fail(LTL_ERR_DTYPE, "gemm: A and B dtypes differ");
     if (g.post_op < 0 || g.post_op > 5) return ltl_fail(LTL_ERR_ARG, "gemm: unknown post_op %d", g.post_op);
+    if (g.pre_op < 0 || g.pre_op > 4) return ltl_fail(LTL_ERR_ARG, "gemm: unknown pre_op %d", g.pre_op);
     const int ti = g.a_dtype, tc = g.c_dtype;
     if (ti == LTL_F32 && tc == LTL_F32) return launch<float, float>(g, s);
     if (ti == LTL_BF16 && tc == LTL_BF16) return launch<bf16, bf16>(g, s);

@@ -26,6 +26,7 @@
 
 int ltl_comm_world();
 int ltl_comm_allreduce(float* dev, uint64_t n, cudaStream_t s);
+int ltl_comm_wait(cudaStream_t s, const char* what);
 
 namespace {
 
@@ -101,6 +102,13 @@ struct luaTL_lm_s {
     float prefill_ms = 0, decode_ms = 0;
     int64_t launches = 0;
     int adam_alloc = 0;
+    // whole-model optimizer launch: element ranges without weight decay (the gains), on the device
+    long long* d_nodecay = nullptr;
+    int n_nodecay = 0, flat_opt = 0;
+    // captured forward + loss + backward of the training step (luaTL_lm_set_graph)
+    struct StepGraph { cudaGraph_t g = nullptr; cudaGraphExec_t ge = nullptr; int valid = 0, accumulate = 0;
+                       const int32_t *ids = nullptr, *tgt = nullptr; int64_t launches = 0; } step_graph;
+    int graph_steps = 0, warm_steps = 0;
     int use_tc = 1, fuse_swiglu = 0, use_pdl = 1, rows_gemm = 1, fuse_norm = 0;
 };
 
@@ -188,10 +196,15 @@ __global__ void posids_kernel(int32_t* p, int rows, int T) {
     if (i < rows) p[i] = i % T;
 }
 
+void drop_graphs(LM* m);
+
+// Grows the scratch buffer.  Captured decode graphs carry the old pointer as a kernel argument (the split-KV
+// partials of decode attention), so they are dropped together with the buffer they point into.
 int ensure_ws(LM* m, size_t floats)
 {
     if (floats <= m->ws_floats) return LTL_OK;
     LTL_CUDA("lm workspace sync", cudaStreamSynchronize(m->s));
+    drop_graphs(m);
     cudaFree(m->ws); m->ws = nullptr; m->ws_floats = 0;
     DALLOC(m->ws, floats * 4, "workspace");
     m->ws_floats = floats;
@@ -605,8 +618,10 @@ int loss_and_grad(LM* m, const int32_t* d_ids, const int32_t* d_tgt, int valid_g
     return LTL_OK;
 }
 
+void drop_step_graph(LM* m);
 void drop_graphs(LM* m)
 {
+    drop_step_graph(m);
     for (auto& kv : m->graphs) {
         if (kv.second.ge) cudaGraphExecDestroy(kv.second.ge);
         if (kv.second.g) cudaGraphDestroy(kv.second.g);
@@ -632,9 +647,51 @@ int enter_train_tc(LM* m)
     return LTL_OK;
 }
 
+// The forward + loss + backward of a step as one CUDA graph (what the reference's Model:capture() does for its p_step
+// Program, ai/gpu/gpu_transformer.lua:714-733): captured on the first eligible step after a warm step, replayed while
+// the denominator of the loss - baked into the CE and sum kernels as an argument - and the buffers are the same (the
+// reference's replay rule, ai/gpu/gpu_transformer.lua:643).  The optimizer stays outside: its scalars change per step.
+void drop_step_graph(LM* m)
+{
+    if (m->step_graph.ge) cudaGraphExecDestroy(m->step_graph.ge);
+    if (m->step_graph.g) cudaGraphDestroy(m->step_graph.g);
+    m->step_graph = LM::StepGraph();
+}
+
+int loss_and_grad_graphed(LM* m, const int32_t* d_ids, const int32_t* d_tgt, int valid, int accumulate)
+{
+    LM::StepGraph& sg = m->step_graph;
+    if (sg.ge && (sg.valid != valid || sg.accumulate != accumulate || sg.ids != d_ids || sg.tgt != d_tgt)) drop_step_graph(m);
+    if (sg.ge) {
+        LTL_TRY(sync_mirror(m));                        // the bf16 mirrors follow the master outside the graph
+        LTL_CUDA("step graph launch", cudaGraphLaunch(sg.ge, m->s));
+        m->launches += sg.launches;
+        return LTL_OK;
+    }
+    if (m->warm_steps < 2)                              // lazy allocations (activations, scratch, mirrors) must be warm
+        return loss_and_grad(m, d_ids, d_tgt, valid, 1, accumulate, false);
+    LTL_TRY(sync_mirror(m));
+    LTL_CUDA("pre-capture sync", cudaStreamSynchronize(m->s));
+    const int64_t before = m->launches;
+    LTL_CUDA("begin capture", cudaStreamBeginCapture(m->s, cudaStreamCaptureModeThreadLocal));
+    const int rc = loss_and_grad(m, d_ids, d_tgt, valid, 1, accumulate, false);
+    cudaGraph_t g = nullptr;
+    const cudaError_t ce = cudaStreamEndCapture(m->s, &g);
+    if (rc != LTL_OK) { if (g) cudaGraphDestroy(g); cudaGetLastError(); return rc; }
+    if (ce != cudaSuccess) return ltl_cuda_fail("end capture", ce);
+    cudaGraphExec_t gx = nullptr;
+    const cudaError_t ie = cudaGraphInstantiate(&gx, g, 0);
+    if (ie != cudaSuccess) { cudaGraphDestroy(g); return ltl_cuda_fail("graph instantiate", ie); }
+    sg.g = g; sg.ge = gx; sg.valid = valid; sg.accumulate = accumulate; sg.ids = d_ids; sg.tgt = d_tgt;
+    sg.launches = m->launches - before;
+    LTL_CUDA("step graph launch", cudaGraphLaunch(sg.ge, m->s));      // the capture itself executed nothing
+    return LTL_OK;
+}
+
 int train_step_dev(LM* m, const int32_t* d_ids, const int32_t* d_tgt, const luaTL_lm_train_args_t* a,
                    luaTL_lm_result_t* out, int valid_local)
 {
+    if (a->optimizer != 0 && a->optimizer != 1) return ltl_fail(LTL_ERR_ARG, "lm train_step: unknown optimizer %d", a->optimizer);
     if (m->adt == LTL_BF16) LTL_TRY(enter_train_tc(m));
     LTL_TRY(ensure_train(m));
     const int world = ltl_comm_world();
@@ -645,52 +702,62 @@ int train_step_dev(LM* m, const int32_t* d_ids, const int32_t* d_tgt, const luaT
     // (a layer's slice is final once that backward has passed the layer).
     const bool exchange = world > 1 && !a->skip_allreduce;
     const bool overlap = exchange && m->adt == LTL_BF16 && m->overlap_comm;
-    LTL_TRY(loss_and_grad(m, d_ids, d_tgt, valid, 1, a->accumulate, overlap));
+    if (m->graph_steps && !overlap) LTL_TRY(loss_and_grad_graphed(m, d_ids, d_tgt, valid, a->accumulate));
+    else LTL_TRY(loss_and_grad(m, d_ids, d_tgt, valid, 1, a->accumulate, overlap));
     if (exchange && !overlap) LTL_TRY(ltl_comm_allreduce(m->G, (uint64_t)m->np + 2, m->s));
-    float tail[4] = { 0, 0, 0, 0 };
-    LTL_CUDA("loss download", cudaMemcpyAsync(tail, m->G + m->np, 8, cudaMemcpyDeviceToHost, m->s));
-    LTL_CUDA("loss sync", cudaStreamSynchronize(m->s));
-    const int finite = isfinite(tail[0]) ? 1 : 0;
-    float gnorm = 0.0f;
-    if (finite && !a->no_update) {
-        const int need_norm = a->clip_norm > 0.0f;
-        if (need_norm) { LTL_TRY(ltl_l2_accum(m->G, (uint64_t)m->np, m->G + m->np + 2, LTL_F32, m->s)); m->launches++; }
-        if (a->optimizer == 0) {
-            if (a->weight_decay == 0.0f) {
-                LTL_TRY(ltl_sgd(m->W, m->G, nullptr, (uint64_t)m->np, a->lr, 0.0f, need_norm ? m->G + m->np + 2 : nullptr,
-                                a->clip_norm, m->s));
-                m->launches++;
-            } else {
+    // The loss stays on the device until the end of the step: the optimizer kernels read it there and do nothing when
+    // it is not finite (never apply a non-finite update, ai/gpu/gpu_transformer.lua:653-660) - no host round trip
+    // between the backward and the update.
+    const float* d_loss = m->G + m->np;
+    const int need_norm = !a->no_update && a->clip_norm > 0.0f;
+    if (!a->no_update) {
+        float* nsq = m->G + m->np + 2;
+        if (need_norm) { LTL_TRY(ltl_l2_accum(m->G, (uint64_t)m->np, nsq, LTL_F32, m->s)); m->launches++; }
+        if (a->optimizer == 1 && !m->adam_alloc) {
+            DALLOC(m->M1, (size_t)m->np * 4, "adam m"); DALLOC(m->M2, (size_t)m->np * 4, "adam v");
+            LTL_CUDA("adam zero", cudaMemsetAsync(m->M1, 0, (size_t)m->np * 4, m->s));
+            LTL_CUDA("adam zero", cudaMemsetAsync(m->M2, 0, (size_t)m->np * 4, m->s));
+            m->adam_alloc = 1;
+        }
+        // AdamW clips the gradient in place first (cuda/luaTL_train.cu:947-952), SGD folds the factor into its update.
+        if (a->optimizer == 1 && need_norm) { LTL_TRY(ltl_clip_by_nsq(m->G, (uint64_t)m->np, nsq, a->clip_norm, LTL_F32, m->s)); m->launches++; }
+        if (m->flat_opt) {
+            if (a->optimizer == 0)
+                LTL_TRY(ltl_sgd_flat(m->W, m->G, (uint64_t)m->np, m->d_nodecay, m->n_nodecay, d_loss, need_norm ? nsq : nullptr,
+                                     a->lr, a->weight_decay, a->clip_norm, m->s));
+            else
+                LTL_TRY(ltl_adamw_flat(m->W, m->G, m->M1, m->M2, (uint64_t)m->np, m->d_nodecay, m->n_nodecay, d_loss, a->lr,
+                                       a->beta1, a->beta2, a->adam_eps, a->weight_decay, a->step, m->s));
+            m->launches++;
+        } else {
+            // Parameter offsets off a 16-byte boundary (never the case for dim % 8 == 0): one launch per tensor, and the
+            // finite test has to come to the host first.
+            float l0 = 0.0f;
+            LTL_CUDA("loss download", cudaMemcpyAsync(&l0, d_loss, 4, cudaMemcpyDeviceToHost, m->s));
+            LTL_CUDA("loss sync", cudaStreamSynchronize(m->s));
+            if (isfinite(l0))
                 for (const TensorInfo& t : m->tens) {
-                    LTL_TRY(ltl_sgd(m->W + t.off, m->G + t.off, nullptr, (uint64_t)t.rows * t.cols, a->lr,
-                                    t.decay ? a->weight_decay : 0.0f, need_norm ? m->G + m->np + 2 : nullptr,
-                                    a->clip_norm, m->s));
+                    const float wd = t.decay ? a->weight_decay : 0.0f;
+                    if (a->optimizer == 0)
+                        LTL_TRY(ltl_sgd(m->W + t.off, m->G + t.off, nullptr, (uint64_t)t.rows * t.cols, a->lr, wd,
+                                        need_norm ? nsq : nullptr, a->clip_norm, m->s));
+                    else
+                        LTL_TRY(ltl_adamw(m->W + t.off, m->G + t.off, m->M1 + t.off, m->M2 + t.off, nullptr, (uint64_t)t.rows * t.cols,
+                                          LTL_F32, a->lr, a->beta1, a->beta2, a->adam_eps, wd, a->step, 0.0f, m->s));
                     m->launches++;
                 }
-            }
-        } else if (a->optimizer == 1) {
-            if (!m->adam_alloc) {
-                DALLOC(m->M1, (size_t)m->np * 4, "adam m"); DALLOC(m->M2, (size_t)m->np * 4, "adam v");
-                LTL_CUDA("adam zero", cudaMemsetAsync(m->M1, 0, (size_t)m->np * 4, m->s));
-                LTL_CUDA("adam zero", cudaMemsetAsync(m->M2, 0, (size_t)m->np * 4, m->s));
-                m->adam_alloc = 1;
-            }
-            if (need_norm) { LTL_TRY(ltl_clip_by_nsq(m->G, (uint64_t)m->np, m->G + m->np + 2, a->clip_norm, LTL_F32, m->s)); m->launches++; }
-            for (const TensorInfo& t : m->tens) {
-                LTL_TRY(ltl_adamw(m->W + t.off, m->G + t.off, m->M1 + t.off, m->M2 + t.off, nullptr,
-                                  (uint64_t)t.rows * t.cols, LTL_F32, a->lr, a->beta1, a->beta2, a->adam_eps,
-                                  t.decay ? a->weight_decay : 0.0f, a->step, 0.0f, m->s));
-                m->launches++;
-            }
-        } else return ltl_fail(LTL_ERR_ARG, "lm train_step: unknown optimizer %d", a->optimizer);
-        m->mirror_dirty = 1;
-        if (need_norm) {
-            LTL_CUDA("gnorm download", cudaMemcpyAsync(&tail[2], m->G + m->np + 2, 4, cudaMemcpyDeviceToHost, m->s));
         }
+        m->mirror_dirty = 1;
     }
+    float tail[4] = { 0, 0, 0, 0 };
+    LTL_CUDA("loss download", cudaMemcpyAsync(tail, m->G + m->np, need_norm ? 12 : 8, cudaMemcpyDeviceToHost, m->s));
     LTL_CUDA("event", cudaEventRecord(m->ev[1], m->s));
-    LTL_CUDA("step sync", cudaStreamSynchronize(m->s));
-    if (tail[2] > 0.0f) gnorm = sqrtf(tail[2]);
+    // a step that exchanged gradients is waited for with a time limit (a rank that never arrives must not hang this one)
+    if (exchange) LTL_TRY(ltl_comm_wait(m->s, "training step with gradient all-reduce"));
+    else LTL_CUDA("step sync", cudaStreamSynchronize(m->s));
+    m->warm_steps++;
+    const int finite = isfinite(tail[0]) ? 1 : 0;
+    const float gnorm = (finite && tail[2] > 0.0f) ? sqrtf(tail[2]) : 0.0f;
     if (out) {
         out->loss = tail[0]; out->grad_norm = gnorm; out->correct = (int)(tail[1] + 0.5f);
         out->valid = valid; out->finite = finite;
@@ -1078,6 +1145,17 @@ luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
     A((void**)&m->rope_tab, (size_t)m->T * (hd / 2) * sizeof(float2), "rope table");
     for (int i = 0; i < 4 && rc == LTL_OK; ++i)
         if (cudaEventCreate(&m->ev[i]) != cudaSuccess) rc = ltl_fail(LTL_ERR_CUDA, "lm_create: cudaEventCreate failed");
+    if (rc == LTL_OK) {
+        std::vector<long long> nd;
+        for (const TensorInfo& t : m->tens) if (!t.decay) { nd.push_back(t.off); nd.push_back(t.off + (long long)t.rows * t.cols); }
+        m->n_nodecay = (int)nd.size() / 2;
+        A((void**)&m->d_nodecay, nd.size() * sizeof(long long), "no-decay ranges");
+        if (rc == LTL_OK && !nd.empty() &&
+            cudaMemcpyAsync(m->d_nodecay, nd.data(), nd.size() * sizeof(long long), cudaMemcpyHostToDevice, m->s) != cudaSuccess)
+            rc = ltl_fail(LTL_ERR_CUDA, "lm_create: upload of the no-decay ranges failed");
+        if (rc == LTL_OK && cudaStreamSynchronize(m->s) != cudaSuccess) rc = ltl_fail(LTL_ERR_CUDA, "lm_create: sync failed");
+        m->flat_opt = rc == LTL_OK && ltl_opt_ranges_ok(nd.data(), m->n_nodecay, m->W, m->G);
+    }
     if (rc == LTL_OK) rc = ltl_rope_table(m->rope_tab, m->T, hd, c.rope_base, m->s);
     if (rc == LTL_OK && cudaMemsetAsync(m->W, 0, (size_t)m->np * 4, m->s) != cudaSuccess) rc = ltl_fail(LTL_ERR_CUDA, "lm_create: memset failed");
     if (rc == LTL_OK && cudaMemsetAsync(m->G, 0, (size_t)(m->np + 4) * 4, m->s) != cudaSuccess) rc = ltl_fail(LTL_ERR_CUDA, "lm_create: memset failed");
@@ -1095,7 +1173,7 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
     void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
                      m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
                      m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part,
-                     m->Wm, m->d_done, m->ssq[0], m->ssq[1], m->tile_tickets, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
+                     m->Wm, m->d_done, m->d_nodecay, m->ssq[0], m->ssq[1], m->tile_tickets, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
     for (void* p : ptrs) if (p) cudaFree(p);
     for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
     if (m->ev_grad) cudaEventDestroy(m->ev_grad);
@@ -1162,6 +1240,17 @@ int luaTL_lm_train_step_dev(luaTL_lm_t* m, const int32_t* d_ids, const int32_t* 
     return train_step_dev(m, d_ids, d_targets, a, out, a->valid_global);
 }
 
+// Host-side contract of the id / target blocks, shared by the training and the evaluation step: inputs inside the
+// vocabulary, targets inside it or negative (ignored).
+static int check_tokens(const luaTL_lm_t* m, const int32_t* ids, const int32_t* targets, int rows, const char* ctx)
+{
+    for (int i = 0; i < rows; ++i)
+        if (ids[i] < 0 || ids[i] >= m->V || targets[i] >= m->V)
+            return ltl_fail(LTL_ERR_ARG, "%s: token out of range at row %d (input %d, target %d, vocab %d)",
+                            ctx, i, ids[i], targets[i], m->V);
+    return LTL_OK;
+}
+
 int luaTL_lm_train_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* targets,
                         const luaTL_lm_train_args_t* a, luaTL_lm_result_t* out)
 {
@@ -1169,10 +1258,7 @@ int luaTL_lm_train_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* target
     if (m->B < 1) return ltl_fail(LTL_ERR_ARG, "lm_train_step: model created with batch = 0");
     LTL_TRY(ensure_train(m));
     const int rows = m->B * m->T;
-    for (int i = 0; i < rows; ++i)
-        if (ids[i] < 0 || ids[i] >= m->V || targets[i] >= m->V)
-            return ltl_fail(LTL_ERR_ARG, "lm_train_step: token out of range at row %d (input %d, target %d, vocab %d)",
-                            i, ids[i], targets[i], m->V);
+    LTL_TRY(check_tokens(m, ids, targets, rows, "lm_train_step"));
     LTL_CUDA("ids upload", cudaMemcpyAsync(m->d_ids, ids, (size_t)rows * 4, cudaMemcpyHostToDevice, m->s));
     LTL_CUDA("targets upload", cudaMemcpyAsync(m->d_tgt, targets, (size_t)rows * 4, cudaMemcpyHostToDevice, m->s));
     return train_step_dev(m, m->d_ids, m->d_tgt, a, out, count_valid(targets, rows, m->V));
@@ -1184,6 +1270,7 @@ int luaTL_lm_eval_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* targets
     if (m->B < 1) return ltl_fail(LTL_ERR_ARG, "lm_eval_step: model created with batch = 0");
     LTL_TRY(ensure_train(m));
     const int rows = m->B * m->T;
+    LTL_TRY(check_tokens(m, ids, targets, rows, "lm_eval_step"));
     LTL_CUDA("ids upload", cudaMemcpyAsync(m->d_ids, ids, (size_t)rows * 4, cudaMemcpyHostToDevice, m->s));
     LTL_CUDA("targets upload", cudaMemcpyAsync(m->d_tgt, targets, (size_t)rows * 4, cudaMemcpyHostToDevice, m->s));
     const int valid = count_valid(targets, rows, m->V);
@@ -1311,11 +1398,7 @@ int luaTL_lm_generate(luaTL_lm_t* m, const int32_t* prompts, int nseq, int n_pro
 int luaTL_lm_set_sampling(luaTL_lm_t* m, float temperature, int top_k, float top_p, uint64_t seed, int stop_id)
 {
     if (!m) return ltl_fail(LTL_ERR_NULL, "lm_set_sampling: null model");
-    if (temperature > 0.0f) {
-        if (top_k < 0 || top_k > 128) return ltl_fail(LTL_ERR_UNSUPPORTED, "lm_set_sampling: top_k %d outside 0..128", top_k);
-        if (top_p > 0.0f && top_p < 1.0f && !(top_k > 0 && top_k < m->V))
-            return ltl_fail(LTL_ERR_UNSUPPORTED, "lm_set_sampling: top_p needs top_k in 1..128 on this backend (the nucleus is cut inside the top-k set)");
-    }
+    if (temperature > 0.0f && top_k < 0) return ltl_fail(LTL_ERR_ARG, "lm_set_sampling: top_k %d is negative", top_k);
     if (stop_id >= m->V) return ltl_fail(LTL_ERR_ARG, "lm_set_sampling: stop token %d outside the vocabulary", stop_id);
     LM::Sampling n;
     n.temperature = temperature > 0.0f ? temperature : 0.0f; n.top_k = top_k; n.top_p = top_p; n.seed = seed; n.stop_id = stop_id;
@@ -1327,6 +1410,15 @@ int luaTL_lm_set_sampling(luaTL_lm_t* m, float temperature, int top_k, float top
     }
     return LTL_OK;
 }
+
+int luaTL_lm_set_graph(luaTL_lm_t* m, int on)
+{
+    if (!m) return ltl_fail(LTL_ERR_NULL, "lm_set_graph: null model");
+    if (!on && m->graph_steps) { LTL_CUDA("sync", cudaStreamSynchronize(m->s)); drop_step_graph(m); }
+    m->graph_steps = on ? 1 : 0;
+    return LTL_OK;
+}
+int luaTL_lm_graph_ready(const luaTL_lm_t* m) { return m && m->step_graph.ge ? 1 : 0; }
 
 int luaTL_lm_time_decode_attn(luaTL_lm_t* m, int nseq, int cache_len, int iters, float* ms_per_launch)
 {

@@ -912,6 +912,173 @@ __device__ __forceinline__ uint32_t order_key(float x)       // larger float -> 
 }
 }  // namespace samp
 
+// ---- general rule: any top_k, nucleus over the whole row -------------------------------------------------------
+// The reference sorts the row (or keeps an ordered top-k list) and walks it in descending order accumulating softmax
+// weights (ai/optim/lmtrain.lua:1377-1436).  Nothing is sorted here.  The k-th largest key comes from a radix select;
+// weights are taken as 40-bit fixed point (integer sums do not depend on the order of the atomics, so a draw is
+// reproducible), and "the first candidate, in descending order, at which the running sum reaches tau" is found by a
+// second radix descent over the keys, byte by byte, on per-bucket weight sums.  Equal values rank by index (lower
+// first), as the reference's insertion pass leaves them.
+namespace samp {
+__device__ __forceinline__ float key_value(unsigned key)
+{
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7FFFFFFFu) : ~key);
+}
+__device__ __forceinline__ unsigned long long weight_q(float x, float mx, float invT)
+{
+    return __float2ull_rz(expf((x - mx) * invT) * 1099511627776.0f);      // 2^40
+}
+// Index of the j-th (1-based, ascending index) element whose key equals K; -1 if there are fewer.  cnt: blockDim.x ints.
+__device__ int nth_with_key(const float* __restrict__ row, int V, unsigned K, int j, int* cnt, int* s_out)
+{
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int chunk = (V + nt - 1) / nt, i0 = min(V, tid * chunk), i1 = min(V, i0 + chunk);
+    int c = 0;
+    for (int i = i0; i < i1; ++i) c += order_key(row[i]) == K;
+    __syncthreads();
+    cnt[tid] = c;
+    __syncthreads();
+    if (tid == 0) {
+        int acc = 0, owner = -1, res = -1;
+        for (int t = 0; t < nt; ++t) { if (acc + cnt[t] >= j) { owner = t; break; } acc += cnt[t]; }
+        if (owner >= 0 && j >= 1) {
+            const int a = min(V, owner * chunk), b = min(V, a + chunk);
+            for (int i = a; i < b; ++i) if (order_key(row[i]) == K && ++acc == j) { res = i; break; }
+        }
+        *s_out = res;
+    }
+    __syncthreads();
+    return *s_out;
+}
+}  // namespace samp
+
+// Key of the k-th largest element of the row (1 <= k <= V): radix select, most significant byte first.
+__device__ unsigned select_kth_key(const float* __restrict__ row, int V, int k, unsigned* hist, unsigned* s_prefix, unsigned* s_need)
+{
+    using namespace samp;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    __syncthreads();
+    if (tid == 0) { *s_prefix = 0; *s_need = (unsigned)k; }
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        for (int i = tid; i < 256; i += nt) hist[i] = 0;
+        __syncthreads();
+        const unsigned prefix = *s_prefix, himask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+        for (int i = tid; i < V; i += nt) {
+            const unsigned key = order_key(row[i]);
+            if ((key & himask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            unsigned need = *s_need;
+            int bkt = 255;
+            for (; bkt > 0; --bkt) { if (hist[bkt] >= need) break; need -= hist[bkt]; }
+            *s_prefix = prefix | ((unsigned)bkt << shift);
+            *s_need = need;
+        }
+        __syncthreads();
+    }
+    return *s_prefix;
+}
+
+__device__ int sample_row_general(const float* __restrict__ row, int V, float temperature, int top_k, float top_p, float u)
+{
+    using namespace samp;
+    __shared__ unsigned hist[256];
+    __shared__ unsigned long long mass[256];
+    __shared__ int cnt[1024];
+    __shared__ float red[33];
+    __shared__ unsigned s_prefix, s_need, s_ngt;
+    __shared__ unsigned long long s_total, s_acc;
+    __shared__ int s_idx;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const float invT = 1.0f / temperature;
+    float mxl = -INFINITY;
+    for (int i = tid; i < V; i += nt) mxl = fmaxf(mxl, row[i]);
+    const float mx = block_max(mxl, red);
+    // candidate set: the k largest (ties at the k-th value: lowest indices), or the whole row
+    unsigned kth = 0u;
+    int tie_cut = V;
+    if (top_k > 0 && top_k < V) {
+        kth = select_kth_key(row, V, top_k, hist, &s_prefix, &s_need);
+        if (tid == 0) s_ngt = 0;
+        __syncthreads();
+        unsigned c = 0;
+        for (int i = tid; i < V; i += nt) c += order_key(row[i]) > kth;
+        if (c) atomicAdd(&s_ngt, c);
+        __syncthreads();
+        tie_cut = nth_with_key(row, V, kth, top_k - (int)s_ngt, cnt, &s_idx);
+        if (tie_cut < 0) tie_cut = V;
+    }
+    auto in_set = [&](unsigned key, int i) { return key > kth || (key == kth && i <= tie_cut); };
+    if (tid == 0) s_total = 0ull;
+    __syncthreads();
+    {
+        unsigned long long t = 0ull;
+        for (int i = tid; i < V; i += nt) { const float x = row[i]; if (in_set(order_key(x), i)) t += weight_q(x, mx, invT); }
+        if (t) atomicAdd(&s_total, t);
+    }
+    __syncthreads();
+    // Descending walk to the first candidate at which the running sum reaches tau (1 <= tau <= sum of the set): returns
+    // its index, leaves the running sum including that candidate in s_acc.
+    auto crossing = [&](unsigned long long tau) -> int {
+        __syncthreads();
+        if (tid == 0) { s_prefix = 0u; s_acc = 0ull; }
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            for (int i = tid; i < 256; i += nt) mass[i] = 0ull;
+            __syncthreads();
+            const unsigned prefix = s_prefix, himask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+            for (int i = tid; i < V; i += nt) {
+                const float x = row[i];
+                const unsigned key = order_key(x);
+                if ((key & himask) == prefix && in_set(key, i)) {
+                    const unsigned long long w = weight_q(x, mx, invT);
+                    if (w) atomicAdd(&mass[(key >> shift) & 255u], w);
+                }
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned long long acc = s_acc;
+                int bkt = 255;
+                for (; bkt > 0; --bkt) { if (acc + mass[bkt] >= tau) break; acc += mass[bkt]; }
+                s_prefix = prefix | ((unsigned)bkt << shift);
+                s_acc = acc;
+            }
+            __syncthreads();
+        }
+        const unsigned key = s_prefix;
+        unsigned long long w = weight_q(key_value(key), mx, invT);
+        if (w == 0ull) w = 1ull;
+        const unsigned long long acc = s_acc;
+        const unsigned long long j = tau > acc ? (tau - acc + w - 1ull) / w : 1ull;
+        const int idx = nth_with_key(row, V, key, (int)j, cnt, &s_idx);
+        if (tid == 0) s_acc = acc + j * w;
+        __syncthreads();
+        return idx;
+    };
+    unsigned long long norm = s_total;
+    if (norm == 0ull) norm = 1ull;
+    if (top_p > 0.0f && top_p < 1.0f) {
+        unsigned long long tau = (unsigned long long)ceil((double)top_p * (double)norm);
+        if (tau < 1ull) tau = 1ull;
+        if (tau > norm) tau = norm;
+        (void)crossing(tau);
+        norm = s_acc;                                    // weight of the nucleus: everything down to the candidate that closed it
+    }
+    unsigned long long tau = (unsigned long long)ceil((double)u * (double)norm);
+    if (tau < 1ull) tau = 1ull;
+    if (tau > norm) tau = norm;
+    int pick = crossing(tau);
+    if (pick < 0) {                                       // cannot happen for finite logits; fall back to the largest
+        float best = -INFINITY; int bi = 0;
+        if (tid == 0) { for (int i = 0; i < V; ++i) if (row[i] > best) { best = row[i]; bi = i; } s_idx = bi; }
+        __syncthreads();
+        pick = s_idx;
+    }
+    return pick;
+}
+
 // Returns the sampled index of one row (valid in thread 0).  blockDim.x threads, a multiple of 32, at most 1024.
 __device__ int sample_row(const float* __restrict__ row, int V, float temperature, int top_k, float top_p, float u)
 {
@@ -928,6 +1095,9 @@ __device__ int sample_row(const float* __restrict__ row, int V, float temperatur
     __shared__ int s_pick;
     const int tid = threadIdx.x, nt = blockDim.x;
     const float invT = 1.0f / temperature;
+    const bool nucleus = top_p > 0.0f && top_p < 1.0f;
+    if ((top_k > MAXK && top_k < V) || (nucleus && !(top_k > 0 && top_k < V)))
+        return sample_row_general(row, V, temperature, top_k, top_p, u);
     if (top_k > 0 && top_k < V) {
         const int k = top_k < MAXK ? top_k : MAXK;
         // radix select, most significant byte first: key of the k-th largest element
@@ -1064,10 +1234,9 @@ sample_rows_kernel(const float* __restrict__ logits, int V, float temperature, i
 
 static int check_sampling(float temperature, int top_k, float top_p, int V)
 {
+    (void)top_p; (void)V;
     if (!(temperature > 0.0f)) return ltl_fail(LTL_ERR_ARG, "sample: temperature must be positive (use the greedy pick otherwise)");
-    if (top_k < 0 || top_k > samp::MAXK) return ltl_fail(LTL_ERR_UNSUPPORTED, "sample: top_k %d outside 0..%d", top_k, samp::MAXK);
-    if (top_p > 0.0f && top_p < 1.0f && !(top_k > 0 && top_k < V))
-        return ltl_fail(LTL_ERR_UNSUPPORTED, "sample: top_p needs top_k in 1..%d on this backend (the nucleus is cut inside the top-k set)", samp::MAXK);
+    if (top_k < 0) return ltl_fail(LTL_ERR_ARG, "sample: top_k %d is negative", top_k);
     return LTL_OK;
 }
 

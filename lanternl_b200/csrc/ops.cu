@@ -257,6 +257,13 @@ size_t ltl_rmsnorm_bwd_scratch_floats(int cols)
     return (size_t)ltl_sm_count() * 2 * ROW_WARPS * (size_t)cols;
 }
 
+// The operand tests of the launcher below, without the scratch: does this call take the warp-per-row kernel?
+static bool rmsnorm_bwd_takes_warp_kernel(const void* x, const void* gamma, const void* dy, const void* dx, int cols, int dtype)
+{
+    return row_chunks(cols, ltl_dtype_size(dtype)) && aligned16(x) && aligned16(dy) && aligned16(dx) &&
+           (!gamma || aligned16(gamma));
+}
+
 int ltl_rmsnorm_bwd(const void* x, const void* gamma, const void* dy, void* dx, float* dgamma,
                     int rows, int cols, float eps, int dtype, float* scratch, cudaStream_t s)
 {
@@ -1558,6 +1565,116 @@ int ltl_sgd(float* w, const float* g, bf16* w_lp, uint64_t n, float lr, float wd
 }
 
 // ------------------------------------------------------------------------------------------
+// Whole-model optimizer launches: one kernel over the flat parameter buffer.
+//   * weight decay applies everywhere except inside the `nodecay` ranges (the gain vectors; sorted [begin, end) pairs,
+//     every boundary a multiple of 4 so that a 16-byte packet never straddles one), looked up by binary search in
+//     shared memory;
+//   * `loss` (optional) is the step's loss on the device: a non-finite value turns the launch into a no-op, which is
+//     the reference's "skip the update when the loss is not finite" (ai/gpu/gpu_transformer.lua:653-660) without a
+//     host round trip in the middle of the step.
+// ------------------------------------------------------------------------------------------
+constexpr int OPT_MAX_RANGES = 1024;
+
+__device__ __forceinline__ bool in_ranges(const long long* r, int npairs, long long e)
+{
+    int lo = 0, hi = npairs;                  // first pair with end > e
+    while (lo < hi) { const int mid = (lo + hi) >> 1; if (r[2 * mid + 1] > e) hi = mid; else lo = mid + 1; }
+    return lo < npairs && r[2 * lo] <= e;
+}
+
+__global__ void __launch_bounds__(256)
+sgd_flat_kernel(float* __restrict__ w, const float* __restrict__ g, uint64_t n, const long long* __restrict__ nodecay,
+                int npairs, const float* __restrict__ loss, const float* __restrict__ nsq, float lr, float wd,
+                float max_norm)
+{
+    extern __shared__ long long rng[];
+    if (loss && !isfinite(loss[0])) return;
+    for (int i = threadIdx.x; i < 2 * npairs; i += blockDim.x) rng[i] = nodecay[i];
+    __syncthreads();
+    float f = 1.0f;
+    if (nsq && max_norm > 0.0f) {
+        const float nrm = sqrtf(fmaxf(nsq[0], 0.0f));
+        if (nrm > max_norm) f = max_norm / (nrm + 1e-6f);
+    }
+    const uint64_t np4 = n / 4, nt = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < np4; p += nt) {
+        const float d = (wd != 0.0f && !in_ranges(rng, npairs, (long long)(4 * p))) ? wd : 0.0f;
+        float4 wv = reinterpret_cast<float4*>(w)[p];
+        const float4 gv = reinterpret_cast<const float4*>(g)[p];
+        wv.x -= lr * (f * gv.x + d * wv.x);
+        wv.y -= lr * (f * gv.y + d * wv.y);
+        wv.z -= lr * (f * gv.z + d * wv.z);
+        wv.w -= lr * (f * gv.w + d * wv.w);
+        reinterpret_cast<float4*>(w)[p] = wv;
+    }
+    for (uint64_t i = np4 * 4 + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += nt) {
+        const float d = (wd != 0.0f && !in_ranges(rng, npairs, (long long)i)) ? wd : 0.0f;
+        w[i] -= lr * (f * g[i] + d * w[i]);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+adamw_flat_kernel(float* __restrict__ w, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                  uint64_t n, const long long* __restrict__ nodecay, int npairs, const float* __restrict__ loss,
+                  float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2)
+{
+    extern __shared__ long long rng[];
+    if (loss && !isfinite(loss[0])) return;
+    for (int i = threadIdx.x; i < 2 * npairs; i += blockDim.x) rng[i] = nodecay[i];
+    __syncthreads();
+    const uint64_t np4 = n / 4, nt = (uint64_t)gridDim.x * blockDim.x;
+    // element-wise arithmetic exactly as adamw_kernel above
+    auto upd = [&](float& wi, float gr, float& mi, float& vi, float d) {
+        mi = beta1 * mi + (1.0f - beta1) * gr;
+        vi = beta2 * vi + (1.0f - beta2) * gr * gr;
+        wi -= lr * d * wi;
+        wi -= lr * (mi * bc1) / (sqrtf(vi * bc2) + eps);
+    };
+    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < np4; p += nt) {
+        const float d = (wd != 0.0f && !in_ranges(rng, npairs, (long long)(4 * p))) ? wd : 0.0f;
+        float4 wv = reinterpret_cast<float4*>(w)[p], mv = reinterpret_cast<float4*>(m)[p], vv = reinterpret_cast<float4*>(v)[p];
+        const float4 gv = reinterpret_cast<const float4*>(g)[p];
+        upd(wv.x, gv.x, mv.x, vv.x, d); upd(wv.y, gv.y, mv.y, vv.y, d);
+        upd(wv.z, gv.z, mv.z, vv.z, d); upd(wv.w, gv.w, mv.w, vv.w, d);
+        reinterpret_cast<float4*>(w)[p] = wv; reinterpret_cast<float4*>(m)[p] = mv; reinterpret_cast<float4*>(v)[p] = vv;
+    }
+    for (uint64_t i = np4 * 4 + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += nt) {
+        const float d = (wd != 0.0f && !in_ranges(rng, npairs, (long long)i)) ? wd : 0.0f;
+        upd(w[i], g[i], m[i], v[i], d);
+    }
+}
+
+int ltl_opt_ranges_ok(const long long* host_pairs, int npairs, const void* w, const void* g)
+{
+    if (npairs < 0 || npairs > OPT_MAX_RANGES || !aligned16(w) || !aligned16(g)) return 0;
+    for (int i = 0; i < 2 * npairs; ++i) if (host_pairs[i] % 4) return 0;
+    return 1;
+}
+
+int ltl_sgd_flat(float* w, const float* g, uint64_t n, const long long* d_nodecay, int npairs, const float* loss,
+                 const float* nsq, float lr, float wd, float max_norm, cudaStream_t s)
+{
+    if (!w || !g) return ltl_fail(LTL_ERR_NULL, "sgd: null pointer");
+    if (n == 0) return LTL_OK;
+    sgd_flat_kernel<<<grid1d((n + 3) / 4, 256), 256, (size_t)npairs * 16, s>>>(w, g, n, d_nodecay, npairs, loss, nsq, lr, wd,
+                                                                              max_norm);
+    return ltl_check_launch("sgd");
+}
+
+int ltl_adamw_flat(float* w, const float* g, float* m, float* v, uint64_t n, const long long* d_nodecay, int npairs,
+                   const float* loss, float lr, float beta1, float beta2, float eps, float wd, int step, cudaStream_t s)
+{
+    if (!w || !g || !m || !v) return ltl_fail(LTL_ERR_NULL, "adamw: null pointer");
+    if (n == 0) return LTL_OK;
+    if (step < 1) step = 1;
+    const float bc1 = 1.0f / (1.0f - powf(beta1, (float)step));
+    const float bc2 = 1.0f / (1.0f - powf(beta2, (float)step));
+    adamw_flat_kernel<<<grid1d((n + 3) / 4, 256), 256, (size_t)npairs * 16, s>>>(w, g, m, v, n, d_nodecay, npairs, loss, lr,
+                                                                                beta1, beta2, eps, wd, bc1, bc2);
+    return ltl_check_launch("adamw");
+}
+
+// ------------------------------------------------------------------------------------------
 // RMSNorm backward without any allocation.
 //
 // Who needs it: code that may not call cudaMalloc when it wants a gradient - a host that has
@@ -1586,19 +1703,26 @@ extern "C" int luaTL_rmsnorm_bwd_noalloc(const void* x, const void* gamma, const
     int dev = -1;
     LTL_CUDA("cudaGetDevice", cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return ltl_fail(LTL_ERR_ARG, "rmsnorm_bwd_noalloc: device ordinal %d not supported", dev);
+    // The library's stream belongs to the device luaTL_init bound; a caller that has made another device current
+    // would get this array's address on one GPU and a stream of another.
+    if (dev != ltl_bound_device())
+        return ltl_fail(LTL_ERR_ARG, "rmsnorm_bwd_noalloc: current device %d is not the device the library was initialised on (%d)",
+                        dev, ltl_bound_device());
     if (!dev_ptr[dev]) {
         float* p = nullptr;
         LTL_CUDA("cudaGetSymbolAddress(rmsnorm_bwd scratch)", cudaGetSymbolAddress((void**)&p, g_rmsnorm_bwd_static));
         if (!p) return ltl_fail(LTL_ERR_CUDA, "rmsnorm_bwd_noalloc: the static scratch has no device address");
         dev_ptr[dev] = p;
     }
-    if (dgamma && cols > 0 && ltl_rmsnorm_bwd_scratch_floats(cols) > RMSNORM_BWD_STATIC_FLOATS)
+    // Only the warp-per-row kernel leaves dgamma partials in scratch; shapes that take the CTA-per-row kernel
+    // (row width not a whole number of 16-byte packets per lane, or operands off a 16-byte boundary) need none.
+    const bool wants_scratch = dgamma && cols > 0 && rmsnorm_bwd_takes_warp_kernel(x, gamma, dy, dx, cols, dtype);
+    if (wants_scratch && ltl_rmsnorm_bwd_scratch_floats(cols) > RMSNORM_BWD_STATIC_FLOATS)
         return ltl_fail(LTL_ERR_CAPACITY, "rmsnorm_bwd_noalloc: %d columns need %zu scratch floats, the static scratch holds %zu "
                         "(at most %zu columns on this GPU); use luaTL_rmsnorm_bwd for wider rows", cols,
                         ltl_rmsnorm_bwd_scratch_floats(cols), RMSNORM_BWD_STATIC_FLOATS,
                         RMSNORM_BWD_STATIC_FLOATS / ((size_t)ltl_sm_count() * 2 * ROW_WARPS));
     cudaStream_t s = ltl_default_stream();
     LTL_TRY(ltl_rmsnorm_bwd(x, gamma, dy, dx, dgamma, rows, cols, eps, dtype, dev_ptr[dev], s));
-    LTL_CUDA("rmsnorm_bwd_noalloc", cudaStreamSynchronize(s));
-    return LTL_OK;
+    return ltl_sync_stream("rmsnorm_bwd_noalloc");      // waits unless luaTL_set_deferred(1) is in force
 }

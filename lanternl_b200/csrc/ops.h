@@ -51,10 +51,30 @@ int ltl_adamw(float* w, const void* g, float* m, float* v, void* w_lp, uint64_t 
 // w_lp (optional) receives the bf16 copy of the updated weights.
 int ltl_sgd(float* w, const float* g, bf16* w_lp, uint64_t n, float lr, float wd,
             const float* nsq, float max_norm, cudaStream_t s);
+// One launch over a whole flat parameter buffer.  d_nodecay: device array of npairs sorted [begin, end) element ranges
+// that take no weight decay; loss (optional, device): a non-finite value makes the launch a no-op.
+int ltl_opt_ranges_ok(const long long* host_pairs, int npairs, const void* w, const void* g);
+int ltl_sgd_flat(float* w, const float* g, uint64_t n, const long long* d_nodecay, int npairs, const float* loss,
+                 const float* nsq, float lr, float wd, float max_norm, cudaStream_t s);
+int ltl_adamw_flat(float* w, const float* g, float* m, float* v, uint64_t n, const long long* d_nodecay, int npairs,
+                   const float* loss, float lr, float beta1, float beta2, float eps, float wd, int step, cudaStream_t s);
 // out[c, r] = (bf16) in[r, c]
 // interleave_half = F > 0: output row j < F goes to row 2j, row F + j to row 2j + 1 (gate/up pairs).
 int ltl_transpose_any_to_bf16(const void* in, int in_dtype, bf16* out, int rows, int cols, cudaStream_t s);
 int ltl_transpose_to_bf16(const float* in, bf16* out, int rows, int cols, int interleave_half, cudaStream_t s);
+
+// ---- small ops of the reference's ABI that the token loop itself does not queue (compat.cu) ----
+// out[c] = alpha * sum_r x[r * row_stride + c] + beta * out[c]
+int ltl_reduce_cols(const void* x, float* out, int rows, int cols, long long row_stride, float alpha, float beta,
+                    int dtype, cudaStream_t s);
+// out [cols, rows] = in [rows, cols]^T
+int ltl_transpose(const void* in, void* out, int rows, int cols, int dtype, cudaStream_t s);
+// out[r, c] = x[r, c] + alpha * v[c]  (v may be NULL)
+int ltl_bcast_add(const void* x, const void* v, void* out, int rows, int cols, float alpha, int dtype, cudaStream_t s);
+// dst[r, :] = src[idx[r], :], rows outside [0, src_rows) give zeros
+int ltl_gather_rows(const void* src, const int32_t* idx, void* dst, int n, int cols, int src_rows, int dtype, cudaStream_t s);
+// out[r] = 1 / sqrt(mean_c x(r, c)^2 + eps) with x(r, c) at r * rs + c * cs
+int ltl_row_rms(const void* x, float* out, int rows, int cols, long long rs, long long cs, float eps, int dtype, cudaStream_t s);
 
 // ---- CUDA-core GEMM with explicit strides (gemm_simt.cu) ----
 struct GemmDesc {
@@ -66,6 +86,13 @@ struct GemmDesc {
     float alpha, beta;
     int post_op;           // 0 none, 1 relu, 2 gelu, 3 silu, 4 tanh, 5 sigmoid
     int a_dtype, b_dtype, c_dtype;
+    // Prologue on A (the reference's pre_op, cuda/luaTL_train.cu:159-204): 0 none; 1 RMSNorm - A(m,k) is multiplied by
+    // rowscale[m] (given, or 1/sqrt(mean_k A(m,k)^2 + eps) computed by the kernel) and by gamma[k] (optional);
+    // 2 gelu, 3 silu, 4 relu applied to every element of A.
+    int pre_op;
+    const void* gamma;     // [K], A's dtype
+    const float* rowscale; // [M] fp32
+    float eps;
 };
 int ltl_gemm_simt(const GemmDesc& g, cudaStream_t s);
 

@@ -10,10 +10,25 @@
 #include "../../include/luatl_b200.h"
 #include "ops.h"
 
-float* ltl_library_workspace(size_t floats);
+#include <unordered_map>
 
-// Scratch the op list needs (sized before the first op runs, never inside a capture).
-static int prepare_scratch(const luaTL_prog_t* P, float** ws)
+// Scratch of a Program's ops (the dgamma partials of RMSNORM_BWD).  Every Program owns its buffer: a captured graph
+// carries the pointer as a kernel argument, so it must not move when another Program or an immediate call needs more,
+// and Programs run on their own streams, so a shared buffer would race.  luaTL_prog_t is laid out by the host
+// language, hence the side table.  The buffer grows only in prog_run / prog_capture (never inside a capture); growing
+// drops the Program's captured graph.
+struct ProgScratch { float* p = nullptr; size_t floats = 0; };
+static std::unordered_map<const luaTL_prog_t*, ProgScratch> g_prog_scratch;
+
+static void free_scratch(const luaTL_prog_t* P)
+{
+    auto it = g_prog_scratch.find(P);
+    if (it == g_prog_scratch.end()) return;
+    if (it->second.p) cudaFree(it->second.p);
+    g_prog_scratch.erase(it);
+}
+
+static int prepare_scratch(luaTL_prog_t* P, float** ws)
 {
     size_t need = 0;
     for (int i = 0; i < P->count; ++i) {
@@ -24,10 +39,20 @@ static int prepare_scratch(const luaTL_prog_t* P, float** ws)
         }
     }
     *ws = nullptr;
-    if (need) {
-        *ws = ltl_library_workspace(need);
-        if (!*ws) return LTL_ERR_OOM;
+    if (!need) return LTL_OK;
+    ProgScratch& sc = g_prog_scratch[P];
+    if (need > sc.floats) {
+        cudaStreamSynchronize((cudaStream_t)P->stream);
+        luaTL_prog_graph_free(P);                      // the old pointer is baked into the captured nodes
+        if (sc.p) cudaFree(sc.p);
+        sc.p = nullptr; sc.floats = 0;
+        if (cudaMalloc(&sc.p, need * sizeof(float)) != cudaSuccess) {
+            cudaGetLastError();
+            return ltl_fail(LTL_ERR_OOM, "prog: cudaMalloc of %zu scratch bytes failed", need * sizeof(float));
+        }
+        sc.floats = need;
     }
+    *ws = sc.p;
     return LTL_OK;
 }
 
@@ -37,10 +62,10 @@ static int exec_op(const luaTL_op_t* c, float* ws, cudaStream_t s)
     case LUATL_P_NOP: return LTL_OK;
     case LUATL_P_GEMM: {
         if (c->i0 <= 0 || c->i1 <= 0 || c->i2 <= 0) return ltl_fail(LTL_ERR_SHAPE, "gemm: bad shape %dx%dx%d", c->i0, c->i1, c->i2);
-        if (c->pre != 0) return ltl_fail(LTL_ERR_UNSUPPORTED, "gemm: pre_op %d is not part of this backend", c->pre);
+        // p4 = gamma, p5 = rowscale, f2 = eps of the RMSNorm prologue (cuda/luaTL_train.cu:1353-1359)
         GemmDesc g = { c->p0, c->p1, c->p2, c->p3, nullptr, c->i0, c->i1, c->i2, c->i3 > 0 ? c->i3 : 1,
                        c->s0, c->s1, c->s2, c->s3, c->s4, c->s5, c->s6, c->s7, c->s8, c->f0, c->f1, c->act,
-                       c->dtype, c->dtype, c->dtype };
+                       c->dtype, c->dtype, c->dtype, c->pre, c->p4, (const float*)c->p5, c->f2 };
         return ltl_gemm_simt(g, s);
     }
     case LUATL_P_EW:
@@ -99,10 +124,17 @@ static int exec_op(const luaTL_op_t* c, float* ws, cudaStream_t s)
     case LUATL_P_SYNC:
         LTL_CUDA("cudaStreamSynchronize", cudaStreamSynchronize(s));
         return LTL_OK;
-    case LUATL_P_REDUCE_COLS: case LUATL_P_TRANSPOSE: case LUATL_P_BCAST_ADD: case LUATL_P_GATHER:
+    case LUATL_P_REDUCE_COLS:      // out[c] = f0 * sum_r x[r, c] + f1 * out[c]; s0 = row stride (0: cols)
+        return ltl_reduce_cols(c->p0, (float*)c->p2, c->i0, c->i1, c->s0 > 0 ? c->s0 : c->i1, c->f0, c->f1, c->dtype, s);
+    case LUATL_P_TRANSPOSE:
+        return ltl_transpose(c->p0, c->p2, c->i0, c->i1, c->dtype, s);
+    case LUATL_P_BCAST_ADD:
+        return ltl_bcast_add(c->p0, c->p1, c->p2, c->i0, c->i1, c->f0, c->dtype, s);
+    case LUATL_P_GATHER:
+        return ltl_gather_rows(c->p0, (const int32_t*)c->p1, c->p2, c->i0, c->i1, c->i2, c->dtype, s);
     case LUATL_P_ROWRMS:
-        return ltl_fail(LTL_ERR_UNSUPPORTED, "prog: opcode %d is outside the token-loop path and is not "
-                        "implemented by this backend", c->op);
+        return ltl_row_rms(c->p0, (float*)c->p2, c->i0, c->i1, c->s0 > 0 ? c->s0 : c->i1, c->s1 > 0 ? c->s1 : 1, c->f0,
+                           c->dtype, s);
     default:
         return ltl_fail(LTL_ERR_ARG, "prog: unknown opcode %d", c->op);
     }
@@ -155,7 +187,9 @@ void luaTL_prog_graph_free(luaTL_prog_t* P)
 void luaTL_prog_destroy(luaTL_prog_t* P)
 {
     if (!P) return;
+    if (P->stream) cudaStreamSynchronize((cudaStream_t)P->stream);
     luaTL_prog_graph_free(P);
+    free_scratch(P);
     if (P->ev_start) cudaEventDestroy((cudaEvent_t)P->ev_start);
     if (P->ev_stop) cudaEventDestroy((cudaEvent_t)P->ev_stop);
     if (P->stream && P->owns_stream) cudaStreamDestroy((cudaStream_t)P->stream);

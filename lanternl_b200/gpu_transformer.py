@@ -99,6 +99,8 @@ class Model:
         self.steps = 0
         self.freed = False
         self._last_ms = -1.0
+        self.use_graph = bool(cfg.get("graph", False))      # gpu_transformer.lua:164: capture the step once warm
+        self._graph_on = False
 
         c = _lib.LmConfig(self.vocab, self.dim, self.layers, self.heads, self.ffn, self.T, self.B,
                           self.decode_batch, int(self.tie), self.dtype, int(self.use_rope),
@@ -379,10 +381,25 @@ class Model:
     def last_step_ms(self):
         return self._last_ms
 
-    def maybe_capture(self):
-        return True          # the decode loop captures its own graph; the train step needs none
+    def capture(self):
+        """Model:capture (gpu_transformer.lua:714-728): from now on the forward + loss + backward of train_step run as
+        one captured CUDA graph, replayed while the valid-target count of the batch is the one it was captured with
+        (the reference's replay rule, :643) and captured again when it changes.  The optimizer launches stay outside,
+        their scalars change every step.  The native side captures on the first eligible step after two warm ones."""
+        self._alive("capture")
+        _lib.call("luaTL_lm_set_graph", self._h, 1)
+        self.use_graph = True
+        return True
 
-    capture = maybe_capture
+    def maybe_capture(self):
+        """gpu_transformer.lua:730-733: capture once the model was built with graph = true and two steps have run."""
+        if self.use_graph and not self._graph_on and (self.steps or 0) >= 2:
+            self._graph_on = self.capture()
+        return self.graph_ready
+
+    @property
+    def graph_ready(self):
+        return bool(self._h) and bool(_lib.load().luaTL_lm_graph_ready(self._h))
 
     def free(self):
         if self.freed:

@@ -131,6 +131,8 @@ class EpochLoop:
                 if self.on_step:
                     self.on_step(self, dict(step=gstep, epoch=epoch, batch=b + 1, nbatch=nbatch, loss=loss, lr=lr, gnorm=gnorm,
                                             finite=bool(finite), acc=(100.0 * corr / tok) if tok > 0 else None))
+                if hasattr(m, "maybe_capture"):
+                    m.maybe_capture()                              # lmtrain_gpu.lua:287: graph = true captures the step once warm
             avg = sum_loss / sum_tok if sum_tok > 0 else math.inf
             self.loss, self.grad_norm = avg, last_norm
             self.accuracy = 100.0 * correct / sum_tok if sum_tok > 0 else 0.0

@@ -388,25 +388,45 @@ class IdBatches:
 
     def __init__(self, windows, batch, seq_len, vocab, pinned=None):
         self.windows, self.B, self.T, self.V = windows, int(batch), int(seq_len), int(vocab)
-        self.pinned = False
+        self.pinned, self._host = False, None
         buf = None
         if pinned is not False:
+            # page-locked memory from the backend itself (the reference's luaTL_host_alloc_pinned,
+            # cuda/luaTL_core.cu:1801), once luaTL_init has bound a device
             try:
-                import torch
-                if torch.cuda.is_available():
-                    self._keep = torch.empty((2, self.B, self.T), dtype=torch.int32, pin_memory=True)
-                    buf, self.pinned = self._keep.numpy(), True
+                import ctypes as C
+                from . import _lib
+                _lib.ensure_init()
+                nbytes = 2 * self.B * self.T * 4
+                ptr = _lib.load().luaTL_host_alloc_pinned(nbytes)
+                if not ptr:
+                    raise TokenizerError("IdBatches: " + _lib.last_error())
+                self._host = ptr
+                flat = np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_int32)), shape=(2 * self.B * self.T,))
+                buf, self.pinned = flat.reshape(2, self.B, self.T), True
             except Exception:
                 if pinned:
-                    raise
+                    raise TokenizerError("IdBatches: page-locked memory needs a CUDA device")
         if buf is None:
-            if pinned:
-                raise TokenizerError("IdBatches: page-locked memory needs a CUDA device")
             buf = np.empty((2, self.B, self.T), dtype=np.int32)
         self.ids, self.tgt = buf[0], buf[1]
 
     def __len__(self):
         return (len(self.windows) + self.B - 1) // self.B
+
+    def close(self):
+        """Give the page-locked buffer back (views of it must not be used afterwards)."""
+        if self._host:
+            from . import _lib
+            self.ids = self.tgt = None
+            _lib.load().luaTL_host_free_pinned(self._host)
+            self._host, self.pinned = None, False
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
     def fill(self, first):
         """Pack windows[first : first + batch]; returns (ids, tgt, valid) - views of the reusable buffer."""

@@ -24,7 +24,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 REF_SO = os.path.join(_HERE, "_ref", "luaTL_ref.so")
 
-F32 = 0
+F32, BF16 = 0, 2
 _vp, _i, _f, _u64, _ll = C.c_void_p, C.c_int, C.c_float, C.c_uint64, C.c_longlong
 
 
@@ -87,9 +87,9 @@ def _sv(ptr, rows, cols, rs, cs, bs=0):
 class _T:
     """Owning device tensor of the driven library."""
 
-    def __init__(self, L, rows, cols):
+    def __init__(self, L, rows, cols, dtype=F32):
         self.L, self.t = L, Tensor()
-        if L.luaTL_tensor_init(C.byref(self.t), rows, cols, F32, None) != 0:
+        if L.luaTL_tensor_init(C.byref(self.t), rows, cols, dtype, None) != 0:
             raise RuntimeError("tensor_init: " + L.luaTL_get_last_error().decode())
         L.luaTL_tensor_zero(C.byref(self.t))
         self.rows, self.cols = rows, cols
@@ -122,8 +122,9 @@ class _T:
 class _P:
     """Program builder: the op-struct writers of ai/gpu/luaTL_train.lua:344-605."""
 
-    def __init__(self, L, cap, timing=False):
+    def __init__(self, L, cap, timing=False, dtype=F32):
         self.L = L
+        self.dt = dtype                      # storage type of every floating-point tensor the ops touch
         self.h = L.luaTL_prog_create(cap, 1 if timing else 0)
         if not self.h:
             raise RuntimeError("prog_create: " + L.luaTL_get_last_error().decode())
@@ -140,7 +141,7 @@ class _P:
         a = a if isinstance(a, dict) else a.sv()
         b = b if isinstance(b, dict) else b.sv()
         c = c if isinstance(c, dict) else c.sv()
-        return self._push(op=1, dtype=F32, i0=a["rows"], i1=b["cols"], i2=a["cols"], i3=batch, f0=1.0, f1=beta,
+        return self._push(op=1, dtype=self.dt, i0=a["rows"], i1=b["cols"], i2=a["cols"], i3=batch, f0=1.0, f1=beta,
                           f2=1e-5, s0=a["rs"], s1=a["cs"], s2=b["rs"], s3=b["cs"], s4=c["rs"], s5=c["cs"],
                           s6=a["bs"], s7=b["bs"], s8=c["bs"], p0=a["data"], p1=b["data"], p2=c["data"])
 
@@ -151,54 +152,54 @@ class _P:
         return self.gemm(X.tr(), dY, dW, beta=1.0)
 
     def axpy(self, dst, b, a=1.0):
-        return self._push(op=2, dtype=F32, i0=6, f0=a, f1=0.0, n=dst.nelem, p0=dst.data, p1=b.data, p2=dst.data)
+        return self._push(op=2, dtype=self.dt, i0=6, f0=a, f1=0.0, n=dst.nelem, p0=dst.data, p1=b.data, p2=dst.data)
 
     def rmsnorm(self, x, w, out, eps):
-        return self._push(op=3, dtype=F32, i0=x.rows, i1=x.cols, f0=eps, p0=x.data, p1=w.data, p2=out.data)
+        return self._push(op=3, dtype=self.dt, i0=x.rows, i1=x.cols, f0=eps, p0=x.data, p1=w.data, p2=out.data)
 
     def rmsnorm_bwd(self, x, g, dy, dx, dg, eps):
-        return self._push(op=4, dtype=F32, i0=x.rows, i1=x.cols, f0=eps, p0=x.data, p1=g.data, p2=dy.data,
+        return self._push(op=4, dtype=self.dt, i0=x.rows, i1=x.cols, f0=eps, p0=x.data, p1=g.data, p2=dy.data,
                           p3=dx.data, p4=dg.data)
 
     def softmax(self, x, out, causal, group, scale):
-        return self._push(op=5, dtype=F32, i0=x.rows, i1=x.cols, i2=int(causal), i3=group, i4=0, f0=scale,
+        return self._push(op=5, dtype=self.dt, i0=x.rows, i1=x.cols, i2=int(causal), i3=group, i4=0, f0=scale,
                           p0=x.data, p2=out.data)
 
     def softmax_bwd(self, y, dy, dx, causal, group, scale):
-        return self._push(op=6, dtype=F32, i0=y.rows, i1=y.cols, i2=int(causal), i3=group, i4=0, f0=scale,
+        return self._push(op=6, dtype=self.dt, i0=y.rows, i1=y.cols, i2=int(causal), i3=group, i4=0, f0=scale,
                           p0=y.data, p1=dy.data, p2=dx.data)
 
     def swiglu(self, a_ptr, b_ptr, out, lda, ldb, ldo):
-        return self._push(op=7, dtype=F32, i0=out.rows, i1=out.cols, i2=lda, i3=ldb, i4=ldo, p0=a_ptr, p1=b_ptr,
+        return self._push(op=7, dtype=self.dt, i0=out.rows, i1=out.cols, i2=lda, i3=ldb, i4=ldo, p0=a_ptr, p1=b_ptr,
                           p2=out.data)
 
     def swiglu_bwd(self, a_ptr, b_ptr, dout, da_ptr, db_ptr, lda, ldb, ldo):
-        return self._push(op=8, dtype=F32, i0=dout.rows, i1=dout.cols, i2=lda, i3=ldb, i4=ldo, p0=a_ptr, p1=b_ptr,
+        return self._push(op=8, dtype=self.dt, i0=dout.rows, i1=dout.cols, i2=lda, i3=ldb, i4=ldo, p0=a_ptr, p1=b_ptr,
                           p2=dout.data, p3=da_ptr, p4=db_ptr)
 
     def rope(self, x_ptr, rows, heads, hd, row_stride, pos, theta, inverse=False):
-        return self._push(op=9, dtype=F32, i0=rows, i1=heads, i2=hd, i3=row_stride, i4=0, i5=0, i6=int(inverse),
+        return self._push(op=9, dtype=self.dt, i0=rows, i1=heads, i2=hd, i3=row_stride, i4=0, i5=0, i6=int(inverse),
                           f0=theta, p0=x_ptr, p1=pos.data)
 
     def embed(self, ids, tbl, out):
-        return self._push(op=10, dtype=F32, i0=out.rows, i1=out.cols, i2=tbl.rows, p0=ids.data, p1=tbl.data, p2=out.data)
+        return self._push(op=10, dtype=self.dt, i0=out.rows, i1=out.cols, i2=tbl.rows, p0=ids.data, p1=tbl.data, p2=out.data)
 
     def embed_bwd(self, ids, dout, dtable, scale=1.0):
-        return self._push(op=11, dtype=F32, i0=dout.rows, i1=dout.cols, i2=dtable.rows, f0=scale, p0=ids.data,
+        return self._push(op=11, dtype=self.dt, i0=dout.rows, i1=dout.cols, i2=dtable.rows, f0=scale, p0=ids.data,
                           p1=dout.data, p2=dtable.data)
 
     def cross_entropy(self, logits, tgt, losses, dlogits, gs):
-        return self._push(op=12, dtype=F32, i0=logits.rows, i1=logits.cols, i2=-1, f0=gs, p0=logits.data,
+        return self._push(op=12, dtype=self.dt, i0=logits.rows, i1=logits.cols, i2=-1, f0=gs, p0=logits.data,
                           p1=tgt.data, p2=losses.data, p3=dlogits.data if dlogits is not None else None)
 
     def l2(self, x, acc):
-        return self._push(op=14, dtype=F32, n=x.nelem, p0=x.data, p2=acc.data)
+        return self._push(op=14, dtype=self.dt, n=x.nelem, p0=x.data, p2=acc.data)
 
     def clip(self, x, nsq, max_norm):
-        return self._push(op=15, dtype=F32, n=x.nelem, f0=max_norm, p1=nsq.data, p2=x.data)
+        return self._push(op=15, dtype=self.dt, n=x.nelem, f0=max_norm, p1=nsq.data, p2=x.data)
 
     def adamw(self, w, g, m, v, lr, b1, b2, eps, wd, step):
-        return self._push(op=16, dtype=F32, i0=step, f0=lr, f1=b1, f2=b2, f3=eps, f4=wd, f5=0.0, n=w.nelem,
+        return self._push(op=16, dtype=self.dt, i0=step, f0=lr, f1=b1, f2=b2, f3=eps, f4=wd, f5=0.0, n=w.nelem,
                           p0=w.data, p1=g.data, p2=m.data, p3=v.data)
 
     def zero(self, t):
@@ -208,7 +209,7 @@ class _P:
         return self._push(op=18, n=src.nbytes, p0=src.data, p2=dst.data)
 
     def argmax(self, x, out):
-        return self._push(op=23, dtype=F32, i0=x.rows, i1=x.cols, p0=x.data, p2=out.data)
+        return self._push(op=23, dtype=self.dt, i0=x.rows, i1=x.cols, p0=x.data, p2=out.data)
 
     def sum(self, x, acc, scale):
         return self._push(op=24, n=x.nelem, f0=scale, p0=x.data, p2=acc.data)
@@ -241,8 +242,12 @@ class RefModel:
 
     def __init__(self, vocab, dim, layers, heads, ffn, max_seq, batch_size, tie=True, eps=1e-5,
                  rope_base=10000.0, use_rope=True, causal=True, clip_norm=0.0, weight_decay=0.0,
-                 beta1=0.9, beta2=0.95, adam_eps=1e-8, so_path=REF_SO, timing=True):
+                 beta1=0.9, beta2=0.95, adam_eps=1e-8, so_path=REF_SO, timing=True, dtype=F32):
+        """dtype = BF16 drives the reference's bf16 storage variants of the same kernels (every kernel is a template
+        over the storage type, accumulation stays fp32: TAcc<bf16> in cuda/luaTL_core.cu); the Lua host merely
+        defaults to F32 (ai/gpu/gpu_transformer.lua:60).  Forward only in that mode."""
         self.L = L = load(so_path)
+        self.dt, self.es = dtype, (4 if dtype == F32 else 2)
         self.V, self.D, self.nl, self.H, self.F, self.T, self.B = vocab, dim, layers, heads, ffn, max_seq, batch_size
         self.hd, self.N = dim // heads, batch_size * max_seq
         self.tie, self.eps, self.rope_base, self.use_rope, self.causal = tie, eps, rope_base, use_rope, causal
@@ -254,11 +259,15 @@ class RefModel:
 
     def _alloc(self):
         L, V, D, F, N, B, H, T = self.L, self.V, self.D, self.F, self.N, self.B, self.H, self.T
-        A = lambda r, c: _T(L, r, c)
+        dt = self.dt
+        A = lambda r, c: _T(L, r, c, dt)             # floating-point tensors of the model
+        I = lambda r, c: _T(L, r, c, F32)            # 4-byte cells: ids, targets, positions, predictions, fp32 scalars
         self.params = []
 
         def param(name, r, c, decay):
-            p = dict(name=name, rows=r, cols=c, nelem=r * c, decay=decay, w=A(r, c), g=A(r, c), m=A(r, c), v=A(r, c))
+            p = dict(name=name, rows=r, cols=c, nelem=r * c, decay=decay, w=A(r, c))
+            if dt == F32:
+                p.update(g=A(r, c), m=A(r, c), v=A(r, c))
             self.params.append(p)
             return p
         self.emb = param("tok_emb", V, D, True)
@@ -269,7 +278,7 @@ class RefModel:
                                  w13=param(f"l{l}.w13", D, 2 * F, True), w2=param(f"l{l}.w2", F, D, True)))
         self.lnf = param("lnf", 1, D, False)
         self.wout = param("head", D, V, True) if not self.tie else None
-        self.ids, self.tgt, self.pos = A(N, 1), A(N, 1), A(N, 1)
+        self.ids, self.tgt, self.pos = I(N, 1), I(N, 1), I(N, 1)
         pos = (np.arange(N) % T).astype(np.int32)
         L.luaTL_upload_i32(self.pos.data, pos.ctypes.data_as(_vp), N)
         nl = self.nl
@@ -282,8 +291,10 @@ class RefModel:
         self.h2 = [A(N, D) for _ in range(nl)]
         self.h13 = [A(N, 2 * F) for _ in range(nl)]
         self.hs = [A(N, F) for _ in range(nl)]
-        self.hf, self.logits, self.losses, self.pred = A(N, D), A(N, V), A(N, 1), A(N, 1)
-        self.lossacc, self.nsq = A(1, 1), A(1, 1)
+        self.hf, self.logits, self.losses, self.pred = A(N, D), A(N, V), I(N, 1), I(N, 1)
+        self.lossacc, self.nsq = I(1, 1), I(1, 1)
+        if dt != F32:
+            return                                   # forward only: no backward scratch
         self.dres, self.dbr, self.dhf, self.dh1 = A(N, D), A(N, D), A(N, D), A(N, D)
         self.dqkv, self.dsc, self.dattn, self.dh2 = A(N, 3 * D), A(B * H * T, T), A(N, D), A(N, D)
         self.dh13, self.dhs = A(N, 2 * F), A(N, F)
@@ -292,6 +303,7 @@ class RefModel:
         B, T, D, H, hd, F, V, N = self.B, self.T, self.D, self.H, self.hd, self.F, self.V, self.N
         D3, F2, TT = 3 * D, 2 * F, T * T
         HTT = H * TT
+        es = self.es
         p.zero(self.lossacc)
         p.embed(self.ids, self.emb["w"], self.res[0])
         for l in range(self.nl):
@@ -301,21 +313,21 @@ class RefModel:
             p.gemm(self.h1[l], ly["wqkv"]["w"], qkv)
             if self.use_rope:
                 p.rope(qkv.data, N, H, hd, D3, self.pos, self.rope_base)
-                p.rope(qkv.data + D * 4, N, H, hd, D3, self.pos, self.rope_base)
+                p.rope(qkv.data + D * es, N, H, hd, D3, self.pos, self.rope_base)
             for b in range(B):
-                qb = b * T * D3 * 4
-                p.gemm(_sv(qkv.data + qb, T, hd, D3, 1, hd), _sv(qkv.data + qb + D * 4, hd, T, 1, D3, hd),
-                       _sv(sc.data + b * HTT * 4, T, T, T, 1, TT), batch=H)
+                qb = b * T * D3 * es
+                p.gemm(_sv(qkv.data + qb, T, hd, D3, 1, hd), _sv(qkv.data + qb + D * es, hd, T, 1, D3, hd),
+                       _sv(sc.data + b * HTT * es, T, T, T, 1, TT), batch=H)
             p.softmax(sc, sc, self.causal, T, self.scale)
             for b in range(B):
-                qb = b * T * D3 * 4
-                p.gemm(_sv(sc.data + b * HTT * 4, T, T, T, 1, TT), _sv(qkv.data + qb + 2 * D * 4, T, hd, D3, 1, hd),
-                       _sv(at.data + b * T * D * 4, T, hd, D, 1, hd), batch=H)
+                qb = b * T * D3 * es
+                p.gemm(_sv(sc.data + b * HTT * es, T, T, T, 1, TT), _sv(qkv.data + qb + 2 * D * es, T, hd, D3, 1, hd),
+                       _sv(at.data + b * T * D * es, T, hd, D, 1, hd), batch=H)
             p.copy(xin, mid)
             p.gemm(at, ly["wo"]["w"], mid, beta=1.0)
             p.rmsnorm(mid, ly["ln2"]["w"], self.h2[l], self.eps)
             p.gemm(self.h2[l], ly["w13"]["w"], self.h13[l])
-            p.swiglu(self.h13[l].data, self.h13[l].data + F * 4, self.hs[l], F2, F2, F)
+            p.swiglu(self.h13[l].data, self.h13[l].data + F * es, self.hs[l], F2, F2, F)
             p.copy(mid, xout)
             p.gemm(self.hs[l], ly["w2"]["w"], xout, beta=1.0)
         p.rmsnorm(self.res[self.nl], self.lnf["w"], self.hf, self.eps)
@@ -379,11 +391,15 @@ class RefModel:
         L, B, npar = self.nl, self.B, len(self.params)
         cap = 256 + L * (48 + 8 * B) + npar * 8
         self._ce_ops, self._sum_ops, self._adam_ops = [], [], []
+        self.p_fwd = _P(self.L, cap, self.timing, self.dt)
+        self._queue_forward(self.p_fwd, False)
+        self.graph_ready = False
+        self.p_zero = self.p_step = self.p_opt = None
+        if self.dt != F32:
+            return
         self.p_zero = _P(self.L, npar + 8)
         for p in self.params:
             self.p_zero.zero(p["g"])
-        self.p_fwd = _P(self.L, cap, self.timing)
-        self._queue_forward(self.p_fwd, False)
         self.p_step = _P(self.L, cap, self.timing)
         self._queue_forward(self.p_step, True)
         self._queue_backward(self.p_step)
@@ -474,8 +490,11 @@ class RefModel:
             tgt[:n] = 0
             self._upload(ids, tgt)
             self.p_fwd.run()
-            row = np.empty(self.V, dtype=np.float32)
-            self.L.luaTL_download_f32(self.logits.data + (n - 1) * self.V * 4, row.ctypes.data_as(_vp), self.V)
+            if self.dt == F32:
+                row = np.empty(self.V, dtype=np.float32)
+                self.L.luaTL_download_f32(self.logits.data + (n - 1) * self.V * 4, row.ctypes.data_as(_vp), self.V)
+            else:
+                row = self.logits.download().reshape(self.N, self.V)[n - 1]
             best, bv = 0, -np.inf
             for j in range(self.V):
                 if row[j] > bv:
@@ -486,7 +505,8 @@ class RefModel:
 
     def free(self):
         for p in (self.p_zero, self.p_fwd, self.p_step, self.p_opt):
-            p.free()
+            if p is not None:
+                p.free()
         for name, v in list(vars(self).items()):
             if isinstance(v, _T):
                 v.free()
@@ -495,4 +515,5 @@ class RefModel:
                     t.free()
         for p in self.params:
             for k in ("w", "g", "m", "v"):
-                p[k].free()
+                if k in p:
+                    p[k].free()

@@ -17,7 +17,8 @@ HEADER = os.path.join(ROOT, "include", "luatl_b200.h")
 
 def declared():
     h = open(HEADER).read()
-    names = set(re.findall(r"\b(luaTL_\w+)\s*\(", h))
+    # luaTL_* plus the reference's legacy float-only wrappers (matmul_cuda, fused_*_cuda, add_*_cuda, ...)
+    names = set(re.findall(r"\b(luaTL_\w+|\w+_cuda)\s*\(", h))
     return sorted(n for n in names if not n.endswith("_t"))
 
 

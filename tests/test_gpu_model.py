@@ -488,3 +488,67 @@ def test_config4_width_mixed_precision_against_the_fp32_path():
     assert abs(res["bf16"][0] - res["f32"][0]) < MIXED_LOSS_TOL * res["f32"][0]
     worst = max((l2_err(res["bf16"][1][n], res["f32"][1][n]), n) for n in res["f32"][1])
     assert worst[0] < MIXED_GRAD_TOL, worst
+
+
+# ---- scratch that moves under a captured decode graph ----------------------------------------------------------------
+def test_generate_train_generate_on_an_fp32_model_with_split_kv(monkeypatch):
+    """A captured decode step carries the split-KV scratch pointer; the first training step grows that scratch (RMSNorm
+    backward partials).  The second generation must not replay a graph that points into the freed buffer: it has to
+    give what an uncaptured model with the same weights gives, and what the oracle gives."""
+    cfg = dict(vocab=300, dim=64, layers=2, heads=4, ffn=96, max_seq=96)
+    w = params_for(cfg, seed=11, std=0.1)
+    B, T = 2, cfg["max_seq"]
+    prompts = synth.uniform_ids(12, 2 * 40, cfg["vocab"]).reshape(2, 40)
+    ids = synth.uniform_ids(13, B * T, cfg["vocab"]).reshape(B, T)
+    tgt = shifted_targets(ids)
+    m = make(cfg, B, w, decode_batch=2, kv_splits=4, optimizer="sgd")
+    first = m.generate_batch(prompts, 24, zero_indexed=True)              # captures the decode graph (splits > 1)
+    m.train_step_ids(ids, tgt, lr=0.05)                                   # grows the scratch, updates the weights
+    second = m.generate_batch(prompts, 24, zero_indexed=True)
+    w2 = m.flat_params()
+    fresh = make(cfg, B, w2, decode_batch=2, kv_splits=4)
+    assert np.array_equal(second, fresh.generate_batch(prompts, 24, zero_indexed=True))
+    assert np.array_equal(second, oracle_for(cfg).greedy(w2, prompts, 24))
+    assert np.array_equal(first, oracle_for(cfg).greedy(w, prompts, 24))
+    m.free(); fresh.free()
+
+
+# ---- the captured training step (gpu_transformer.lua:643, :714-733) ------------------------------------------------------
+@pytest.mark.parametrize("dtype,opt", [("f32", "sgd"), ("f32", "adamw"), ("bf16", "sgd")])
+def test_captured_training_step_follows_the_eager_one(dtype, opt):
+    cfg = dict(vocab=512, dim=128, layers=2, heads=2, ffn=192, max_seq=64)
+    w = params_for(cfg, seed=3, std=0.05)
+    B, T = 4, cfg["max_seq"]
+    ids = synth.zipf_ids(5, B * T, cfg["vocab"]).reshape(B, T)
+    tgt = shifted_targets(ids)
+    tgt2 = tgt.copy()
+    tgt2[1, 20:] = -1                                                     # another valid count: the graph is captured again
+    a = make(cfg, B, w, optimizer=opt, dtype=dtype, weight_decay=0.01, clip_norm=1.0)
+    b = make(cfg, B, w, optimizer=opt, dtype=dtype, weight_decay=0.01, clip_norm=1.0, graph=True)
+    la, lb = [], []
+    for step in range(1, 9):
+        t = tgt2 if step in (6, 7) else tgt
+        la.append(a.train_step_ids(ids, t, lr=0.02, step=step)[0])
+        lb.append(b.train_step_ids(ids, t, lr=0.02, step=step)[0])
+        b.maybe_capture()
+        assert b.graph_ready == (step >= 3)
+    tol = 1e-5 if dtype == "f32" else 2e-3                                # atomics reorder sums; bf16 also rounds operands
+    assert np.allclose(la, lb, rtol=tol, atol=0)
+    assert rel_err(b.flat_params(), a.flat_params()) < (1e-5 if dtype == "f32" else 1e-3)
+    assert la[-1] < la[0]
+    a.free(); b.free()
+
+
+def test_non_finite_loss_skips_the_update_without_a_host_round_trip():
+    cfg = dict(vocab=64, dim=32, layers=1, heads=2, ffn=48, max_seq=16)
+    w = params_for(cfg, seed=7, std=0.2)
+    w[5] = np.inf                                                          # one weight of the embedding table
+    B, T = 2, cfg["max_seq"]
+    ids = np.zeros((B, T), np.int32)                                       # token 0 reads that row
+    m = make(cfg, B, w, optimizer="sgd", weight_decay=0.1, clip_norm=1.0)
+    loss, _, _, gnorm, finite = m.train_step_ids(ids, shifted_targets(ids), lr=0.05)
+    assert not finite and not np.isfinite(loss) and gnorm == 0.0
+    after = m.flat_params()
+    keep = np.isfinite(w)
+    assert np.array_equal(after[keep], w[keep]) and m.steps == 0
+    m.free()

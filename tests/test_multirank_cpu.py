@@ -79,3 +79,37 @@ def test_shard_rows_rejects_uneven_split():
     import pytest
     with pytest.raises(SystemExit):
         bench.shard_rows(np.zeros((5, 2), np.int32), 2, 0)
+
+
+# ---- a rank that never reaches the exchange -------------------------------------------------------------------------
+def exchange_worker(rank, out_dir):
+    """Two host processes around one 'collective' whose completion is the other rank's arrival file.  Round 1: both
+    arrive.  Round 2: rank 1 skips the exchange (a host-made failure); rank 0's wait must run out, tear the
+    communicator down and report - not hang.  Round 3: the communicator itself reports an asynchronous error."""
+    import ctypes as C
+    import time
+    from lanternl_b200 import _lib
+    L = _lib.load()
+    mine, peer = os.path.join(out_dir, f"arrive{rank}"), os.path.join(out_dir, f"arrive{1 - rank}")
+    aborted = C.c_int(-1)
+    if rank == 1:
+        time.sleep(0.15)
+    open(mine + ".r1", "w").close()
+    rc = L.luaTL_comm_selftest_wait((peer + ".r1").encode(), 5000, 0, 0, C.byref(aborted))
+    assert rc == 0 and aborted.value == 0, (rc, aborted.value)
+    if rank == 0:
+        t0 = time.time()
+        rc = L.luaTL_comm_selftest_wait((peer + ".r2").encode(), 300, 0, 0, C.byref(aborted))     # rank 1 never writes it
+        assert rc == -4 and aborted.value == 1 and 0.25 < time.time() - t0 < 3.0
+        msg = L.luaTL_get_last_error().decode()
+        assert "did not finish within 300 ms" in msg and "communicator aborted" in msg, msg
+        L.luaTL_clear_error()
+        rc = L.luaTL_comm_selftest_wait(None, 5000, 6, 3, C.byref(aborted))                       # ncclRemoteError at the third poll
+        assert rc == -4 and aborted.value == 1 and b"asynchronous error 6" in L.luaTL_get_last_error()
+        L.luaTL_clear_error()
+    open(os.path.join(out_dir, f"xok{rank}"), "w").close()
+
+
+def test_a_rank_that_skips_the_exchange_ends_the_wait_with_an_error(tmp_path):
+    mp.spawn(exchange_worker, args=(str(tmp_path),), nprocs=WORLD, join=True)
+    assert all((tmp_path / f"xok{r}").exists() for r in range(WORLD))

@@ -1,6 +1,8 @@
 """The BPE tokenizer and the id batches in front of the token loop (CPU only): the reference's own test case,
 vectors derived by hand from ai/data/tokenizer.lua, the saved file byte for byte, the module against the
 literal restatement in oracle/ on seeded corpora, error messages, windows and batch packing."""
+import os
+
 import numpy as np
 import pytest
 
@@ -208,11 +210,9 @@ def test_id_batches_layout_and_range_check():
     assert blocks[0][0].dtype == np.int32 and blocks[0][0].flags["C_CONTIGUOUS"]
     with pytest.raises(ValueError, match=r"token out of range at window 3, pos 1 \(input 9, target 8, vocab 8\)"):
         list(T.IdBatches(w, batch=2, seq_len=3, vocab=8, pinned=False))
-    with pytest.raises(T.TokenizerError, match="needs a CUDA device"):
-        import torch
-        if torch.cuda.is_available():
-            raise T.TokenizerError("IdBatches: page-locked memory needs a CUDA device")
-        T.IdBatches(w, 2, 3, 10, pinned=True)
+    if not os.path.exists("/dev/nvidia0"):
+        with pytest.raises(T.TokenizerError, match="needs a CUDA device"):
+            T.IdBatches(w, 2, 3, 10, pinned=True)
 
 
 @pytest.mark.gpu
@@ -238,3 +238,5 @@ def test_text_to_device_steps_through_page_locked_batches():
     a, b, _ = m._pack(w[:8], 8)
     i0, t0, _ = ib.fill(0)
     assert np.array_equal(a, i0) and np.array_equal(b, t0)
+    ib.close()
+    assert not ib.pinned

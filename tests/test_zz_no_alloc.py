@@ -45,6 +45,25 @@ def test_noalloc_matches_regular_entry_point_on_two_calls_in_a_row(rows, cols):
         assert np.abs(dg_new.toflat() - dg_ref.toflat()).max() <= 2e-5 * max(1.0, float(np.abs(b).max()))
 
 
+@pytest.mark.parametrize("rows,cols", [(333, 256), (4, 1030)])
+def test_noalloc_against_the_analytic_gradient_in_float64(rows, cols):
+    """Independent of the regular entry point: dx and dgamma of y = x * rsqrt(mean x^2 + eps) * g in float64.  The
+    second shape (a row width that is no whole number of 16-byte packets per lane) takes the kernel that needs no
+    scratch, so it is accepted although it is wider than the static array's limit."""
+    n = rows * cols
+    x = synth.normal(11, 0, n).reshape(rows, cols).astype(np.float32)
+    g = (1.0 + 0.1 * synth.normal(12, 0, cols)).reshape(1, cols).astype(np.float32)
+    dy = synth.normal(13, 0, n).reshape(rows, cols).astype(np.float32)
+    dx, dg = run("luaTL_rmsnorm_bwd_noalloc", x, g, dy, rows, cols)
+    x64, g64, dy64 = x.astype(np.float64), g.astype(np.float64), dy.astype(np.float64)
+    sc = 1.0 / np.sqrt((x64 ** 2).mean(1, keepdims=True) + 1e-5)
+    dot = (dy64 * g64 * x64).sum(1, keepdims=True)
+    want_dx = sc * g64 * dy64 - sc ** 3 / cols * dot * x64
+    want_dg = (dy64 * x64 * sc).sum(0)
+    assert np.abs(dx - want_dx).max() <= 1e-5 * max(1.0, np.abs(want_dx).max())
+    assert np.abs(dg.toflat() - want_dg).max() <= 2e-5 * max(1.0, np.abs(want_dg).max())
+
+
 def test_noalloc_rejects_rows_wider_than_its_static_scratch():
     rows, cols = 4, 2048
     x = np.ones((rows, cols), np.float32)
