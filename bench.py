@@ -13,6 +13,9 @@ sequences sharded over the GPUs (256/N per GPU, no communication).  One step = o
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|train|train4|sweep]
 
+The default run adds `train`: a sub-record with a few steps of --workload train4 over the same ranks (the metric names both
+decode and training throughput); --no-train leaves it out.
+
 Prints ONE JSON line (rank 0).  `value` is timed with the inputs resident in HBM; `e2e` goes
 through the host-facing call with host buffers (H2D of the prompts / ids, D2H of the result).
 `--impl reference` times the CPU restatement of the reference's path (the reference's own CPU
@@ -171,7 +174,7 @@ def shard_rows(rows, world, rank):
 
 
 # DRAM bytes per algorithmic byte of the decode attention kernel: 101.08 MB read + 3.16 MB written for 100.9 MB of K/V
-# rows in the committed ncu summary of a 128-sequence launch (profiles/decode_attn_bulk_ncu_full.md).  Every K/V byte
+# rows in an ncu capture of a 128-sequence launch at cache length 385.  Every K/V byte
 # crosses HBM once whatever the batch, so the traffic of a full-size launch is this ratio times its algorithmic bytes.
 ATTN_TRAFFIC_PER_ALGORITHMIC_BYTE = 104.24 / 100.9
 
@@ -372,11 +375,13 @@ def fill_params_tiled(m, seed=0, std=0.02, block=1 << 24):
             _lib.call("luaTL_lm_write_params", m._h, t["offset"], t["nelem"], ones.ctypes.data_as(C.c_void_p))
 
 
-def run_train4(args, dist):
+def run_train4(args, dist, steps=None, warmup=None):
     """configs[4]: data-parallel mixed-precision training (bf16 tensor-core GEMMs, fp32 master weights, SGD).  The
     global batch of 64 sequences x 2048 tokens is split over the ranks; each rank walks its share in micro-batches
     that accumulate into the flat gradient, then one NCCL all-reduce and the SGD kernel."""
     from lanternl_b200 import _lib, gpu_transformer as GT, luatl_adapter as ad, synth
+    steps = args.steps if steps is None else steps
+    warmup = args.warmup if warmup is None else warmup
     cfg = dict(TRAIN4)
     if args.layers:
         cfg["layers"] = args.layers
@@ -409,14 +414,14 @@ def run_train4(args, dist):
         ad.upload_i32(d_tgt[i], tgt[i])
     res = _lib.LmResult()
 
-    def micro_args(i, step):
+    def micro_args(i, step, exchange=True):
         last = i == n_micro - 1
-        return m._args(0.01, step, valid_global, no_update=not last, accumulate=i > 0, skip_allreduce=not last)
+        return m._args(0.01, step, valid_global, no_update=not last, accumulate=i > 0, skip_allreduce=not (last and exchange))
 
-    def step_dev(step):
+    def step_dev(step, exchange=True):
         ms, launches = 0.0, 0
         for i in range(n_micro):
-            a = micro_args(i, step)
+            a = micro_args(i, step, exchange)
             _lib.call("luaTL_lm_train_step_dev", m._h, d_ids[i].t.data, d_tgt[i].t.data, C.byref(a), C.byref(res))
             ms += res.step_ms
             launches += m.last_timing()["launches"]
@@ -431,13 +436,13 @@ def run_train4(args, dist):
     gemm_tf = 2.0 * R * F2 * D / (gms.value * 1e-3) / 1e12
     clocks = Clocks(dist.local)
     clocks.start()
-    for w in range(args.warmup):
+    for w in range(warmup):
         step_dev(w + 1)
     dist.barrier()
     clocks.mark()
     dev_ms, launches = 0.0, 0
     t0 = time.perf_counter()
-    for s in range(args.steps):
+    for s in range(steps):
         ms, ln = step_dev(s + 1)
         dev_ms += ms
         launches += ln
@@ -445,10 +450,19 @@ def run_train4(args, dist):
     wall_ms = (time.perf_counter() - t0) * 1e3
     clk = clocks.stop()
     loss = res.loss
+    # the same steps without the exchange (every rank keeps its local gradient): what the all-reduce adds to a step
+    noex_ms = None
+    if dist.world > 1:
+        dist.barrier()
+        noex_ms = 0.0
+        for s in range(steps):
+            noex_ms += step_dev(s + 1, exchange=False)[0]
+        dist.barrier()
+        noex_ms = dist.max(noex_ms)
     # end to end: ids and targets come from host memory every micro-batch, the loss goes back
     dist.barrier()
     t0 = time.perf_counter()
-    for s in range(args.steps):
+    for s in range(steps):
         for i in range(n_micro):
             last = i == n_micro - 1
             m.train_step_ids(ids[i], tgt[i], 0.01, s + 1, valid_global=valid_global, no_update=not last,
@@ -456,17 +470,17 @@ def run_train4(args, dist):
     dist.barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     dev_ms, e2e_ms, wall_ms = dist.max(dev_ms), dist.max(e2e_ms), dist.max(wall_ms)
-    tokens = gb * T * args.steps
+    tokens = gb * T * steps
     pk = peaks()
     # model FLOPs of the step: 6 x parameters in matrices x tokens (+ attention)
     L, H, hd, V = cfg["layers"], cfg["heads"], cfg["dim"] // cfg["heads"], cfg["vocab"]
     mat = L * (4 * D * D + 3 * D * cfg["ffn"]) + V * D
     gemm_flops = 6.0 * mat * gb * T
     attn_flops = 3.0 * L * gb * H * 2 * T * T * hd          # causal halves the 4 T^2 hd of QK^T + PV; x3 for fwd + bwd
-    step_tf = (gemm_flops + attn_flops) * args.steps / (dev_ms * 1e-3) / 1e12 / dist.world
+    step_tf = (gemm_flops + attn_flops) * steps / (dev_ms * 1e-3) / 1e12 / dist.world
     line = dict(
         metric="train_tokens_per_s", value=tokens / (dev_ms * 1e-3), unit="tokens/s", n_gpus=dist.world,
-        steps=args.steps, warmup=args.warmup, ms_per_step=dev_ms / args.steps, higher_is_better=True, scaling="strong",
+        steps=steps, warmup=warmup, ms_per_step=dev_ms / steps, higher_is_better=True, scaling="strong",
         vs_baseline=None, dtype="bf16", data="synthetic",
         config=dict(workload=f"configs[4] data-parallel training: V32000 D2048 L{L} H16 F5632 ctx2048, global batch {gb} x 2048 "
                              "(Zipf 1.1), bf16 tensor-core GEMMs with fp32 master weights, gradients and residual stream, SGD",
@@ -487,8 +501,16 @@ def run_train4(args, dist):
                                            "frac_of_burst of the burst figure the isolated GEMM above is compared with",
                                       achieved=step_tf, peak=pk["bf16_tflops_sustained"], frac=step_tf / pk["bf16_tflops_sustained"],
                                       frac_of_burst=step_tf / pk["bf16_tflops"])),
-        final_loss=loss, wall_ms_per_step=wall_ms / args.steps, clocks=clk)
+        final_loss=loss, wall_ms_per_step=wall_ms / steps, clocks=clk)
+    if dist.world > 1:
+        nbytes = 4 * (m.nparams() + 2)
+        line["allreduce"] = dict(bytes_per_step=nbytes, wire_bytes_per_gpu=int(2 * (dist.world - 1) / dist.world * nbytes),
+                                 overlapped_with_backward=os.environ.get("LUATL_OVERLAP_COMM", "1") != "0",
+                                 ms_per_step_without_exchange=noex_ms / steps,
+                                 exposed_ms_per_step=(dev_ms - noex_ms) / steps)
     m.free()
+    for t in d_ids + d_tgt:
+        t.free()
     return line
 
 
@@ -607,13 +629,18 @@ def run_sweep(args, dist):
         kernels=rows_out)
 
 
+CPU_THREADS = 16
+
+
 def host_threads():
-    """Host threads this process may use (cgroup / affinity aware), at most 32 and at most one per sequence."""
+    """Threads of the CPU baseline: one sequence per host thread, CPU_THREADS of them (fewer only where the process may use
+    fewer cores), the same in every record.  LuaJIT itself is single-threaded; sixteen independent sequences on sixteen
+    cores is what sixteen LuaJIT processes would give, and a fixed count keeps the figure comparable between boxes."""
     try:
         n = len(os.sched_getaffinity(0))
     except AttributeError:
         n = os.cpu_count() or 1
-    return max(1, min(n, 32, NSEQ_TOTAL))
+    return max(1, min(n, CPU_THREADS, NSEQ_TOTAL))
 
 
 def cpu_sample(threads, n_new=24):
@@ -709,6 +736,9 @@ def main():
     ap.add_argument("--global-batch", type=int, default=TRAIN4_GLOBAL_BATCH, help="train4: sequences per optimizer step over all GPUs")
     ap.add_argument("--layers", type=int, default=0, help="train4: layer count override (profiling aid; the metric uses 16)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-train", action="store_true", help="decode: leave the configs[4] training sub-record out")
+    ap.add_argument("--train-steps", type=int, default=5, help="decode: timed steps of the training sub-record")
+    ap.add_argument("--train-warmup", type=int, default=3, help="decode: warm-up steps of the training sub-record")
     ap.add_argument("--nseq", type=int, default=NSEQ_TOTAL, help="sequences over all GPUs (profiling aid; the metric uses 256)")
     ap.add_argument("--decode-scaling", default="strong", choices=["strong", "weak"],
                     help="decode: strong = the configuration's sequences split over the GPUs (configs[2]: 32/64/128/256 per GPU at "
@@ -727,6 +757,15 @@ def main():
         return
     dist = Dist(args.gpus)
     line = {"decode": run_decode, "train": run_train, "train4": run_train4, "sweep": run_sweep}[args.workload](args, dist)
+    if args.workload == "decode" and not args.no_train and args.nseq == 256:
+        # the other half of the metric: configs[4] data-parallel training over the same ranks (tensor-core GEMMs and
+        # attention, NCCL all-reduce of the flat gradient), a few steps, as a sub-record of the headline line
+        t = run_train4(args, dist, steps=args.train_steps, warmup=args.train_warmup)
+        line["train"] = {k: t[k] for k in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "scaling", "dtype",
+                                           "config", "e2e", "gpu_launches", "roofline", "final_loss", "clocks") if k in t}
+        if "allreduce" in t:
+            line["train"]["allreduce"] = t["allreduce"]
+        line["gpu_launches"] = int(line["gpu_launches"]) + int(t["gpu_launches"])
     if dist.rank == 0:
         if dist.world == 1 and not args.no_cpu_baseline:
             threads = host_threads()

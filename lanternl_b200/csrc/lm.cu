@@ -97,6 +97,8 @@ struct luaTL_lm_s {
     float* part = nullptr;       // split-K partial sums of the decode GEMMs [8][nseq_cap][D]
     float* ssq[2] = { nullptr, nullptr };   // per-row sums of squares by 32-column tile [nseq_cap][D / 32] (fused residual GEMMs)
     int* tile_tickets = nullptr; // arrival counters of the fused residual GEMMs, one per output tile, zero between launches
+    unsigned* chain_bar = nullptr;   // grid barrier words of the chain kernel (arrivals, generation)
+    int use_chain = 0, chain_pdl = 1;
     std::map<int, GraphEntry> graphs;
     cudaEvent_t ev[4] = { nullptr, nullptr, nullptr, nullptr };
     float prefill_ms = 0, decode_ms = 0;
@@ -790,6 +792,8 @@ int ensure_decode(LM* m, int nseq, int n_prompt, int n_new)
             DALLOC(m->ssq[1], (size_t)m->nseq_cap * tiles * 4, "row sums of squares");
             DALLOC(m->tile_tickets, ntick * 4, "tile tickets");
             LTL_CUDA("memset", cudaMemsetAsync(m->tile_tickets, 0, ntick * 4, m->s));
+            DALLOC(m->chain_bar, 16, "chain barrier");
+            LTL_CUDA("memset", cudaMemsetAsync(m->chain_bar, 0, 16, m->s));
         }
         LTL_CUDA("memset", cudaMemsetAsync(m->d_pos, 0, (size_t)m->nseq_cap * 4, m->s));
         LTL_CUDA("memset", cudaMemsetAsync(m->d_count, 0, (size_t)m->nseq_cap * 4, m->s));
@@ -936,6 +940,52 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
     return LTL_OK;
 }
 
+// Decode step with the chain kernel: one launch gathers the embedding and forms layer 0's q | k | v; every layer is then the
+// attention kernel and ONE cooperative launch that runs Wo (+ residual), RMSNorm + W13 + SwiGLU, W2 (+ residual) and RMSNorm +
+// the next layer's QKV (after the last layer: the lm_head) with grid barriers in between: 2 + 2 L launches per step
+// instead of 2 + 7 L.
+int decode_step_chain(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t* d_out, int out_stride, int pick,
+                      int32_t* hist, int hist_stride, int hist_base)
+{
+    const int D = m->D, F = m->F, V = m->V, L = m->L, H = m->H, hd = m->hd;
+    const size_t e = 2;
+    Act& a = m->dec;
+    float* x = a.res;
+    const int32_t* pos = m->d_pos + slot0;
+    const size_t cl = (size_t)m->nseq_cap * H * m->T * hd * e;
+    const size_t cslot = (size_t)slot0 * H * m->T * hd * e;
+    struct PdlScope { bool prev; PdlScope(bool on) : prev(ltl_pdl_enabled()) { ltl_pdl_set(on); } ~PdlScope() { ltl_pdl_set(prev); } } pdl(m->use_pdl);
+    LtlChainDesc d;
+    memset(&d, 0, sizeof(d));
+    d.M = nseq; d.eps = m->c.eps; d.tok = d_tok; d.vocab = V; d.x = x; d.bar = m->chain_bar; d.err = m->d_err; d.allow_pdl = m->chain_pdl;
+    d.nphases = 1;
+    d.ph[0] = LtlChainPhase{ 2, 2, 3 * D, D, m->Wb + m->off_emb, m->W + m->lo[0].ln1, m->Wb + m->lo[0].wqkv, a.qkv };
+    LTL_TRY(ltl_decode_chain(d, m->s));
+    m->launches++;
+    const bf16* head = m->Wb + (m->c.tie ? m->off_emb : m->off_head);
+    for (int l = 0; l < L; ++l) {
+        const LayerOff& o = m->lo[l];
+        void* kcl = (char*)m->kc + l * cl + cslot;
+        void* vcl = (char*)m->vc + l * cl + cslot;
+        const bool last = l + 1 == L;
+        LTL_TRY(ltl_decode_attn(a.qkv, kcl, vcl, a.attn, pos, nseq, H, hd, m->T, m->scale, LTL_BF16, m->splits, m->ws,
+                                m->rope_tab, m->c.rope_interleaved, m->c.use_rope, m->d_err, m->s));
+        d.nphases = 4;
+        d.ph[0] = LtlChainPhase{ 0, 0, D, D, a.attn, nullptr, m->Wb + o.wo, x };
+        d.ph[1] = LtlChainPhase{ 1, 1, 2 * F, D, x, m->W + o.ln2, m->Wb + o.w13, a.hs };
+        d.ph[2] = LtlChainPhase{ 0, 0, D, F, a.hs, nullptr, m->Wb + o.w2, x };
+        if (last) d.ph[3] = LtlChainPhase{ 1, 3, V, D, x, m->W + m->off_lnf, head, a.logits };
+        else d.ph[3] = LtlChainPhase{ 1, 2, 3 * D, D, x, m->W + m->lo[l + 1].ln1, m->Wb + m->lo[l + 1].wqkv, a.qkv };
+        LTL_TRY(ltl_decode_chain(d, m->s));
+        m->launches += 2 + (m->splits > 1 ? 1 : 0);
+    }
+    if (pick) {
+        LTL_TRY(pick_next(m, a.logits, nseq, slot0, d_out, out_stride, hist, hist_stride, hist_base, m->s));
+        m->launches++;
+    }
+    return LTL_OK;
+}
+
 // One token for every sequence: consumes d_next / d_pos, appends K/V, picks the next token.
 // Everything it reads that changes between steps lives in device memory, so the launch
 // sequence can be captured once and replayed.
@@ -943,6 +993,8 @@ int decode_step(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t* d_out
                 int32_t* hist = nullptr, int hist_stride = 0, int hist_base = 0)
 {
     const int D = m->D, F = m->F, V = m->V, L = m->L, H = m->H, hd = m->hd, adt = m->adt;
+    if (m->fuse_swiglu && m->use_chain && !m->fuse_norm && m->chain_bar && ltl_decode_chain_supported(D, F, V))
+        return decode_step_chain(m, nseq, slot0, d_tok, d_out, out_stride, pick, hist, hist_stride, hist_base);
     if (m->fuse_swiglu && ltl_gemm_tc_supported(m->dec.h1, m->Wb, nseq, D, D) && F % 8 == 0 && D % 8 == 0)
         return decode_step_split(m, nseq, slot0, d_tok, d_out, out_stride, pick, hist, hist_stride, hist_base);
     const size_t e = esz(adt);
@@ -1076,6 +1128,11 @@ int generate_dev(LM* m, const int32_t* d_prompts, int nseq, int n_prompt, int n_
     int err = 0;
     LTL_CUDA("error flag", cudaMemcpyAsync(&err, m->d_err, 4, cudaMemcpyDeviceToHost, m->s));
     LTL_CUDA("generate sync", cudaStreamSynchronize(m->s));
+    if (err == 3) {
+        cudaMemsetAsync(m->chain_bar, 0, 16, m->s);               // the barrier words may be mid-count: start clean next time
+        cudaStreamSynchronize(m->s);
+        return ltl_fail(LTL_ERR_CUDA, "lm generate: a grid barrier of the decode chain kernel ran out of polls");
+    }
     if (err) return ltl_fail(LTL_ERR_CAPACITY, "lm generate: a position left the KV cache");
     if (m->adt == LTL_BF16 && m->use_tc) LTL_TRY(ltl_gemm_tc_check(m->s));
     cudaEventElapsedTime(&m->prefill_ms, m->ev[0], m->ev[1]);
@@ -1133,6 +1190,17 @@ luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
         // while the fence + ticket + reduction of the fused form add three to the GEMM's critical path.
         const char* fn = getenv("LUATL_DECODE_FUSE_NORM");
         m->fuse_norm = fn && fn[0] == '1';
+        // LUATL_DECODE_CHAIN=1: the products of a layer between two attention kernels as ONE cooperative launch with grid
+        // barriers (decode_chain.cu), 2 + 2 L launches per step instead of 2 + 7 L.  Off by default: measured slower at every
+        // shard size (256 sequences 253.9 -> 387.6 ms per pass of 511 steps, 32 sequences 131.8 -> 183.6 ms).  A phase of that
+        // kernel costs about 6 us - panel load, product, epilogue, fence + arrival + poll of the barrier are five dependent
+        // L2 round trips - against about 4.3 us for a stand-alone kernel launched with programmatic dependent launch, whose
+        // prologue and weight fetch run under its predecessor's tail.  LUATL_CHAIN_PDL=0: the chain kernel waits for the whole
+        // of its predecessor instead of starting under its tail.
+        const char* ch = getenv("LUATL_DECODE_CHAIN");
+        m->use_chain = ch && ch[0] == '1';
+        const char* cp = getenv("LUATL_CHAIN_PDL");
+        m->chain_pdl = !(cp && cp[0] == '0');
         const char* oc = getenv("LUATL_OVERLAP_COMM");
         m->overlap_comm = !(oc && oc[0] == '0');
     }
@@ -1173,7 +1241,7 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
     void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
                      m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
                      m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part,
-                     m->Wm, m->d_done, m->d_nodecay, m->ssq[0], m->ssq[1], m->tile_tickets, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
+                     m->Wm, m->d_done, m->d_nodecay, m->chain_bar, m->ssq[0], m->ssq[1], m->tile_tickets, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
     for (void* p : ptrs) if (p) cudaFree(p);
     for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
     if (m->ev_grad) cudaEventDestroy(m->ev_grad);

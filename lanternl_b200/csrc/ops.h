@@ -183,6 +183,23 @@ bool ltl_gemm_rows_supported(const void* A, const void* B, int M, int N, int K, 
 int ltl_gemm_rows_plan_split(int N, int K, int max_parts);
 int ltl_gemm_rows(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, int epi, int ksplit, cudaStream_t s,
                   const LtlGemmFuse* fuse = nullptr);
+// ---- the products of a decode step between two attention kernels as one cooperative launch (decode_chain.cu) ----
+// A phase: out = epilogue(load(A) [M, K] . B[N, K]^T).  a_kind 0: A is bf16 [M, K]; 1: A = RMSNorm(x fp32 [M, K]) * gain rounded
+// to bf16; 2: the same over rows gathered from a bf16 table by desc.tok (also written to desc.x).  epi 0: out (fp32 [M, N])
+// += product; 1: SwiGLU over interleaved (gate, up) rows of B, out bf16 [M, N / 2]; 2: out bf16 [M, N]; 3: out fp32 [M, N].
+// Phases run in order, a grid barrier between them; `bar` = two zero-initialised words, `err` is raised (3) by a wait that ran out.
+struct LtlChainPhase { int a_kind, epi, N, K; const void* a; const float* gain; const void* b; void* out; };
+struct LtlChainDesc {
+    int M, nphases;
+    float eps;
+    const int32_t* tok; int vocab; float* x;
+    unsigned* bar; int* err;
+    int allow_pdl;
+    LtlChainPhase ph[4];
+};
+bool ltl_decode_chain_supported(int D, int F, int V);
+int ltl_decode_chain(const LtlChainDesc& d, cudaStream_t s);
+
 // CUtensorMap (128 bytes, written to out_map) of a bf16 matrix [rows, cols] with rows `pitch` elements apart:
 // boxes of box_rows x 64 columns, 128-byte swizzle.  Cached per (base, shape).
 int ltl_tensor_map_bf16(const void* base, int rows, int cols, long long pitch, int box_rows, void* out_map);

@@ -133,7 +133,7 @@ def test_legacy_float_wrappers():
     _lib.call("softmax_cuda", Cc.t.data, P.t.data, M, N)
     assert np.abs(host(P).sum(1) - 1).max() < 1e-5
     _lib.call("fused_add_bias_softmax_cuda", Cc.t.data, Bi.t.data, P.t.data, M, N, 0.5, 0)
-    z = (host(Cc).astype(np.float64) + bias) * 0.5
+    z = host(Cc).astype(np.float64) * 0.5 + bias                                   # scale first, then the column bias (core.cu:1138-1139)
     e = np.exp(z - z.max(1, keepdims=True))
     assert np.abs(host(P) - e / e.sum(1, keepdims=True)).max() < 1e-5
 

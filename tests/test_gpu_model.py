@@ -17,31 +17,28 @@ from tests.util import CFG0, CFG1, CFG2, bf16_round, l2_err, params_for, rel_err
 pytestmark = pytest.mark.gpu
 
 TOL_F32 = 1e-4          # max |err| / max |ref|, fp32 path
-TOL_BF16 = 2e-3         # same measure where bf16 operands feed tensor-core GEMMs.  The comparison is with the
-                        # reference path AT THE SAME STORAGE PRECISION: the oracle rounds to bf16 wherever the
-                        # reference's kernels would store a bf16 tensor (Oracle(act_bf16=True)).  Against the
-                        # pure float64 oracle a bf16 model cannot do better than ~5e-3 (one bf16 rounding of a
-                        # GEMM input alone moves the logits by 1.6e-3 of their norm); that figure is printed.
+TOL_BF16 = 2e-3         # same measure where bf16 operands feed tensor-core GEMMs, reached at SMALL widths only (dim <= 128:
+                        # few rounded values per row).  bf16 storage cannot meet it at the widths of configs[2]: there the
+                        # stated bound is median 6e-3 / no row above 1e-2 against the fp32 path, the level of any bf16-storage
+                        # implementation including the reference's own kernels run with bf16 tensors (7.4e-3 median); that
+                        # bound, with the measurements behind it, is asserted in tests/test_gpu_parity_config2.py.
+BF16_MEDIAN, BF16_ROW = 6e-3, 1e-2
 
 
 def bf16_steps_close(m, o, o64, w, ids):
-    """Feed `ids` through the one-token step and compare every logits row with the oracle at bf16
-    storage precision.  Rows agree to fp32 round-off except where a single activation lands on the
-    other side of a bf16 rounding boundary (fp32 vs float64 arithmetic before the store): such a
-    flip moves one element by one bf16 ulp.  At small widths flips are rare (median 2e-7, an odd
-    row at 2e-3); at the widths of configs[2] (512 / 1536 / 2816 rounded values per layer) several
-    happen in every row and the rows sit at 2e-3 .. 4e-3.  Bar: median below 5e-3, no row above
-    1e-2; the measured figures are printed.  Returns the last row."""
+    """Feed `ids` through the one-token step and compare every logits row with the fp32 path (float64 oracle) under the
+    bound stated for bf16 storage, and with the oracle that rounds to bf16 where a bf16 tensor would be stored (printed:
+    it models where the roundings happen, not their exact outcome - a value on the other side of a rounding boundary
+    moves one element by a bf16 ulp).  Returns the last row."""
     ref, ref64 = o.step_logits(w, ids), o64.step_logits(w, ids)
     st = m.new_state(0)
     rows = [m.step(int(t) + 1, st) for t in ids]
     errs = np.array([rel_err(r, ref[i]) for i, r in enumerate(rows)])
     e64 = np.array([rel_err(r, ref64[i]) for i, r in enumerate(rows)])
-    print(f"bf16 logits vs oracle at bf16 storage precision over {len(ids)} positions: median {np.median(errs):.1e}, "
-          f"max {errs.max():.1e}, rows above {TOL_BF16}: {(errs > TOL_BF16).sum()}; vs pure float64: median "
-          f"{np.median(e64):.1e}, max {e64.max():.1e}")
-    assert np.median(errs) < 5e-3 and errs.max() < 1e-2
-    assert e64.max() < 2e-2
+    print(f"bf16 logits over {len(ids)} positions vs the fp32 path: median {np.median(e64):.1e}, max {e64.max():.1e}; "
+          f"vs the oracle at bf16 storage precision: median {np.median(errs):.1e}, max {errs.max():.1e}")
+    assert np.median(e64) <= BF16_MEDIAN and e64.max() <= BF16_ROW
+    assert np.median(errs) <= BF16_MEDIAN and errs.max() <= BF16_ROW
     return rows[-1]
 
 
@@ -534,7 +531,8 @@ def test_captured_training_step_follows_the_eager_one(dtype, opt):
         assert b.graph_ready == (step >= 3)
     tol = 1e-5 if dtype == "f32" else 2e-3                                # atomics reorder sums; bf16 also rounds operands
     assert np.allclose(la, lb, rtol=tol, atol=0)
-    assert rel_err(b.flat_params(), a.flat_params()) < (1e-5 if dtype == "f32" else 1e-3)
+    # AdamW divides by sqrt(v): where a gradient is tiny, the last bits of differently ordered atomic sums show in the step
+    assert rel_err(b.flat_params(), a.flat_params()) < (1e-3 if dtype == "bf16" else 1e-4 if opt == "adamw" else 1e-5)
     assert la[-1] < la[0]
     a.free(); b.free()
 
@@ -552,3 +550,28 @@ def test_non_finite_loss_skips_the_update_without_a_host_round_trip():
     keep = np.isfinite(w)
     assert np.array_equal(after[keep], w[keep]) and m.steps == 0
     m.free()
+
+
+# ---- the cooperative chain kernel (one launch per layer between two attention kernels), kept as a measured alternative -----
+@pytest.mark.parametrize("nseq", [1, 6, 40, 130])
+def test_decode_chain_kernel_gives_the_tokens_of_the_default_path(nseq, monkeypatch):
+    """Tile shapes 16 / 32 / 64 rows, row blocks with a ragged tail, the gathering and the normalising panel loads, residual,
+    SwiGLU, bf16 and fp32 epilogues, three grid barriers per launch: same greedy tokens as the one-kernel-per-product path."""
+    cfg = dict(vocab=1000, dim=128, layers=3, heads=2, ffn=352, max_seq=64)
+    w = bf16_round(params_for(cfg, seed=2, std=0.05))
+    prompts = synth.zipf_ids(3, nseq * 12, cfg["vocab"]).reshape(nseq, 12)
+    monkeypatch.setenv("LUATL_DECODE_CHAIN", "0")
+    a = make(cfg, 1, w, decode_batch=nseq, dtype="bf16")
+    ta = a.generate_batch(prompts, 30, zero_indexed=True)
+    a.free()
+    monkeypatch.setenv("LUATL_DECODE_CHAIN", "1")
+    b = make(cfg, 1, w, decode_batch=nseq, dtype="bf16")
+    tb = b.generate_batch(prompts, 30, zero_indexed=True)
+    launches = b.last_timing()["launches"]
+    b.free()
+    # the two paths round at the same places but sum in different orders (split-K slices vs one pass): a rare near-tie may flip
+    differ = int((ta != tb).any(axis=1).sum())
+    assert differ <= max(1, nseq // 20), differ
+    o = oracle_for(cfg)
+    assert_tokens_consistent(o, w, prompts[:4], tb[:4], 5e-3)
+    assert launches < 29 * (2 + 3 * cfg["layers"]) + 40            # 2 + 2 L (+ split-KV combines) launches per step, not 2 + 7 L
