@@ -292,6 +292,11 @@ int luaTL_sgd(float* w, const float* g, uint64_t n, float lr, float wd, const fl
  * The reference has no tensor-core path for bf16 (its only one is fp16 wmma, cuda/luaTL_core.cu:1296). */
 int luaTL_gemm_bf16_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
                        int c_dtype, int tile_n);
+/* New: the same product on fp32 operands read by the tensor cores as TF32: C[M,N] = A[M,K] B[N,K]^T + R (accumulate = 0;
+ * R optional) or C += A B^T (accumulate = 1; ksplit slices of K added with atomics, 0 = choose).  K a multiple of 4,
+ * operands 16-byte aligned.  Replaces the CUDA-core kernels behind luaTL_gemm_ex (cuda/luaTL_train.cu:127,242) where a
+ * 2e-3 tolerance is accepted. */
+int luaTL_gemm_tf32_tc(const float* A, const float* B, float* C, const float* R, int M, int N, int K, int accumulate, int ksplit);
 /* New: fused causal attention over a packed qkv [B*T, 3*H*head_dim] (q | k | v in every row): out [B*T, H*head_dim],
  * lse [B*H*T] (natural log of the softmax denominator, may be NULL).  The reference composes attention from
  * batched score GEMMs, a [B*H*T, T] softmax and a second GEMM (ai/gpu/gpu_transformer.lua:333-352); it has no fused
@@ -435,6 +440,11 @@ int luaTL_lm_train_step_dev(luaTL_lm_t* m, const int32_t* d_ids, const int32_t* 
  * luaTL_lm_graph_ready: 1 while a captured step exists. */
 int luaTL_lm_set_graph(luaTL_lm_t* m, int on);
 int luaTL_lm_graph_ready(const luaTL_lm_t* m);
+/* fp32 models: on = 1 runs every weight product of the forward, the backward and the decode step on the tensor cores
+ * (tcgen05 kind::tf32: fp32 operands read with a 10-bit mantissa, fp32 accumulation), results within 2e-3 of the exact
+ * path; on = 0 (the default) keeps the exact CUDA-core products (1e-4).  The reference's dominant kernel for these
+ * products is its register-tiled CUDA-core GEMM (cuda/luaTL_train.cu:242, chosen at :425). */
+int luaTL_lm_set_tf32(luaTL_lm_t* m, int on);
 /* Forward only: loss / accuracy, optionally the logits [rows_out, vocab] to the host
  * (last_only = 1: only row n_tokens - 1 of sequence 0, what generate reads). */
 int luaTL_lm_eval_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* targets, luaTL_lm_result_t* out);

@@ -211,6 +211,7 @@ SIGNATURES = {
     "luaTL_lm_params_device": (_vp, [_vp]), "luaTL_lm_grads_device": (_vp, [_vp]),
     "luaTL_lm_train_step": (_i, [_vp, _vp, _vp, C.POINTER(LmTrainArgs), C.POINTER(LmResult)]),
     "luaTL_lm_train_step_dev": (_i, [_vp, _vp, _vp, C.POINTER(LmTrainArgs), C.POINTER(LmResult)]),
+    "luaTL_lm_set_tf32": (_i, [_vp, _i]), "luaTL_gemm_tf32_tc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i]),
     "luaTL_lm_set_graph": (_i, [_vp, _i]), "luaTL_lm_graph_ready": (_i, [_vp]),
     "luaTL_lm_eval_step": (_i, [_vp, _vp, _vp, C.POINTER(LmResult)]),
     "luaTL_lm_forward": (_i, [_vp, _vp, _i, _i, _vp, _i]),

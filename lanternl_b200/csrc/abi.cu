@@ -791,6 +791,13 @@ int luaTL_attention_bwd(const void* qkv, const void* out, const void* dout, cons
     LTL_TRY(rc);
     return tc ? ltl_gemm_tc_check(g_stream) : LTL_OK;
 }
+int luaTL_gemm_tf32_tc(const float* A, const float* B, float* C, const float* R, int M, int N, int K, int accumulate, int ksplit)
+{
+    LTL_TRY(ltl_require_init("gemm_tf32_tc"));
+    LTL_TRY(ltl_gemm_tf32(A, B, C, R, M, N, K, accumulate, ksplit, g_stream));
+    LTL_TRY(sync_stream("gemm_tf32_tc"));
+    return g_deferred ? LTL_OK : ltl_gemm_tc_check(g_stream);
+}
 int luaTL_sgd(float* w, const float* g, uint64_t n, float lr, float wd, const float* nsq, float max_norm)
 {
     ONE_SHOT("sgd", ltl_sgd(w, g, nullptr, n, lr, wd, nsq, max_norm, g_stream));

@@ -28,7 +28,8 @@ __device__ __forceinline__ float act_apply(int op, float v)
     }
 }
 
-template <typename TI, typename TC>
+// PRE: the instantiation that carries the prologue on A; the plain one has none of its code (the tile loader is the hot loop).
+template <typename TI, typename TC, bool PRE>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
                  const TI* __restrict__ bias, const TC* R, int M, int N, int K,
@@ -39,7 +40,7 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
 {
     __shared__ __align__(16) float As[BK][BM + PAD];
     __shared__ __align__(16) float Bs[BK][BN + PAD];
-    __shared__ float rowsc[BM];
+    __shared__ float rowsc[PRE ? BM : 1];
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     // ksplit > 1 (batch == 1 only): blockIdx.z selects a slice of K and the partial product is
@@ -56,7 +57,7 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
         if (R) R += (long long)blockIdx.z * c_bs;
     }
     const int tx = tid & 15, ty = tid >> 4;
-    if (pre_op == 1) {
+    if (PRE && pre_op == 1) {
         // RMSNorm prologue: the factor of each of the tile's 64 rows - taken from rowscale, or computed here over the
         // whole of K (four threads per row; every CTA of a row block repeats it, which keeps the op free of scratch).
         const int r = tid >> 2, q = tid & 3, gm = m0 + r;
@@ -88,10 +89,12 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
             else         { mm = tid & 63; kk = (tid >> 6) + 4 * p; }
             const int gm = m0 + mm, gk = k0 + kk;
             float av = (gm < M && gk < k_end) ? Cvt<TI>::ld(A, (size_t)(gm * a_rs + gk * a_cs)) : 0.0f;
-            if (pre_op == 1) av = av * rowsc[mm] * ((gamma && gk < k_end) ? Cvt<TI>::ld(gamma, gk) : 1.0f);
-            else if (pre_op == 2) av = act_apply(2, av);
-            else if (pre_op == 3) av = act_apply(3, av);
-            else if (pre_op == 4) av = fmaxf(av, 0.0f);
+            if (PRE) {
+                if (pre_op == 1) av = av * rowsc[mm] * ((gamma && gk < k_end) ? Cvt<TI>::ld(gamma, gk) : 1.0f);
+                else if (pre_op == 2) av = act_apply(2, av);
+                else if (pre_op == 3) av = act_apply(3, av);
+                else if (pre_op == 4) av = fmaxf(av, 0.0f);
+            }
             As[kk][mm] = av;
             int nn, kb;
             if (b_nfast) { nn = tid & 63; kb = (tid >> 6) + 4 * p; }
@@ -150,10 +153,16 @@ int launch(const GemmDesc& g, cudaStream_t s)
         if (ksplit < 1) ksplit = 1;
     }
     dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM, ksplit > 1 ? ksplit : g.batch);
-    gemm_simt_kernel<TI, TC><<<grid, 256, 0, s>>>(
-        (const TI*)g.A, (const TI*)g.B, (TC*)g.C, (const TI*)g.bias, (const TC*)g.R, g.M, g.N, g.K,
-        g.a_rs, g.a_cs, g.b_rs, g.b_cs, g.c_rs, g.c_cs, g.a_bs, g.b_bs, g.c_bs, g.alpha, g.beta,
-        g.post_op, ksplit, g.pre_op, (const TI*)g.gamma, g.rowscale, g.eps);
+    if (g.pre_op)
+        gemm_simt_kernel<TI, TC, true><<<grid, 256, 0, s>>>(
+            (const TI*)g.A, (const TI*)g.B, (TC*)g.C, (const TI*)g.bias, (const TC*)g.R, g.M, g.N, g.K,
+            g.a_rs, g.a_cs, g.b_rs, g.b_cs, g.c_rs, g.c_cs, g.a_bs, g.b_bs, g.c_bs, g.alpha, g.beta,
+            g.post_op, ksplit, g.pre_op, (const TI*)g.gamma, g.rowscale, g.eps);
+    else
+        gemm_simt_kernel<TI, TC, false><<<grid, 256, 0, s>>>(
+            (const TI*)g.A, (const TI*)g.B, (TC*)g.C, (const TI*)g.bias, (const TC*)g.R, g.M, g.N, g.K,
+            g.a_rs, g.a_cs, g.b_rs, g.b_cs, g.c_rs, g.c_cs, g.a_bs, g.b_bs, g.c_bs, g.alpha, g.beta,
+            g.post_op, ksplit, 0, nullptr, nullptr, 0.0f);
     return ltl_check_launch("gemm");
 }
 

@@ -64,6 +64,12 @@ struct luaTL_lm_s {
     bf16* Wb = nullptr;          // bf16 mirror, matrices transposed to [out, in]
     bf16* Wm = nullptr;          // second bf16 mirror for the backward: the other orientation of every matrix
     int mirror_dirty = 1;
+    // fp32 model on the tensor cores (luaTL_lm_set_tf32): every matrix transposed to [out, in] in fp32 (the K-major B operand
+    // of the forward products), and scratch for the transposed activations of the weight-gradient products
+    int tf32 = 0;
+    float* Wt = nullptr;
+    float *tA = nullptr, *tB = nullptr;
+    size_t tA_floats = 0, tB_floats = 0;
     int train_tc = 0;            // bf16 model that has been asked to train: mixed-precision step
     // sampling of the generation loop (temperature <= 0: greedy); captured decode graphs are specific to these values
     struct Sampling { float temperature = 0.0f; int top_k = 0; float top_p = 0.0f; uint64_t seed = 0; int stop_id = -1; } samp;
@@ -222,6 +228,13 @@ bool use_attn_tc(const LM* m, int T)
 // GEMM wants for its B operand), tok_emb and gains cast in place.
 int sync_mirror(LM* m)
 {
+    if (m->adt == LTL_F32 && m->tf32 && m->mirror_dirty) {
+        if (!m->Wt) DALLOC(m->Wt, (size_t)m->np * 4, "transposed fp32 weights");
+        for (const TensorInfo& t : m->tens)
+            if (t.is_matrix) LTL_TRY(ltl_transpose(m->W + t.off, m->Wt + t.off, t.rows, t.cols, LTL_F32, m->s));
+        m->mirror_dirty = 0;
+        return LTL_OK;
+    }
     if (m->adt != LTL_BF16 || !m->mirror_dirty) return LTL_OK;
     for (const TensorInfo& t : m->tens) {
         if (t.is_matrix) {
@@ -253,6 +266,12 @@ int wgemm(LM* m, const void* A, int M, int K, int64_t w_off, int Nout, void* C, 
     g.alpha = 1.0f; g.beta = 0.0f; g.a_dtype = m->adt; g.b_dtype = m->adt; g.c_dtype = c_dt;
     m->launches++;
     if (m->adt == LTL_F32) {
+        if (m->tf32 && m->Wt && c_dt == LTL_F32 && !epi) {
+            // tensor cores: B = the weight as [Nout, K] (the transposed mirror, or tok_emb itself as the tied head)
+            const float* Bt = transposed_master ? m->W + w_off : m->Wt + w_off;
+            if (ltl_gemm_tf32_supported(A, Bt, C, M, Nout, K))
+                return ltl_gemm_tf32((const float*)A, Bt, (float*)C, (const float*)R, M, Nout, K, 0, 1, m->s);
+        }
         g.B = m->W + w_off;
         if (transposed_master) { g.b_rs = 1; g.b_cs = K; } else { g.b_rs = Nout; g.b_cs = 1; }
     } else {
@@ -266,16 +285,57 @@ int wgemm(LM* m, const void* A, int M, int K, int64_t w_off, int Nout, void* C, 
     return ltl_gemm_simt(g, m->s);
 }
 
+// Scratch of the transposed operands (grown outside of any capture: the first training step sizes it).
+int ensure_tscratch(LM* m, size_t a_floats, size_t b_floats)
+{
+    if (a_floats > m->tA_floats) {
+        LTL_CUDA("scratch sync", cudaStreamSynchronize(m->s));
+        cudaFree(m->tA); m->tA = nullptr; m->tA_floats = 0;
+        DALLOC(m->tA, a_floats * 4, "transposed A operand");
+        m->tA_floats = a_floats;
+    }
+    if (b_floats > m->tB_floats) {
+        LTL_CUDA("scratch sync", cudaStreamSynchronize(m->s));
+        cudaFree(m->tB); m->tB = nullptr; m->tB_floats = 0;
+        DALLOC(m->tB, b_floats * 4, "transposed B operand");
+        m->tB_floats = b_floats;
+    }
+    return LTL_OK;
+}
+
 // Generic fp32 strided GEMM used by the backward.
 int sgemm(LM* m, const float* A, long long a_rs, long long a_cs, const float* B, long long b_rs, long long b_cs,
           float* C, int M, int N, int K, float beta)
 {
+    m->launches++;
+    if (m->tf32 && (beta == 0.0f || beta == 1.0f)) {
+        // Tensor cores want both operands with the contraction index contiguous.  An operand given the other way round
+        // (dW = X^T dY reads token-major activations down their rows) is transposed into scratch first.
+        const bool a_k = a_cs == 1 && a_rs == K, a_mn = a_rs == 1 && a_cs == M;
+        const bool b_k = b_rs == 1 && b_cs == K, b_mn = b_cs == 1 && b_rs == N;
+        if ((a_k || a_mn) && (b_k || b_mn) && K % 4 == 0 && M % 4 == 0 && N % 4 == 0) {
+            const float *Ak = A, *Bk = B;
+            if (a_mn) {
+                LTL_TRY(ensure_tscratch(m, (size_t)M * K, 0));
+                LTL_TRY(ltl_transpose(A, m->tA, K, M, LTL_F32, m->s));       // stored [K, M] -> [M, K]
+                Ak = m->tA;
+                m->launches++;
+            }
+            if (b_mn) {
+                LTL_TRY(ensure_tscratch(m, 0, (size_t)N * K));
+                LTL_TRY(ltl_transpose(B, m->tB, K, N, LTL_F32, m->s));       // stored [K, N] -> [N, K]
+                Bk = m->tB;
+                m->launches++;
+            }
+            if (ltl_gemm_tf32_supported(Ak, Bk, C, M, N, K))
+                return ltl_gemm_tf32(Ak, Bk, C, nullptr, M, N, K, beta == 1.0f ? 1 : 0, 0, m->s);
+        }
+    }
     GemmDesc g;
     memset(&g, 0, sizeof(g));
     g.A = A; g.B = B; g.C = C; g.M = M; g.N = N; g.K = K; g.batch = 1;
     g.a_rs = a_rs; g.a_cs = a_cs; g.b_rs = b_rs; g.b_cs = b_cs; g.c_rs = N; g.c_cs = 1;
     g.alpha = 1.0f; g.beta = beta;
-    m->launches++;
     return ltl_gemm_simt(g, m->s);
 }
 
@@ -1241,7 +1301,7 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
     void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
                      m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
                      m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part,
-                     m->Wm, m->d_done, m->d_nodecay, m->chain_bar, m->ssq[0], m->ssq[1], m->tile_tickets, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
+                     m->Wm, m->d_done, m->d_nodecay, m->chain_bar, m->Wt, m->tA, m->tB, m->ssq[0], m->ssq[1], m->tile_tickets, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
     for (void* p : ptrs) if (p) cudaFree(p);
     for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);
     if (m->ev_grad) cudaEventDestroy(m->ev_grad);
@@ -1487,6 +1547,18 @@ int luaTL_lm_set_graph(luaTL_lm_t* m, int on)
     return LTL_OK;
 }
 int luaTL_lm_graph_ready(const luaTL_lm_t* m) { return m && m->step_graph.ge ? 1 : 0; }
+
+int luaTL_lm_set_tf32(luaTL_lm_t* m, int on)
+{
+    if (!m) return ltl_fail(LTL_ERR_NULL, "lm_set_tf32: null model");
+    if (m->adt != LTL_F32) return ltl_fail(LTL_ERR_UNSUPPORTED, "lm_set_tf32: only fp32 models have an exact and a TF32 path (bf16 models always use the tensor cores)");
+    if ((on != 0) == (m->tf32 != 0)) return LTL_OK;
+    LTL_CUDA("sync", cudaStreamSynchronize(m->s));
+    drop_graphs(m);                                       // captured steps hold the other path's kernels
+    m->tf32 = on ? 1 : 0;
+    m->mirror_dirty = 1;
+    return LTL_OK;
+}
 
 int luaTL_lm_time_decode_attn(luaTL_lm_t* m, int nseq, int cache_len, int iters, float* ms_per_launch)
 {

@@ -200,6 +200,11 @@ struct LtlChainDesc {
 bool ltl_decode_chain_supported(int D, int F, int V);
 int ltl_decode_chain(const LtlChainDesc& d, cudaStream_t s);
 
+// ---- tcgen05 / TMA GEMM on fp32 operands read as TF32 (gemm_tf32.cu): C[M,N] (+)= A[M,K] B[N,K]^T (+ R) ----
+bool ltl_gemm_tf32_supported(const void* A, const void* B, const void* C, int M, int N, int K);
+int ltl_gemm_tf32(const float* A, const float* B, float* C, const float* R, int M, int N, int K, int accumulate, int ksplit,
+                  cudaStream_t s);
+
 // CUtensorMap (128 bytes, written to out_map) of a bf16 matrix [rows, cols] with rows `pitch` elements apart:
 // boxes of box_rows x 64 columns, 128-byte swizzle.  Cached per (base, shape).
 int ltl_tensor_map_bf16(const void* base, int rows, int cols, long long pitch, int box_rows, void* out_map);

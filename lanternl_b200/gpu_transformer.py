@@ -116,6 +116,9 @@ class Model:
             _lib.call("luaTL_lm_tensor_info", self._h, i, name, C.byref(r), C.byref(cc), C.byref(off), C.byref(dec))
             self.params.append(dict(name=name.value.decode(), rows=r.value, cols=cc.value, nelem=r.value * cc.value,
                                     offset=off.value, decay=bool(dec.value)))
+        self.tf32 = bool(cfg.get("tf32", False))
+        if self.tf32:                       # fp32 model on the tensor cores (2e-3 instead of 1e-4)
+            _lib.call("luaTL_lm_set_tf32", self._h, 1)
         if cfg.get("init", True):           # init = False: weights stay zero until load_flat / write_param
             self._init_weights(cfg.get("seed"))
         self._slots_used = 0

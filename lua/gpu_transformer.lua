@@ -130,6 +130,8 @@ function GT.new(cfg)
     self._row   = ffi.new("float[?]", self.vocab)
     self._last_ms = -1
 
+    -- fp32 model on the tensor cores (TF32 products, 2e-3 instead of 1e-4)
+    if cfg.tf32 then lm.check(C.luaTL_lm_set_tf32(self.h, 1), "lm.set_tf32") end
     if cfg.init ~= false then self:_init_weights(cfg.seed) end
     return self
 end

@@ -57,6 +57,7 @@ int luaTL_lm_train_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* target
                         const luaTL_lm_train_args_t* a, luaTL_lm_result_t* out);
 int luaTL_lm_train_step_dev(luaTL_lm_t* m, const int32_t* d_ids, const int32_t* d_targets,
                             const luaTL_lm_train_args_t* a, luaTL_lm_result_t* out);
+int luaTL_lm_set_tf32(luaTL_lm_t* m, int on);
 int luaTL_lm_set_graph(luaTL_lm_t* m, int on);
 int luaTL_lm_graph_ready(const luaTL_lm_t* m);
 int luaTL_lm_eval_step(luaTL_lm_t* m, const int32_t* ids, const int32_t* targets, luaTL_lm_result_t* out);
