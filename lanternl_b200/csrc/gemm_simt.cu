@@ -29,7 +29,7 @@ __device__ __forceinline__ float act_apply(int op, float v)
 }
 
 // PRE: the instantiation that carries the prologue on A; the plain one has none of its code (the tile loader is the hot loop).
-template <typename TI, typename TC, bool PRE, int GROUP>
+template <typename TI, typename TC, bool PRE>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
                  const TI* __restrict__ bias, const TC* R, int M, int N, int K,
@@ -81,63 +81,39 @@ gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C,
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
 
-    // GROUP k-tiles are fetched from global memory into registers at once (4 A and 4 B elements per thread and tile) and
-    // then passed through shared memory one by one, in k order: the sums are those of the one-tile-at-a-time loop, but a
-    // CTA pays one memory round trip per GROUP tiles.  Few-row products (a handful of CTAs, nothing else to hide the latency
-    // behind) take GROUP = 4; full grids keep GROUP = 1 and their registers.
-    for (int kg = k_begin; kg < k_end; kg += GROUP * BK) {
-        float ra[GROUP][4], rb[GROUP][4];
+    for (int k0 = k_begin; k0 < k_end; k0 += BK) {
 #pragma unroll
-        for (int u = 0; u < GROUP; ++u) {
-            const int k0 = kg + u * BK;
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                int mm, kk;
-                if (a_kfast) { kk = tid & 15; mm = (tid >> 4) + 16 * p; }
-                else         { mm = tid & 63; kk = (tid >> 6) + 4 * p; }
-                const int gm = m0 + mm, gk = k0 + kk;
-                float av = (gm < M && gk < k_end) ? Cvt<TI>::ld(A, (size_t)(gm * a_rs + gk * a_cs)) : 0.0f;
-                if (PRE) {
-                    if (pre_op == 1) av = av * rowsc[mm] * ((gamma && gk < k_end) ? Cvt<TI>::ld(gamma, gk) : 1.0f);
-                    else if (pre_op == 2) av = act_apply(2, av);
-                    else if (pre_op == 3) av = act_apply(3, av);
-                    else if (pre_op == 4) av = fmaxf(av, 0.0f);
-                }
-                ra[u][p] = av;
-                int nn, kb;
-                if (b_nfast) { nn = tid & 63; kb = (tid >> 6) + 4 * p; }
-                else         { kb = tid & 15; nn = (tid >> 4) + 16 * p; }
-                const int gn = n0 + nn, gkb = k0 + kb;
-                rb[u][p] = (gn < N && gkb < k_end) ? Cvt<TI>::ld(B, (size_t)(gkb * b_rs + gn * b_cs)) : 0.0f;
+        for (int p = 0; p < 4; ++p) {
+            int mm, kk;
+            if (a_kfast) { kk = tid & 15; mm = (tid >> 4) + 16 * p; }
+            else         { mm = tid & 63; kk = (tid >> 6) + 4 * p; }
+            const int gm = m0 + mm, gk = k0 + kk;
+            float av = (gm < M && gk < k_end) ? Cvt<TI>::ld(A, (size_t)(gm * a_rs + gk * a_cs)) : 0.0f;
+            if (PRE) {
+                if (pre_op == 1) av = av * rowsc[mm] * ((gamma && gk < k_end) ? Cvt<TI>::ld(gamma, gk) : 1.0f);
+                else if (pre_op == 2) av = act_apply(2, av);
+                else if (pre_op == 3) av = act_apply(3, av);
+                else if (pre_op == 4) av = fmaxf(av, 0.0f);
             }
+            As[kk][mm] = av;
+            int nn, kb;
+            if (b_nfast) { nn = tid & 63; kb = (tid >> 6) + 4 * p; }
+            else         { kb = tid & 15; nn = (tid >> 4) + 16 * p; }
+            const int gn = n0 + nn, gkb = k0 + kb;
+            Bs[kb][nn] = (gn < N && gkb < k_end) ? Cvt<TI>::ld(B, (size_t)(gkb * b_rs + gn * b_cs)) : 0.0f;
         }
+        __syncthreads();
 #pragma unroll
-        for (int u = 0; u < GROUP; ++u) {
-            if (kg + u * BK >= k_end) break;                  // uniform over the CTA
+        for (int kk = 0; kk < BK; ++kk) {
+            const float4 a = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+            const float4 b = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
+            const float av[4] = { a.x, a.y, a.z, a.w }, bv[4] = { b.x, b.y, b.z, b.w };
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                int mm, kk;
-                if (a_kfast) { kk = tid & 15; mm = (tid >> 4) + 16 * p; }
-                else         { mm = tid & 63; kk = (tid >> 6) + 4 * p; }
-                As[kk][mm] = ra[u][p];
-                int nn, kb;
-                if (b_nfast) { nn = tid & 63; kb = (tid >> 6) + 4 * p; }
-                else         { kb = tid & 15; nn = (tid >> 4) + 16 * p; }
-                Bs[kb][nn] = rb[u][p];
-            }
-            __syncthreads();
+            for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int kk = 0; kk < BK; ++kk) {
-                const float4 a = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
-                const float4 b = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
-                const float av[4] = { a.x, a.y, a.z, a.w }, bv[4] = { b.x, b.y, b.z, b.w };
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
-            }
-            __syncthreads();
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
         }
+        __syncthreads();
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -177,16 +153,16 @@ int launch(const GemmDesc& g, cudaStream_t s)
         if (ksplit < 1) ksplit = 1;
     }
     dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM, ksplit > 1 ? ksplit : g.batch);
-    // few CTAs in all (few rows, or a small output): nothing hides a tile's load latency, so fetch four tiles per round trip
-    const bool few = (long long)grid.x * grid.y * grid.z <= 2LL * ltl_sm_count() && g.K >= 4 * BK;
-#define SIMT_LAUNCH(PREV, GRP)                                                                                              \
-    gemm_simt_kernel<TI, TC, PREV, GRP><<<grid, 256, 0, s>>>(                                                               \
-        (const TI*)g.A, (const TI*)g.B, (TC*)g.C, (const TI*)g.bias, (const TC*)g.R, g.M, g.N, g.K,                         \
-        g.a_rs, g.a_cs, g.b_rs, g.b_cs, g.c_rs, g.c_cs, g.a_bs, g.b_bs, g.c_bs, g.alpha, g.beta,                            \
-        g.post_op, ksplit, g.pre_op, (const TI*)g.gamma, g.rowscale, g.eps)
-    if (g.pre_op) { if (few) SIMT_LAUNCH(true, 4); else SIMT_LAUNCH(true, 1); }
-    else { if (few) SIMT_LAUNCH(false, 4); else SIMT_LAUNCH(false, 1); }
-#undef SIMT_LAUNCH
+    if (g.pre_op)
+        gemm_simt_kernel<TI, TC, true><<<grid, 256, 0, s>>>(
+            (const TI*)g.A, (const TI*)g.B, (TC*)g.C, (const TI*)g.bias, (const TC*)g.R, g.M, g.N, g.K,
+            g.a_rs, g.a_cs, g.b_rs, g.b_cs, g.c_rs, g.c_cs, g.a_bs, g.b_bs, g.c_bs, g.alpha, g.beta,
+            g.post_op, ksplit, g.pre_op, (const TI*)g.gamma, g.rowscale, g.eps);
+    else
+        gemm_simt_kernel<TI, TC, false><<<grid, 256, 0, s>>>(
+            (const TI*)g.A, (const TI*)g.B, (TC*)g.C, (const TI*)g.bias, (const TC*)g.R, g.M, g.N, g.K,
+            g.a_rs, g.a_cs, g.b_rs, g.b_cs, g.c_rs, g.c_cs, g.a_bs, g.b_bs, g.c_bs, g.alpha, g.beta,
+            g.post_op, ksplit, 0, nullptr, nullptr, 0.0f);
     return ltl_check_launch("gemm");
 }
 
