@@ -578,6 +578,9 @@ int launch_persist(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const 
     return ltl_check_launch("gemm_tc_persist");
 }
 
+// Host-side switch for the launches that follow: shallow rings whose shared memory is allocated at its real size (see launch).
+bool g_lean = false;
+
 template <int BN, typename TC, int EPI>
 int launch(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int ksplit, cudaStream_t s,
            const LtlGemmFuse& fz = LtlGemmFuse{})
@@ -597,9 +600,14 @@ int launch(const void* A, const void* B, void* C, const void* R, int M, int N, i
     // the full ring whatever the depth used, which keeps one CTA per SM (each then has an SM's load path alone).
     const bool many = (long long)grid.x * grid.y * grid.z >= 2LL * ltl_sm_count();
     if (many) stages = BN == 256 ? 2 : (BN == 128 ? 3 : (BN == 64 ? 4 : 5));
+    if (g_lean) {
+        // a ring of at most ~80 KB, allocated as such: the CTA then fits beside the kernels of another stream
+        const int cap = BN == 32 ? 4 : (BN == 64 ? 3 : (BN == 128 ? 2 : 1));
+        if (stages > cap) stages = cap;
+    }
     if (stages > kb_per) stages = kb_per;
     if (stages < 1) stages = 1;
-    const size_t smem = smem_bytes<BN>(many ? stages : Ring<BN>::STAGES);
+    const size_t smem = smem_bytes<BN>((many || g_lean) ? stages : Ring<BN>::STAGES);
     static bool attr_set = false;
     if (!attr_set) {
         LTL_CUDA("gemm_tc attr", cudaFuncSetAttribute(gemm_tc_kernel<BN, TC, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -710,6 +718,8 @@ static int pick_bn(int M, int N)
     if (best_ctas < 0 && wide == 256 && N >= 256 && (long long)mt * ((N + 255) / 256) >= 4LL * sms) best = 256;
     return best;
 }
+
+void ltl_gemm_tc_set_lean(int on) { g_lean = on != 0; }
 
 // Split-K plan for a skinny GEMM: tile width and slice count that fill the SMs in one wave.
 void ltl_gemm_tc_plan_split(int M, int N, int K, int* bn, int* ksplit)

@@ -118,6 +118,17 @@ struct luaTL_lm_s {
                        const int32_t *ids = nullptr, *tgt = nullptr; int64_t launches = 0; } step_graph;
     int graph_steps = 0, warm_steps = 0;
     int use_tc = 1, fuse_swiglu = 0, use_pdl = 1, rows_gemm = 1, fuse_norm = 0;
+    // two-halves decode loop (see generate_halves): second stream, its activation set and split-K scratch, fork / join
+    // events, and the two captured steps (full: both halves; tail: the last step)
+    int halves = 0, halves_min = 128;
+    int pref_rows = -1;          // rows per (sequence, head) of the decode step's L2 prefetch rider; -1: by batch size
+    cudaStream_t s2 = nullptr;
+    Act dec2;
+    float* part2 = nullptr;
+    int half_cap = 0;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    GraphEntry hgraph[2];
+    int hgraph_nseq = 0;
 };
 
 namespace {
@@ -689,6 +700,12 @@ void drop_graphs(LM* m)
         if (kv.second.g) cudaGraphDestroy(kv.second.g);
     }
     m->graphs.clear();
+    for (GraphEntry& ge : m->hgraph) {
+        if (ge.ge) cudaGraphExecDestroy(ge.ge);
+        if (ge.g) cudaGraphDestroy(ge.g);
+        ge = GraphEntry();
+    }
+    m->hgraph_nseq = 0;
 }
 
 // A bf16 model asked to train: from now on the feed-forward keeps gate|up (the backward needs them), so the
@@ -907,12 +924,22 @@ int pick_next(LM* m, const float* logits, int nseq, int slot0, int32_t* d_out, i
 // fp32 partial sums are added to the residual stream, in a fixed order, by the RMSNorm kernel that
 // follows anyway (2 + 7 L launches per step; the default), or - fused form, LUATL_DECODE_FUSE_NORM=1 - by the
 // last-arriving CTA of the GEMM itself, with the normalisation factor applied by the next GEMM's epilogue (2 + 5 L).
+// cx (optional): the activation set, split-K scratch and stream of the step, and a window [op_lo, op_hi) of its launch
+// sequence (numbered 0 = embed, 1 + 7 l .. 7 + 7 l = the seven launches of layer l, then head and pick) - what the
+// two-halves generation loop uses to issue half a batch on its own stream and to cut a step after an attention kernel.
+struct DecCtx { Act* a; float* part; cudaStream_t s; int op_lo, op_hi; };
+
 int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t* d_out, int out_stride, int pick,
-                      int32_t* hist, int hist_stride, int hist_base)
+                      int32_t* hist, int hist_stride, int hist_base, const DecCtx* cx = nullptr)
 {
     const int D = m->D, F = m->F, V = m->V, L = m->L, H = m->H, hd = m->hd;
     const size_t e = 2;
-    Act& a = m->dec;
+    Act& a = cx ? *cx->a : m->dec;
+    float* const part = cx ? cx->part : m->part;
+    const cudaStream_t st = cx ? cx->s : m->s;
+    const int op_lo = cx ? cx->op_lo : 0, op_hi = cx ? cx->op_hi : 0x7FFFFFFF;
+    int opi = 0;
+    auto on = [&]() { const bool r = opi >= op_lo && opi < op_hi; ++opi; return r; };
     float* x = a.res;
     const int32_t* pos = m->d_pos + slot0;
     const size_t cl = (size_t)m->nseq_cap * H * m->T * hd * e;
@@ -923,6 +950,12 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
     // what does write them - the mirror kernels after an optimizer step or a parameter upload - is separated from this
     // chain by a fully ordered operation: the token upload of a single step, or the prefill of a generation).
     struct PdlScope { bool prev; PdlScope(bool on) : prev(ltl_pdl_enabled()) { ltl_pdl_set(on); } ~PdlScope() { ltl_pdl_set(prev); } } pdl(m->use_pdl);
+    // L2 prefetch rider on the second reduce of a layer: the first rows of every (sequence, head) slab of the next attention
+    // kernel's cache are asked into L2 while the products run, so that kernel's first tiles arrive without the HBM ramp.
+    // Measured per pass of 511 steps: 256 sequences 255.2 -> 246.3 ms with 38 rows (20 MB per layer), 251.1 with 76;
+    // 128 sequences 185.7 -> 182.4 with 38 rows, 185.1 with 76; no gain at 64 sequences and fewer, where the products
+    // slow down under the extra traffic by as much as the attention kernel gains.  LUATL_KV_PREFETCH_ROWS overrides.
+    const int pref_rows = m->pref_rows >= 0 ? m->pref_rows : (nseq * H >= 1024 ? 40 : 0);
     int bn_o, s_o, bn_d, s_d;
     ltl_gemm_tc_plan_split(nseq, D, D, &bn_o, &s_o);
     ltl_gemm_tc_plan_split(nseq, D, F, &bn_d, &s_d);
@@ -938,16 +971,18 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
     }
     auto gemm = [&](const void* A, const bf16* Wt, void* C, int N, int K, int c_dt, int bn, int epi, int ks,
                     const LtlGemmFuse* fz = nullptr) -> int {
-        if (rows) return ltl_gemm_rows(A, Wt, C, nseq, N, K, c_dt, epi, ks, m->s, fz);
-        return ltl_gemm_tc(A, Wt, C, nullptr, nseq, N, K, c_dt, bn, epi, ks, m->s, fz);
+        if (rows) return ltl_gemm_rows(A, Wt, C, nseq, N, K, c_dt, epi, ks, st, fz);
+        return ltl_gemm_tc(A, Wt, C, nullptr, nseq, N, K, c_dt, bn, epi, ks, st, fz);
     };
-    LTL_TRY(ltl_lm_embed_rmsnorm(d_tok, m->Wb + m->off_emb, LTL_BF16, x, m->W + m->lo[0].ln1, a.h1, LTL_BF16, nseq, D, V,
-                                 m->c.eps, m->s));
-    m->launches++;
+    if (on()) {
+        LTL_TRY(ltl_lm_embed_rmsnorm(d_tok, m->Wb + m->off_emb, LTL_BF16, x, m->W + m->lo[0].ln1, a.h1, LTL_BF16, nseq, D, V,
+                                     m->c.eps, st));
+        m->launches++;
+    }
     // Fused form: the split-K reduce, the residual add and the gain of the next RMSNorm ride in the residual GEMM
     // (its last-arriving CTA per tile), the normalisation factor of a row is applied by the epilogue of the GEMM that
     // consumes it (a per-row scale commutes with the product): 5 launches per layer instead of 7.  Optional, see create.
-    const bool fuse = m->fuse_norm && D % 32 == 0 && m->ssq[0] && m->tile_tickets;
+    const bool fuse = !cx && m->fuse_norm && D % 32 == 0 && m->ssq[0] && m->tile_tickets;
     const int tiles = D / 32;
     auto resid = [&](const float* gain, void* h, int which) {
         LtlGemmFuse f = {};
@@ -978,23 +1013,32 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
             m->launches += 5 + (m->splits > 1 ? 1 : 0);
             continue;
         }
-        LTL_TRY(gemm(a.h1, m->Wb + o.wqkv, a.qkv, 3 * D, D, LTL_BF16, 0, 0, 1));
-        LTL_TRY(ltl_decode_attn(a.qkv, kcl, vcl, a.attn, pos, nseq, H, hd, m->T, m->scale, LTL_BF16, m->splits, m->ws,
-                                m->rope_tab, m->c.rope_interleaved, m->c.use_rope, m->d_err, m->s));
-        LTL_TRY(gemm(a.attn, m->Wb + o.wo, m->part, D, D, LTL_F32, bn_o, 0, s_o));
-        LTL_TRY(ltl_lm_residual_rmsnorm(x, m->part, s_o, m->W + o.ln2, a.h2, LTL_BF16, nseq, D, m->c.eps, m->s));
-        LTL_TRY(gemm(a.h2, m->Wb + o.w13, a.hs, 2 * F, D, LTL_BF16, 0, 1, 1));
-        LTL_TRY(gemm(a.hs, m->Wb + o.w2, m->part, D, F, LTL_F32, bn_d, 0, s_d));
-        LTL_TRY(ltl_lm_residual_rmsnorm(x, m->part, s_d, next_gain, next_h, LTL_BF16, nseq, D, m->c.eps, m->s));
-        m->launches += 7 + (m->splits > 1 ? 1 : 0);
+        if (on()) { LTL_TRY(gemm(a.h1, m->Wb + o.wqkv, a.qkv, 3 * D, D, LTL_BF16, 0, 0, 1)); m->launches++; }
+        if (on()) {
+            LTL_TRY(ltl_decode_attn(a.qkv, kcl, vcl, a.attn, pos, nseq, H, hd, m->T, m->scale, LTL_BF16, m->splits, m->ws,
+                                    m->rope_tab, m->c.rope_interleaved, m->c.use_rope, m->d_err, st));
+            m->launches += 1 + (m->splits > 1 ? 1 : 0);
+        }
+        if (on()) { LTL_TRY(gemm(a.attn, m->Wb + o.wo, part, D, D, LTL_F32, bn_o, 0, s_o)); m->launches++; }
+        if (on()) { LTL_TRY(ltl_lm_residual_rmsnorm(x, part, s_o, m->W + o.ln2, a.h2, LTL_BF16, nseq, D, m->c.eps, st)); m->launches++; }
+        if (on()) { LTL_TRY(gemm(a.h2, m->Wb + o.w13, a.hs, 2 * F, D, LTL_BF16, 0, 1, 1)); m->launches++; }
+        if (on()) { LTL_TRY(gemm(a.hs, m->Wb + o.w2, part, D, F, LTL_F32, bn_d, 0, s_d)); m->launches++; }
+        if (on()) {
+            const int ln = last ? 0 : l + 1;          // after the last layer: layer 0 of the next step, one row longer
+            const LtlKvPrefetch pf = { (char*)m->kc + ln * cl + cslot, (char*)m->vc + ln * cl + cslot, pos, H, m->T, (int)(hd * e), nseq,
+                                       last ? 1 : 0, pref_rows };
+            LTL_TRY(ltl_lm_residual_rmsnorm(x, part, s_d, next_gain, next_h, LTL_BF16, nseq, D, m->c.eps, st,
+                                            pref_rows > 0 ? &pf : nullptr));
+            m->launches++;
+        }
     }
-    {
+    if (on()) {
         const LtlGemmFuse in1 = scale_by(1);
         LTL_TRY(gemm(a.hf, m->Wb + (m->c.tie ? m->off_emb : m->off_head), a.logits, V, D, LTL_F32, 0, 0, 1, fuse ? &in1 : nullptr));
+        m->launches++;
     }
-    m->launches++;
-    if (pick) {
-        LTL_TRY(pick_next(m, a.logits, nseq, slot0, d_out, out_stride, hist, hist_stride, hist_base, m->s));
+    if (pick && on()) {
+        LTL_TRY(pick_next(m, a.logits, nseq, slot0, d_out, out_stride, hist, hist_stride, hist_base, st));
         m->launches++;
     }
     return LTL_OK;
@@ -1127,6 +1171,127 @@ int prefill_and_pick(LM* m, int nseq, int len, int hist_stride, int hist_base, i
     return LTL_OK;
 }
 
+// The decode loop of a large batch as two halves, half a layer out of phase.
+//
+// A decode step is a chain of 2 + 7 L dependent launches: the attention kernels stream the KV cache (bound by HBM), the
+// launches between them are products over L2-resident weights, each a few microseconds of launch and memory latency that
+// leave HBM idle.  Here the batch is cut in two halves with their own activations; half A runs on the model's stream,
+// half B on a second one, and one captured graph per step holds both branches:
+//     branch A:  [Wo ... of layer 0, layers 1 .. L-1, head, pick] of step k, then [embed, QKV, attention of layer 0] of step k + 1
+//     branch B:  the whole of step k
+// so that when the graph starts A enters the products after an attention kernel while B is about to enter one, and the
+// two stay in antiphase for the L layers of the step: one half's cache streaming runs under the other's latency chain.
+// For the two to share an SM the attention kernel runs as a fixed number of CTAs per SM that walk the (sequence, head)
+// items, and the GEMM CTAs take a shallow ring (ltl_decode_attn_shape, ltl_gemm_tc_set_lean).  No kernel waits on
+// another: the only cross-branch edges are the fork and the join of the graph.
+struct HalvesShape {
+    HalvesShape(int ctas, int stages) { ltl_gemm_tc_set_lean(1); ltl_decode_attn_shape(ctas, stages); }
+    ~HalvesShape() { ltl_gemm_tc_set_lean(0); ltl_decode_attn_shape(0, 0); }
+};
+
+bool halves_eligible(LM* m, int nseq, int n_prompt, int n_new)
+{
+    return m->halves && nseq >= m->halves_min && (nseq % 2) == 0 && n_prompt + n_new <= m->T && m->splits == 1 &&
+           m->adt == LTL_BF16 && m->use_tc && m->fuse_swiglu && !m->use_chain && !m->fuse_norm && m->F % 8 == 0 && m->D % 8 == 0 &&
+           ltl_gemm_tc_supported(m->dec.h1, m->Wb, nseq / 2, m->D, m->D) && n_new >= 4;
+}
+
+int ensure_halves(LM* m, int nh)
+{
+    if (!m->s2) LTL_CUDA("second stream", cudaStreamCreateWithFlags(&m->s2, cudaStreamNonBlocking));
+    if (!m->ev_fork) LTL_CUDA("fork event", cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming));
+    if (!m->ev_join) LTL_CUDA("join event", cudaEventCreateWithFlags(&m->ev_join, cudaEventDisableTiming));
+    if (m->half_cap < nh) {
+        LTL_CUDA("sync", cudaStreamSynchronize(m->s));
+        LTL_CUDA("sync", cudaStreamSynchronize(m->s2));
+        drop_graphs(m);
+        free_act(m->dec2);
+        if (m->part2) { cudaFree(m->part2); m->part2 = nullptr; }
+        m->half_cap = 0;
+        LTL_TRY(alloc_act(m, m->dec2, nh, 0, nh));
+        DALLOC(m->part2, (size_t)8 * nh * m->D * 4, "split-K partial sums of the second half");
+        m->half_cap = nh;
+    }
+    return LTL_OK;
+}
+
+// Decode steps 1 .. n_new - 1 after the prefill (which picked token 0).  Leaves everything ordered on m->s.
+int generate_halves(LM* m, int nseq, int n_prompt, int n_new, int32_t* d_out, int hs)
+{
+    const int nh = nseq / 2, L = m->L;
+    LTL_TRY(ensure_halves(m, nh));
+    static const int attn_ctas = [] { const char* e = getenv("LUATL_HALVES_ATTN_CTAS"); return e && atoi(e) > 0 ? atoi(e) : 4; }();
+    static const int attn_stages = [] { const char* e = getenv("LUATL_HALVES_ATTN_STAGES"); return e && atoi(e) > 0 ? atoi(e) : 2; }();
+    HalvesShape shape(attn_ctas, attn_stages);
+    static const int cut = [] { const char* e = getenv("LUATL_HALVES_CUT"); return e ? atoi(e) : 3; }();   // 3: embed, QKV and attention of layer 0 (0: halves in phase, A/B aid)
+    const int all = 0x7FFFFFFF;
+    auto piece = [&](int h, cudaStream_t st, int lo, int hi) -> int {
+        DecCtx cx = { h ? &m->dec2 : &m->dec, h ? m->part2 : m->part, st, lo, hi };
+        return decode_step_split(m, nh, h * nh, m->d_next + h * nh, d_out + (size_t)h * nh * n_new, n_new, 1,
+                                 m->d_hist + (size_t)h * nh * hs, hs, n_prompt, &cx);
+    };
+    int steps = n_new - 1;
+    GraphEntry& full = m->hgraph[0];
+    GraphEntry& tail = m->hgraph[1];
+    if (full.ge && (m->hgraph_nseq != nseq || full.out != d_out || full.out_stride != n_new || full.hist != m->d_hist ||
+                    full.hist_stride != hs || full.hist_base != n_prompt)) {
+        for (GraphEntry& ge : m->hgraph) {
+            if (ge.ge) cudaGraphExecDestroy(ge.ge);
+            if (ge.g) cudaGraphDestroy(ge.g);
+            ge = GraphEntry();
+        }
+    }
+    if (!full.ge) {
+        // First use: one step eagerly, both halves in turn on the model's stream (a real step), then the two captures.
+        const int64_t before = m->launches;
+        LTL_TRY(piece(0, m->s, 0, all));
+        LTL_TRY(piece(1, m->s, 0, all));
+        const int64_t per_step = m->launches - before;
+        --steps;
+        LTL_CUDA("pre-capture sync", cudaStreamSynchronize(m->s));
+        LTL_CUDA("pre-capture sync", cudaStreamSynchronize(m->s2));
+        for (int which = 0; which < 2; ++which) {
+            const int64_t b0 = m->launches;
+            LTL_CUDA("begin capture", cudaStreamBeginCapture(m->s, cudaStreamCaptureModeThreadLocal));
+            int rc = LTL_OK;
+            cudaError_t ce = cudaEventRecord(m->ev_fork, m->s);
+            if (ce == cudaSuccess) ce = cudaStreamWaitEvent(m->s2, m->ev_fork, 0);
+            if (ce == cudaSuccess) {
+                rc = piece(0, m->s, cut, all);
+                if (rc == LTL_OK && which == 0) rc = piece(0, m->s, 0, cut);
+                if (rc == LTL_OK) rc = piece(1, m->s2, 0, all);
+                ce = cudaEventRecord(m->ev_join, m->s2);
+                if (ce == cudaSuccess) ce = cudaStreamWaitEvent(m->s, m->ev_join, 0);
+            }
+            cudaGraph_t g = nullptr;
+            const cudaError_t ee = cudaStreamEndCapture(m->s, &g);
+            const int64_t captured = m->launches - b0;
+            m->launches = b0;                     // the captured copy did not execute
+            if (rc != LTL_OK) { if (g) cudaGraphDestroy(g); cudaGetLastError(); return rc; }
+            if (ce != cudaSuccess) { if (g) cudaGraphDestroy(g); return ltl_cuda_fail("capture of the two-halves step", ce); }
+            if (ee != cudaSuccess) return ltl_cuda_fail("end capture", ee);
+            cudaGraphExec_t gx = nullptr;
+            const cudaError_t ie = cudaGraphInstantiate(&gx, g, 0);
+            if (ie != cudaSuccess) { cudaGraphDestroy(g); return ltl_cuda_fail("graph instantiate", ie); }
+            GraphEntry& ge = m->hgraph[which];
+            ge.g = g; ge.ge = gx; ge.launches = captured; ge.out = d_out; ge.out_stride = n_new;
+            ge.hist = m->d_hist; ge.hist_stride = hs; ge.hist_base = n_prompt;
+        }
+        (void)per_step;
+        m->hgraph_nseq = nseq;
+    }
+    if (steps <= 0) return LTL_OK;
+    // Half A's head start, then steps - 1 full graphs and the tail.
+    LTL_TRY(piece(0, m->s, 0, cut));
+    for (int k = 0; k + 1 < steps; ++k) {
+        LTL_CUDA("graph launch", cudaGraphLaunch(full.ge, m->s));
+        m->launches += full.launches;
+    }
+    LTL_CUDA("graph launch", cudaGraphLaunch(tail.ge, m->s));
+    m->launches += tail.launches;
+    return LTL_OK;
+}
+
 int generate_dev(LM* m, const int32_t* d_prompts, int nseq, int n_prompt, int n_new, int32_t* d_out,
                  luaTL_lm_result_t* timing)
 {
@@ -1145,7 +1310,9 @@ int generate_dev(LM* m, const int32_t* d_prompts, int nseq, int n_prompt, int n_
     LTL_CUDA("event", cudaEventRecord(m->ev[1], m->s));
     int len = n_prompt;                     // tokens in the history before the one just picked
     int cached = n_prompt < m->T ? n_prompt : m->T;   // tokens in the cache
-    for (int step = 1; step < n_new; ++step) {
+    const bool halves = halves_eligible(m, nseq, n_prompt, n_new);
+    if (halves) LTL_TRY(generate_halves(m, nseq, n_prompt, n_new, d_out, hs));
+    for (int step = 1; step < n_new && !halves; ++step) {
         ++len;                                // the pick that produced d_next also appended it to the history
         if (cached >= m->T) {
             // cache full: rebuild it from the last max_seq tokens (ai/optim/lmtrain.lua:1511-1515)
@@ -1261,6 +1428,14 @@ luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
         m->use_chain = ch && ch[0] == '1';
         const char* cp = getenv("LUATL_CHAIN_PDL");
         m->chain_pdl = !(cp && cp[0] == '0');
+        // LUATL_DECODE_HALVES=1: batches of at least LUATL_DECODE_HALVES_MIN (128) sequences are generated as two halves on
+        // two streams, half a layer out of phase (generate_halves).
+        const char* hv = getenv("LUATL_DECODE_HALVES");
+        m->halves = hv && hv[0] == '1';
+        const char* hm = getenv("LUATL_DECODE_HALVES_MIN");
+        if (hm && atoi(hm) >= 2) m->halves_min = atoi(hm);
+        const char* pm = getenv("LUATL_KV_PREFETCH_ROWS");
+        m->pref_rows = pm ? atoi(pm) : -1;
         const char* oc = getenv("LUATL_OVERLAP_COMM");
         m->overlap_comm = !(oc && oc[0] == '0');
     }
@@ -1297,7 +1472,11 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
     if (!m) return;
     cudaDeviceSynchronize();
     drop_graphs(m);
-    free_act(m->train); free_act(m->infer); free_act(m->dec);
+    free_act(m->train); free_act(m->infer); free_act(m->dec); free_act(m->dec2);
+    if (m->part2) cudaFree(m->part2);
+    if (m->ev_fork) cudaEventDestroy(m->ev_fork);
+    if (m->ev_join) cudaEventDestroy(m->ev_join);
+    if (m->s2) cudaStreamDestroy(m->s2);
     void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
                      m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
                      m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part,

@@ -131,10 +131,24 @@ lm_residual_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ part
 template <typename TO>
 __global__ void __launch_bounds__(1024)
 lm_residual_rmsnorm_row_kernel(float* __restrict__ x, const float* __restrict__ partial, int nparts,
-                               const float* __restrict__ gain, TO* __restrict__ out, int rows, int cols, float eps)
+                               const float* __restrict__ gain, TO* __restrict__ out, int rows, int cols, float eps,
+                               const LtlKvPrefetch pf)
 {
     __shared__ float red[32];
     pdl_trigger();
+    if (pf.k && (int)blockIdx.x < pf.nseq && (int)threadIdx.x < 2 * pf.heads) {
+        // L2 prefetch hint for the next attention kernel (ahead of the dependency wait: nothing in flight writes these rows;
+        // a stale position only changes how much is asked for, and the range is clamped to this sequence's slab)
+        const int h = threadIdx.x >> 1, isv = threadIdx.x & 1;
+        int n = pf.pos[blockIdx.x] + pf.pos_add;
+        n = min(min(n, pf.max_rows), pf.ctx);
+        if (n > 0) {
+            const char* base = reinterpret_cast<const char*>(isv ? pf.v : pf.k) +
+                               ((size_t)blockIdx.x * pf.heads + h) * pf.ctx * pf.row_bytes;
+            const uint32_t bytes = (uint32_t)n * (uint32_t)pf.row_bytes;
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base), "r"(bytes) : "memory");
+        }
+    }
     pdl_wait();
     const int row = blockIdx.x, c = threadIdx.x * 4;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
@@ -172,8 +186,12 @@ lm_residual_rmsnorm_row_kernel(float* __restrict__ x, const float* __restrict__ 
 }
 
 int ltl_lm_residual_rmsnorm(float* x, const float* partial, int nparts, const float* gain, void* out,
-                            int out_dtype, int rows, int cols, float eps, cudaStream_t s)
+                            int out_dtype, int rows, int cols, float eps, cudaStream_t s, const LtlKvPrefetch* pfp)
 {
+    LtlKvPrefetch pf = {};
+    if (pfp && pfp->k && pfp->v && pfp->pos && pfp->row_bytes % 16 == 0 && pfp->max_rows > 0 && 2 * pfp->heads <= 32 &&
+        aligned16(pfp->k) && aligned16(pfp->v))
+        pf = *pfp;
     if (!x || !partial || !gain || !out) return ltl_fail(LTL_ERR_NULL, "lm_residual_rmsnorm: null pointer");
     if (cols % 4 || !aligned16(x) || !aligned16(gain) || !aligned16(partial))
         return ltl_fail(LTL_ERR_SHAPE, "lm_residual_rmsnorm: width %d must be a multiple of 4 and 16-byte aligned", cols);
@@ -181,7 +199,7 @@ int ltl_lm_residual_rmsnorm(float* x, const float* partial, int nparts, const fl
     if (cols <= 4096 && out_dtype == LTL_BF16 && aligned16(out) && cols % 8 == 0) {
         const int threads = ((cols / 4) + 31) / 32 * 32;
         LTL_CUDA("lm_residual_rmsnorm launch", ltl_launch(lm_residual_rmsnorm_row_kernel<bf16>, dim3(rows), dim3(threads), 0, s,
-                                                          ltl_pdl_enabled(), x, partial, nparts, gain, (bf16*)out, rows, cols, eps));
+                                                          ltl_pdl_enabled(), x, partial, nparts, gain, (bf16*)out, rows, cols, eps, pf));
         return ltl_check_launch("lm_residual_rmsnorm");
     }
     const int grid = (rows + 3) / 4;
@@ -571,10 +589,13 @@ struct Smem {
 };
 }  // namespace bulk
 
-template <typename T, int HD, int STG>
-__global__ void __launch_bounds__(128)
+// MINB: resident CTAs per SM the register allocation is held to.  5: 96 registers, the kernel that runs alone, one item
+// per CTA (0.86 of HBM; with 80 registers it measures 0.83, with the 116 an unbounded allocation takes 0.78).
+// 6: 80 registers and the item walk - the form that leaves registers and shared memory for another stream's GEMM CTAs.
+template <typename T, int HD, int STG, int MINB>
+__global__ void __launch_bounds__(128, MINB)
 decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
-                        T* __restrict__ out, const int32_t* __restrict__ pos, int H, int ctx, float scale,
+                        T* __restrict__ out, const int32_t* __restrict__ pos, int B, int H, int ctx, float scale,
                         int splits, float* __restrict__ scratch, const float2* __restrict__ cs,
                         int interleaved, int use_rope, int* __restrict__ err)
 {
@@ -585,10 +606,28 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     constexpr int EPW = 4 / sizeof(T);       // elements per 4-byte word (dims per lane in P V)
     extern __shared__ uint8_t smem_raw[];
     Smem<STG>& sm = *reinterpret_cast<Smem<STG>*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
-    const int h = blockIdx.x, b = blockIdx.y, z = blockIdx.z;
     const int D = H * HD, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     pdl_trigger();
     pdl_wait();
+    const uint64_t pol = evict_first_policy();
+    if (tid == 0) {
+        for (int s = 0; s < STG; ++s)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&sm.full[s])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    // Work items are (head, sequence, cache slice) triples.  A grid that covers them all gives each CTA one; a smaller
+    // grid (a fixed number of CTAs per SM, which leaves room on every SM for the kernels of another stream) walks them
+    // with a stride.  The ring's stage index and barrier parity run on across items (tbase = tiles consumed so far).
+    // MINB == 5 is the one-item form (grid = H x B x splits), compiled without the loop.
+    constexpr bool WALK = MINB > 5;
+    const int nitems = H * B * splits;
+    uint32_t tbase = 0;
+    int item = WALK ? (int)blockIdx.x : 0;
+    do {
+    const int h = WALK ? item % H : (int)blockIdx.x;
+    const int b = WALK ? (item / H) % B : (int)blockIdx.y;
+    const int z = WALK ? item / (H * B) : (int)blockIdx.z;
     int ps = pos[b];
     const bool in_range = ps >= 0 && ps < ctx;
     if (!in_range) { if (err && tid == 0) *err = 1; ps = ps < 0 ? 0 : ctx; }
@@ -599,18 +638,13 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     const uint8_t* kg = reinterpret_cast<const uint8_t*>(kc + cbase);
     const uint8_t* vg = reinterpret_cast<const uint8_t*>(vc + cbase);
 
-    const uint64_t pol = evict_first_policy();
     if (tid == 0) {
-        for (int s = 0; s < STG; ++s)
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&sm.full[s])));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         for (int t = 0; t < ntiles && t < STG; ++t) {
-            const int k0 = kbeg + t * KT;
+            const int k0 = kbeg + t * KT, s = WALK ? (int)((tbase + t) % STG) : t;
             const uint32_t bytes = (uint32_t)min(KT, kend - k0) * ROWB;
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(&sm.full[t])), "r"(2 * bytes) : "memory");
-            copy(sm.k[t], kg + (size_t)k0 * ROWB, bytes, &sm.full[t], pol);
-            copy(sm.v[t], vg + (size_t)k0 * ROWB, bytes, &sm.full[t], pol);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(&sm.full[s])), "r"(2 * bytes) : "memory");
+            copy(sm.k[s], kg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
+            copy(sm.v[s], vg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
         }
     }
     // new token: the first GL lanes of warp 1 rotate q and k, append k / v, publish q, k, v as fp32
@@ -662,8 +696,8 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     load_q_chunks<N>(sm.q, j, half, qr);
     bool ok = true;
     for (int t = 0; t < ntiles; ++t) {
-        const int s = t % STG;
-        ok = wait(&sm.full[s], (t / STG) & 1) && ok;
+        const int s = WALK ? (int)((tbase + t) % STG) : t % STG;
+        ok = wait(&sm.full[s], (WALK ? (tbase + t) / STG : (uint32_t)(t / STG)) & 1) && ok;
         const int nk = min(KT, kend - (kbeg + t * KT));
         consume_tile<T, N, EPW>(sm.k[s], sm.v[s], nk, qr, j, half, warp, lane, m, lsum, acc);
         __syncthreads();                                      // everyone is done with stage s
@@ -675,6 +709,7 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
             copy(sm.v[s], vg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
         }
     }
+    if (WALK) tbase += (uint32_t)ntiles;
     if (!ok && err && tid == 0) *err = 2;
     float l = 0.5f * warp_sum(lsum);                             // every key sits in two lanes
     if (warp == 0 && z == 0) {     // the new token's own score, from the fp32 copies
@@ -714,6 +749,10 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
             if (d == 0) { sp[0] = M; sp[1] = L; }
         }
     }
+    if (!WALK) break;
+    __syncthreads();                                          // the next item rewrites q, kn, vn and the per-warp states
+    item += (int)gridDim.x;
+    } while (item < nitems);
 }
 
 template <typename T, int HD>
@@ -736,6 +775,12 @@ __global__ void decode_attn_combine_kernel(const float* __restrict__ scratch, T*
     Cvt<T>::st(out, (size_t)b * H * HD + (size_t)h * HD + d, L > 0.0f ? o / L : 0.0f);
 }
 
+// Launch shape of the bulk kernel for the calls that follow (host-side, like the programmatic-launch switch):
+// ctas_per_sm > 0 caps the grid at that many CTAs per SM, which then walk the (head, sequence) items - the form used when
+// a second stream runs beside this kernel and needs shared memory and registers on every SM; stages > 0 overrides the ring depth.
+static int g_attn_ctas_per_sm = 0, g_attn_stages = 0;
+void ltl_decode_attn_shape(int ctas_per_sm, int stages) { g_attn_ctas_per_sm = ctas_per_sm; g_attn_stages = stages; }
+
 size_t ltl_decode_attn_scratch_floats(int B, int H, int hd, int splits)
 {
     return splits > 1 ? (size_t)B * H * splits * (hd + 2) : 0;
@@ -749,25 +794,32 @@ static int launch_decode_attn(const void* qkv, void* kc, void* vc, void* out,
 {
     dim3 grid(H, B, splits);
     if constexpr (HD * sizeof(T) == 128 && HD <= 64) {
+        static const int env_ctas = [] { const char* e = getenv("LUATL_ATTN_CTAS"); return e ? atoi(e) : 0; }();   // A/B aid
+        const int per_sm = g_attn_ctas_per_sm > 0 ? g_attn_ctas_per_sm : env_ctas;
+        const int nitems = H * B * splits, cap = per_sm > 0 ? per_sm * ltl_sm_count() : nitems;
+        const dim3 bgrid(nitems < cap ? nitems : cap);
         // 128-byte rows: the bulk-copy staged kernel (LUATL_ATTN_REGS=1 selects the register kernel)
         static const bool use_regs = [] { const char* e = getenv("LUATL_ATTN_REGS"); return e && e[0] == '1'; }();
         static const int stages = [] { const char* e = getenv("LUATL_ATTN_STAGES"); return e ? atoi(e) : 2; }();
         if (!use_regs) {
-#define BULK_LAUNCH(STG)                                                                                           \
+#define BULK_LAUNCH_M(STG, MINB)                                                                                   \
             {                                                                                                      \
                 const size_t smem = sizeof(bulk::Smem<STG>) + 128;                                                 \
                 static bool attr = false;                                                                          \
                 if (!attr) {                                                                                       \
-                    LTL_CUDA("decode_attn attr", cudaFuncSetAttribute(decode_attn_bulk_kernel<T, HD, STG>,         \
+                    LTL_CUDA("decode_attn attr", cudaFuncSetAttribute(decode_attn_bulk_kernel<T, HD, STG, MINB>,   \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                             \
                     attr = true;                                                                                   \
                 }                                                                                                  \
-                LTL_CUDA("decode_attn launch", ltl_launch(decode_attn_bulk_kernel<T, HD, STG>, grid, dim3(128), smem, s,     \
-                    ltl_pdl_enabled() && splits == 1, (const T*)qkv, (T*)kc, (T*)vc, (T*)out, pos, H, ctx, scale,   \
+                LTL_CUDA("decode_attn launch", ltl_launch(decode_attn_bulk_kernel<T, HD, STG, MINB>, MINB > 5 ? bgrid : grid, dim3(128), smem, s, \
+                    ltl_pdl_enabled() && splits == 1, (const T*)qkv, (T*)kc, (T*)vc, (T*)out, pos, B, H, ctx, scale, \
                     splits, scratch, cs, interleaved, use_rope, err));                                             \
             }
-            if (stages <= 1) BULK_LAUNCH(1) else if (stages == 2) BULK_LAUNCH(2) else BULK_LAUNCH(4)
+#define BULK_LAUNCH(STG) { if (per_sm > 0) BULK_LAUNCH_M(STG, 6) else BULK_LAUNCH_M(STG, 5) }
+            const int stg = g_attn_stages > 0 ? g_attn_stages : stages;
+            if (stg <= 1) BULK_LAUNCH(1) else if (stg == 2) BULK_LAUNCH(2) else if (stg == 3) BULK_LAUNCH(3) else BULK_LAUNCH(4)
 #undef BULK_LAUNCH
+#undef BULK_LAUNCH_M
             if (splits > 1) {
                 dim3 g2(H, B);
                 decode_attn_combine_kernel<T, HD><<<g2, HD < 32 ? 32 : HD, 0, s>>>(scratch, (T*)out, H, splits);

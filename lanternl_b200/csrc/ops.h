@@ -115,8 +115,13 @@ int ltl_lm_rmsnorm(const float* x, const float* gain, void* out, int out_dtype, 
                    float eps, cudaStream_t s);
 // x[r, :] += sum_s partial[s][r, :] (s = 0 .. nparts-1 in order; slices rows*cols apart), then
 // out[r, :] = rmsnorm(x[r, :]) * gain.  The consumer side of the split-K GEMMs.
+// Optional rider of ltl_lm_residual_rmsnorm in the decode step: CTA b asks the memory system to bring the first rows of
+// sequence b's K and V cache of the NEXT attention kernel into L2 (cp.async.bulk.prefetch.L2, a hint: no data reaches
+// the SM), so that HBM works during the latency-bound products between two attention kernels.  k / v: that layer's
+// cache [nseq][heads][ctx][row_bytes]; the number of rows is min(pos[b] + pos_add, max_rows, ctx).
+struct LtlKvPrefetch { const void* k; const void* v; const int32_t* pos; int heads, ctx, row_bytes, nseq, pos_add, max_rows; };
 int ltl_lm_residual_rmsnorm(float* x, const float* partial, int nparts, const float* gain, void* out,
-                            int out_dtype, int rows, int cols, float eps, cudaStream_t s);
+                            int out_dtype, int rows, int cols, float eps, cudaStream_t s, const LtlKvPrefetch* pf = nullptr);
 // x[r, :] = table[ids[r], :] and out[r, :] = rmsnorm(x[r, :]) * gain in one launch.
 int ltl_lm_embed_rmsnorm(const int32_t* ids, const void* table, int table_dtype, float* x, const float* gain,
                          void* out, int out_dtype, int rows, int cols, int vocab, float eps, cudaStream_t s);
@@ -130,6 +135,7 @@ int ltl_kv_store(const void* qkv, void* kcache, void* vcache, int B, int T, int 
 // decode_attn_scratch_floats(B, H, hd, splits) floats.  err is set to 1 if a position is outside
 // [0, ctx).
 size_t ltl_decode_attn_scratch_floats(int B, int H, int hd, int splits);
+void ltl_decode_attn_shape(int ctas_per_sm, int stages);   // 0, 0 = one CTA per item, default ring depth
 int ltl_decode_attn(const void* qkv, void* kcache, void* vcache, void* out,
                     const int32_t* pos, int B, int H, int hd, int ctx, float scale, int dtype,
                     int splits, float* scratch, const float2* cs_table, int interleaved, int use_rope,
@@ -174,6 +180,7 @@ bool ltl_gemm_tc_supported(const void* A, const void* B, int M, int N, int K);
 // ksplit > 1: C receives ksplit fp32 partial matrices [ksplit][M][N] (no residual, no epilogue).
 int ltl_gemm_tc(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int c_dtype,
                 int bn, int epi, int ksplit, cudaStream_t s, const LtlGemmFuse* fuse = nullptr);
+void ltl_gemm_tc_set_lean(int on);   // shallow shared-memory rings (a CTA that shares its SM with another stream's kernels)
 void ltl_gemm_tc_plan_split(int M, int N, int K, int* bn, int* ksplit);
 int ltl_gemm_tc_check(cudaStream_t s);
 int ltl_gemm_tc_plan_accum(int M, int N, int K, int bn);

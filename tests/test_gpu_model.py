@@ -575,3 +575,42 @@ def test_decode_chain_kernel_gives_the_tokens_of_the_default_path(nseq, monkeypa
     o = oracle_for(cfg)
     assert_tokens_consistent(o, w, prompts[:4], tb[:4], 5e-3)
     assert launches < 29 * (2 + 3 * cfg["layers"]) + 40            # 2 + 2 L (+ split-KV combines) launches per step, not 2 + 7 L
+
+
+# ---- the two-halves generation loop and the L2 prefetch rider, kept as measured alternatives (both off by default) -----
+@pytest.mark.parametrize("nseq", [76, 96, 130])
+def test_two_halves_loop_gives_the_tokens_of_the_default_loop(nseq, monkeypatch):
+    """Two streams inside one captured step, half A a third of a layer ahead; the attention kernel in its item-walking
+    form (80 registers, a fixed number of CTAs per SM) and the GEMMs with shallow rings: same kernels per row, same
+    split-K plans (one row tile either way), so the greedy tokens are identical; the launch count doubles.  Batches of at
+    least 74 sequences: below that the attention kernel slices the cache and the loop keeps to one stream."""
+    cfg = dict(vocab=1000, dim=128, layers=3, heads=2, ffn=352, max_seq=64)
+    w = bf16_round(params_for(cfg, seed=4, std=0.05))
+    prompts = synth.zipf_ids(5, nseq * 12, cfg["vocab"]).reshape(nseq, 12)
+    monkeypatch.setenv("LUATL_DECODE_HALVES", "0")
+    a = make(cfg, 1, w, decode_batch=nseq, dtype="bf16")
+    ta = a.generate_batch(prompts, 30, zero_indexed=True)
+    la = a.last_timing()["launches"]
+    a.free()
+    monkeypatch.setenv("LUATL_DECODE_HALVES", "1")
+    monkeypatch.setenv("LUATL_DECODE_HALVES_MIN", "2")
+    b = make(cfg, 1, w, decode_batch=nseq, dtype="bf16")
+    tb = b.generate_batch(prompts, 30, zero_indexed=True)
+    tb2 = b.generate_batch(prompts, 30, zero_indexed=True)          # second call: captured steps only
+    lb = b.last_timing()["launches"]
+    b.free()
+    assert np.array_equal(ta, tb) and np.array_equal(tb, tb2)
+    assert lb > 1.8 * (la - 40)
+
+
+def test_kv_prefetch_rider_changes_no_token(monkeypatch):
+    cfg = dict(vocab=1000, dim=128, layers=3, heads=2, ffn=352, max_seq=64)
+    w = bf16_round(params_for(cfg, seed=4, std=0.05))
+    prompts = synth.zipf_ids(6, 40 * 12, cfg["vocab"]).reshape(40, 12)
+    out = []
+    for rows in ("0", "20"):
+        monkeypatch.setenv("LUATL_KV_PREFETCH_ROWS", rows)
+        m = make(cfg, 1, w, decode_batch=40, dtype="bf16")
+        out.append(m.generate_batch(prompts, 40, zero_indexed=True))
+        m.free()
+    assert np.array_equal(out[0], out[1])
