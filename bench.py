@@ -249,6 +249,8 @@ def run_decode(args, dist):
         _lib.call("luaTL_lm_time_decode_attn", m._h, nseq, n, 20, C.byref(ms))
         nbytes = nseq * cfg["heads"] * (cfg["dim"] // cfg["heads"]) * 2 * 2 * (n + 1)      # K and V rows, bf16
         attn[n] = dict(us=ms.value * 1e3, bytes=nbytes, gbs=nbytes / (ms.value * 1e-3) / 1e9)
+    # what each launch kind of the step costs inside a dependent chain (60 copies in a captured chain, 50 replays)
+    launch_us = m.time_decode_launches(nseq, (N_PROMPT + 1 + N_PROMPT + N_NEW - 1) // 2, 50)
     dev_ms, dec_ms, pre_ms, e2e_ms = dist.max(dev_ms), dist.max(dec_ms), dist.max(pre_ms), dist.max(e2e_ms)
     tokens = NSEQ_TOTAL * N_NEW * args.steps
     pk = peaks()
@@ -282,6 +284,9 @@ def run_decode(args, dist):
                                         frac=phase_gbs / pk["hbm_gbs"])),
         phases=dict(prefill_ms=pre_ms / args.steps, decode_ms=dec_ms / args.steps,
                     decode_only_tokens_per_s=NSEQ_TOTAL * (N_NEW - 1) * args.steps / (dec_ms * 1e-3)),
+        decode_launch_us=dict(note="microseconds per launch inside a captured dependent chain of 60 copies of that launch; a step is "
+                                   "embed + layers x (qkv, attention, wo, reduce, w13, w2, reduce) + lm_head + pick",
+                              **{k: round(v, 3) for k, v in launch_us.items()}),
         wall_ms_per_step=wall_ms / args.steps, clocks=clk)
     m.free()
     return line

@@ -468,6 +468,13 @@ int luaTL_lm_generate_dev(luaTL_lm_t* m, const int32_t* d_prompts, int nseq, int
  * launch per layer, each over its own layer of the cache (inputs larger than L2).  Leaves the
  * generation state reset. */
 int luaTL_lm_time_decode_attn(luaTL_lm_t* m, int nseq, int cache_len, int iters, float* ms_per_launch);
+/* Measurement aid: microseconds per launch of each kind of launch of the decode step (bf16 tensor-core path), measured
+ * as 60 copies back to back in a captured chain, `reps` replays after 3 warm-up replays, every sequence at `cache_len`:
+ *   us[0] embed + RMSNorm, [1] QKV, [2] Wo (split-K), [3] reduce + RMSNorm, [4] W13 + SwiGLU, [5] W2 (split-K),
+ *   [6] reduce + RMSNorm with the prefetch rider, [7] lm_head, [8] pick, [9] one layer's chain Wo .. next QKV (six
+ *   launches, total).  n >= 10.  Attention is timed by luaTL_lm_time_decode_attn.  Leaves the generation state reset.
+ * New entry point: no counterpart in the reference. */
+int luaTL_lm_time_decode_launches(luaTL_lm_t* m, int nseq, int cache_len, int reps, float* us, int n);
 /* Sampling rule of luaTL_lm_generate* (see luaTL_sample_rows); temperature <= 0 restores the greedy pick. */
 int luaTL_lm_set_sampling(luaTL_lm_t* m, float temperature, int top_k, float top_p, uint64_t seed, int stop_id);
 /* Device time (ms) and kernel launches of the last prefill and decode phases. */

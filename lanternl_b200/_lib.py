@@ -221,6 +221,7 @@ SIGNATURES = {
     "luaTL_lm_generate_dev": (_i, [_vp, _vp, _i, _i, _i, _vp, C.POINTER(LmResult)]),
     "luaTL_lm_time_decode_attn": (_i, [_vp, _i, _i, _i, C.POINTER(_f)]),
     "luaTL_lm_last_timing": (_i, [_vp, C.POINTER(_f), C.POINTER(_f), C.POINTER(_i64)]),
+    "luaTL_lm_time_decode_launches": (_i, [_vp, _i, _i, _i, C.POINTER(_f), _i]),
     "luaTL_comm_unique_id": (_i, [_cp]), "luaTL_comm_init": (_i, [_cp, _i, _i]),
     "luaTL_comm_world": (_i, []), "luaTL_comm_allreduce_f32": (_i, [_vp, _u64]),
     "luaTL_comm_destroy": (None, []), "luaTL_comm_set_timeout": (None, [_i]),

@@ -1769,6 +1769,64 @@ int luaTL_lm_time_decode_attn(luaTL_lm_t* m, int nseq, int cache_len, int iters,
     return LTL_OK;
 }
 
+// Measurement aid: what each launch of the decode step costs inside a dependent chain.  Every launch kind of the step
+// (the product path's own launch code, windowed) is captured 60 times back to back into a CUDA graph - programmatic
+// dependent launch as in the step - and replayed; us[i] = microseconds per launch:
+//   0 embed + RMSNorm   1 QKV   2 Wo (split-K)   3 reduce + RMSNorm   4 W13 + SwiGLU   5 W2 (split-K)
+//   6 reduce + RMSNorm (+ prefetch rider)   7 lm_head   8 pick   9 one layer's chain Wo .. next QKV (six launches, total)
+// Attention is left out (luaTL_lm_time_decode_attn times it over a cache larger than L2).
+int luaTL_lm_time_decode_launches(luaTL_lm_t* m, int nseq, int cache_len, int reps, float* us, int n)
+{
+    if (!m || !us) return ltl_fail(LTL_ERR_NULL, "lm_time_decode_launches: null pointer");
+    if (nseq < 1 || reps < 1 || n < 10 || cache_len < 0 || cache_len >= m->T)
+        return ltl_fail(LTL_ERR_ARG, "lm_time_decode_launches: need nseq >= 1, reps >= 1, 0 <= cache_len < max_seq and room for 10 values");
+    LTL_TRY(ensure_decode(m, nseq, 0, 0));
+    if (!(m->adt == LTL_BF16 && m->use_tc && m->fuse_swiglu && m->F % 8 == 0 && m->D % 8 == 0 &&
+          ltl_gemm_tc_supported(m->dec.h1, m->Wb, nseq, m->D, m->D)))
+        return ltl_fail(LTL_ERR_UNSUPPORTED, "lm_time_decode_launches: the model does not decode on the bf16 tensor-core path");
+    LTL_TRY(sync_mirror(m));
+    LTL_TRY(ltl_fill_i32(m->d_pos, nseq, cache_len, m->s));
+    const int L = m->L, CH = 60;
+    const int lo[10] = { 0, 1, 3, 4, 5, 6, 7, 1 + 7 * L, 2 + 7 * L, 3 };
+    const int hi[10] = { 1, 2, 4, 5, 6, 7, 8, 2 + 7 * L, 3 + 7 * L, L >= 2 ? 9 : 8 };
+    const int64_t keep = m->launches;
+    int rc = LTL_OK;
+    for (int i = 0; i < 10 && rc == LTL_OK; ++i) {
+        const DecCtx cx = { &m->dec, m->part, m->s, lo[i], hi[i] };
+        auto issue = [&]() { return decode_step_split(m, nseq, 0, m->d_next, nullptr, 0, 1, nullptr, 0, 0, &cx); };
+        const int per = i == 9 ? CH / 6 : CH;            // graph launches of (hi - lo) kernels each
+        if ((rc = issue()) != LTL_OK) break;             // first use of a shape sets kernel attributes: outside the capture
+        LTL_CUDA("pre-capture sync", cudaStreamSynchronize(m->s));
+        LTL_CUDA("begin capture", cudaStreamBeginCapture(m->s, cudaStreamCaptureModeThreadLocal));
+        for (int k = 0; k < per && rc == LTL_OK; ++k) rc = issue();
+        cudaGraph_t g = nullptr;
+        const cudaError_t ce = cudaStreamEndCapture(m->s, &g);
+        if (rc != LTL_OK) { if (g) cudaGraphDestroy(g); cudaGetLastError(); break; }
+        if (ce != cudaSuccess) { rc = ltl_cuda_fail("end capture", ce); break; }
+        cudaGraphExec_t gx = nullptr;
+        const cudaError_t ie = cudaGraphInstantiate(&gx, g, 0);
+        if (ie != cudaSuccess) { cudaGraphDestroy(g); rc = ltl_cuda_fail("graph instantiate", ie); break; }
+        cudaError_t e = cudaSuccess;
+        for (int w = 0; w < 3 && e == cudaSuccess; ++w) e = cudaGraphLaunch(gx, m->s);
+        if (e == cudaSuccess) e = cudaEventRecord(m->ev[0], m->s);
+        for (int r = 0; r < reps && e == cudaSuccess; ++r) e = cudaGraphLaunch(gx, m->s);
+        if (e == cudaSuccess) e = cudaEventRecord(m->ev[1], m->s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(m->s);
+        cudaGraphExecDestroy(gx); cudaGraphDestroy(g);
+        if (e != cudaSuccess) { rc = ltl_cuda_fail("lm_time_decode_launches", e); break; }
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, m->ev[0], m->ev[1]);
+        us[i] = ms * 1000.0f / (float)(reps * per);      // slot 9: per pass over the layer's chain
+    }
+    m->launches = keep;
+    cudaMemsetAsync(m->d_pos, 0, (size_t)m->nseq_cap * 4, m->s);
+    cudaMemsetAsync(m->d_count, 0, (size_t)m->nseq_cap * 4, m->s);
+    cudaMemsetAsync(m->d_err, 0, 4, m->s);
+    cudaStreamSynchronize(m->s);
+    if (rc == LTL_OK) rc = ltl_gemm_tc_check(m->s);
+    return rc;
+}
+
 int luaTL_lm_last_timing(luaTL_lm_t* m, float* prefill_ms, float* decode_ms, int64_t* launches)
 {
     if (!m) return ltl_fail(LTL_ERR_NULL, "lm_last_timing: null model");

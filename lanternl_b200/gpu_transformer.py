@@ -332,6 +332,16 @@ class Model:
         self._last_ms = res.step_ms
         return out if zero_indexed else out + 1
 
+    DECODE_LAUNCH_KINDS = ("embed_rmsnorm", "qkv", "wo_splitk", "reduce_rmsnorm", "w13_swiglu", "w2_splitk",
+                           "reduce_rmsnorm_prefetch", "lm_head", "pick", "layer_chain_6_launches")
+
+    def time_decode_launches(self, nseq, cache_len, reps=50):
+        """Microseconds per launch of every kind of launch of the decode step inside a captured chain (measurement aid)."""
+        self._alive("time_decode_launches")
+        us = (C.c_float * 10)()
+        _lib.call("luaTL_lm_time_decode_launches", self._h, nseq, cache_len, reps, us, 10)
+        return {k: float(us[i]) for i, k in enumerate(self.DECODE_LAUNCH_KINDS)}
+
     def last_timing(self):
         a, b, n = C.c_float(), C.c_float(), C.c_int64()
         _lib.call("luaTL_lm_last_timing", self._h, C.byref(a), C.byref(b), C.byref(n))

@@ -578,7 +578,7 @@ def test_decode_chain_kernel_gives_the_tokens_of_the_default_path(nseq, monkeypa
 
 
 # ---- the two-halves generation loop and the L2 prefetch rider, kept as measured alternatives (both off by default) -----
-@pytest.mark.parametrize("nseq", [76, 96, 130])
+@pytest.mark.parametrize("nseq", [76, 96, 128])
 def test_two_halves_loop_gives_the_tokens_of_the_default_loop(nseq, monkeypatch):
     """Two streams inside one captured step, half A a third of a layer ahead; the attention kernel in its item-walking
     form (80 registers, a fixed number of CTAs per SM) and the GEMMs with shallow rings: same kernels per row, same
@@ -614,3 +614,17 @@ def test_kv_prefetch_rider_changes_no_token(monkeypatch):
         out.append(m.generate_batch(prompts, 40, zero_indexed=True))
         m.free()
     assert np.array_equal(out[0], out[1])
+
+
+def test_decode_launch_timing_aid_reports_every_kind_and_resets_the_state():
+    cfg = dict(vocab=1000, dim=128, layers=3, heads=2, ffn=352, max_seq=64)
+    w = bf16_round(params_for(cfg, seed=4, std=0.05))
+    prompts = synth.zipf_ids(7, 80 * 12, cfg["vocab"]).reshape(80, 12)
+    m = make(cfg, 1, w, decode_batch=80, dtype="bf16")
+    before = m.generate_batch(prompts, 20, zero_indexed=True)
+    us = m.time_decode_launches(80, 30, reps=3)
+    assert set(us) == set(m.DECODE_LAUNCH_KINDS) and all(0.2 < v < 200.0 for v in us.values()), us
+    assert us["layer_chain_6_launches"] > 3 * min(us["wo_splitk"], us["reduce_rmsnorm"])
+    after = m.generate_batch(prompts, 20, zero_indexed=True)
+    assert np.array_equal(before, after)
+    m.free()
