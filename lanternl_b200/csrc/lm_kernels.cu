@@ -579,21 +579,24 @@ __device__ __forceinline__ void consume_tile(const uint8_t* ks, const uint8_t* v
 #pragma unroll
     for (int e = 0; e < EPW; ++e) acc[e] += odd[e];
 }
-template <int STG>
+template <int STG, int G>
 struct Smem {
-    alignas(128) uint8_t k[STG][KT * ROWB];
-    alignas(128) uint8_t v[STG][KT * ROWB];
+    alignas(128) uint8_t k[G * STG][KT * ROWB];
+    alignas(128) uint8_t v[G * STG][KT * ROWB];
     alignas(16) float q[64], kn[64], vn[64];
-    float wm[4], wl[4], wacc[4][64];
-    alignas(8) uint64_t full[STG];
+    float wm[4 * G], wl[4 * G], wacc[4 * G][64];
+    alignas(8) uint64_t full[G * STG];
 };
 }  // namespace bulk
 
 // MINB: resident CTAs per SM the register allocation is held to.  5: 96 registers, the kernel that runs alone, one item
 // per CTA (0.86 of HBM; with 80 registers it measures 0.83, with the 116 an unbounded allocation takes 0.78).
 // 6: 80 registers and the item walk - the form that leaves registers and shared memory for another stream's GEMM CTAs.
-template <typename T, int HD, int STG, int MINB>
-__global__ void __launch_bounds__(128, MINB)
+// G: groups of four warps per CTA.  G = 2 (small batches, where an SM holds one or two items and a CTA's chain of tiles is
+// what the launch waits for): the groups take alternate tiles of the item from rings of their own and meet in the final
+// combine, which halves that chain without a second launch.
+template <typename T, int HD, int STG, int MINB, int G>
+__global__ void __launch_bounds__(128 * G, G == 1 ? MINB : 2)
 decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
                         T* __restrict__ out, const int32_t* __restrict__ pos, int B, int H, int ctx, float scale,
                         int splits, float* __restrict__ scratch, const float2* __restrict__ cs,
@@ -605,13 +608,14 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     constexpr int GL = HD / N;               // 8 chunks per row
     constexpr int EPW = 4 / sizeof(T);       // elements per 4-byte word (dims per lane in P V)
     extern __shared__ uint8_t smem_raw[];
-    Smem<STG>& sm = *reinterpret_cast<Smem<STG>*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    Smem<STG, G>& sm = *reinterpret_cast<Smem<STG, G>*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     const int D = H * HD, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int grp = G > 1 ? warp >> 2 : 0, lw = warp & 3, ltid = tid & 127;     // group, warp and thread inside the group
     pdl_trigger();
     pdl_wait();
     const uint64_t pol = evict_first_policy();
     if (tid == 0) {
-        for (int s = 0; s < STG; ++s)
+        for (int s = 0; s < G * STG; ++s)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&sm.full[s])));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -621,6 +625,7 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     // with a stride.  The ring's stage index and barrier parity run on across items (tbase = tiles consumed so far).
     // MINB == 5 is the one-item form (grid = H x B x splits), compiled without the loop.
     constexpr bool WALK = MINB > 5;
+    static_assert(!(WALK && G > 1), "the item walk runs with one group");
     const int nitems = H * B * splits;
     uint32_t tbase = 0;
     int item = WALK ? (int)blockIdx.x : 0;
@@ -639,13 +644,15 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     const uint8_t* vg = reinterpret_cast<const uint8_t*>(vc + cbase);
 
     if (tid == 0) {
-        for (int t = 0; t < ntiles && t < STG; ++t) {
-            const int k0 = kbeg + t * KT, s = WALK ? (int)((tbase + t) % STG) : t;
-            const uint32_t bytes = (uint32_t)min(KT, kend - k0) * ROWB;
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(&sm.full[s])), "r"(2 * bytes) : "memory");
-            copy(sm.k[s], kg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
-            copy(sm.v[s], vg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
-        }
+        // first STG tiles of every group (this thread initialised the barriers; the groups' own producers take over below)
+        for (int g = 0; g < G; ++g)
+            for (int lt = 0; lt < STG && lt * G + g < ntiles; ++lt) {
+                const int k0 = kbeg + (lt * G + g) * KT, s = g * STG + (WALK ? (int)((tbase + lt) % STG) : lt);
+                const uint32_t bytes = (uint32_t)min(KT, kend - k0) * ROWB;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(&sm.full[s])), "r"(2 * bytes) : "memory");
+                copy(sm.k[s], kg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
+                copy(sm.v[s], vg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
+            }
     }
     // new token: the first GL lanes of warp 1 rotate q and k, append k / v, publish q, k, v as fp32
     if (warp == 1 && lane < GL) {
@@ -688,21 +695,24 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     }
     __syncthreads();
 
-    const int j = tid >> 1, half = tid & 1;          // two threads per key of the tile
+    const int j = ltid >> 1, half = ltid & 1;        // two threads per key of the tile
     float m = -INFINITY, lsum = 0.0f, acc[EPW];
 #pragma unroll
     for (int i = 0; i < EPW; ++i) acc[i] = 0.0f;
     float qr[4][N];
     load_q_chunks<N>(sm.q, j, half, qr);
     bool ok = true;
-    for (int t = 0; t < ntiles; ++t) {
-        const int s = WALK ? (int)((tbase + t) % STG) : t % STG;
-        ok = wait(&sm.full[s], (WALK ? (tbase + t) / STG : (uint32_t)(t / STG)) & 1) && ok;
-        const int nk = min(KT, kend - (kbeg + t * KT));
-        consume_tile<T, N, EPW>(sm.k[s], sm.v[s], nk, qr, j, half, warp, lane, m, lsum, acc);
-        __syncthreads();                                      // everyone is done with stage s
-        if (tid == 0 && t + STG < ntiles) {
-            const int k0 = kbeg + (t + STG) * KT;
+    const int mine = ntiles > grp ? (ntiles - grp + G - 1) / G : 0;      // tiles grp, grp + G, ... of the item
+    for (int lt = 0; lt < mine; ++lt) {
+        const int s = grp * STG + (WALK ? (int)((tbase + lt) % STG) : lt % STG);
+        ok = wait(&sm.full[s], (WALK ? (tbase + lt) / STG : (uint32_t)(lt / STG)) & 1) && ok;
+        const int nk = min(KT, kend - (kbeg + (lt * G + grp) * KT));
+        consume_tile<T, N, EPW>(sm.k[s], sm.v[s], nk, qr, j, half, lw, lane, m, lsum, acc);
+        if (G == 1) __syncthreads();                          // everyone is done with stage s
+        else if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");      // the group's own barrier (immediate ids: 3 in use)
+        else asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (ltid == 0 && lt + STG < mine) {
+            const int k0 = kbeg + ((lt + STG) * G + grp) * KT;
             const uint32_t bytes = (uint32_t)min(KT, kend - k0) * ROWB;
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(&sm.full[s])), "r"(2 * bytes) : "memory");
             copy(sm.k[s], kg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
@@ -732,10 +742,12 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     if (tid < HD) {
         const int d = tid;
         float M = fmaxf(fmaxf(sm.wm[0], sm.wm[1]), fmaxf(sm.wm[2], sm.wm[3]));
+#pragma unroll
+        for (int w = 4; w < 4 * G; ++w) M = fmaxf(M, sm.wm[w]);
         float L = 0.0f, o = 0.0f;
         if (M > -INFINITY) {
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
+            for (int w = 0; w < 4 * G; ++w) {
                 const float e = expf(sm.wm[w] - M);
                 L = fmaf(sm.wl[w], e, L);
                 o = fmaf(sm.wacc[w][d], e, o);
@@ -802,20 +814,24 @@ static int launch_decode_attn(const void* qkv, void* kc, void* vc, void* out,
         static const bool use_regs = [] { const char* e = getenv("LUATL_ATTN_REGS"); return e && e[0] == '1'; }();
         static const int stages = [] { const char* e = getenv("LUATL_ATTN_STAGES"); return e ? atoi(e) : 2; }();
         if (!use_regs) {
-#define BULK_LAUNCH_M(STG, MINB)                                                                                   \
+#define BULK_LAUNCH_M(STG, MINB, G)                                                                                \
             {                                                                                                      \
-                const size_t smem = sizeof(bulk::Smem<STG>) + 128;                                                 \
+                const size_t smem = sizeof(bulk::Smem<STG, G>) + 128;                                              \
                 static bool attr = false;                                                                          \
                 if (!attr) {                                                                                       \
-                    LTL_CUDA("decode_attn attr", cudaFuncSetAttribute(decode_attn_bulk_kernel<T, HD, STG, MINB>,   \
+                    LTL_CUDA("decode_attn attr", cudaFuncSetAttribute(decode_attn_bulk_kernel<T, HD, STG, MINB, G>, \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                             \
                     attr = true;                                                                                   \
                 }                                                                                                  \
-                LTL_CUDA("decode_attn launch", ltl_launch(decode_attn_bulk_kernel<T, HD, STG, MINB>, MINB > 5 ? bgrid : grid, dim3(128), smem, s, \
+                LTL_CUDA("decode_attn launch", ltl_launch(decode_attn_bulk_kernel<T, HD, STG, MINB, G>, MINB > 5 ? bgrid : grid, dim3(128 * G), smem, s, \
                     ltl_pdl_enabled() && splits == 1, (const T*)qkv, (T*)kc, (T*)vc, (T*)out, pos, B, H, ctx, scale, \
                     splits, scratch, cs, interleaved, use_rope, err));                                             \
             }
-#define BULK_LAUNCH(STG) { if (per_sm > 0) BULK_LAUNCH_M(STG, 6) else BULK_LAUNCH_M(STG, 5) }
+#define BULK_LAUNCH(STG) { if (per_sm > 0) BULK_LAUNCH_M(STG, 6, 1) else if (groups == 2) BULK_LAUNCH_M(STG, 5, 2) else BULK_LAUNCH_M(STG, 5, 1) }
+            // Two groups of warps per item while an SM holds fewer than four items (LUATL_ATTN_GROUPS=1|2 overrides).
+            const char* eg = getenv("LUATL_ATTN_GROUPS");        // read per launch: a test switches it between models
+            const int env_groups = eg ? atoi(eg) : 0;
+            const int groups = env_groups > 0 ? env_groups : (nitems < 4 * ltl_sm_count() ? 2 : 1);
             const int stg = g_attn_stages > 0 ? g_attn_stages : stages;
             if (stg <= 1) BULK_LAUNCH(1) else if (stg == 2) BULK_LAUNCH(2) else if (stg == 3) BULK_LAUNCH(3) else BULK_LAUNCH(4)
 #undef BULK_LAUNCH

@@ -353,10 +353,13 @@ def test_bf16_training_needs_multiples_of_8():
         m.train_step_ids(np.zeros((1, 64), np.int32), np.zeros((1, 64), np.int32), lr=0.1)
 
 
+@pytest.mark.parametrize("groups", ["1", "2"])
 @pytest.mark.parametrize("dtype,heads", [("f32", 4), ("bf16", 2)])
-def test_bulk_staged_decode_attention_long_context(dtype, heads):
+def test_bulk_staged_decode_attention_long_context(dtype, heads, groups, monkeypatch):
     """128-byte cache rows (fp32 head_dim 32, bf16 head_dim 64) take the bulk-copy staged decode
-    attention: several 64-key tiles, a ragged last tile, split-KV, against the oracle."""
+    attention: several 64-key tiles, a ragged last tile, split-KV, one group of four warps per item or two groups on
+    alternate tiles (the form small batches take), against the oracle."""
+    monkeypatch.setenv("LUATL_ATTN_GROUPS", groups)
     cfg = dict(vocab=300, dim=128, layers=2, heads=heads, ffn=96, max_seq=400)
     w = params_for(cfg, seed=11, std=0.1)
     if dtype == "bf16":
@@ -485,6 +488,27 @@ def test_config4_width_mixed_precision_against_the_fp32_path():
     assert abs(res["bf16"][0] - res["f32"][0]) < MIXED_LOSS_TOL * res["f32"][0]
     worst = max((l2_err(res["bf16"][1][n], res["f32"][1][n]), n) for n in res["f32"][1])
     assert worst[0] < MIXED_GRAD_TOL, worst
+
+
+def test_config4_width_one_layer_against_the_oracle():
+    """configs[4]'s widths (dim 2048, 16 heads of 128, ffn 5632) on one layer, 256 tokens and a 4096-word vocabulary: the
+    mixed-precision step (persistent tcgen05 GEMMs, head_dim-128 tensor-core attention forward and backward over two key
+    tiles, MN-major weight-gradient products) against the double-precision oracle rounding where this path rounds.
+    Loss within 2e-3 relative, every gradient tensor within 3e-2 in L2 - the bounds of the narrow mixed-precision tests."""
+    cfg = dict(vocab=4096, dim=2048, layers=1, heads=16, ffn=5632, max_seq=256)
+    T = cfg["max_seq"]
+    w = bf16_round(synth.init_params(cfg["vocab"], cfg["dim"], cfg["layers"], cfg["heads"], cfg["ffn"], seed=0))
+    ids = synth.zipf_ids(10, T, cfg["vocab"]).reshape(1, T)
+    tgt = shifted_targets(ids)
+    ref = oracle_for(cfg, act_bf16=True).loss_grad(w, ids, tgt)
+    m = make(cfg, 1, w, dtype="bf16", optimizer="sgd", decode_batch=0, init=False)
+    loss, _, valid, _, finite = m.train_step_ids(ids, tgt, lr=0.0, no_update=True)
+    assert finite and valid == ref["valid"] == T - 1
+    assert abs(loss - ref["loss"]) < MIXED_LOSS_TOL * abs(ref["loss"]), (loss, ref["loss"])
+    got, want = split_params(m.flat_grads(), cfg), split_params(ref["grads"], cfg)
+    worst = max((l2_err(got[n], want[n]), n) for n in want)
+    assert worst[0] < MIXED_GRAD_TOL, worst
+    m.free()
 
 
 # ---- scratch that moves under a captured decode graph ----------------------------------------------------------------
