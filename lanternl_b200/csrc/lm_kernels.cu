@@ -828,10 +828,12 @@ static int launch_decode_attn(const void* qkv, void* kc, void* vc, void* out,
                     splits, scratch, cs, interleaved, use_rope, err));                                             \
             }
 #define BULK_LAUNCH(STG) { if (per_sm > 0) BULK_LAUNCH_M(STG, 6, 1) else if (groups == 2) BULK_LAUNCH_M(STG, 5, 2) else BULK_LAUNCH_M(STG, 5, 1) }
-            // Two groups of warps per item while an SM holds fewer than four items (LUATL_ATTN_GROUPS=1|2 overrides).
+            // Two groups of warps per item when the cache is not sliced and an SM holds fewer than two items: measured per pass
+            // of 511 steps at 32 sequences x 8 heads 130.7 -> 123.2 ms; slower from 64 sequences up (145.7 -> 148.7 ms, 128:
+            // 182.9 -> 192.6) and on sliced caches (8 sequences: 101.6 -> 109.6).  LUATL_ATTN_GROUPS=1|2 overrides.
             const char* eg = getenv("LUATL_ATTN_GROUPS");        // read per launch: a test switches it between models
             const int env_groups = eg ? atoi(eg) : 0;
-            const int groups = env_groups > 0 ? env_groups : (nitems < 4 * ltl_sm_count() ? 2 : 1);
+            const int groups = env_groups > 0 ? env_groups : (splits == 1 && nitems < 2 * ltl_sm_count() ? 2 : 1);
             const int stg = g_attn_stages > 0 ? g_attn_stages : stages;
             if (stg <= 1) BULK_LAUNCH(1) else if (stg == 2) BULK_LAUNCH(2) else if (stg == 3) BULK_LAUNCH(3) else BULK_LAUNCH(4)
 #undef BULK_LAUNCH
