@@ -101,6 +101,7 @@ struct luaTL_lm_s {
     int* d_err = nullptr;
     float* xlast = nullptr;
     float* part = nullptr;       // split-K partial sums of the decode GEMMs [8][nseq_cap][D]
+    float* part_q = nullptr;     // split-K partial sums of the QKV projection of small decode batches [8][<= 32][3 D]
     float* ssq[2] = { nullptr, nullptr };   // per-row sums of squares by 32-column tile [nseq_cap][D / 32] (fused residual GEMMs)
     int* tile_tickets = nullptr; // arrival counters of the fused residual GEMMs, one per output tile, zero between launches
     unsigned* chain_bar = nullptr;   // grid barrier words of the chain kernel (arrivals, generation)
@@ -121,6 +122,7 @@ struct luaTL_lm_s {
     // two-halves decode loop (see generate_halves): second stream, its activation set and split-K scratch, fork / join
     // events, and the two captured steps (full: both halves; tail: the last step)
     int halves = 0, halves_min = 128;
+    int split_qkv = 1;           // LUATL_DECODE_SPLIT_QKV=0: the QKV projection of small batches in one piece (A/B aid)
     int pref_rows = -1;          // rows per (sequence, head) of the decode step's L2 prefetch rider; -1: by batch size
     cudaStream_t s2 = nullptr;
     Act dec2;
@@ -863,6 +865,7 @@ int ensure_decode(LM* m, int nseq, int n_prompt, int n_new)
         DALLOC(m->d_win, (size_t)m->nseq_cap * m->T * 4, "window ids");
         DALLOC(m->xlast, (size_t)m->nseq_cap * m->D * 4, "last rows");
         DALLOC(m->part, (size_t)8 * m->nseq_cap * m->D * 4, "split-K partial sums");
+        DALLOC(m->part_q, (size_t)8 * (m->nseq_cap < 32 ? m->nseq_cap : 32) * 3 * m->D * 4, "split-K partial sums of q | k | v");
         {
             const size_t tiles = (size_t)(m->D + 31) / 32, ntick = ((size_t)m->nseq_cap / 128 + 1) * tiles;
             DALLOC(m->ssq[0], (size_t)m->nseq_cap * tiles * 4, "row sums of squares");
@@ -965,9 +968,17 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
     // tcgen05 tiles win (152 vs 176 ms: four row tiles per warp and a 64 KB activation stage per CTA).
     const bool rows = m->rows_gemm && nseq <= 32 && ltl_gemm_rows_supported(a.h1, m->Wb, nseq, D, D, 1) &&
                       ltl_gemm_rows_supported(a.hs, m->Wb, nseq, D, F, 8);
+    // Few rows: the QKV projection is split over K as well (every CTA then stages a quarter of the activation rows) and
+    // the attention kernel adds the slices when it fetches q | k | v of its (sequence, head).  Measured per pass of 511
+    // steps: 32 sequences 123.7 -> 118.7 ms (the projection 3.9 -> 2.8 us in a chain), 16 sequences 111.8 -> 110.3; not
+    // with the cache cut in more than three slices (8 sequences: 102.0 -> 102.9, every slice's CTA adds the partial sums).
+    int s_q = 1;
     if (rows) {
         s_o = ltl_gemm_rows_plan_split(D, D, 8);
         s_d = ltl_gemm_rows_plan_split(D, F, 8);
+        if ((!cx || cx->a == &m->dec) && m->split_qkv && m->part_q && nseq <= 32 && m->splits <= 3 && ltl_decode_attn_takes_parts(hd, LTL_BF16) &&
+            ltl_gemm_rows_supported(a.h1, m->Wb, nseq, 3 * D, D, 8))
+            s_q = ltl_gemm_rows_plan_split(3 * D, D, 8);
     }
     auto gemm = [&](const void* A, const bf16* Wt, void* C, int N, int K, int c_dt, int bn, int epi, int ks,
                     const LtlGemmFuse* fz = nullptr) -> int {
@@ -1013,10 +1024,15 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
             m->launches += 5 + (m->splits > 1 ? 1 : 0);
             continue;
         }
-        if (on()) { LTL_TRY(gemm(a.h1, m->Wb + o.wqkv, a.qkv, 3 * D, D, LTL_BF16, 0, 0, 1)); m->launches++; }
+        if (on()) {
+            if (s_q > 1) LTL_TRY(gemm(a.h1, m->Wb + o.wqkv, m->part_q, 3 * D, D, LTL_F32, 0, 0, s_q));
+            else LTL_TRY(gemm(a.h1, m->Wb + o.wqkv, a.qkv, 3 * D, D, LTL_BF16, 0, 0, 1));
+            m->launches++;
+        }
         if (on()) {
             LTL_TRY(ltl_decode_attn(a.qkv, kcl, vcl, a.attn, pos, nseq, H, hd, m->T, m->scale, LTL_BF16, m->splits, m->ws,
-                                    m->rope_tab, m->c.rope_interleaved, m->c.use_rope, m->d_err, st));
+                                    m->rope_tab, m->c.rope_interleaved, m->c.use_rope, m->d_err, st,
+                                    s_q > 1 ? m->part_q : nullptr, s_q > 1 ? s_q : 0));
             m->launches += 1 + (m->splits > 1 ? 1 : 0);
         }
         if (on()) { LTL_TRY(gemm(a.attn, m->Wb + o.wo, part, D, D, LTL_F32, bn_o, 0, s_o)); m->launches++; }
@@ -1434,6 +1450,8 @@ luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
         m->halves = hv && hv[0] == '1';
         const char* hm = getenv("LUATL_DECODE_HALVES_MIN");
         if (hm && atoi(hm) >= 2) m->halves_min = atoi(hm);
+        const char* sq = getenv("LUATL_DECODE_SPLIT_QKV");
+        m->split_qkv = !(sq && sq[0] == '0');
         const char* pm = getenv("LUATL_KV_PREFETCH_ROWS");
         m->pref_rows = pm ? atoi(pm) : -1;
         const char* oc = getenv("LUATL_OVERLAP_COMM");
@@ -1479,7 +1497,7 @@ void luaTL_lm_destroy(luaTL_lm_t* m)
     if (m->s2) cudaStreamDestroy(m->s2);
     void* ptrs[] = { m->W, m->G, m->M1, m->M2, m->Wb, m->rope_tab, m->dres, m->dbr, m->dhf, m->dh1, m->dqkv, m->dattn,
                      m->dh2, m->dh13, m->dhs, m->delta, m->losses, m->d_ids, m->d_tgt, m->d_pred, m->ws, m->kc, m->vc,
-                     m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part,
+                     m->d_pos, m->d_count, m->d_next, m->d_hist, m->d_win, m->d_prompt, m->d_out, m->d_err, m->xlast, m->part, m->part_q,
                      m->Wm, m->d_done, m->d_nodecay, m->chain_bar, m->Wt, m->tA, m->tB, m->ssq[0], m->ssq[1], m->tile_tickets, m->b_dres, m->b_dhs, m->b_dh13, m->b_dattn, m->b_dqkv, m->b_dl };
     for (void* p : ptrs) if (p) cudaFree(p);
     for (int i = 0; i < 4; ++i) if (m->ev[i]) cudaEventDestroy(m->ev[i]);

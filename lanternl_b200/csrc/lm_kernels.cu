@@ -600,7 +600,8 @@ __global__ void __launch_bounds__(128 * G, G == 1 ? MINB : 2)
 decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
                         T* __restrict__ out, const int32_t* __restrict__ pos, int B, int H, int ctx, float scale,
                         int splits, float* __restrict__ scratch, const float2* __restrict__ cs,
-                        int interleaved, int use_rope, int* __restrict__ err)
+                        int interleaved, int use_rope, int* __restrict__ err,
+                        const float* __restrict__ qparts, int nparts)
 {
     using namespace bulk;
     static_assert(HD * sizeof(T) == ROWB && HD <= 64, "rows of 128 bytes");
@@ -657,9 +658,31 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     // new token: the first GL lanes of warp 1 rotate q and k, append k / v, publish q, k, v as fp32
     if (warp == 1 && lane < GL) {
         const int r = lane;
-        const T* row = qkv + (size_t)b * 3 * D + (size_t)h * HD + r * N;
         float q[N], kn[N], vn[N];
-        ld16<T>(row, q); ld16<T>(row + D, kn); ld16<T>(row + 2 * D, vn);
+        if (nparts > 0) {
+            // q | k | v arrive as split-K partial sums [nparts][B][3 D] of the projection: added in slice order and rounded
+            // to the storage type, which is what the stored row would hold
+            const size_t off = (size_t)b * 3 * D + (size_t)h * HD + r * N, slice = (size_t)B * 3 * D;
+#pragma unroll
+            for (int i = 0; i < N; ++i) { q[i] = 0.0f; kn[i] = 0.0f; vn[i] = 0.0f; }
+            for (int p = 0; p < nparts; ++p) {
+                const float* pp = qparts + p * slice + off;
+#pragma unroll
+                for (int i = 0; i < N; i += 4) {
+                    const float4 a = __ldcg(reinterpret_cast<const float4*>(pp + i));
+                    const float4 c = __ldcg(reinterpret_cast<const float4*>(pp + D + i));
+                    const float4 d = __ldcg(reinterpret_cast<const float4*>(pp + 2 * D + i));
+                    q[i] += a.x; q[i + 1] += a.y; q[i + 2] += a.z; q[i + 3] += a.w;
+                    kn[i] += c.x; kn[i + 1] += c.y; kn[i + 2] += c.z; kn[i + 3] += c.w;
+                    vn[i] += d.x; vn[i + 1] += d.y; vn[i + 2] += d.z; vn[i + 3] += d.w;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < N; ++i) { q[i] = round_to<T>(q[i]); kn[i] = round_to<T>(kn[i]); vn[i] = round_to<T>(vn[i]); }
+        } else {
+            const T* row = qkv + (size_t)b * 3 * D + (size_t)h * HD + r * N;
+            ld16<T>(row, q); ld16<T>(row + D, kn); ld16<T>(row + 2 * D, vn);
+        }
         if (use_rope) {
             const float2* tab = cs + (size_t)(in_range ? ps : 0) * (HD / 2);
             constexpr unsigned GM = (1u << GL) - 1u;
@@ -793,6 +816,15 @@ __global__ void decode_attn_combine_kernel(const float* __restrict__ scratch, T*
 static int g_attn_ctas_per_sm = 0, g_attn_stages = 0;
 void ltl_decode_attn_shape(int ctas_per_sm, int stages) { g_attn_ctas_per_sm = ctas_per_sm; g_attn_stages = stages; }
 
+// 1 when ltl_decode_attn can take q | k | v as split-K partial sums for this head size and type (the bulk-copy kernel:
+// cache rows of 128 bytes, and the register kernel not forced).
+bool ltl_decode_attn_takes_parts(int hd, int dtype)
+{
+    const char* e = getenv("LUATL_ATTN_REGS");
+    if (e && e[0] == '1') return false;
+    return (dtype == LTL_BF16 && hd == 64) || (dtype == LTL_F32 && hd == 32);
+}
+
 size_t ltl_decode_attn_scratch_floats(int B, int H, int hd, int splits)
 {
     return splits > 1 ? (size_t)B * H * splits * (hd + 2) : 0;
@@ -802,7 +834,7 @@ template <typename T, int HD>
 static int launch_decode_attn(const void* qkv, void* kc, void* vc, void* out,
                               const int32_t* pos, int B, int H, int ctx, float scale, int splits,
                               float* scratch, const float2* cs, int interleaved, int use_rope, int* err,
-                              cudaStream_t s)
+                              cudaStream_t s, const float* qparts, int nparts)
 {
     dim3 grid(H, B, splits);
     if constexpr (HD * sizeof(T) == 128 && HD <= 64) {
@@ -825,7 +857,7 @@ static int launch_decode_attn(const void* qkv, void* kc, void* vc, void* out,
                 }                                                                                                  \
                 LTL_CUDA("decode_attn launch", ltl_launch(decode_attn_bulk_kernel<T, HD, STG, MINB, G>, MINB > 5 ? bgrid : grid, dim3(128 * G), smem, s, \
                     ltl_pdl_enabled() && splits == 1, (const T*)qkv, (T*)kc, (T*)vc, (T*)out, pos, B, H, ctx, scale, \
-                    splits, scratch, cs, interleaved, use_rope, err));                                             \
+                    splits, scratch, cs, interleaved, use_rope, err, qparts, nparts));                             \
             }
 #define BULK_LAUNCH(STG) { if (per_sm > 0) BULK_LAUNCH_M(STG, 6, 1) else if (groups == 2) BULK_LAUNCH_M(STG, 5, 2) else BULK_LAUNCH_M(STG, 5, 1) }
             // Two groups of warps per item when the cache is not sliced and an SM holds fewer than two items: measured per pass
@@ -845,6 +877,7 @@ static int launch_decode_attn(const void* qkv, void* kc, void* vc, void* out,
             return ltl_check_launch("decode_attn");
         }
     }
+    if (nparts > 0) return ltl_fail(LTL_ERR_UNSUPPORTED, "decode_attn: only the bulk-copy kernel takes q | k | v as partial sums");
     decode_attn_kernel<T, HD><<<grid, 128, 0, s>>>((const T*)qkv, (T*)kc, (T*)vc, (T*)out, pos, H, ctx, scale,
                                                    splits, scratch, cs, interleaved, use_rope, err);
     if (splits > 1) {
@@ -857,9 +890,12 @@ static int launch_decode_attn(const void* qkv, void* kc, void* vc, void* out,
 int ltl_decode_attn(const void* qkv, void* kcache, void* vcache, void* out,
                     const int32_t* pos, int B, int H, int hd, int ctx, float scale, int dtype,
                     int splits, float* scratch, const float2* cs_table, int interleaved, int use_rope,
-                    int* err, cudaStream_t s)
+                    int* err, cudaStream_t s, const float* qkv_parts, int nparts)
 {
     if (use_rope && !cs_table) return ltl_fail(LTL_ERR_NULL, "decode_attn: missing angle table");
+    if (nparts > 0 && (!qkv_parts || !aligned16(qkv_parts) || (H * hd) % 4))
+        return ltl_fail(LTL_ERR_ARG, "decode_attn: partial sums need a 16-byte aligned buffer and a width that is a multiple of 4");
+    if (nparts > 0) qkv = qkv_parts;                          // the stored q | k | v row is not read
     if (!qkv || !kcache || !vcache || !out || !pos) return ltl_fail(LTL_ERR_NULL, "decode_attn: null pointer");
     if (B <= 0 || H <= 0) return ltl_fail(LTL_ERR_SHAPE, "decode_attn: bad shape");
     if (B > 65535 || splits > 65535) return ltl_fail(LTL_ERR_SHAPE, "decode_attn: grid too large");
@@ -867,7 +903,7 @@ int ltl_decode_attn(const void* qkv, void* kcache, void* vcache, void* out,
     if (splits > 1 && !scratch) return ltl_fail(LTL_ERR_NULL, "decode_attn: split-KV needs scratch");
     if (!aligned16(qkv) || !aligned16(kcache) || !aligned16(vcache))
         return ltl_fail(LTL_ERR_ARG, "decode_attn: operands must be 16-byte aligned");
-#define DA(TT, HH) return launch_decode_attn<TT, HH>(qkv, kcache, vcache, out, pos, B, H, ctx, scale, splits, scratch, cs_table, interleaved, use_rope, err, s)
+#define DA(TT, HH) return launch_decode_attn<TT, HH>(qkv, kcache, vcache, out, pos, B, H, ctx, scale, splits, scratch, cs_table, interleaved, use_rope, err, s, qkv_parts, nparts < 0 ? 0 : nparts)
     if (dtype == LTL_F32) {
         if (hd == 16) DA(float, 16);
         if (hd == 32) DA(float, 32);

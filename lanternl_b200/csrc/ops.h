@@ -139,7 +139,10 @@ void ltl_decode_attn_shape(int ctas_per_sm, int stages);   // 0, 0 = one CTA per
 int ltl_decode_attn(const void* qkv, void* kcache, void* vcache, void* out,
                     const int32_t* pos, int B, int H, int hd, int ctx, float scale, int dtype,
                     int splits, float* scratch, const float2* cs_table, int interleaved, int use_rope,
-                    int* err, cudaStream_t s);
+                    int* err, cudaStream_t s, const float* qkv_parts = nullptr, int nparts = 0);
+// nparts > 0: q | k | v are read as the sum of nparts fp32 slices [nparts][B][3 D] (a split-K projection), rounded to the
+// storage type, instead of from qkv (which may then be null).  Only where ltl_decode_attn_takes_parts says so.
+bool ltl_decode_attn_takes_parts(int hd, int dtype);
 // Greedy pick and bookkeeping of one decode step, per sequence b:
 //   next[b] = argmax(logits[b, :]) (ties -> lowest index);
 //   out_ids[b * out_stride + count[b]] = next[b] when count[b] < out_stride; count[b] += 1; pos[b] += 1.
