@@ -101,7 +101,7 @@ struct luaTL_lm_s {
     int* d_err = nullptr;
     float* xlast = nullptr;
     float* part = nullptr;       // split-K partial sums of the decode GEMMs [8][nseq_cap][D]
-    float* part_q = nullptr;     // split-K partial sums of the QKV projection of small decode batches [8][<= 32][3 D]
+    float* part_q = nullptr;     // split-K partial sums of the QKV projection of the decode step [8][nseq_cap][3 D]
     float* ssq[2] = { nullptr, nullptr };   // per-row sums of squares by 32-column tile [nseq_cap][D / 32] (fused residual GEMMs)
     int* tile_tickets = nullptr; // arrival counters of the fused residual GEMMs, one per output tile, zero between launches
     unsigned* chain_bar = nullptr;   // grid barrier words of the chain kernel (arrivals, generation)
@@ -865,7 +865,7 @@ int ensure_decode(LM* m, int nseq, int n_prompt, int n_new)
         DALLOC(m->d_win, (size_t)m->nseq_cap * m->T * 4, "window ids");
         DALLOC(m->xlast, (size_t)m->nseq_cap * m->D * 4, "last rows");
         DALLOC(m->part, (size_t)8 * m->nseq_cap * m->D * 4, "split-K partial sums");
-        DALLOC(m->part_q, (size_t)8 * (m->nseq_cap < 32 ? m->nseq_cap : 32) * 3 * m->D * 4, "split-K partial sums of q | k | v");
+        DALLOC(m->part_q, (size_t)8 * m->nseq_cap * 3 * m->D * 4, "split-K partial sums of q | k | v");
         {
             const size_t tiles = (size_t)(m->D + 31) / 32, ntick = ((size_t)m->nseq_cap / 128 + 1) * tiles;
             DALLOC(m->ssq[0], (size_t)m->nseq_cap * tiles * 4, "row sums of squares");
@@ -972,13 +972,17 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
     // the attention kernel adds the slices when it fetches q | k | v of its (sequence, head).  Measured per pass of 511
     // steps: 32 sequences 123.7 -> 118.7 ms (the projection 3.9 -> 2.8 us in a chain), 16 sequences 111.8 -> 110.3; not
     // with the cache cut in more than three slices (8 sequences: 102.0 -> 102.9, every slice's CTA adds the partial sums).
-    int s_q = 1;
+    int s_q = 1, bn_q = 0;
+    const bool parts_ok = (!cx || cx->a == &m->dec) && m->split_qkv && m->part_q && m->splits <= 3 && ltl_decode_attn_takes_parts(hd, LTL_BF16);
     if (rows) {
         s_o = ltl_gemm_rows_plan_split(D, D, 8);
         s_d = ltl_gemm_rows_plan_split(D, F, 8);
-        if ((!cx || cx->a == &m->dec) && m->split_qkv && m->part_q && nseq <= 32 && m->splits <= 3 && ltl_decode_attn_takes_parts(hd, LTL_BF16) &&
-            ltl_gemm_rows_supported(a.h1, m->Wb, nseq, 3 * D, D, 8))
-            s_q = ltl_gemm_rows_plan_split(3 * D, D, 8);
+        if (parts_ok && ltl_gemm_rows_supported(a.h1, m->Wb, nseq, 3 * D, D, 8)) s_q = ltl_gemm_rows_plan_split(3 * D, D, 8);
+    } else if (parts_ok && m->split_qkv >= 2) {
+        // tcgen05 tiles (LUATL_DECODE_SPLIT_QKV=2, off): the projection gets faster in a chain (4.5 -> 3.7 us at 128 rows) but the
+        // attention kernel, whose every CTA then adds three slices, loses more: 128 sequences 185.6 -> 188.3 ms per pass, 64: 148.0 -> 146.7
+        ltl_gemm_tc_plan_split(nseq, 3 * D, D, &bn_q, &s_q);
+        if (s_q <= 1) { s_q = 1; bn_q = 0; }
     }
     auto gemm = [&](const void* A, const bf16* Wt, void* C, int N, int K, int c_dt, int bn, int epi, int ks,
                     const LtlGemmFuse* fz = nullptr) -> int {
@@ -1025,7 +1029,7 @@ int decode_step_split(LM* m, int nseq, int slot0, const int32_t* d_tok, int32_t*
             continue;
         }
         if (on()) {
-            if (s_q > 1) LTL_TRY(gemm(a.h1, m->Wb + o.wqkv, m->part_q, 3 * D, D, LTL_F32, 0, 0, s_q));
+            if (s_q > 1) LTL_TRY(gemm(a.h1, m->Wb + o.wqkv, m->part_q, 3 * D, D, LTL_F32, bn_q, 0, s_q));
             else LTL_TRY(gemm(a.h1, m->Wb + o.wqkv, a.qkv, 3 * D, D, LTL_BF16, 0, 0, 1));
             m->launches++;
         }
@@ -1451,7 +1455,7 @@ luaTL_lm_t* luaTL_lm_create(const luaTL_lm_config_t* cfg)
         const char* hm = getenv("LUATL_DECODE_HALVES_MIN");
         if (hm && atoi(hm) >= 2) m->halves_min = atoi(hm);
         const char* sq = getenv("LUATL_DECODE_SPLIT_QKV");
-        m->split_qkv = !(sq && sq[0] == '0');
+        m->split_qkv = sq ? atoi(sq) : 1;          // 0: never, 1: few-row kernel only, 2: tcgen05 tiles too
         const char* pm = getenv("LUATL_KV_PREFETCH_ROWS");
         m->pref_rows = pm ? atoi(pm) : -1;
         const char* oc = getenv("LUATL_OVERLAP_COMM");
