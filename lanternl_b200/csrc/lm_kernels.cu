@@ -282,6 +282,28 @@ __global__ void kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T
     }
 }
 
+// The same in 16-byte packets (head_dim a multiple of the packet, aligned operands): one thread moves one packet of k and
+// one of v; consecutive threads walk a token's row, so reads are contiguous and writes run in head_dim-sized pieces.
+template <typename T>
+__global__ void kv_store_vec_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
+                                    int B, int T_, int H, int hd, int ctx)
+{
+    constexpr int N = 16 / (int)sizeof(T);
+    const int D = H * hd, pr = hd / N, prow = D / N;          // packets per head row and per token row
+    const uint64_t n = (uint64_t)B * T_ * prow;
+    for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+         idx += (uint64_t)gridDim.x * blockDim.x) {
+        const int p = (int)(idx % prow);
+        const uint64_t bt = idx / prow;
+        const int t = (int)(bt % T_), b = (int)(bt / T_);
+        const int h = p / pr, d = (p - h * pr) * N;
+        const size_t src = (size_t)bt * 3 * D + (size_t)h * hd + d;
+        const size_t dst = (((size_t)b * H + h) * ctx + t) * hd + d;
+        *reinterpret_cast<uint4*>(kc + dst) = __ldg(reinterpret_cast<const uint4*>(qkv + src + D));
+        *reinterpret_cast<uint4*>(vc + dst) = __ldg(reinterpret_cast<const uint4*>(qkv + src + 2 * D));
+    }
+}
+
 int ltl_kv_store(const void* qkv, void* kcache, void* vcache, int B, int T, int H, int hd, int ctx,
                  int dtype, cudaStream_t s)
 {
@@ -289,8 +311,16 @@ int ltl_kv_store(const void* qkv, void* kcache, void* vcache, int B, int T, int 
     if (T > ctx) return ltl_fail(LTL_ERR_SHAPE, "kv_store: %d positions exceed the cache (%d)", T, ctx);
     const uint64_t n = (uint64_t)B * T * H * hd;
     if (n == 0) return LTL_OK;
-    unsigned grid = (unsigned)((n + 255) / 256);
     const unsigned cap = (unsigned)ltl_sm_count() * 16;
+    const int pk = dtype == LTL_F32 ? 4 : 8;                  // elements per 16-byte packet
+    if ((dtype == LTL_F32 || dtype == LTL_BF16) && hd % pk == 0 && aligned16(qkv) && aligned16(kcache) && aligned16(vcache)) {
+        unsigned grid = (unsigned)((n / pk + 255) / 256);
+        if (grid > cap) grid = cap;
+        if (dtype == LTL_F32) kv_store_vec_kernel<float><<<grid, 256, 0, s>>>((const float*)qkv, (float*)kcache, (float*)vcache, B, T, H, hd, ctx);
+        else kv_store_vec_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)qkv, (bf16*)kcache, (bf16*)vcache, B, T, H, hd, ctx);
+        return ltl_check_launch("kv_store");
+    }
+    unsigned grid = (unsigned)((n + 255) / 256);
     if (grid > cap) grid = cap;
     if (dtype == LTL_F32) kv_store_kernel<float><<<grid, 256, 0, s>>>((const float*)qkv, (float*)kcache, (float*)vcache, B, T, H, hd, ctx);
     else if (dtype == LTL_BF16) kv_store_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)qkv, (bf16*)kcache, (bf16*)vcache, B, T, H, hd, ctx);
