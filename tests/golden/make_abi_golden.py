@@ -59,4 +59,6 @@ def main(ref):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_abi_golden.py <path of the lanternl tree>")
+    main(sys.argv[1])

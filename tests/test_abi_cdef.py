@@ -13,11 +13,11 @@ import re
 import cffi
 import pytest
 
+from __graft_entry__ import REFERENCE_ROOT as REF
 from lanternl_b200 import _lib
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 GOLDEN = json.load(open(os.path.join(ROOT, "tests", "golden", "reference_abi.json")))
-REF = "/root/reference"
 
 
 def describe(ffi):

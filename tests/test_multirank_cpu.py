@@ -83,9 +83,9 @@ def test_shard_rows_rejects_uneven_split():
 
 # ---- a rank that never reaches the exchange -------------------------------------------------------------------------
 def exchange_worker(rank, out_dir):
-    """Two host processes around one 'collective' whose completion is the other rank's arrival file.  Round 1: both
-    arrive.  Round 2: rank 1 skips the exchange (a host-made failure); rank 0's wait must run out, tear the
-    communicator down and report - not hang.  Round 3: the communicator itself reports an asynchronous error."""
+    """Two host processes around one 'collective' whose completion is the other rank's arrival file.  Exchange 1: both
+    arrive.  Exchange 2: rank 1 skips it (a host-made failure); rank 0's wait must run out, tear the
+    communicator down and report - not hang.  Exchange 3: the communicator itself reports an asynchronous error."""
     import ctypes as C
     import time
     from lanternl_b200 import _lib
