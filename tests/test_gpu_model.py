@@ -652,3 +652,23 @@ def test_decode_launch_timing_aid_reports_every_kind_and_resets_the_state():
     after = m.generate_batch(prompts, 20, zero_indexed=True)
     assert np.array_equal(before, after)
     m.free()
+
+
+def test_split_qkv_projection_of_small_batches_gives_the_tokens_of_the_unsplit_one(monkeypatch):
+    """Up to 32 sequences the QKV projection is split over K and the decode-attention kernel adds the fp32 slices (rounding
+    the sum to bf16, as the stored row would be) when it fetches q | k | v.  Same products, another summation order: the
+    greedy tokens agree except at rare near-ties, and stay consistent with the oracle."""
+    cfg = dict(vocab=1000, dim=256, layers=2, heads=4, ffn=352, max_seq=64)
+    w = bf16_round(params_for(cfg, seed=8, std=0.05))
+    prompts = synth.zipf_ids(9, 32 * 12, cfg["vocab"]).reshape(32, 12)
+    out, launches = [], []
+    for flag in ("0", "1"):
+        monkeypatch.setenv("LUATL_DECODE_SPLIT_QKV", flag)
+        m = make(cfg, 1, w, decode_batch=32, dtype="bf16")
+        out.append(m.generate_batch(prompts, 40, zero_indexed=True))
+        launches.append(m.time_decode_launches(32, 20, reps=3)["qkv"])
+        m.free()
+    differ = int((out[0] != out[1]).any(axis=1).sum())
+    assert differ <= 2, differ
+    assert_tokens_consistent(oracle_for(cfg), w, prompts[:4], out[1][:4], 5e-3)
+    assert all(0.2 < v < 200.0 for v in launches)
