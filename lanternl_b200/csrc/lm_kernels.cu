@@ -661,162 +661,162 @@ decode_attn_bulk_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __rest
     uint32_t tbase = 0;
     int item = WALK ? (int)blockIdx.x : 0;
     do {
-    const int h = WALK ? item % H : (int)blockIdx.x;
-    const int b = WALK ? (item / H) % B : (int)blockIdx.y;
-    const int z = WALK ? item / (H * B) : (int)blockIdx.z;
-    int ps = pos[b];
-    const bool in_range = ps >= 0 && ps < ctx;
-    if (!in_range) { if (err && tid == 0) *err = 1; ps = ps < 0 ? 0 : ctx; }
-    const int chunk = (ps + splits - 1) / splits;
-    const int kbeg = z * chunk, kend = min(ps, kbeg + chunk);
-    const int ntiles = kend > kbeg ? (kend - kbeg + KT - 1) / KT : 0;
-    const size_t cbase = ((size_t)b * H + h) * ctx * HD;
-    const uint8_t* kg = reinterpret_cast<const uint8_t*>(kc + cbase);
-    const uint8_t* vg = reinterpret_cast<const uint8_t*>(vc + cbase);
+        const int h = WALK ? item % H : (int)blockIdx.x;
+        const int b = WALK ? (item / H) % B : (int)blockIdx.y;
+        const int z = WALK ? item / (H * B) : (int)blockIdx.z;
+        int ps = pos[b];
+        const bool in_range = ps >= 0 && ps < ctx;
+        if (!in_range) { if (err && tid == 0) *err = 1; ps = ps < 0 ? 0 : ctx; }
+        const int chunk = (ps + splits - 1) / splits;
+        const int kbeg = z * chunk, kend = min(ps, kbeg + chunk);
+        const int ntiles = kend > kbeg ? (kend - kbeg + KT - 1) / KT : 0;
+        const size_t cbase = ((size_t)b * H + h) * ctx * HD;
+        const uint8_t* kg = reinterpret_cast<const uint8_t*>(kc + cbase);
+        const uint8_t* vg = reinterpret_cast<const uint8_t*>(vc + cbase);
 
-    if (tid == 0) {
-        // first STG tiles of every group (this thread initialised the barriers; the groups' own producers take over below)
-        for (int g = 0; g < G; ++g)
-            for (int lt = 0; lt < STG && lt * G + g < ntiles; ++lt) {
-                const int k0 = kbeg + (lt * G + g) * KT, s = g * STG + (WALK ? (int)((tbase + lt) % STG) : lt);
+        if (tid == 0) {
+            // first STG tiles of every group (this thread initialised the barriers; the groups' own producers take over below)
+            for (int g = 0; g < G; ++g)
+                for (int lt = 0; lt < STG && lt * G + g < ntiles; ++lt) {
+                    const int k0 = kbeg + (lt * G + g) * KT, s = g * STG + (WALK ? (int)((tbase + lt) % STG) : lt);
+                    const uint32_t bytes = (uint32_t)min(KT, kend - k0) * ROWB;
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(&sm.full[s])), "r"(2 * bytes) : "memory");
+                    copy(sm.k[s], kg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
+                    copy(sm.v[s], vg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
+                }
+        }
+        // new token: the first GL lanes of warp 1 rotate q and k, append k / v, publish q, k, v as fp32
+        if (warp == 1 && lane < GL) {
+            const int r = lane;
+            float q[N], kn[N], vn[N];
+            if (nparts > 0) {
+                // q | k | v arrive as split-K partial sums [nparts][B][3 D] of the projection: added in slice order and rounded
+                // to the storage type, which is what the stored row would hold
+                const size_t off = (size_t)b * 3 * D + (size_t)h * HD + r * N, slice = (size_t)B * 3 * D;
+#pragma unroll
+                for (int i = 0; i < N; ++i) { q[i] = 0.0f; kn[i] = 0.0f; vn[i] = 0.0f; }
+                for (int p = 0; p < nparts; ++p) {
+                    const float* pp = qparts + p * slice + off;
+#pragma unroll
+                    for (int i = 0; i < N; i += 4) {
+                        const float4 a = __ldcg(reinterpret_cast<const float4*>(pp + i));
+                        const float4 c = __ldcg(reinterpret_cast<const float4*>(pp + D + i));
+                        const float4 d = __ldcg(reinterpret_cast<const float4*>(pp + 2 * D + i));
+                        q[i] += a.x; q[i + 1] += a.y; q[i + 2] += a.z; q[i + 3] += a.w;
+                        kn[i] += c.x; kn[i + 1] += c.y; kn[i + 2] += c.z; kn[i + 3] += c.w;
+                        vn[i] += d.x; vn[i + 1] += d.y; vn[i + 2] += d.z; vn[i + 3] += d.w;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < N; ++i) { q[i] = round_to<T>(q[i]); kn[i] = round_to<T>(kn[i]); vn[i] = round_to<T>(vn[i]); }
+            } else {
+                const T* row = qkv + (size_t)b * 3 * D + (size_t)h * HD + r * N;
+                ld16<T>(row, q); ld16<T>(row + D, kn); ld16<T>(row + 2 * D, vn);
+            }
+            if (use_rope) {
+                const float2* tab = cs + (size_t)(in_range ? ps : 0) * (HD / 2);
+                constexpr unsigned GM = (1u << GL) - 1u;
+                if (interleaved) {
+#pragma unroll
+                    for (int i = 0; i < N; i += 2) {
+                        const float2 t = tab[(r * N + i) >> 1];
+                        const float q0 = q[i], q1 = q[i + 1], k0 = kn[i], k1 = kn[i + 1];
+                        q[i] = q0 * t.x - q1 * t.y; q[i + 1] = q1 * t.x + q0 * t.y;
+                        kn[i] = k0 * t.x - k1 * t.y; kn[i + 1] = k1 * t.x + k0 * t.y;
+                    }
+                } else {
+                    const bool low = r < GL / 2;
+                    const int pbase = (r % (GL / 2)) * N;
+#pragma unroll
+                    for (int i = 0; i < N; ++i) {
+                        const float qo = __shfl_xor_sync(GM, q[i], GL / 2);
+                        const float ko = __shfl_xor_sync(GM, kn[i], GL / 2);
+                        const float2 t = tab[pbase + i];
+                        q[i] = low ? q[i] * t.x - qo * t.y : q[i] * t.x + qo * t.y;
+                        kn[i] = low ? kn[i] * t.x - ko * t.y : kn[i] * t.x + ko * t.y;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < N; ++i) { q[i] = round_to<T>(q[i]); kn[i] = round_to<T>(kn[i]); }
+            }
+            if (z == 0 && in_range) {
+                st16<T>(kc + cbase + (size_t)ps * HD + r * N, kn);
+                st16<T>(vc + cbase + (size_t)ps * HD + r * N, vn);
+            }
+#pragma unroll
+            for (int i = 0; i < N; ++i) { sm.q[r * N + i] = q[i] * scale; sm.kn[r * N + i] = kn[i]; sm.vn[r * N + i] = vn[i]; }
+        }
+        __syncthreads();
+
+        const int j = ltid >> 1, half = ltid & 1;        // two threads per key of the tile
+        float m = -INFINITY, lsum = 0.0f, acc[EPW];
+#pragma unroll
+        for (int i = 0; i < EPW; ++i) acc[i] = 0.0f;
+        float qr[4][N];
+        load_q_chunks<N>(sm.q, j, half, qr);
+        bool ok = true;
+        const int mine = ntiles > grp ? (ntiles - grp + G - 1) / G : 0;      // tiles grp, grp + G, ... of the item
+        for (int lt = 0; lt < mine; ++lt) {
+            const int s = grp * STG + (WALK ? (int)((tbase + lt) % STG) : lt % STG);
+            ok = wait(&sm.full[s], (WALK ? (tbase + lt) / STG : (uint32_t)(lt / STG)) & 1) && ok;
+            const int nk = min(KT, kend - (kbeg + (lt * G + grp) * KT));
+            consume_tile<T, N, EPW>(sm.k[s], sm.v[s], nk, qr, j, half, lw, lane, m, lsum, acc);
+            if (G == 1) __syncthreads();                          // everyone is done with stage s
+            else if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");      // the group's own barrier (immediate ids: 3 in use)
+            else asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (ltid == 0 && lt + STG < mine) {
+                const int k0 = kbeg + ((lt + STG) * G + grp) * KT;
                 const uint32_t bytes = (uint32_t)min(KT, kend - k0) * ROWB;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(&sm.full[s])), "r"(2 * bytes) : "memory");
                 copy(sm.k[s], kg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
                 copy(sm.v[s], vg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
             }
-    }
-    // new token: the first GL lanes of warp 1 rotate q and k, append k / v, publish q, k, v as fp32
-    if (warp == 1 && lane < GL) {
-        const int r = lane;
-        float q[N], kn[N], vn[N];
-        if (nparts > 0) {
-            // q | k | v arrive as split-K partial sums [nparts][B][3 D] of the projection: added in slice order and rounded
-            // to the storage type, which is what the stored row would hold
-            const size_t off = (size_t)b * 3 * D + (size_t)h * HD + r * N, slice = (size_t)B * 3 * D;
+        }
+        if (WALK) tbase += (uint32_t)ntiles;
+        if (!ok && err && tid == 0) *err = 2;
+        float l = 0.5f * warp_sum(lsum);                             // every key sits in two lanes
+        if (warp == 0 && z == 0) {     // the new token's own score, from the fp32 copies
+            float sdot = 0.0f;
 #pragma unroll
-            for (int i = 0; i < N; ++i) { q[i] = 0.0f; kn[i] = 0.0f; vn[i] = 0.0f; }
-            for (int p = 0; p < nparts; ++p) {
-                const float* pp = qparts + p * slice + off;
+            for (int i = 0; i < EPW; ++i) sdot = fmaf(sm.q[lane * EPW + i], sm.kn[lane * EPW + i], sdot);
+            sdot = warp_sum(sdot);
+            const float mn = fmaxf(m, sdot);
+            const float corr = (m == -INFINITY) ? 0.0f : expf(m - mn);
+            const float p = expf(sdot - mn);
+            l = l * corr + p;
 #pragma unroll
-                for (int i = 0; i < N; i += 4) {
-                    const float4 a = __ldcg(reinterpret_cast<const float4*>(pp + i));
-                    const float4 c = __ldcg(reinterpret_cast<const float4*>(pp + D + i));
-                    const float4 d = __ldcg(reinterpret_cast<const float4*>(pp + 2 * D + i));
-                    q[i] += a.x; q[i + 1] += a.y; q[i + 2] += a.z; q[i + 3] += a.w;
-                    kn[i] += c.x; kn[i + 1] += c.y; kn[i + 2] += c.z; kn[i + 3] += c.w;
-                    vn[i] += d.x; vn[i + 1] += d.y; vn[i + 2] += d.z; vn[i + 3] += d.w;
+            for (int i = 0; i < EPW; ++i) acc[i] = fmaf(p, sm.vn[lane * EPW + i], acc[i] * corr);
+            m = mn;
+        }
+        if (lane == 0) { sm.wm[warp] = m; sm.wl[warp] = l; }
+#pragma unroll
+        for (int i = 0; i < EPW; ++i) sm.wacc[warp][lane * EPW + i] = acc[i];
+        __syncthreads();
+        if (tid < HD) {
+            const int d = tid;
+            float M = fmaxf(fmaxf(sm.wm[0], sm.wm[1]), fmaxf(sm.wm[2], sm.wm[3]));
+#pragma unroll
+            for (int w = 4; w < 4 * G; ++w) M = fmaxf(M, sm.wm[w]);
+            float L = 0.0f, o = 0.0f;
+            if (M > -INFINITY) {
+#pragma unroll
+                for (int w = 0; w < 4 * G; ++w) {
+                    const float e = expf(sm.wm[w] - M);
+                    L = fmaf(sm.wl[w], e, L);
+                    o = fmaf(sm.wacc[w][d], e, o);
                 }
             }
-#pragma unroll
-            for (int i = 0; i < N; ++i) { q[i] = round_to<T>(q[i]); kn[i] = round_to<T>(kn[i]); vn[i] = round_to<T>(vn[i]); }
-        } else {
-            const T* row = qkv + (size_t)b * 3 * D + (size_t)h * HD + r * N;
-            ld16<T>(row, q); ld16<T>(row + D, kn); ld16<T>(row + 2 * D, vn);
-        }
-        if (use_rope) {
-            const float2* tab = cs + (size_t)(in_range ? ps : 0) * (HD / 2);
-            constexpr unsigned GM = (1u << GL) - 1u;
-            if (interleaved) {
-#pragma unroll
-                for (int i = 0; i < N; i += 2) {
-                    const float2 t = tab[(r * N + i) >> 1];
-                    const float q0 = q[i], q1 = q[i + 1], k0 = kn[i], k1 = kn[i + 1];
-                    q[i] = q0 * t.x - q1 * t.y; q[i + 1] = q1 * t.x + q0 * t.y;
-                    kn[i] = k0 * t.x - k1 * t.y; kn[i + 1] = k1 * t.x + k0 * t.y;
-                }
+            if (splits == 1) {
+                Cvt<T>::st(out, (size_t)b * D + (size_t)h * HD + d, L > 0.0f ? o / L : 0.0f);
             } else {
-                const bool low = r < GL / 2;
-                const int pbase = (r % (GL / 2)) * N;
-#pragma unroll
-                for (int i = 0; i < N; ++i) {
-                    const float qo = __shfl_xor_sync(GM, q[i], GL / 2);
-                    const float ko = __shfl_xor_sync(GM, kn[i], GL / 2);
-                    const float2 t = tab[pbase + i];
-                    q[i] = low ? q[i] * t.x - qo * t.y : q[i] * t.x + qo * t.y;
-                    kn[i] = low ? kn[i] * t.x - ko * t.y : kn[i] * t.x + ko * t.y;
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < N; ++i) { q[i] = round_to<T>(q[i]); kn[i] = round_to<T>(kn[i]); }
-        }
-        if (z == 0 && in_range) {
-            st16<T>(kc + cbase + (size_t)ps * HD + r * N, kn);
-            st16<T>(vc + cbase + (size_t)ps * HD + r * N, vn);
-        }
-#pragma unroll
-        for (int i = 0; i < N; ++i) { sm.q[r * N + i] = q[i] * scale; sm.kn[r * N + i] = kn[i]; sm.vn[r * N + i] = vn[i]; }
-    }
-    __syncthreads();
-
-    const int j = ltid >> 1, half = ltid & 1;        // two threads per key of the tile
-    float m = -INFINITY, lsum = 0.0f, acc[EPW];
-#pragma unroll
-    for (int i = 0; i < EPW; ++i) acc[i] = 0.0f;
-    float qr[4][N];
-    load_q_chunks<N>(sm.q, j, half, qr);
-    bool ok = true;
-    const int mine = ntiles > grp ? (ntiles - grp + G - 1) / G : 0;      // tiles grp, grp + G, ... of the item
-    for (int lt = 0; lt < mine; ++lt) {
-        const int s = grp * STG + (WALK ? (int)((tbase + lt) % STG) : lt % STG);
-        ok = wait(&sm.full[s], (WALK ? (tbase + lt) / STG : (uint32_t)(lt / STG)) & 1) && ok;
-        const int nk = min(KT, kend - (kbeg + (lt * G + grp) * KT));
-        consume_tile<T, N, EPW>(sm.k[s], sm.v[s], nk, qr, j, half, lw, lane, m, lsum, acc);
-        if (G == 1) __syncthreads();                          // everyone is done with stage s
-        else if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");      // the group's own barrier (immediate ids: 3 in use)
-        else asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (ltid == 0 && lt + STG < mine) {
-            const int k0 = kbeg + ((lt + STG) * G + grp) * KT;
-            const uint32_t bytes = (uint32_t)min(KT, kend - k0) * ROWB;
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(&sm.full[s])), "r"(2 * bytes) : "memory");
-            copy(sm.k[s], kg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
-            copy(sm.v[s], vg + (size_t)k0 * ROWB, bytes, &sm.full[s], pol);
-        }
-    }
-    if (WALK) tbase += (uint32_t)ntiles;
-    if (!ok && err && tid == 0) *err = 2;
-    float l = 0.5f * warp_sum(lsum);                             // every key sits in two lanes
-    if (warp == 0 && z == 0) {     // the new token's own score, from the fp32 copies
-        float sdot = 0.0f;
-#pragma unroll
-        for (int i = 0; i < EPW; ++i) sdot = fmaf(sm.q[lane * EPW + i], sm.kn[lane * EPW + i], sdot);
-        sdot = warp_sum(sdot);
-        const float mn = fmaxf(m, sdot);
-        const float corr = (m == -INFINITY) ? 0.0f : expf(m - mn);
-        const float p = expf(sdot - mn);
-        l = l * corr + p;
-#pragma unroll
-        for (int i = 0; i < EPW; ++i) acc[i] = fmaf(p, sm.vn[lane * EPW + i], acc[i] * corr);
-        m = mn;
-    }
-    if (lane == 0) { sm.wm[warp] = m; sm.wl[warp] = l; }
-#pragma unroll
-    for (int i = 0; i < EPW; ++i) sm.wacc[warp][lane * EPW + i] = acc[i];
-    __syncthreads();
-    if (tid < HD) {
-        const int d = tid;
-        float M = fmaxf(fmaxf(sm.wm[0], sm.wm[1]), fmaxf(sm.wm[2], sm.wm[3]));
-#pragma unroll
-        for (int w = 4; w < 4 * G; ++w) M = fmaxf(M, sm.wm[w]);
-        float L = 0.0f, o = 0.0f;
-        if (M > -INFINITY) {
-#pragma unroll
-            for (int w = 0; w < 4 * G; ++w) {
-                const float e = expf(sm.wm[w] - M);
-                L = fmaf(sm.wl[w], e, L);
-                o = fmaf(sm.wacc[w][d], e, o);
+                float* sp = scratch + (((size_t)b * H + h) * splits + z) * (HD + 2);
+                sp[2 + d] = o;
+                if (d == 0) { sp[0] = M; sp[1] = L; }
             }
         }
-        if (splits == 1) {
-            Cvt<T>::st(out, (size_t)b * D + (size_t)h * HD + d, L > 0.0f ? o / L : 0.0f);
-        } else {
-            float* sp = scratch + (((size_t)b * H + h) * splits + z) * (HD + 2);
-            sp[2 + d] = o;
-            if (d == 0) { sp[0] = M; sp[1] = L; }
-        }
-    }
-    if (!WALK) break;
-    __syncthreads();                                          // the next item rewrites q, kn, vn and the per-warp states
-    item += (int)gridDim.x;
+        if (!WALK) break;
+        __syncthreads();                                          // the next item rewrites q, kn, vn and the per-warp states
+        item += (int)gridDim.x;
     } while (item < nitems);
 }
 
